@@ -1,0 +1,165 @@
+"""Host-side binding of libembla_cuda_attn.so (the C ABI in include/embla_cuda_attn.h).
+
+The reference dispatches attention from Swift (Engine.encodeAttention, Sources/EmblaMetal/
+Engine.swift:743-832; Prefill.encode, Sources/EmblaMetal/Prefill.swift:265-407). No Swift toolchain
+exists where this is built, so this ctypes layer is the tested caller of the C ABI; it keeps the
+reference's vocabulary (qkv rows, kv heads, seq_lens = pos + 1, selecting past topk + recent keys).
+torch is used for device memory and streams only. There is no CPU fallback: if the CUDA library is
+missing, importing `lib()` raises.
+"""
+import ctypes as C
+import os
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libembla_cuda_attn.so")
+
+BF16, F16 = 0, 1
+KV_INT8, KV_16BIT = 0, 1
+SCALE_F32, SCALE_F16 = 0, 1
+HEAD_DIM, BLOCK, TOPK, RECENT = 128, 128, 1024, 128
+OK, BAD_ARG, OOM, CUDA_ERR, NCCL_ERR, TIMEOUT, UNSUPPORTED = range(7)
+
+_TORCH_DT = {BF16: torch.bfloat16, F16: torch.float16}
+
+
+class EmblaError(RuntimeError):
+    def __init__(self, status, msg):
+        super().__init__(f"embla status {status}: {msg}")
+        self.status = status
+
+
+class AttnConfig(C.Structure):
+    _fields_ = [("n_q_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("act_dtype", C.c_int32),
+                ("max_batch", C.c_int32), ("max_context", C.c_int32)]
+
+
+class Query(C.Structure):
+    _fields_ = [("q_dev", C.c_void_p), ("q_stride", C.c_int64), ("prenormed", C.c_int32), ("ng", C.c_int32),
+                ("g1_dev", C.c_void_p), ("g2_dev", C.c_void_p)]
+
+
+class KVView(C.Structure):
+    _fields_ = [("block_table_dev", C.c_void_p), ("table_stride", C.c_int32), ("seq_lens_dev", C.c_void_p),
+                ("batch", C.c_int32), ("layer", C.c_int32), ("max_seq_len", C.c_int32)]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded CUDA library; raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: run `python -m embla_metal_b200.build` (needs nvcc)")
+        L = C.CDLL(LIB_PATH)
+        L.embla_version.restype = C.c_char_p
+        L.embla_last_error.restype = C.c_char_p
+        L.embla_kv_block_bytes.restype = C.c_size_t
+        L.embla_kv_page_bytes.restype = C.c_size_t
+        L.embla_kv_pool_base.restype = C.c_void_p
+        for name in ("embla_kv_block_bytes", "embla_kv_page_bytes", "embla_kv_pool_base", "embla_kv_pool_destroy",
+                     "embla_attn_destroy"):
+            getattr(L, name).argtypes = [C.c_void_p]
+        _lib = L
+    return _lib
+
+
+def _check(status):
+    if status != OK:
+        raise EmblaError(status, lib().embla_last_error().decode())
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class KVPool:
+    """Paged KV pool of 128-position blocks (the full layers' cache of Engine.swift:269-284)."""
+
+    def __init__(self, n_layers, n_kv_heads, num_blocks, kv_dtype=KV_INT8, scale_dtype=SCALE_F16):
+        self.handle = C.c_void_p()
+        _check(lib().embla_kv_pool_create(n_layers, n_kv_heads, kv_dtype, scale_dtype, num_blocks, C.byref(self.handle)))
+        self.n_layers, self.n_kv_heads, self.num_blocks = n_layers, n_kv_heads, num_blocks
+        self.kv_dtype, self.scale_dtype = kv_dtype, scale_dtype
+        self.block_bytes = lib().embla_kv_block_bytes(self.handle)
+        self.page_bytes = lib().embla_kv_page_bytes(self.handle)
+
+    def close(self):
+        if self.handle:
+            lib().embla_kv_pool_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        self.close()
+
+    def raw(self):
+        """The pool as a uint8 tensor [num_blocks, n_layers, n_kv_heads, page_bytes] aliasing device memory."""
+        base = lib().embla_kv_pool_base(self.handle)
+        shape = (self.num_blocks, self.n_layers, self.n_kv_heads, self.page_bytes)
+
+        class _Dev:
+            __cuda_array_interface__ = {"shape": shape, "typestr": "|u1", "data": (base, False), "version": 3}
+
+        self._keep = _Dev()
+        return torch.as_tensor(self._keep, device="cuda")
+
+    def export_block(self, block, dst):
+        _check(lib().embla_kv_block_export(self.handle, block, _ptr(dst), _stream()))
+
+    def import_block(self, block, src):
+        _check(lib().embla_kv_block_import(self.handle, block, _ptr(src), _stream()))
+
+
+class Attention:
+    """Context of the attention path: shape, activation dtype, split-K scratch."""
+
+    def __init__(self, n_q_heads=16, n_kv_heads=4, act_dtype=F16, max_batch=1, max_context=32768):
+        self.cfg = AttnConfig(n_q_heads, n_kv_heads, act_dtype, max_batch, max_context)
+        self.handle = C.c_void_p()
+        _check(lib().embla_attn_create(C.byref(self.cfg), C.byref(self.handle)))
+        self.torch_dtype = _TORCH_DT[act_dtype]
+
+    def close(self):
+        if self.handle:
+            lib().embla_attn_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        self.close()
+
+    def check(self):
+        _check(lib().embla_attn_check(self.handle, _stream()))
+
+    @staticmethod
+    def view(block_table, seq_lens, layer, max_seq_len=0):
+        return KVView(block_table.data_ptr(), block_table.stride(0), None if seq_lens is None else seq_lens.data_ptr(),
+                      block_table.shape[0], layer, max_seq_len)
+
+    @staticmethod
+    def query(q, gains=None):
+        """q [batch, >= n_q_heads * 128] (row stride = the tensor's); gains = (g1, g2) or None (prenormed)."""
+        if gains is None:
+            return Query(q.data_ptr(), q.stride(0), 1, 0, None, None)
+        g1, g2 = gains
+        ng = 2 if g2 is not None else 1
+        return Query(q.data_ptr(), q.stride(0), 0, ng, g1.data_ptr(), None if g2 is None else g2.data_ptr())
+
+    def kv_append(self, pool, block_table, layer, pos0, k, v, norm_k=True):
+        """k, v [batch, n_tokens, n_kv_heads * 128 (or wider rows)]; pos0 int32 [batch] first position."""
+        view = self.view(block_table, None, layer)
+        _check(lib().embla_kv_append(self.handle, pool.handle, C.byref(view), _ptr(pos0), k.shape[1], _ptr(k), _ptr(v),
+                                     C.c_int64(k.stride(1)), C.c_int64(k.stride(0)), int(norm_k), _stream()))
+
+    def full_decode(self, pool, block_table, seq_lens, layer, q, o, gains=None, scores=None, max_seq_len=0):
+        view = self.view(block_table, seq_lens, layer, max_seq_len)
+        qd = self.query(q, gains)
+        _check(lib().embla_attn_full_decode(self.handle, pool.handle, C.byref(view), C.byref(qd), _ptr(o),
+                                            C.c_int64(o.stride(0)), _ptr(scores),
+                                            C.c_int64(0 if scores is None else scores.stride(1)), _stream()))

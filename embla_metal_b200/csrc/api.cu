@@ -1,0 +1,192 @@
+// Context, KV pool and block copies of the embla CUDA attention library.
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+namespace embla {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+TensorMapEncodeTiledFn tensor_map_encoder() {
+    static TensorMapEncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<TensorMapEncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+}  // namespace embla
+
+using namespace embla;
+
+extern "C" {
+
+const char* embla_version(void) { return "embla-cuda-attn 0.1 (sm_100a)"; }
+const char* embla_last_error(void) { return g_error; }
+
+EmblaStatus embla_attn_create(const EmblaAttnConfig* cfg, EmblaAttn** out) {
+    if (!cfg || !out) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_create: null argument");
+    *out = nullptr;
+    if (cfg->n_kv_heads <= 0 || cfg->n_q_heads <= 0 || cfg->n_q_heads % cfg->n_kv_heads != 0)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_create: n_q_heads %d must be a positive multiple of n_kv_heads %d",
+                   cfg->n_q_heads, cfg->n_kv_heads);
+    const int G = cfg->n_q_heads / cfg->n_kv_heads;
+    if (G > 8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_create: %d query heads per kv head (at most 8)", G);
+    if (cfg->act_dtype != EMBLA_BF16 && cfg->act_dtype != EMBLA_F16)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_create: act_dtype %d", cfg->act_dtype);
+    if (cfg->max_batch <= 0 || cfg->max_context <= 0)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_create: max_batch %d, max_context %d", cfg->max_batch, cfg->max_context);
+
+    EmblaAttn* ctx = new (std::nothrow) EmblaAttn();
+    if (!ctx) EMBLA_FAIL(EMBLA_OOM, "embla_attn_create: host allocation failed");
+    ctx->cfg = *cfg;
+    ctx->partials = nullptr;
+    ctx->counters = nullptr;
+    ctx->err_dev = nullptr;
+    cudaError_t e = cudaGetDevice(&ctx->device);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, ctx->device);
+    if (e != cudaSuccess) {
+        delete ctx;
+        EMBLA_FAIL(EMBLA_CUDA, "embla_attn_create: no usable CUDA device: %s", cudaGetErrorString(e));
+    }
+    // Split-K scratch: a (sequence, kv head) pair is cut into key ranges, each
+    // leaving G rows of 128 sums + 2 scalars (sum of weights, or running max and sum for softmax).
+    // Slots: enough key ranges to fill the GPU several times over at any batch up to max_batch.
+    const long pairs = long(cfg->max_batch) * cfg->n_kv_heads;
+    ctx->partial_slots = int(8L * ctx->sm_count + 2 * pairs);
+    ctx->partial_floats = size_t(ctx->partial_slots) * G * (HD + 4);
+    e = cudaMalloc(&ctx->partials, ctx->partial_floats * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->counters, size_t(pairs) * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->err_dev, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->counters, 0, size_t(pairs) * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->err_dev, 0, sizeof(int));
+    if (e != cudaSuccess) {
+        embla_attn_destroy(ctx);
+        set_error("embla_attn_create: scratch allocation failed: %s", cudaGetErrorString(e));
+        return e == cudaErrorMemoryAllocation ? EMBLA_OOM : EMBLA_CUDA;
+    }
+    *out = ctx;
+    return EMBLA_OK;
+}
+
+void embla_attn_destroy(EmblaAttn* ctx) {
+    if (!ctx) return;
+    cudaFree(ctx->partials);
+    cudaFree(ctx->counters);
+    cudaFree(ctx->err_dev);
+    delete ctx;
+}
+
+EmblaStatus embla_attn_check(EmblaAttn* ctx, void* stream) {
+    if (!ctx) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_check: null context");
+    int err = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    EMBLA_CUDA_TRY(cudaMemcpyAsync(&err, ctx->err_dev, sizeof(int), cudaMemcpyDeviceToHost, s));
+    EMBLA_CUDA_TRY(cudaStreamSynchronize(s));
+    if (err != 0) {
+        EMBLA_CUDA_TRY(cudaMemsetAsync(ctx->err_dev, 0, sizeof(int), s));
+        EMBLA_CUDA_TRY(cudaStreamSynchronize(s));
+        EMBLA_FAIL(EMBLA_TIMEOUT, "a kernel gave up a bounded wait (code %d)", err);
+    }
+    return EMBLA_OK;
+}
+
+EmblaStatus embla_kv_pool_create(int32_t n_layers, int32_t n_kv_heads, int32_t kv_dtype, int32_t scale_dtype,
+                                 int32_t num_blocks, EmblaKVPool** out) {
+    if (!out) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_pool_create: null output");
+    *out = nullptr;
+    if (n_layers <= 0 || n_kv_heads <= 0 || num_blocks <= 0)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_pool_create: n_layers %d, n_kv_heads %d, num_blocks %d", n_layers, n_kv_heads,
+                   num_blocks);
+    if (kv_dtype != EMBLA_KV_INT8 && kv_dtype != EMBLA_KV_16BIT)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_pool_create: kv_dtype %d", kv_dtype);
+    if (scale_dtype != EMBLA_SCALE_F32 && scale_dtype != EMBLA_SCALE_F16)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_pool_create: scale_dtype %d", scale_dtype);
+    EmblaKVPool* p = new (std::nothrow) EmblaKVPool();
+    if (!p) EMBLA_FAIL(EMBLA_OOM, "embla_kv_pool_create: host allocation failed");
+    p->n_layers = n_layers;
+    p->n_kv_heads = n_kv_heads;
+    p->kv_dtype = kv_dtype;
+    p->scale_dtype = scale_dtype;
+    p->num_blocks = num_blocks;
+    p->scale_bytes = scale_dtype == EMBLA_SCALE_F32 ? 4 : 2;
+    p->page_bytes = kv_dtype == EMBLA_KV_INT8 ? size_t(2 * CODE_BYTES + 2 * BLK * p->scale_bytes) : size_t(2 * BLK * HD * 2);
+    p->rows_per_page = int(p->page_bytes / 128);
+    p->block_bytes = p->page_bytes * n_layers * n_kv_heads;
+    p->total_bytes = p->block_bytes * num_blocks;
+    p->base = nullptr;
+    cudaError_t e = cudaGetDevice(&p->device);
+    if (e == cudaSuccess) e = cudaMalloc(&p->base, p->total_bytes);
+    if (e == cudaSuccess) e = cudaMemset(p->base, 0, p->total_bytes);
+    if (e != cudaSuccess) {
+        const size_t want = p->total_bytes;
+        cudaFree(p->base);
+        delete p;
+        set_error("embla_kv_pool_create: %zu bytes: %s", want, cudaGetErrorString(e));
+        return e == cudaErrorMemoryAllocation ? EMBLA_OOM : EMBLA_CUDA;
+    }
+    // The whole pool as rows of 128 bytes; one box = the 256 code rows (K then V) of an int8 page,
+    // or half of a 16-bit page side. 128-byte swizzle: 16-byte chunk c of row r lands at c ^ (r % 8).
+    TensorMapEncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) {
+        cudaFree(p->base);
+        delete p;
+        EMBLA_FAIL(EMBLA_CUDA, "embla_kv_pool_create: cuTensorMapEncodeTiled is not available from this driver");
+    }
+    const cuuint64_t dims[2] = {128, cuuint64_t(p->total_bytes / 128)};
+    const cuuint64_t strides[1] = {128};
+    const cuuint32_t box[2] = {128, 256};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(&p->tmap_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, p->base, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        cudaFree(p->base);
+        delete p;
+        EMBLA_FAIL(EMBLA_CUDA, "embla_kv_pool_create: cuTensorMapEncodeTiled failed (%d)", int(r));
+    }
+    *out = p;
+    return EMBLA_OK;
+}
+
+void embla_kv_pool_destroy(EmblaKVPool* pool) {
+    if (!pool) return;
+    cudaFree(pool->base);
+    delete pool;
+}
+
+size_t embla_kv_block_bytes(const EmblaKVPool* pool) { return pool ? pool->block_bytes : 0; }
+size_t embla_kv_page_bytes(const EmblaKVPool* pool) { return pool ? pool->page_bytes : 0; }
+void* embla_kv_pool_base(const EmblaKVPool* pool) { return pool ? pool->base : nullptr; }
+
+EmblaStatus embla_kv_block_export(const EmblaKVPool* pool, int32_t block, void* dst, void* stream) {
+    if (!pool || !dst) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_block_export: null argument");
+    if (block < 0 || block >= pool->num_blocks)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_block_export: block %d outside 0..%d", block, pool->num_blocks - 1);
+    EMBLA_CUDA_TRY(cudaMemcpyAsync(dst, pool->base + size_t(block) * pool->block_bytes, pool->block_bytes,
+                                   cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+    return EMBLA_OK;
+}
+
+EmblaStatus embla_kv_block_import(EmblaKVPool* pool, int32_t block, const void* src, void* stream) {
+    if (!pool || !src) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_block_import: null argument");
+    if (block < 0 || block >= pool->num_blocks)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_block_import: block %d outside 0..%d", block, pool->num_blocks - 1);
+    EMBLA_CUDA_TRY(cudaMemcpyAsync(pool->base + size_t(block) * pool->block_bytes, src, pool->block_bytes,
+                                   cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+    return EMBLA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,163 @@
+// Shared device/host helpers of the embla CUDA attention library (sm_100a only).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "embla_cuda_attn.h"
+
+namespace embla {
+
+constexpr int HD = EMBLA_HEAD_DIM;       // head dim
+constexpr int BLK = EMBLA_BLOCK;         // positions per KV block
+constexpr int CODE_BYTES = BLK * HD;     // int8 codes of one page side (K or V): 16 KiB
+constexpr float EPS32 = 1.1920929e-07f;  // head-norm epsilon (common.metal:9)
+constexpr float NEG_BIG = -1e30f;        // "-inf" of the running maxima (common.metal:10)
+
+// Device-side error word values (EmblaAttn::err_dev).
+constexpr int ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_WAIT_DRAIN = 3;
+// Bounded waits: tries before a kernel gives up, records an error and leaves.
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+
+// ---- host-side error plumbing -------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+#define EMBLA_FAIL(status, ...)       \
+    do {                              \
+        ::embla::set_error(__VA_ARGS__); \
+        return (status);              \
+    } while (0)
+#define EMBLA_CUDA_TRY(expr)                                                                         \
+    do {                                                                                             \
+        cudaError_t e_ = (expr);                                                                     \
+        if (e_ != cudaSuccess) {                                                                     \
+            ::embla::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); \
+            return e_ == cudaErrorMemoryAllocation ? EMBLA_OOM : EMBLA_CUDA;                         \
+        }                                                                                            \
+    } while (0)
+
+}  // namespace embla
+
+// ---- handles --------------------------------------------------------------------------------------
+struct EmblaKVPool {
+    int n_layers, n_kv_heads, kv_dtype, scale_dtype, num_blocks;
+    int scale_bytes;        // 2 or 4
+    int rows_per_page;      // page bytes / 128
+    size_t page_bytes, block_bytes, total_bytes;
+    uint8_t* base;          // device
+    CUtensorMap tmap_codes; // [total rows][128 B] uint8, box 256 rows, 128-byte swizzle
+    int device;
+};
+
+struct EmblaAttn {
+    EmblaAttnConfig cfg;
+    int device, sm_count;
+    float* partials;        // split-K partial sums
+    size_t partial_floats;
+    int* counters;          // one arrival counter per (sequence, kv head); zero between launches
+    int* err_dev;           // device error word
+    int partial_slots;      // (sequence, kv head, key range) partials the scratch holds
+};
+
+namespace embla {
+
+#ifdef __CUDACC__
+// ---- activations --------------------------------------------------------------------------------
+template <int DT> struct Act;
+template <> struct Act<EMBLA_BF16> {
+    __device__ static float load(const void* p, size_t i) { return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]); }
+    __device__ static void store(void* p, size_t i, float v) { static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v); }
+    __device__ static float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+template <> struct Act<EMBLA_F16> {
+    __device__ static float load(const void* p, size_t i) { return __half2float(static_cast<const __half*>(p)[i]); }
+    __device__ static void store(void* p, size_t i, float v) { static_cast<__half*>(p)[i] = __float2half_rn(v); }
+    __device__ static float round(float v) { return __half2float(__float2half_rn(v)); }
+};
+
+__device__ __forceinline__ float load_scale(const void* p, int i, int scale_bytes) {
+    return scale_bytes == 4 ? static_cast<const float*>(p)[i] : __half2float(static_cast<const __half*>(p)[i]);
+}
+
+// ---- warp-level tensor-core tile: D[16x8] += A[16x16] * B[16x8], fp16 in, fp32 accumulate --------
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Two int8 codes -> half2, exactly: the bytes (offset to unsigned by ^0x80 beforehand) become the
+// low mantissa bits of 1024.0, and 1152 = 1024 + 128 is subtracted.
+constexpr uint32_t H2_1024 = 0x64646464u;   // byte source for the 0x64 exponent bytes
+constexpr uint32_t H2_1152 = 0x64806480u;   // half2(1152, 1152)
+__device__ __forceinline__ uint32_t h2_from_biased_bytes(uint32_t x, uint32_t sel) {
+    uint32_t r = __byte_perm(x, H2_1024, sel), m = H2_1152;
+    __half2 h = __hsub2(*reinterpret_cast<__half2*>(&r), *reinterpret_cast<__half2*>(&m));
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// ---- shared-memory barriers and bulk (TMA) copies, every wait bounded ----------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits for the barrier's phase `parity`; gives up after WAIT_LIMIT tries and returns false.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// 2-D tiled TMA load (no multicast): box at (x, y) of `map` into `dst`, completion on `bar`.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+// 1-D bulk copy global -> shared (both 16-byte aligned, bytes a multiple of 16).
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+#endif  // __CUDACC__
+
+// Host: the driver's cuTensorMapEncodeTiled, fetched through the runtime (no link against libcuda).
+typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                           const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                           CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                           CUtensorMapFloatOOBfill);
+TensorMapEncodeTiledFn tensor_map_encoder();
+
+}  // namespace embla

@@ -1,0 +1,113 @@
+// Quantised KV append: the reference's kv_append / kv_append_b with write_row8
+// (Sources/EmblaMetal/Kernels/attention.metal:113-140, prefill.metal:184-212, common.metal:74-84),
+// writing into the paged pool. One warp per (sequence, token, kv head, K|V); a lane holds dims
+// lane + 32 i like the reference. Every fp32 operation is an explicit round-to-nearest intrinsic in
+// the order the CPU oracle uses, so codes and scales are bit-exact.
+#include "common.cuh"
+
+namespace embla {
+
+struct AppendParams {
+    uint8_t* pool;
+    const int32_t* block_table;
+    const int32_t* pos0;
+    const void* k;
+    const void* v;
+    int64_t token_stride, seq_stride;
+    size_t page_bytes;
+    int table_stride, batch, n_tokens, layer, n_layers, n_kv_heads, scale_bytes, norm_k;
+};
+
+template <int DT>
+__global__ void __launch_bounds__(128) kv_append_kernel(const AppendParams p) {
+    const int lane = threadIdx.x & 31;
+    const long warp = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const long total = long(p.batch) * p.n_tokens * p.n_kv_heads * 2;
+    if (warp >= total) return;
+    const int is_v = int(warp & 1);
+    const int h = int((warp >> 1) % p.n_kv_heads);
+    const long bt = (warp >> 1) / p.n_kv_heads;
+    const int t = int(bt % p.n_tokens), b = int(bt / p.n_tokens);
+    const void* src = is_v ? p.v : p.k;
+    const size_t off = size_t(b) * p.seq_stride + size_t(t) * p.token_stride + size_t(h) * HD;
+
+    float x[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) x[i] = Act<DT>::load(src, off + lane + 32 * i);
+    if (!is_v && p.norm_k) {
+        // head_norm without gains (common.metal:30-41): lane sums, then the 32 lanes in lane order
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
+        float tot = 0.0f;
+        for (int l = 0; l < 32; l++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, ss, l));
+        const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, float(HD)), EPS32)));
+#pragma unroll
+        for (int i = 0; i < 4; i++) x[i] = __fmul_rn(x[i], r);
+    }
+    float a = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        x[i] = Act<DT>::round(x[i]);
+        a = fmaxf(a, fabsf(x[i]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    const float inv = a > 0.0f ? __fdiv_rn(127.0f, a) : 0.0f;
+
+    const int pos = p.pos0[b] + t;
+    const int block = p.block_table[size_t(b) * p.table_stride + pos / BLK];
+    const int row = pos % BLK;
+    uint8_t* page = p.pool + ((size_t(block) * p.n_layers + p.layer) * p.n_kv_heads + h) * p.page_bytes;
+    int8_t* codes = reinterpret_cast<int8_t*>(page) + (is_v ? CODE_BYTES : 0) + row * HD;
+#pragma unroll
+    for (int i = 0; i < 4; i++) codes[lane + 32 * i] = int8_t(int(rintf(__fmul_rn(x[i], inv))));
+    if (lane == 0) {
+        const float s = __fdiv_rn(a, 127.0f);
+        uint8_t* sc = page + 2 * CODE_BYTES + (is_v ? BLK * p.scale_bytes : 0);
+        if (p.scale_bytes == 4) reinterpret_cast<float*>(sc)[row] = s;
+        else reinterpret_cast<__half*>(sc)[row] = __float2half_rn(s);
+    }
+}
+
+}  // namespace embla
+
+using namespace embla;
+
+extern "C" EmblaStatus embla_kv_append(EmblaAttn* ctx, EmblaKVPool* pool, const EmblaKVView* view,
+                                       const int32_t* pos0_dev, int32_t n_tokens,
+                                       const void* k_dev, const void* v_dev, int64_t token_stride, int64_t seq_stride,
+                                       int32_t norm_k, void* stream) {
+    if (!ctx || !pool || !view || !pos0_dev || !k_dev || !v_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_append: null argument");
+    if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_kv_append: the pool is not int8");
+    if (view->layer < 0 || view->layer >= pool->n_layers)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_append: layer %d outside the pool's %d", view->layer, pool->n_layers);
+    if (view->batch <= 0 || n_tokens <= 0 || !view->block_table_dev)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_append: batch %d, n_tokens %d", view->batch, n_tokens);
+    if (pool->n_kv_heads != ctx->cfg.n_kv_heads)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_append: pool has %d kv heads, context %d", pool->n_kv_heads, ctx->cfg.n_kv_heads);
+    AppendParams p;
+    p.pool = pool->base;
+    p.block_table = view->block_table_dev;
+    p.pos0 = pos0_dev;
+    p.k = k_dev;
+    p.v = v_dev;
+    p.token_stride = token_stride;
+    p.seq_stride = seq_stride;
+    p.page_bytes = pool->page_bytes;
+    p.table_stride = view->table_stride;
+    p.batch = view->batch;
+    p.n_tokens = n_tokens;
+    p.layer = view->layer;
+    p.n_layers = pool->n_layers;
+    p.n_kv_heads = pool->n_kv_heads;
+    p.scale_bytes = pool->scale_bytes;
+    p.norm_k = norm_k;
+    const long warps = long(p.batch) * n_tokens * p.n_kv_heads * 2;
+    const unsigned blocks = unsigned((warps + 3) / 4);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (ctx->cfg.act_dtype == EMBLA_BF16) kv_append_kernel<EMBLA_BF16><<<blocks, 128, 0, s>>>(p);
+    else kv_append_kernel<EMBLA_F16><<<blocks, 128, 0, s>>>(p);
+    EMBLA_CUDA_TRY(cudaGetLastError());
+    return EMBLA_OK;
+}

@@ -1,0 +1,148 @@
+/*
+ * embla_cuda_attn.h — C ABI of the B200 (sm_100a) attention hot path for the embla engine.
+ *
+ * The reference engine (sevren-ai/embla-metal) has no plugin or FFI interface for attention: the
+ * path sits behind two private Swift methods, Engine.encodeAttention (Sources/EmblaMetal/
+ * Engine.swift:743-832) and Prefill.encode / encodeFullNAX (Sources/EmblaMetal/Prefill.swift:265-407),
+ * which bind buffers and dispatch Metal kernels. This header gives one entry point per kernel
+ * dispatch of those methods, with the same operands, so that a Swift caller can replace each
+ * `dispatchThreadgroups` with one C call (a module map + wrapper are shown in INTEGRATION.md).
+ *
+ * Conventions
+ *  - Every function returns an EmblaStatus (0 = ok) and never aborts or throws; a message for the
+ *    last failure of the calling thread is available from embla_last_error(). (The reference
+ *    throws at init, MetalContext.swift:78-90, and traps on a failed command buffer,
+ *    Engine.swift:1070, 1170.)
+ *  - All pointers named *_dev are device pointers owned by the caller unless stated otherwise.
+ *    Work is enqueued on the given CUDA stream (a cudaStream_t passed as void*) and the call
+ *    returns without synchronising, like encoding into a Metal command buffer.
+ *  - A handle is not thread-safe; distinct handles may be used from distinct threads/streams.
+ *  - Activations are 16-bit (bfloat16 as in the reference, or float16); head_dim is 128.
+ *  - Batched: every call takes `batch` independent sequences (the reference runs one).
+ *    `seq_lens_dev[b]` is the number of keys the call sees for sequence b, the current token
+ *    included — the reference's AttnParams.S = pos + 1 (Engine.swift:796-801).
+ *
+ * KV cache layout (replaces Engine.swift:269-284 and the span lists of PrefixCache.swift:153-186)
+ *  - A pool holds `num_blocks` physical blocks. A block covers 128 consecutive positions of one
+ *    sequence for every layer of the pool and every kv head, and is contiguous in memory:
+ *        block = [layer][kv head] pages;  int8 page = K codes [128][128] | V codes [128][128] |
+ *        K scales [128] | V scales [128]   (scales fp32 as the reference, or fp16).
+ *    A sequence is a row of a block table (int32 physical block ids, position p lives in entry
+ *    p / 128). A prefix-cache hit is a block-table edit (share) or one contiguous copy
+ *    (embla_kv_block_export / _import), where the reference blits ~40 spans per block.
+ */
+#ifndef EMBLA_CUDA_ATTN_H
+#define EMBLA_CUDA_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    EMBLA_OK = 0,
+    EMBLA_BAD_ARG = 1,
+    EMBLA_OOM = 2,
+    EMBLA_CUDA = 3,      /* a CUDA runtime / driver call failed */
+    EMBLA_NCCL = 4,
+    EMBLA_TIMEOUT = 5,   /* a bounded device-side wait ran out (see embla_attn_check) */
+    EMBLA_UNSUPPORTED = 6
+} EmblaStatus;
+
+enum { EMBLA_BF16 = 0, EMBLA_F16 = 1 };                       /* activation dtype */
+enum { EMBLA_KV_INT8 = 0, EMBLA_KV_16BIT = 1 };               /* cache element type (16BIT = activation dtype) */
+enum { EMBLA_SCALE_F32 = 0, EMBLA_SCALE_F16 = 1 };            /* int8 row scale dtype */
+enum { EMBLA_HEAD_DIM = 128, EMBLA_BLOCK = 128, EMBLA_TOPK = 1024, EMBLA_RECENT = 128 };
+
+typedef struct EmblaAttn EmblaAttn;       /* context: device, scratch (split-K partials, counters) */
+typedef struct EmblaKVPool EmblaKVPool;   /* paged KV pool */
+
+/* Model shape of the path; the counterpart of `enum Embla` (Engine.swift:7-27) for attention. */
+typedef struct {
+    int32_t n_q_heads;     /* 16 */
+    int32_t n_kv_heads;    /* 4 (the reference's full/sparse layers use 2) */
+    int32_t act_dtype;     /* EMBLA_BF16 | EMBLA_F16 */
+    int32_t max_batch;     /* sequences per call; sizes the scratch */
+    int32_t max_context;   /* keys per sequence; sizes the scratch */
+} EmblaAttnConfig;
+
+/* Queries of a call. `prenormed` = 0 reproduces the reference: the kernel applies the per-head RMS
+ * norm with gains (1 + g1)(1 + g2) (`ng` of them; common.metal:30-41) and rounds to the activation
+ * dtype before use (attention.metal:166-169). `prenormed` = 1 takes q as given. */
+typedef struct {
+    const void* q_dev;        /* [batch][q_stride] elements, head h at h * 128 (the reference's qkv buffer) */
+    int64_t     q_stride;     /* elements between sequences (4096 for the reference's qkv rows) */
+    int32_t     prenormed;
+    int32_t     ng;           /* 0, 1 or 2 gain vectors */
+    const void* g1_dev;       /* [128] gains, activation dtype; may be NULL when ng < 1 */
+    const void* g2_dev;       /* [128]; may be NULL when ng < 2 */
+} EmblaQuery;
+
+/* A sequence batch's view of a pool: which blocks, how many keys. */
+typedef struct {
+    const int32_t* block_table_dev;   /* [batch][table_stride] physical block ids */
+    int32_t        table_stride;
+    const int32_t* seq_lens_dev;      /* [batch] keys visible (current token included) */
+    int32_t        batch;
+    int32_t        layer;             /* layer index inside the pool */
+    int32_t        max_seq_len;       /* host-side upper bound of seq_lens (sizes the key split);
+                                         0 = the context's max_context */
+} EmblaKVView;
+
+/* ---- lifetime ---------------------------------------------------------------------------------- */
+const char* embla_version(void);
+/* Message of the calling thread's last failing call (never NULL). */
+const char* embla_last_error(void);
+
+/* Replaces Engine.init's pipeline + scratch set-up for attention (Engine.swift:221-230, 242-258:
+ * `apart`, `counter`, `scores`, `sel`). Allocates split-K scratch on the current device. */
+EmblaStatus embla_attn_create(const EmblaAttnConfig* cfg, EmblaAttn** out);
+void        embla_attn_destroy(EmblaAttn* ctx);
+/* Reads (and clears) the device-side error word: EMBLA_TIMEOUT if a bounded wait of an earlier
+ * kernel ran out. Synchronises the stream. */
+EmblaStatus embla_attn_check(EmblaAttn* ctx, void* stream);
+
+/* Replaces the cache allocation of Engine.swift:269-284 for the full layers. */
+EmblaStatus embla_kv_pool_create(int32_t n_layers, int32_t n_kv_heads, int32_t kv_dtype, int32_t scale_dtype,
+                                 int32_t num_blocks, EmblaKVPool** out);
+void        embla_kv_pool_destroy(EmblaKVPool* pool);
+/* Bytes of one physical block, and of one (layer, kv head) page inside it. */
+size_t      embla_kv_block_bytes(const EmblaKVPool* pool);
+size_t      embla_kv_page_bytes(const EmblaKVPool* pool);
+/* Device address of the pool (block 0), for tests and for callers that fill pages themselves. */
+void*       embla_kv_pool_base(const EmblaKVPool* pool);
+
+/* Replaces Engine.copy over fullSpans (PrefixCache.swift:153-168, 200-212): one block out of / into
+ * the pool as one contiguous copy. `dst`/`src` may be host (pinned or pageable) or device memory. */
+EmblaStatus embla_kv_block_export(const EmblaKVPool* pool, int32_t block, void* dst, void* stream);
+EmblaStatus embla_kv_block_import(EmblaKVPool* pool, int32_t block, const void* src, void* stream);
+
+/* ---- KV append ---------------------------------------------------------------------------------- */
+/* Replaces kv_append (attention.metal:113-140) and kv_append_b (prefill.metal:184-212) with
+ * write_row8 (common.metal:74-84): for each sequence b and token t < n_tokens at position
+ * pos0_dev[b] + t, quantises the k and v rows of every kv head into the view's layer.
+ * `norm_k` = 1 RMS-norms k without gains first, as the reference does. k/v are
+ * [batch][n_tokens][stride] elements with kv head h at h * 128. Codes and scales are bit-exact
+ * against the reference arithmetic. seq_lens_dev of the view is not read. */
+EmblaStatus embla_kv_append(EmblaAttn* ctx, EmblaKVPool* pool, const EmblaKVView* view,
+                            const int32_t* pos0_dev, int32_t n_tokens,
+                            const void* k_dev, const void* v_dev, int64_t token_stride, int64_t seq_stride,
+                            int32_t norm_k, void* stream);
+
+/* ---- decode, full layers (ReLU²) ------------------------------------------------------------------ */
+/* Replaces attn_full8 (attention.metal:235-363; dispatch Engine.swift:796-818): ReLU² attention
+ * of one query token per sequence over the int8 cache, split over key ranges with a deterministic
+ * combine. o_dev is [batch][o_stride] elements, head h at h * 128. When `scores_dev` is not NULL
+ * (the reference's SCORES variant, attention.metal:146, 296-306) the kernel also writes
+ * scores[b][kv head][j] = max over the kv head's query heads of q·k_j·kscale_j for j < seq_len,
+ * rows of `scores_stride` floats, bit-exact against the oracle's summation order. */
+EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                   const EmblaQuery* q, void* o_dev, int64_t o_stride,
+                                   float* scores_dev, int64_t scores_stride, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EMBLA_CUDA_ATTN_H */

@@ -1,0 +1,75 @@
+"""Shared helpers of the tests: seeded inputs in the shapes of the benchmark configurations, pool
+filling, and the tolerance check (2e-3 max-abs and 1e-3 relative RMS against the fp32 oracle)."""
+import numpy as np
+
+from oracle import oracle as orc
+
+MAX_ABS, REL_RMS = 2e-3, 1e-3
+
+
+def close(got, want, max_abs=MAX_ABS, rel_rms=REL_RMS):
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    err = np.abs(got - want).max()
+    rms = np.sqrt(((got - want) ** 2).mean() / max((want ** 2).mean(), 1e-30))
+    return err <= max_abs and rms <= rel_rms, f"max-abs {err:.3e} (<= {max_abs}), rel-rms {rms:.3e} (<= {rel_rms})"
+
+
+def int8_cache(rng, Hkv, S, scale_f16=True, lo=0.005, hi=0.02):
+    """K/V int8 uniform in [-127, 127] with per-token per-head scales uniform in [lo, hi]."""
+    k = rng.integers(-127, 128, (Hkv, S, 128)).astype(np.int8)
+    v = rng.integers(-127, 128, (Hkv, S, 128)).astype(np.int8)
+    ks = rng.uniform(lo, hi, (Hkv, S)).astype(np.float32)
+    vs = rng.uniform(lo, hi, (Hkv, S)).astype(np.float32)
+    if scale_f16:
+        ks = ks.astype(np.float16).astype(np.float32)
+        vs = vs.astype(np.float16).astype(np.float32)
+    return k, ks, v, vs
+
+
+def page_bytes_np(k, ks, v, vs, scale_f16):
+    """int8 pages [Hkv, npages, page_bytes] (uint8) of dense caches [Hkv, S, 128], zero padded."""
+    Hkv, S = k.shape[0], k.shape[1]
+    npg = (S + 127) // 128
+    sdt = np.float16 if scale_f16 else np.float32
+    ssz = 2 if scale_f16 else 4
+    pages = np.zeros((Hkv, npg, 32768 + 256 * ssz), np.uint8)
+
+    def pad(a, shape):
+        out = np.zeros(shape, a.dtype)
+        out[tuple(slice(0, n) for n in a.shape)] = a
+        return out
+
+    kp = pad(k, (Hkv, npg * 128, 128)).reshape(Hkv, npg, 128 * 128).view(np.uint8)
+    vp = pad(v, (Hkv, npg * 128, 128)).reshape(Hkv, npg, 128 * 128).view(np.uint8)
+    ksp = pad(ks.astype(sdt), (Hkv, npg * 128)).reshape(Hkv, npg, 128).view(np.uint8)
+    vsp = pad(vs.astype(sdt), (Hkv, npg * 128)).reshape(Hkv, npg, 128).view(np.uint8)
+    pages[:, :, :16384] = kp
+    pages[:, :, 16384:32768] = vp
+    pages[:, :, 32768:32768 + 128 * ssz] = ksp
+    pages[:, :, 32768 + 128 * ssz:] = vsp
+    return pages
+
+
+def fill_pool(pool, layer, blocks, k, ks, v, vs):
+    """Writes dense int8 caches of one sequence into `pool` at physical blocks `blocks` (list)."""
+    import torch
+    from embla_metal_b200 import attn
+    pages = page_bytes_np(k, ks, v, vs, pool.scale_dtype == attn.SCALE_F16)
+    raw = pool.raw()
+    t = torch.from_numpy(pages).cuda()
+    idx = torch.as_tensor(list(blocks[:pages.shape[1]]), device="cuda", dtype=torch.long)
+    raw[idx, layer] = t.permute(1, 0, 2)
+
+
+def act_tensor(bits, dtype):
+    """uint16 numpy storage -> torch tensor of the activation dtype on the GPU."""
+    import torch
+    t = torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).cuda()
+    return t.view(torch.bfloat16 if dtype == orc.BF16 else torch.float16)
+
+
+def act_bits(t):
+    """torch 16-bit tensor -> uint16 numpy storage."""
+    import torch
+    return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
