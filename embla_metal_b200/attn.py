@@ -97,7 +97,10 @@ class KVPool:
             self.handle = C.c_void_p()
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:   # interpreter shutdown
+            pass
 
     def raw(self):
         """The pool as a uint8 tensor [num_blocks, n_layers, n_kv_heads, page_bytes] aliasing device memory."""
@@ -132,7 +135,10 @@ class Attention:
             self.handle = C.c_void_p()
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:   # interpreter shutdown
+            pass
 
     def check(self):
         _check(lib().embla_attn_check(self.handle, _stream()))

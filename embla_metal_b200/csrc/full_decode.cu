@@ -20,8 +20,6 @@
 
 namespace embla {
 
-constexpr int FD_CONSUMERS = 4;
-constexpr int FD_THREADS = (FD_CONSUMERS + 1) * 32;
 constexpr int FD_STAGE_BYTES = 2 * CODE_BYTES + 1024;   // codes + K and V scales (fp32 at most)
 constexpr int FD_PART = HD + 4;                         // floats per (split, head): 128 sums, sum of weights
 
@@ -51,15 +49,64 @@ __device__ __forceinline__ int rho(int g) {
     return base ^ ((g & 1) << 2);
 }
 
-template <int DT>
-__device__ __forceinline__ void prep_query_smem(const FullDecodeParams& p, int b, int kvh, __half (*qh)[HD], float (*qf)[HD],
-                                                int warp, int lane, int nwarps) {
+// 8x8 b16 transpose across the warp: lane (g, c) gives row g, columns 2c, 2c+1 and receives row g,
+// columns 2c, 2c+1 of the transpose.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(x));
+    return r;
+}
+
+template <int SB>
+__device__ __forceinline__ float ld_scale(const uint8_t* p, int i) {
+    if (SB == 4) return reinterpret_cast<const float*>(p)[i];
+    return __half2float(reinterpret_cast<const __half*>(p)[i]);
+}
+
+// int8 code (already ^0x80, byte `k` of x) -> fp32, exactly: 2^23 + 128 + code, minus 2^23 + 128.
+__device__ __forceinline__ float f32_from_biased_byte(uint32_t x, int k) {
+    return __fadd_rn(__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7440 | k)), -8388736.0f);
+}
+
+constexpr int QF_LD = HD + 4;   // fp32 query rows padded so that two heads never share a bank
+
+template <int DT, int SB, int NCONS, int STAGES, bool SCORES>
+__global__ void __launch_bounds__((NCONS + 1) * 32) full_decode_kernel(const __grid_constant__ CUtensorMap tmap,
+                                                                      const FullDecodeParams p) {
+    constexpr int THREADS = (NCONS + 1) * 32;
+    constexpr int KPW = BLK / NCONS;   // keys of a page per consumer warp
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* stages = smem;
+    __half(*qh)[HD] = reinterpret_cast<__half(*)[HD]>(smem + STAGES * FD_STAGE_BYTES);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * FD_STAGE_BYTES + 8 * HD * 2);
+    uint64_t* empty = full + STAGES;
+    float(*qf)[QF_LD] = reinterpret_cast<float(*)[QF_LD]>(empty + STAGES);   // SCORES only
+    __shared__ int s_last, s_failed, s_issued;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int S = p.seq_lens[b];
+    const int npages = (S + BLK - 1) / BLK;
+    const int pps = (npages + p.nsplit - 1) / p.nsplit;
+    const int pg0 = split * pps;
+    const int n = max(0, min(npages, pg0 + pps) - pg0);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], NCONS);
+        }
+        s_failed = 0;
+        s_issued = 0;
+        fence_barrier_init();
+    }
     // Heads of this kv head into shared memory as fp16 (and fp32 for the scoring chain): optional
     // head norm with gains in the oracle's operation order, rounded to the activation dtype.
-    for (int g = warp; g < 8; g += nwarps) {
+    for (int hh = warp; hh < 8; hh += NCONS + 1) {
         float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (g < p.G) {
-            const size_t off = size_t(b) * p.q_stride + size_t(kvh * p.G + g) * HD;
+        if (hh < p.G) {
+            const size_t off = size_t(b) * p.q_stride + size_t(kvh * p.G + hh) * HD;
 #pragma unroll
             for (int i = 0; i < 4; i++) x[i] = Act<DT>::load(p.q, off + lane + 32 * i);
             if (!p.prenormed) {
@@ -81,54 +128,24 @@ __device__ __forceinline__ void prep_query_smem(const FullDecodeParams& p, int b
         }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            qh[g][lane + 32 * i] = __float2half_rn(x[i]);
-            if (qf) qf[g][lane + 32 * i] = x[i];
+            qh[hh][lane + 32 * i] = __float2half_rn(x[i]);
+            if (SCORES) qf[hh][lane + 32 * i] = x[i];
         }
     }
-}
-
-template <int DT, int STAGES, bool SCORES>
-__global__ void __launch_bounds__(FD_THREADS) full_decode_kernel(const __grid_constant__ CUtensorMap tmap,
-                                                                const FullDecodeParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* stages = smem;
-    __half(*qh)[HD] = reinterpret_cast<__half(*)[HD]>(smem + STAGES * FD_STAGE_BYTES);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * FD_STAGE_BYTES + 8 * HD * 2);
-    uint64_t* empty = full + STAGES;
-    float(*qf)[HD] = SCORES ? reinterpret_cast<float(*)[HD]>(empty + STAGES) : nullptr;
-    __shared__ int s_last, s_failed, s_issued;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int S = p.seq_lens[b];
-    const int npages = (S + BLK - 1) / BLK;
-    const int pps = (npages + p.nsplit - 1) / p.nsplit;
-    const int pg0 = split * pps;
-    const int n = max(0, min(npages, pg0 + pps) - pg0);
-
-    if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], FD_CONSUMERS);
-        }
-        s_failed = 0;
-        s_issued = 0;
-        fence_barrier_init();
-    }
-    prep_query_smem<DT>(p, b, kvh, qh, qf, warp, lane, FD_CONSUMERS + 1);
     __syncthreads();
 
+    // Lane (g, c) of a consumer warp. S^T = K Q^T: M rows are 16 keys, N columns the 8 (padded)
+    // query heads; O^T = V^T P^T: M rows are 16 head dims, K the same 16 keys.
     const int g = lane >> 2, c = lane & 3;
-    float O[16][4];
+    float OT[8][4];
 #pragma unroll
-    for (int i = 0; i < 16; i++) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.0f;
-    float psum = 0.0f;
+    for (int i = 0; i < 8; i++) OT[i][0] = OT[i][1] = OT[i][2] = OT[i][3] = 0.0f;
+    float ps0 = 0.0f, ps1 = 0.0f;   // sums of weights of heads 2c, 2c + 1
 
-    if (warp == FD_CONSUMERS) {
+    if (warp == NCONS) {
         // ---- producer: one lane keeps the ring of stages full
         if (lane == 0) {
-            const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * p.scale_bytes;
+            const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * SB;
             for (int i = 0; i < n; i++) {
                 const int st = i % STAGES, use = i / STAGES;
                 if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
@@ -140,21 +157,21 @@ __global__ void __launch_bounds__(FD_THREADS) full_decode_kernel(const __grid_co
                 uint8_t* dst = stages + st * FD_STAGE_BYTES;
                 mbar_expect_tx(&full[st], tx);
                 tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &full[st]);
-                bulk_load_1d(dst + 2 * CODE_BYTES, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES,
-                             2 * BLK * p.scale_bytes, &full[st]);
+                bulk_load_1d(dst + 2 * CODE_BYTES, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB,
+                             &full[st]);
                 *reinterpret_cast<volatile int*>(&s_issued) = i + 1;
             }
         }
     } else {
         // ---- consumers
-        uint32_t qa0[8], qa2[8];
+        uint32_t qb0[8], qb1[8];
 #pragma unroll
         for (int t = 0; t < 8; t++) {
             const int d0 = (t < 4) ? 16 * c + 4 * t : 64 + 16 * c + 4 * (t - 4);
-            qa0[t] = *reinterpret_cast<const uint32_t*>(&qh[g][d0]);
-            qa2[t] = *reinterpret_cast<const uint32_t*>(&qh[g][d0 + 2]);
+            qb0[t] = *reinterpret_cast<const uint32_t*>(&qh[g][d0]);
+            qb1[t] = *reinterpret_cast<const uint32_t*>(&qh[g][d0 + 2]);
         }
-        const int rho_g = rho(g), kA = rho(2 * c), kB = kA ^ 4;
+        const int rg = rho(g), kA = rho(2 * c), kB = kA ^ 4;
         const float scale = rsqrtf(float(HD));
         for (int i = 0; i < n; i++) {
             const int st = i % STAGES, use = i / STAGES;
@@ -166,11 +183,12 @@ __global__ void __launch_bounds__(FD_THREADS) full_decode_kernel(const __grid_co
             const uint8_t* Kb = stages + st * FD_STAGE_BYTES;
             const uint8_t* Vb = Kb + CODE_BYTES;
             const uint8_t* ksc = Kb + 2 * CODE_BYTES;
-            const uint8_t* vsc = ksc + BLK * p.scale_bytes;
+            const uint8_t* vsc = ksc + BLK * SB;
             const int key_base = (pg0 + i) * BLK;
 
             if (SCORES) {
-                // one key a thread: the kv head's heads' dots as one fmaf chain over d ascending
+                // one key a thread (KPW = 32): the kv head's heads' dots, each one fmaf chain over d ascending
+                static_assert(!SCORES || KPW == 32, "scoring takes one key a thread");
                 const int r = warp * 32 + lane;
                 if (key_base + r < S) {
                     float dot[8];
@@ -180,17 +198,25 @@ __global__ void __launch_bounds__(FD_THREADS) full_decode_kernel(const __grid_co
 #pragma unroll
                     for (int ch = 0; ch < 8; ch++) {
                         const uint4 w4 = *reinterpret_cast<const uint4*>(krow + ((ch ^ (r & 7)) << 4));
-                        const uint32_t w[4] = {w4.x, w4.y, w4.z, w4.w};
+                        const uint32_t w[4] = {w4.x ^ 0x80808080u, w4.y ^ 0x80808080u, w4.z ^ 0x80808080u, w4.w ^ 0x80808080u};
 #pragma unroll
-                        for (int e = 0; e < 16; e++) {
-                            const float kv = float(int(int8_t((w[e >> 2] >> (8 * (e & 3))) & 0xff)));
-                            const int d = ch * 16 + e;
+                        for (int e4 = 0; e4 < 4; e4++) {
+                            const float k0 = f32_from_biased_byte(w[e4], 0), k1 = f32_from_biased_byte(w[e4], 1);
+                            const float k2 = f32_from_biased_byte(w[e4], 2), k3 = f32_from_biased_byte(w[e4], 3);
+                            const int d = ch * 16 + e4 * 4;
 #pragma unroll
-                            for (int h = 0; h < 8; h++)
-                                if (h < p.G) dot[h] = __fmaf_rn(qf[h][d], kv, dot[h]);
+                            for (int h = 0; h < 8; h++) {
+                                if (h < p.G) {
+                                    const float4 q4 = *reinterpret_cast<const float4*>(&qf[h][d]);
+                                    dot[h] = __fmaf_rn(q4.x, k0, dot[h]);
+                                    dot[h] = __fmaf_rn(q4.y, k1, dot[h]);
+                                    dot[h] = __fmaf_rn(q4.z, k2, dot[h]);
+                                    dot[h] = __fmaf_rn(q4.w, k3, dot[h]);
+                                }
+                            }
                         }
                     }
-                    const float ks = load_scale(ksc, r, p.scale_bytes);
+                    const float ks = ld_scale<SB>(ksc, r);
                     float best = __fmul_rn(dot[0], ks);
 #pragma unroll
                     for (int h = 1; h < 8; h++) {
@@ -204,36 +230,40 @@ __global__ void __launch_bounds__(FD_THREADS) full_decode_kernel(const __grid_co
             }
 
 #pragma unroll
-            for (int step = 0; step < 2; step++) {
-                const int R0 = warp * 32 + step * 16;
-                float pw[2][2];
-#pragma unroll
-                for (int j = 0; j < 2; j++) {
-                    const int r = R0 + 8 * j + rho_g;
-                    const uint8_t* krow = Kb + r * 128;
-                    const uint4 lo = *reinterpret_cast<const uint4*>(krow + ((c ^ rho_g) << 4));
-                    const uint4 hi = *reinterpret_cast<const uint4*>(krow + (((c + 4) ^ rho_g) << 4));
-                    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                    float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int step = 0; step < KPW / 16; step++) {
+                const int R0 = warp * KPW + step * 16;
+                const int r0 = R0 + rg, r1 = r0 + 8;
+                float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                {
+                    const uint8_t* k0 = Kb + r0 * 128;
+                    const uint4 lo0 = *reinterpret_cast<const uint4*>(k0 + ((c ^ rg) << 4));
+                    const uint4 hi0 = *reinterpret_cast<const uint4*>(k0 + (((c + 4) ^ rg) << 4));
+                    const uint4 lo1 = *reinterpret_cast<const uint4*>(k0 + 8 * 128 + ((c ^ rg) << 4));
+                    const uint4 hi1 = *reinterpret_cast<const uint4*>(k0 + 8 * 128 + (((c + 4) ^ rg) << 4));
+                    const uint32_t w0[8] = {lo0.x, lo0.y, lo0.z, lo0.w, hi0.x, hi0.y, hi0.z, hi0.w};
+                    const uint32_t w1[8] = {lo1.x, lo1.y, lo1.z, lo1.w, hi1.x, hi1.y, hi1.z, hi1.w};
 #pragma unroll
                     for (int t = 0; t < 8; t++) {
-                        const uint32_t x = w[t] ^ 0x80808080u;
-                        mma_16816(s, qa0[t], 0u, qa2[t], 0u, h2_from_biased_bytes(x, 0x4140), h2_from_biased_bytes(x, 0x4342));
+                        const uint32_t x0 = w0[t] ^ 0x80808080u, x1 = w1[t] ^ 0x80808080u;
+                        mma_16816(s, h2_from_biased_bytes(x0, 0x4140), h2_from_biased_bytes(x1, 0x4140),
+                                  h2_from_biased_bytes(x0, 0x4342), h2_from_biased_bytes(x1, 0x4342), qb0[t], qb1[t]);
                     }
-                    const int keyA = R0 + 8 * j + kA, keyB = R0 + 8 * j + kB;
-                    const float tA = s[0] * load_scale(ksc, keyA, p.scale_bytes);
-                    const float tB = s[1] * load_scale(ksc, keyB, p.scale_bytes);
-                    const float aA = fmaxf(tA * scale, 0.0f), aB = fmaxf(tB * scale, 0.0f);
-                    const float wA = (key_base + keyA < S) ? aA * aA : 0.0f;
-                    const float wB = (key_base + keyB < S) ? aB * aB : 0.0f;
-                    psum += wA + wB;
-                    pw[j][0] = wA != 0.0f ? wA * load_scale(vsc, keyA, p.scale_bytes) : 0.0f;
-                    pw[j][1] = wB != 0.0f ? wB * load_scale(vsc, keyB, p.scale_bytes) : 0.0f;
                 }
+                // s[0], s[1]: key r0, heads 2c, 2c+1; s[2], s[3]: key r1
+                const bool v0 = key_base + r0 < S, v1 = key_base + r1 < S;
+                const float ks0 = ld_scale<SB>(ksc, r0), ks1 = ld_scale<SB>(ksc, r1);
+                const float a00 = fmaxf(s[0] * ks0 * scale, 0.0f), a01 = fmaxf(s[1] * ks0 * scale, 0.0f);
+                const float a10 = fmaxf(s[2] * ks1 * scale, 0.0f), a11 = fmaxf(s[3] * ks1 * scale, 0.0f);
+                const float w00 = v0 ? a00 * a00 : 0.0f, w01 = v0 ? a01 * a01 : 0.0f;
+                const float w10 = v1 ? a10 * a10 : 0.0f, w11 = v1 ? a11 * a11 : 0.0f;
+                ps0 += w00 + w10;
+                ps1 += w01 + w11;
                 // V-skip: a 16-key tile whose weights are all zero adds nothing (attention.metal:310)
-                const bool live = pw[0][0] != 0.0f || pw[0][1] != 0.0f || pw[1][0] != 0.0f || pw[1][1] != 0.0f;
+                const bool live = (w00 != 0.0f) | (w01 != 0.0f) | (w10 != 0.0f) | (w11 != 0.0f);
                 if (!__any_sync(0xffffffffu, live)) continue;
-                const uint32_t pa0 = pack_h2(pw[0][0], pw[0][1]), pa2 = pack_h2(pw[1][0], pw[1][1]);
+                const float vs0 = v0 ? ld_scale<SB>(vsc, r0) : 0.0f, vs1 = v1 ? ld_scale<SB>(vsc, r1) : 0.0f;
+                const uint32_t pb0 = movmatrix_trans(pack_h2(w00 * vs0, w01 * vs0));
+                const uint32_t pb1 = movmatrix_trans(pack_h2(w10 * vs1, w11 * vs1));
                 const uint8_t* vA = Vb + (R0 + kA) * 128 + ((g ^ kA) << 4);
                 const uint8_t* vB = Vb + (R0 + kB) * 128 + ((g ^ kB) << 4);
                 const uint4 a4 = *reinterpret_cast<const uint4*>(vA);
@@ -243,15 +273,24 @@ __global__ void __launch_bounds__(FD_THREADS) full_decode_kernel(const __grid_co
                 const uint32_t va[4] = {a4.x, a4.y, a4.z, a4.w}, vb[4] = {b4.x, b4.y, b4.z, b4.w};
                 const uint32_t vc[4] = {c4.x, c4.y, c4.z, c4.w}, vd[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
-                for (int wq = 0; wq < 4; wq++) {
-                    const uint32_t x = va[wq] ^ 0x80808080u, y = vb[wq] ^ 0x80808080u;
-                    const uint32_t x2 = vc[wq] ^ 0x80808080u, y2 = vd[wq] ^ 0x80808080u;
-                    const uint32_t z0 = __byte_perm(x, y, 0x5140), z1 = __byte_perm(x, y, 0x7362);
-                    const uint32_t u0 = __byte_perm(x2, y2, 0x5140), u1 = __byte_perm(x2, y2, 0x7362);
-                    mma_16816(O[4 * wq + 0], pa0, 0u, pa2, 0u, h2_from_biased_bytes(z0, 0x4140), h2_from_biased_bytes(u0, 0x4140));
-                    mma_16816(O[4 * wq + 1], pa0, 0u, pa2, 0u, h2_from_biased_bytes(z0, 0x4342), h2_from_biased_bytes(u0, 0x4342));
-                    mma_16816(O[4 * wq + 2], pa0, 0u, pa2, 0u, h2_from_biased_bytes(z1, 0x4140), h2_from_biased_bytes(u1, 0x4140));
-                    mma_16816(O[4 * wq + 3], pa0, 0u, pa2, 0u, h2_from_biased_bytes(z1, 0x4342), h2_from_biased_bytes(u1, 0x4342));
+                for (int wq = 0; wq < 2; wq++) {
+                    // dims 16g + 4wq + e (rows g of tiles 4wq + e) and 16g + 8 + 4wq + e (rows g + 8)
+                    const uint32_t xl = va[wq] ^ 0x80808080u, yl = vb[wq] ^ 0x80808080u;
+                    const uint32_t xh = va[wq + 2] ^ 0x80808080u, yh = vb[wq + 2] ^ 0x80808080u;
+                    const uint32_t x2l = vc[wq] ^ 0x80808080u, y2l = vd[wq] ^ 0x80808080u;
+                    const uint32_t x2h = vc[wq + 2] ^ 0x80808080u, y2h = vd[wq + 2] ^ 0x80808080u;
+                    const uint32_t zl0 = __byte_perm(xl, yl, 0x5140), zl1 = __byte_perm(xl, yl, 0x7362);
+                    const uint32_t zh0 = __byte_perm(xh, yh, 0x5140), zh1 = __byte_perm(xh, yh, 0x7362);
+                    const uint32_t ul0 = __byte_perm(x2l, y2l, 0x5140), ul1 = __byte_perm(x2l, y2l, 0x7362);
+                    const uint32_t uh0 = __byte_perm(x2h, y2h, 0x5140), uh1 = __byte_perm(x2h, y2h, 0x7362);
+                    mma_16816(OT[4 * wq + 0], h2_from_biased_bytes(zl0, 0x4140), h2_from_biased_bytes(zh0, 0x4140),
+                              h2_from_biased_bytes(ul0, 0x4140), h2_from_biased_bytes(uh0, 0x4140), pb0, pb1);
+                    mma_16816(OT[4 * wq + 1], h2_from_biased_bytes(zl0, 0x4342), h2_from_biased_bytes(zh0, 0x4342),
+                              h2_from_biased_bytes(ul0, 0x4342), h2_from_biased_bytes(uh0, 0x4342), pb0, pb1);
+                    mma_16816(OT[4 * wq + 2], h2_from_biased_bytes(zl1, 0x4140), h2_from_biased_bytes(zh1, 0x4140),
+                              h2_from_biased_bytes(ul1, 0x4140), h2_from_biased_bytes(uh1, 0x4140), pb0, pb1);
+                    mma_16816(OT[4 * wq + 3], h2_from_biased_bytes(zl1, 0x4342), h2_from_biased_bytes(zh1, 0x4342),
+                              h2_from_biased_bytes(ul1, 0x4342), h2_from_biased_bytes(uh1, 0x4342), pb0, pb1);
                 }
             }
             __syncwarp();
@@ -259,8 +298,9 @@ __global__ void __launch_bounds__(FD_THREADS) full_decode_kernel(const __grid_co
         }
     }
 
-    // ---- the 4 consumer warps' sums into one partial (the stage ring is free now: every page that
-    // was requested has been waited for, unless a wait gave up — then drain what is still in flight)
+    // ---- the consumer warps' sums into one partial. The stage ring is free now: every page that
+    // was requested has been waited for, unless a wait gave up — then wait (bounded) for what is
+    // still in flight first.
     __syncthreads();
     if (s_failed) {
         if (tid == 0) {
@@ -270,36 +310,46 @@ __global__ void __launch_bounds__(FD_THREADS) full_decode_kernel(const __grid_co
         __syncthreads();
     }
     float(*red)[8][HD] = reinterpret_cast<float(*)[8][HD]>(stages);
-    float(*redp)[8] = reinterpret_cast<float(*)[8]>(stages + FD_CONSUMERS * 8 * HD * 4);
-    if (warp < FD_CONSUMERS) {
-        psum += __shfl_xor_sync(0xffffffffu, psum, 1);
-        psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+    float(*redp)[8] = reinterpret_cast<float(*)[8]>(stages + NCONS * 8 * HD * 4);
+    if (warp < NCONS) {
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-            red[warp][g][32 * c + i] = O[i][0];
-            red[warp][g][32 * c + 16 + i] = O[i][1];
+        for (int o = 4; o < 32; o <<= 1) {
+            ps0 += __shfl_xor_sync(0xffffffffu, ps0, o);
+            ps1 += __shfl_xor_sync(0xffffffffu, ps1, o);
         }
-        if (c == 0) redp[warp][g] = psum;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            red[warp][2 * c][16 * g + i] = OT[i][0];
+            red[warp][2 * c + 1][16 * g + i] = OT[i][1];
+            red[warp][2 * c][16 * g + 8 + i] = OT[i][2];
+            red[warp][2 * c + 1][16 * g + 8 + i] = OT[i][3];
+        }
+        if (g == 0) {
+            redp[warp][2 * c] = ps0;
+            redp[warp][2 * c + 1] = ps1;
+        }
     }
     __syncthreads();
 
     const int pair = b * p.n_kv_heads + kvh;
     const float sink = sqrtf(float(HD));
-    if (p.nsplit == 1) {
-        for (int idx = tid; idx < p.G * HD; idx += FD_THREADS) {
-            const int hh = idx >> 7, d = idx & 127;
-            const float num = ((red[0][hh][d] + red[1][hh][d]) + red[2][hh][d]) + red[3][hh][d];
-            const float den = sink + (((redp[0][hh] + redp[1][hh]) + redp[2][hh]) + redp[3][hh]);
-            Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / den);
-        }
-        return;
-    }
     float* part = p.partials + (size_t(pair) * p.nsplit + split) * p.G * FD_PART;
-    for (int idx = tid; idx < p.G * HD; idx += FD_THREADS) {
+    for (int idx = tid; idx < p.G * HD; idx += THREADS) {
         const int hh = idx >> 7, d = idx & 127;
-        part[hh * FD_PART + d] = ((red[0][hh][d] + red[1][hh][d]) + red[2][hh][d]) + red[3][hh][d];
-        if (d == 0) part[hh * FD_PART + HD] = ((redp[0][hh] + redp[1][hh]) + redp[2][hh]) + redp[3][hh];
+        float num = 0.0f, den = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NCONS; w++) {
+            num += red[w][hh][d];
+            den += redp[w][hh];
+        }
+        if (p.nsplit == 1) {
+            Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / (sink + den));
+        } else {
+            part[hh * FD_PART + d] = num;
+            if (d == 0) part[hh * FD_PART + HD] = den;
+        }
     }
+    if (p.nsplit == 1) return;
     // last CTA of the pair to arrive adds the splits in order (arrive_last, common.metal:88-99)
     __threadfence();
     __syncthreads();
@@ -312,7 +362,7 @@ __global__ void __launch_bounds__(FD_THREADS) full_decode_kernel(const __grid_co
     if (!s_last) return;
     __threadfence();
     const float* base = p.partials + size_t(pair) * p.nsplit * p.G * FD_PART;
-    for (int idx = tid; idx < p.G * HD; idx += FD_THREADS) {
+    for (int idx = tid; idx < p.G * HD; idx += THREADS) {
         const int hh = idx >> 7, d = idx & 127;
         float num = 0.0f, den = sink;
         for (int s = 0; s < p.nsplit; s++) {
@@ -326,7 +376,7 @@ __global__ void __launch_bounds__(FD_THREADS) full_decode_kernel(const __grid_co
 
 template <int STAGES, bool SCORES>
 constexpr size_t fd_smem_bytes() {
-    return 1024 + size_t(STAGES) * FD_STAGE_BYTES + 8 * HD * 2 + 2 * STAGES * 8 + (SCORES ? 8 * HD * 4 : 0);
+    return 1024 + size_t(STAGES) * FD_STAGE_BYTES + 8 * HD * 2 + 2 * STAGES * 8 + (SCORES ? 8 * QF_LD * 4 : 0);
 }
 
 // Key ranges per (sequence, kv head): fill `slots` resident CTAs in whole waves, with ranges long
@@ -352,12 +402,14 @@ int choose_splits(int pairs, int pages, int slots, int max_slots) {
 
 using namespace embla;
 
-template <int DT, bool SCORES>
+template <int DT, int SB, bool SCORES>
 static EmblaStatus launch_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const FullDecodeParams& p, int batch,
                                       cudaStream_t s) {
     constexpr int STAGES = 3;
+    constexpr int NCONS = SCORES ? 4 : 8;
+    constexpr int FD_THREADS = (NCONS + 1) * 32;
     constexpr size_t smem = fd_smem_bytes<STAGES, SCORES>();
-    auto kern = full_decode_kernel<DT, STAGES, SCORES>;
+    auto kern = full_decode_kernel<DT, SB, NCONS, STAGES, SCORES>;
     static bool configured[64] = {};   // per instantiation and device
     if (!configured[ctx->device & 63]) {
         EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
@@ -419,10 +471,13 @@ extern "C" EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool*
     p.nsplit = choose_splits(pairs, pages, 2 * ctx->sm_count, ctx->partial_slots);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
+    const bool s4 = pool->scale_bytes == 4;
+#define EMBLA_FD(DT, SB, SC) launch_full_decode<DT, SB, SC>(ctx, pool, p, view->batch, s)
     if (scores_dev) {
-        return bf ? launch_full_decode<EMBLA_BF16, true>(ctx, pool, p, view->batch, s)
-                  : launch_full_decode<EMBLA_F16, true>(ctx, pool, p, view->batch, s);
+        if (bf) return s4 ? EMBLA_FD(EMBLA_BF16, 4, true) : EMBLA_FD(EMBLA_BF16, 2, true);
+        return s4 ? EMBLA_FD(EMBLA_F16, 4, true) : EMBLA_FD(EMBLA_F16, 2, true);
     }
-    return bf ? launch_full_decode<EMBLA_BF16, false>(ctx, pool, p, view->batch, s)
-              : launch_full_decode<EMBLA_F16, false>(ctx, pool, p, view->batch, s);
+    if (bf) return s4 ? EMBLA_FD(EMBLA_BF16, 4, false) : EMBLA_FD(EMBLA_BF16, 2, false);
+    return s4 ? EMBLA_FD(EMBLA_F16, 4, false) : EMBLA_FD(EMBLA_F16, 2, false);
+#undef EMBLA_FD
 }
