@@ -169,3 +169,45 @@ class Attention:
         _check(lib().embla_attn_full_decode(self.handle, pool.handle, C.byref(view), C.byref(qd), _ptr(o),
                                             C.c_int64(o.stride(0)), _ptr(scores),
                                             C.c_int64(0 if scores is None else scores.stride(1)), _stream()))
+
+    def score_keys(self, pool, block_table, seq_lens, layer, q, scores, max_seq_len=0):
+        """scores [batch, n_kv_heads, >= max_seq_len] fp32 <- max over the kv head's query heads of q·k."""
+        view = self.view(block_table, seq_lens, layer, max_seq_len)
+        _check(lib().embla_score_keys(self.handle, pool.handle, C.byref(view), _ptr(q), C.c_int64(q.stride(0)),
+                                      _ptr(scores), C.c_int64(scores.stride(1)), _stream()))
+
+    def select_keys(self, scores, seq_lens, idx, max_seq_len=0):
+        """idx [batch, n_kv_heads, 1152] uint32 (int32 tensor) <- top 1024 + 128 latest per kv head."""
+        _check(lib().embla_select_keys(self.handle, _ptr(scores), C.c_int64(scores.stride(1)), _ptr(seq_lens),
+                                       scores.shape[0], max_seq_len, _ptr(idx), _stream()))
+
+    def sparse_decode(self, pool, block_table, seq_lens, layer, q, o, idx=None, gains=None, max_seq_len=0):
+        view = self.view(block_table, seq_lens, layer, max_seq_len)
+        qd = self.query(q, gains)
+        _check(lib().embla_attn_sparse_decode(self.handle, pool.handle, C.byref(view), C.byref(qd), _ptr(idx), _ptr(o),
+                                              C.c_int64(o.stride(0)), _stream()))
+
+    def sliding_write(self, ring, pos0, k, v, kgain=None):
+        """k, v [batch, n_tokens, n_kv_heads * 128 (or wider rows)] into the rings at positions pos0[b] + t."""
+        _check(lib().embla_sliding_write(self.handle, C.byref(ring.desc), _ptr(pos0), k.shape[0], k.shape[1], _ptr(k),
+                                         _ptr(v), C.c_int64(k.stride(1)), C.c_int64(k.stride(0)), int(kgain is None),
+                                         _ptr(kgain), _stream()))
+
+    def sliding_decode(self, ring, seq_lens, q, o, qgain=None):
+        qd = self.query(q, None if qgain is None else (qgain, None))
+        _check(lib().embla_attn_sliding_decode(self.handle, C.byref(ring.desc), _ptr(seq_lens), q.shape[0], C.byref(qd),
+                                               _ptr(o), C.c_int64(o.stride(0)), _stream()))
+
+
+class RingDesc(C.Structure):
+    _fields_ = [("k_dev", C.c_void_p), ("v_dev", C.c_void_p), ("seq_stride", C.c_int64), ("ring", C.c_int32),
+                ("window", C.c_int32)]
+
+
+class Ring:
+    """Sliding-layer rings of a batch: k, v [batch, n_kv_heads, ring, 128] in the activation dtype."""
+
+    def __init__(self, batch, n_kv_heads, ring, window, torch_dtype):
+        self.k = torch.zeros(batch, n_kv_heads, ring, HEAD_DIM, dtype=torch_dtype, device="cuda")
+        self.v = torch.zeros_like(self.k)
+        self.desc = RingDesc(self.k.data_ptr(), self.v.data_ptr(), self.k.stride(0), ring, window)

@@ -123,7 +123,9 @@ EmblaStatus embla_kv_pool_create(int32_t n_layers, int32_t n_kv_heads, int32_t k
     p->num_blocks = num_blocks;
     p->scale_bytes = scale_dtype == EMBLA_SCALE_F32 ? 4 : 2;
     p->page_bytes = kv_dtype == EMBLA_KV_INT8 ? size_t(2 * CODE_BYTES + 2 * BLK * p->scale_bytes) : size_t(2 * BLK * HD * 2);
-    p->rows_per_page = int(p->page_bytes / 128);
+    // tensor-map rows: 128 bytes for int8 pages, 256 bytes (one key) for 16-bit pages
+    const int row_bytes = kv_dtype == EMBLA_KV_INT8 ? 128 : 256;
+    p->rows_per_page = int(p->page_bytes / row_bytes);
     p->block_bytes = p->page_bytes * n_layers * n_kv_heads;
     p->total_bytes = p->block_bytes * num_blocks;
     p->base = nullptr;
@@ -145,9 +147,11 @@ EmblaStatus embla_kv_pool_create(int32_t n_layers, int32_t n_kv_heads, int32_t k
         delete p;
         EMBLA_FAIL(EMBLA_CUDA, "embla_kv_pool_create: cuTensorMapEncodeTiled is not available from this driver");
     }
-    const cuuint64_t dims[2] = {128, cuuint64_t(p->total_bytes / 128)};
-    const cuuint64_t strides[1] = {128};
-    const cuuint32_t box[2] = {128, 256};
+    // (16-bit pages: rows of 256 bytes seen through 128-byte-wide boxes of 128 keys, so that a key's
+    // dims 0-63 and 64-127 land in two tiles, each [128 keys][128 B] under the same swizzle.)
+    const cuuint64_t dims[2] = {cuuint64_t(row_bytes), cuuint64_t(p->total_bytes / row_bytes)};
+    const cuuint64_t strides[1] = {cuuint64_t(row_bytes)};
+    const cuuint32_t box[2] = {128, kv_dtype == EMBLA_KV_INT8 ? 256u : 128u};
     const cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(&p->tmap_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, p->base, dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

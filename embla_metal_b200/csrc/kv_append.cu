@@ -2,7 +2,8 @@
 // (Sources/EmblaMetal/Kernels/attention.metal:113-140, prefill.metal:184-212, common.metal:74-84),
 // writing into the paged pool. One warp per (sequence, token, kv head, K|V); a lane holds dims
 // lane + 32 i like the reference. Every fp32 operation is an explicit round-to-nearest intrinsic in
-// the order the CPU oracle uses, so codes and scales are bit-exact.
+// the order the CPU oracle uses, so codes and scales are bit-exact. A 16-bit pool (sparse layers that
+// keep their own keys) takes the rows as they are, rounded to the activation dtype.
 #include "common.cuh"
 
 namespace embla {
@@ -15,7 +16,7 @@ struct AppendParams {
     const void* v;
     int64_t token_stride, seq_stride;
     size_t page_bytes;
-    int table_stride, batch, n_tokens, layer, n_layers, n_kv_heads, scale_bytes, norm_k;
+    int table_stride, batch, n_tokens, layer, n_layers, n_kv_heads, scale_bytes, norm_k, kv16;
 };
 
 template <int DT>
@@ -45,6 +46,16 @@ __global__ void __launch_bounds__(128) kv_append_kernel(const AppendParams p) {
 #pragma unroll
         for (int i = 0; i < 4; i++) x[i] = __fmul_rn(x[i], r);
     }
+    const int pos = p.pos0[b] + t;
+    const int block = p.block_table[size_t(b) * p.table_stride + pos / BLK];
+    const int row = pos % BLK;
+    uint8_t* page = p.pool + ((size_t(block) * p.n_layers + p.layer) * p.n_kv_heads + h) * p.page_bytes;
+    if (p.kv16) {   // 16-bit pages: K rows [128][128], then V rows, in the activation dtype
+        uint8_t* dst = page + (is_v ? BLK * HD * 2 : 0);
+#pragma unroll
+        for (int i = 0; i < 4; i++) Act<DT>::store(dst, size_t(row) * HD + lane + 32 * i, x[i]);
+        return;
+    }
     float a = 0.0f;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -54,11 +65,6 @@ __global__ void __launch_bounds__(128) kv_append_kernel(const AppendParams p) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
     const float inv = a > 0.0f ? __fdiv_rn(127.0f, a) : 0.0f;
-
-    const int pos = p.pos0[b] + t;
-    const int block = p.block_table[size_t(b) * p.table_stride + pos / BLK];
-    const int row = pos % BLK;
-    uint8_t* page = p.pool + ((size_t(block) * p.n_layers + p.layer) * p.n_kv_heads + h) * p.page_bytes;
     int8_t* codes = reinterpret_cast<int8_t*>(page) + (is_v ? CODE_BYTES : 0) + row * HD;
 #pragma unroll
     for (int i = 0; i < 4; i++) codes[lane + 32 * i] = int8_t(int(rintf(__fmul_rn(x[i], inv))));
@@ -79,7 +85,6 @@ extern "C" EmblaStatus embla_kv_append(EmblaAttn* ctx, EmblaKVPool* pool, const 
                                        const void* k_dev, const void* v_dev, int64_t token_stride, int64_t seq_stride,
                                        int32_t norm_k, void* stream) {
     if (!ctx || !pool || !view || !pos0_dev || !k_dev || !v_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_append: null argument");
-    if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_kv_append: the pool is not int8");
     if (view->layer < 0 || view->layer >= pool->n_layers)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_append: layer %d outside the pool's %d", view->layer, pool->n_layers);
     if (view->batch <= 0 || n_tokens <= 0 || !view->block_table_dev)
@@ -103,6 +108,7 @@ extern "C" EmblaStatus embla_kv_append(EmblaAttn* ctx, EmblaKVPool* pool, const 
     p.n_kv_heads = pool->n_kv_heads;
     p.scale_bytes = pool->scale_bytes;
     p.norm_k = norm_k;
+    p.kv16 = pool->kv_dtype == EMBLA_KV_16BIT;
     const long warps = long(p.batch) * n_tokens * p.n_kv_heads * 2;
     const unsigned blocks = unsigned((warps + 3) / 4);
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -1,0 +1,203 @@
+// Key scoring of sparse layers that hold their own 16-bit keys: scores[kv head][j] = max over the
+// kv head's query heads of q·k_j, the by-product the reference's full layers emit with SCORES
+// (Sources/EmblaMetal/Kernels/attention.metal:146, 189, 203-205), as a pass of its own over the
+// paged pool. The selection that follows compares index sets bit for bit, so every dot is ONE fp32
+// fmaf chain over d = 0..127 (the order the CPU oracle fixes) — CUDA cores, not tensor cores.
+//
+// HBM-bound in bytes (256 B a key) but heavy in issue slots (G x 128 FMAs + 128 converts a key):
+// a producer warp streams pages through a TMA ring (two 128-byte-wide swizzled boxes a page, dims
+// 0-63 and 64-127); each consumer thread owns one key of the page and reads its row 16 bytes at a
+// time, conflict-free under the swizzle; queries sit in shared memory as fp32 and are read as
+// broadcast float4s.
+#include "common.cuh"
+
+namespace embla {
+
+constexpr int SK_CONSUMERS = 4;
+constexpr int SK_THREADS = (SK_CONSUMERS + 1) * 32;
+constexpr int SK_STAGE = BLK * HD * 2;   // K side of a 16-bit page
+constexpr int SK_QLD = HD + 4;
+
+struct ScoreParams {
+    const int32_t* block_table;
+    const int32_t* seq_lens;
+    const void* q;
+    float* scores;
+    int* err;
+    int64_t q_stride, scores_stride;
+    int table_stride, layer, n_layers, n_kv_heads, rows_per_page, nsplit;
+};
+
+template <int DT>
+__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
+    const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if (DT == EMBLA_F16) {
+            const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&v[i]));
+            f[2 * i] = t.x;
+            f[2 * i + 1] = t.y;
+        } else {
+            f[2 * i] = __uint_as_float(v[i] << 16);
+            f[2 * i + 1] = __uint_as_float(v[i] & 0xffff0000u);
+        }
+    }
+}
+
+template <int DT, int G, int STAGES>
+__global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_constant__ CUtensorMap tmap,
+                                                                 const ScoreParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* stages = smem;
+    float(*qf)[SK_QLD] = reinterpret_cast<float(*)[SK_QLD]>(smem + STAGES * SK_STAGE);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * SK_STAGE + G * SK_QLD * 4);
+    uint64_t* empty = full + STAGES;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int S = p.seq_lens[b];
+    const int npages = (S + BLK - 1) / BLK;
+    const int pps = (npages + p.nsplit - 1) / p.nsplit;
+    const int pg0 = split * pps;
+    const int n = max(0, min(npages, pg0 + pps) - pg0);
+    if (n == 0) return;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], SK_CONSUMERS);
+        }
+        fence_barrier_init();
+    }
+    for (int i = tid; i < G * HD; i += SK_THREADS) {
+        const int hh = i >> 7, d = i & 127;
+        qf[hh][d] = Act<DT>::load(p.q, size_t(b) * p.q_stride + size_t(kvh * G + hh) * HD + d);
+    }
+    __syncthreads();
+
+    if (warp == SK_CONSUMERS) {
+        if (lane == 0) {
+            for (int i = 0; i < n; i++) {
+                const int st = i % STAGES, use = i / STAGES;
+                if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
+                    atomicExch(p.err, ERR_WAIT_EMPTY);
+                    break;
+                }
+                const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
+                const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
+                uint8_t* dst = stages + st * SK_STAGE;
+                mbar_expect_tx(&full[st], SK_STAGE);
+                tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &full[st]);
+                tma_load_2d(dst + BLK * 128, &tmap, 128, int(page * p.rows_per_page), &full[st]);
+            }
+        }
+        return;
+    }
+    const int r = warp * 32 + lane;   // this thread's key of every page
+    for (int i = 0; i < n; i++) {
+        const int st = i % STAGES, use = i / STAGES;
+        if (!mbar_wait_bounded(&full[st], use & 1)) {
+            atomicExch(p.err, ERR_WAIT_FULL);
+            return;
+        }
+        const uint8_t* Kb = stages + st * SK_STAGE;
+        float dot[G];
+#pragma unroll
+        for (int h = 0; h < G; h++) dot[h] = 0.0f;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ch++) {
+                const uint4 w = *reinterpret_cast<const uint4*>(Kb + half * (BLK * 128) + r * 128 + ((ch ^ (r & 7)) << 4));
+                float kf[8];
+                unpack8<DT>(w, kf);
+                const int d = half * 64 + ch * 8;
+#pragma unroll
+                for (int h = 0; h < G; h++) {
+                    const float4 qa = *reinterpret_cast<const float4*>(&qf[h][d]);
+                    const float4 qb = *reinterpret_cast<const float4*>(&qf[h][d + 4]);
+                    dot[h] = __fmaf_rn(qa.x, kf[0], dot[h]);
+                    dot[h] = __fmaf_rn(qa.y, kf[1], dot[h]);
+                    dot[h] = __fmaf_rn(qa.z, kf[2], dot[h]);
+                    dot[h] = __fmaf_rn(qa.w, kf[3], dot[h]);
+                    dot[h] = __fmaf_rn(qb.x, kf[4], dot[h]);
+                    dot[h] = __fmaf_rn(qb.y, kf[5], dot[h]);
+                    dot[h] = __fmaf_rn(qb.z, kf[6], dot[h]);
+                    dot[h] = __fmaf_rn(qb.w, kf[7], dot[h]);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);
+        float best = dot[0];
+#pragma unroll
+        for (int h = 1; h < G; h++)
+            if (dot[h] > best) best = dot[h];
+        const int key = (pg0 + i) * BLK + r;
+        if (key < S) p.scores[(size_t(b) * p.n_kv_heads + kvh) * p.scores_stride + key] = best;
+    }
+}
+
+int choose_splits(int pairs, int pages, int slots, int max_slots);
+
+template <int DT, int G>
+static EmblaStatus launch_score(EmblaAttn* ctx, const EmblaKVPool* pool, const ScoreParams& p, int batch, cudaStream_t s) {
+    constexpr int STAGES = 3;
+    constexpr size_t smem = 1024 + STAGES * SK_STAGE + G * SK_QLD * 4 + 2 * STAGES * 8;
+    auto kern = score_keys16_kernel<DT, G, STAGES>;
+    static bool configured[64] = {};
+    if (!configured[ctx->device & 63]) {
+        EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        configured[ctx->device & 63] = true;
+    }
+    dim3 grid(p.nsplit, p.n_kv_heads, batch);
+    kern<<<grid, SK_THREADS, smem, s>>>(pool->tmap_codes, p);
+    EMBLA_CUDA_TRY(cudaGetLastError());
+    return EMBLA_OK;
+}
+
+}  // namespace embla
+
+using namespace embla;
+
+extern "C" EmblaStatus embla_score_keys(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                        const void* q_dev, int64_t q_stride, float* scores_dev, int64_t scores_stride,
+                                        void* stream) {
+    if (!ctx || !pool || !view || !q_dev || !scores_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_score_keys: null argument");
+    if (pool->kv_dtype != EMBLA_KV_16BIT) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_score_keys: the pool is not 16-bit");
+    if (pool->n_kv_heads != ctx->cfg.n_kv_heads || view->layer < 0 || view->layer >= pool->n_layers)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_score_keys: pool/layer mismatch");
+    if (view->batch <= 0 || view->batch > ctx->cfg.max_batch || !view->block_table_dev || !view->seq_lens_dev)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_score_keys: bad view (batch %d)", view->batch);
+    const int max_len = view->max_seq_len > 0 ? view->max_seq_len : ctx->cfg.max_context;
+    if (scores_stride < max_len)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_score_keys: scores_stride %lld under max_seq_len %d", (long long)scores_stride, max_len);
+    ScoreParams p;
+    p.block_table = view->block_table_dev;
+    p.seq_lens = view->seq_lens_dev;
+    p.q = q_dev;
+    p.scores = scores_dev;
+    p.err = ctx->err_dev;
+    p.q_stride = q_stride;
+    p.scores_stride = scores_stride;
+    p.table_stride = view->table_stride;
+    p.layer = view->layer;
+    p.n_layers = pool->n_layers;
+    p.n_kv_heads = pool->n_kv_heads;
+    p.rows_per_page = pool->rows_per_page;
+    const int pages = (max_len + BLK - 1) / BLK;
+    p.nsplit = choose_splits(view->batch * pool->n_kv_heads, pages, 2 * ctx->sm_count, 1 << 30);
+    const int G = ctx->cfg.n_q_heads / ctx->cfg.n_kv_heads;
+    const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define EMBLA_SK(G_) (bf ? launch_score<EMBLA_BF16, G_>(ctx, pool, p, view->batch, s) : launch_score<EMBLA_F16, G_>(ctx, pool, p, view->batch, s))
+    switch (G) {
+        case 1: return EMBLA_SK(1);
+        case 2: return EMBLA_SK(2);
+        case 4: return EMBLA_SK(4);
+        case 8: return EMBLA_SK(8);
+        default: EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_score_keys: %d query heads per kv head (1, 2, 4 or 8)", G);
+    }
+#undef EMBLA_SK
+}

@@ -142,6 +142,57 @@ EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, cons
                                    const EmblaQuery* q, void* o_dev, int64_t o_stride,
                                    float* scores_dev, int64_t scores_stride, void* stream);
 
+/* ---- key scoring and selection (sparse layers) --------------------------------------------------- */
+/* The SCORES by-product of attn_full (attention.metal:146, 189, 203-205) as a pass of its own, for
+ * sparse layers that keep their own 16-bit keys in a EMBLA_KV_16BIT pool: scores[b][kv head][j] =
+ * max over the kv head's query heads of q·k_j for j < seq_len. q is taken as given ([batch][q_stride],
+ * head h at h * 128). Bit-exact against the oracle's summation order. */
+EmblaStatus embla_score_keys(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                             const void* q_dev, int64_t q_stride, float* scores_dev, int64_t scores_stride,
+                             void* stream);
+
+/* Replaces select_keys (attention.metal:655-744; dispatch Engine.swift:819-827): for every sequence
+ * with seq_len > 1152 and every kv head, idx[b][kv head][0..1151] = the 1024 highest-scoring keys among
+ * j < seq_len - 128 (ties: lowest index; order: greater ascending, then equal ascending), then the 128
+ * latest. Rows of shorter sequences are left untouched (the reference does not select yet,
+ * Engine.swift:796). scores rows are scores_stride floats apart per (sequence, kv head). Exact. */
+EmblaStatus embla_select_keys(EmblaAttn* ctx, const float* scores_dev, int64_t scores_stride,
+                              const int32_t* seq_lens_dev, int32_t batch, int32_t max_seq_len,
+                              uint32_t* idx_dev, void* stream);
+
+/* ---- decode, sparse layers (softmax) ---------------------------------------------------------------- */
+/* Replaces attn_sparse / attn_sparse8 / attn_sparse_short (attention.metal:370-441, 448-584, 593-645;
+ * dispatch Engine.swift:796-818) over a EMBLA_KV_16BIT pool: softmax attention over all keys of a
+ * sequence with at most 1152, else over its selected rows idx[b][kv head][0..1151]. */
+EmblaStatus embla_attn_sparse_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                     const EmblaQuery* q, const uint32_t* idx_dev, void* o_dev, int64_t o_stride,
+                                     void* stream);
+
+/* ---- sliding layers ------------------------------------------------------------------------------------ */
+/* The sliding layers' rings (Engine.swift:269-276; RING = 4096, attention.metal:4-6): per sequence
+ * [n_kv_heads][ring][128] keys and the same for values, in the activation dtype, owned by the caller. */
+typedef struct {
+    void*   k_dev;
+    void*   v_dev;
+    int64_t seq_stride;   /* elements between sequences (>= n_kv_heads * ring * 128) */
+    int32_t ring;         /* slots; must hold window + one prefill chunk */
+    int32_t window;       /* positions attended, the current one included (128 in the reference) */
+} EmblaRing;
+
+/* Replaces the ring write of attn_sliding (attention.metal:47-62) and kv_sliding_b (prefill.metal:105-125):
+ * for token t < n_tokens of sequence b at position pos0_dev[b] + t, k = round(rope(norm(k) (1 + kgain)))
+ * and v go to slot pos % ring. `prenormed` stores k as given. k/v are [batch][n_tokens][stride]. */
+EmblaStatus embla_sliding_write(EmblaAttn* ctx, const EmblaRing* ring, const int32_t* pos0_dev, int32_t batch,
+                                int32_t n_tokens, const void* k_dev, const void* v_dev, int64_t token_stride,
+                                int64_t seq_stride, int32_t prenormed, const void* kgain_dev, void* stream);
+
+/* Replaces the attention of attn_sliding (attention.metal:63-101): softmax over the last
+ * min(seq_len, window) positions, which must already be in the ring (embla_sliding_write first).
+ * Without `prenormed`, q is normed with gain g1, rotated at position seq_len - 1 and rounded. */
+EmblaStatus embla_attn_sliding_decode(EmblaAttn* ctx, const EmblaRing* ring, const int32_t* seq_lens_dev,
+                                      int32_t batch, const EmblaQuery* q, void* o_dev, int64_t o_stride,
+                                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif
