@@ -1,0 +1,294 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path: batched decode at 32k context through a 24-layer stack.
+
+Workload (BASELINE.json config 4): 64 independent sequences at 32768 context, layers cycling
+sparse, sliding(1024), sliding(1024), full(int8 KV); 16 query / 4 kv heads, head_dim 128, fp16
+activations; KV state synthetic in the configs' distributions (seeded). A "step" decodes one token
+for every sequence through all 24 layers' attention (KV write + attention per layer). Sequences are
+sharded across GPUs (strong scaling: 64 in total), no collective on the data path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One JSON line on stdout (rank 0). `--impl reference` times the CPU restatement of the reference's
+kernels (oracle/) on the host cores instead; nothing else in this file touches oracle/ except the
+cpu_baseline leg.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+TOTAL_SEQS, CONTEXT, N_LAYERS, HQ, HKV, WINDOW, RING = 64, 32768, 24, 16, 4, 1024, 4096
+METRIC, UNIT = "decode attn tok/s @32k ctx", "tok/s"
+
+
+def workload_config(n_gpus):
+    return {"workload": "config 4: batched decode, 64 seqs x 32768 ctx x 24 layers [sparse, sliding1024, sliding1024, full int8]",
+            "sequences": TOTAL_SEQS, "context": CONTEXT, "layers": N_LAYERS, "q_heads": HQ, "kv_heads": HKV, "head_dim": 128,
+            "sparse_mode": "own fp16 K/V: score all keys, radix-select 1024 + 128 latest, attend",
+            "sharding": f"by sequence, {TOTAL_SEQS // n_gpus} per GPU, no collective",
+            "l2": "inputs larger than L2: each step streams the whole KV state (tens of GB) once"}
+
+
+def algorithmic_bytes(batch, entry):
+    """Bytes one launch of `entry` must move for `batch` sequences at CONTEXT keys ('bytes per unit')."""
+    pairs = batch * HKV
+    return {
+        "full_decode": pairs * CONTEXT * (2 * 128 + 2 * 2),          # int8 K, V rows + fp16 scales
+        "score": pairs * CONTEXT * 256,                               # fp16 K rows
+        "sparse_decode": pairs * 1152 * 512,                          # gathered fp16 K, V rows
+        "sliding_decode": pairs * WINDOW * 512,                       # ring fp16 K, V rows
+        "select": pairs * (CONTEXT - 128) * 4,                        # scores read once
+        "append": pairs * 2 * 256, "sliding_write": pairs * 512,
+    }[entry]
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs (read-only NVML)."""
+
+    def __init__(self, index, period=0.02):
+        super().__init__(daemon=True)
+        self.index, self.period, self.samples, self.reasons, self.stop_flag = index, period, [], set(), False
+        self.max_mhz = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake": 0x80}
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def result(self):
+        self.stop_flag = True
+        self.join(timeout=1.0)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+def ncu_traffic(entry, batch):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, scaled to this launch."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(path):
+        return None
+    t = json.load(open(path)).get(entry)
+    if not t:
+        return None
+    return t["dram_bytes_per_key_row"] * batch * HKV * CONTEXT
+
+
+# ---------------------------------------------------------------------------------------------- CPU arm
+def cpu_sample(n_threads, n_items, seed=4):
+    """Times `n_items` sequence-cycles (one sequence through sparse, sliding, sliding, full at CONTEXT keys)
+    of the CPU oracle on `n_threads` host threads. Returns seconds. The KV state of one sequence is shared
+    by all items (distinct queries)."""
+    import numpy as np
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import oracle as orc
+    rng = np.random.default_rng(seed)
+    S = CONTEXT
+    k8 = rng.integers(-127, 128, (HKV, S, 128), dtype=np.int8)
+    v8 = rng.integers(-127, 128, (HKV, S, 128), dtype=np.int8)
+    ks = rng.uniform(0.005, 0.02, (HKV, S)).astype(np.float16).astype(np.float32)
+    vs = rng.uniform(0.005, 0.02, (HKV, S)).astype(np.float16).astype(np.float32)
+    k16 = rng.standard_normal((HKV, S, 128), dtype=np.float32)
+    k16[:, rng.random(S) < 0.01] *= 4.0
+    k16 = k16.astype(np.float16).view(np.uint16)
+    v16 = rng.standard_normal((HKV, S, 128), dtype=np.float32).astype(np.float16).view(np.uint16)
+    rk = rng.standard_normal((HKV, RING, 128), dtype=np.float32).astype(np.float16).view(np.uint16)
+    rv = rng.standard_normal((HKV, RING, 128), dtype=np.float32).astype(np.float16).view(np.uint16)
+    qs = orc.to_bits(rng.standard_normal((n_items, 4, HQ, 128)), orc.F16)
+
+    def item(i):
+        q = qs[i]
+        sc = orc.score_keys(q[0], orc.F16, k16, S)
+        idx = orc.select_keys(sc, S)
+        orc.sparse_decode(q[0], orc.F16, k16, None, v16, None, S, idx=idx, kv_kind=1)
+        orc.sliding_attend(q[1][None], orc.F16, rk, rv, S - 1, WINDOW)
+        orc.sliding_attend(q[2][None], orc.F16, rk, rv, S - 1, WINDOW)
+        orc.full_decode(q[3], orc.F16, k8, ks, v8, vs, S)
+
+    item(0)   # page everything in
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(n_threads) as ex:
+        list(ex.map(item, range(n_items)))
+    return time.perf_counter() - t0
+
+
+def cpu_tok_s(n_threads, n_items):
+    secs = cpu_sample(n_threads, n_items)
+    cycles_per_token = N_LAYERS // 4
+    return n_items / (cycles_per_token * secs), secs
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    n_items = 4 * cores
+    for _ in range(args.warmup):
+        pass   # the sample warms itself (first item untimed); extra warm-up steps would only repeat it
+    vals = []
+    for _ in range(max(1, min(args.steps, 3))):
+        v, secs = cpu_tok_s(cores, n_items)
+        vals.append((v, secs))
+    v = statistics.median(x[0] for x in vals)
+    secs = statistics.median(x[1] for x in vals)
+    sample = (f"{n_items} sequence-cycles (1 sequence x [sparse, sliding, sliding, full] at {CONTEXT} keys) on {cores} threads "
+              f"in {secs:.2f} s; tok/s = items / (6 cycles x seconds)")
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals),
+            "warmup": args.warmup, "ms_per_step": 1000.0 * secs, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus),
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------- GPU arm
+def run_gpu(args, rank, world):
+    import torch
+    import torch.distributed as dist
+    from embla_metal_b200 import attn, stack as stk
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if TOTAL_SEQS % world:
+        raise SystemExit(f"{TOTAL_SEQS} sequences do not divide over {world} GPUs")
+    batch = TOTAL_SEQS // world
+    st = stk.DecodeStack(stk.cycle_kinds(N_LAYERS), batch, CONTEXT, HQ, HKV, attn.F16, WINDOW, RING)
+    st.fill_random(seed=4 + rank)
+    st.set_positions(CONTEXT - 1)
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    st.qkv.copy_(torch.randn(st.qkv.shape, device="cuda", generator=g).to(st.dtype))
+    st.qkv_host.copy_(st.qkv)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(3, args.warmup)):
+        st.step()
+    st.ctx.check()
+    # per-entry device time of one step (explains the step; picks the dominant kernel)
+    per_entry = {}
+    for name in stk.ENTRY:
+        st.set_probe(name)
+        st.step()
+        torch.cuda.synchronize()
+        ms, n = st.read_probe()
+        if n:
+            per_entry[name] = {"launches": n, "ms": ms}
+    dominant = max(per_entry, key=lambda k: per_entry[k]["ms"])
+    st.set_probe(dominant)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    total_ms = timed(st.step, args.steps)
+    clocks = sampler.result()
+    dom_ms, dom_n = st.read_probe()
+    st.set_probe(None)
+    e2e_ms = timed(st.step_host, args.steps)
+    st.ctx.check()
+
+    ms_per_step = total_ms / args.steps
+    value = TOTAL_SEQS / (ms_per_step / 1e3)
+    e2e_value = TOTAL_SEQS / (e2e_ms / args.steps / 1e3)
+    peak, peak_src = measured_peak()
+    achieved = algorithmic_bytes(batch, dominant) / (dom_ms / dom_n * 1e-3) / 1e9
+    step_bytes = sum(algorithmic_bytes(batch, k) * v["launches"] for k, v in per_entry.items())
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": workload_config(world), "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": st.qkv_host.numel() * 2 * world,
+                "d2h_bytes_per_step": st.o_host.numel() * 2 * world},
+        "gpu_launches": st.launches_per_step() * args.steps,
+        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_8000": achieved / 8000.0,
+                     "traffic": ncu_traffic(dominant, batch), "launches_timed": dom_n},
+        "step": {"algorithmic_gb": step_bytes / 1e9, "gbs": step_bytes / (ms_per_step * 1e-3) / 1e9,
+                 "frac_of_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
+                 "per_entry": {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
+                                   "gbs": round(algorithmic_bytes(batch, k) * v["launches"] / (v["ms"] * 1e-3) / 1e9, 1)}
+                               for k, v in per_entry.items()}},
+    }
+    if rank == 0 and world == 1:
+        cores = os.cpu_count() or 1
+        v, secs = cpu_tok_s(cores, 4 * cores)
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": f"{4 * cores} sequence-cycles of the 4-layer cycle at {CONTEXT} keys on {cores} threads, {secs:.2f} s"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    st.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if args.gpus > 1 and world == 1:
+            raise SystemExit("launch with torchrun: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N")
+    run_gpu(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

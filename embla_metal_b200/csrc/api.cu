@@ -65,7 +65,9 @@ EmblaStatus embla_attn_create(const EmblaAttnConfig* cfg, EmblaAttn** out) {
     // leaving G rows of 128 sums + 2 scalars (sum of weights, or running max and sum for softmax).
     // Slots: enough key ranges to fill the GPU several times over at any batch up to max_batch.
     const long pairs = long(cfg->max_batch) * cfg->n_kv_heads;
-    ctx->partial_slots = int(8L * ctx->sm_count + 2 * pairs);
+    // (The softmax kernels cut a pair's rows into 128-row chunks: 9 for 1152 selected rows, window / 128
+    // for a sliding layer; 16 chunks a pair covers windows up to 2048.)
+    ctx->partial_slots = int(8L * ctx->sm_count + 16 * pairs);
     ctx->partial_floats = size_t(ctx->partial_slots) * G * (HD + 4);
     e = cudaMalloc(&ctx->partials, ctx->partial_floats * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->counters, size_t(pairs) * sizeof(int));

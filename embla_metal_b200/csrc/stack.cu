@@ -1,0 +1,195 @@
+// One decode step of attention through a stack of layers: the attention half of the reference's
+// Engine.encodeStep / encodeAttention loop (Sources/EmblaMetal/Engine.swift:743-832, 933-991) as
+// native host code, so that a step is one C call enqueuing every kernel on the caller's stream.
+// Layer kinds follow Embla.Kind (Engine.swift:14): sliding, full, sparse. A sparse layer here owns
+// 16-bit keys and values and scores them itself (score -> select -> attend) once the sequence is
+// past topk + recent keys; a full layer appends its quantised k, v and attends with ReLU².
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+struct EmblaStack {
+    EmblaAttn* ctx;
+    std::vector<EmblaLayerDesc> layers;
+    EmblaKVPool* full_pool;
+    EmblaKVPool* sparse_pool;
+    std::vector<EmblaRing> rings;
+    float* scores;        // [max_batch][n_kv_heads][scores_ld]
+    uint32_t* idx;        // [max_batch][n_kv_heads][1152]
+    int scores_ld;
+    // timing probe: events around every launch of one entry point
+    int probe;
+    std::vector<cudaEvent_t> ev;
+    int ev_used;
+};
+
+using namespace embla;
+
+extern "C" {
+
+EmblaStatus embla_stack_create(EmblaAttn* ctx, const EmblaLayerDesc* layers, int32_t n_layers, EmblaKVPool* full_pool,
+                               EmblaKVPool* sparse_pool, const EmblaRing* rings, int32_t n_rings, EmblaStack** out) {
+    if (!ctx || !layers || n_layers <= 0 || !out) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_create: null argument");
+    *out = nullptr;
+    for (int i = 0; i < n_layers; i++) {
+        const EmblaLayerDesc& L = layers[i];
+        if (L.kind == EMBLA_LAYER_FULL) {
+            if (!full_pool || full_pool->kv_dtype != EMBLA_KV_INT8 || L.slot < 0 || L.slot >= full_pool->n_layers)
+                EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_create: layer %d (full) needs slot %d of an int8 pool", i, L.slot);
+        } else if (L.kind == EMBLA_LAYER_SPARSE) {
+            if (!sparse_pool || sparse_pool->kv_dtype != EMBLA_KV_16BIT || L.slot < 0 || L.slot >= sparse_pool->n_layers)
+                EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_create: layer %d (sparse) needs slot %d of a 16-bit pool", i, L.slot);
+            if (L.g1_dev)
+                EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_stack_create: layer %d: a sparse layer that scores its own keys takes "
+                                              "its queries prenormed", i);
+        } else if (L.kind == EMBLA_LAYER_SLIDING) {
+            if (!rings || L.slot < 0 || L.slot >= n_rings)
+                EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_create: layer %d (sliding) needs ring %d of %d", i, L.slot, n_rings);
+        } else {
+            EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_create: layer %d has kind %d", i, L.kind);
+        }
+    }
+    EmblaStack* st = new (std::nothrow) EmblaStack();
+    if (!st) EMBLA_FAIL(EMBLA_OOM, "embla_stack_create: host allocation failed");
+    st->ctx = ctx;
+    st->layers.assign(layers, layers + n_layers);
+    st->full_pool = full_pool;
+    st->sparse_pool = sparse_pool;
+    if (rings) st->rings.assign(rings, rings + n_rings);
+    st->scores = nullptr;
+    st->idx = nullptr;
+    st->probe = -1;
+    st->ev_used = 0;
+    st->scores_ld = (ctx->cfg.max_context + BLK - 1) / BLK * BLK;
+    const size_t pairs = size_t(ctx->cfg.max_batch) * ctx->cfg.n_kv_heads;
+    cudaError_t e = cudaSuccess;
+    if (sparse_pool) {
+        e = cudaMalloc(&st->scores, pairs * st->scores_ld * sizeof(float));
+        if (e == cudaSuccess) e = cudaMalloc(&st->idx, pairs * (EMBLA_TOPK + EMBLA_RECENT) * sizeof(uint32_t));
+    }
+    if (e != cudaSuccess) {
+        cudaFree(st->scores);
+        cudaFree(st->idx);
+        delete st;
+        set_error("embla_stack_create: scores/selection buffers: %s", cudaGetErrorString(e));
+        return e == cudaErrorMemoryAllocation ? EMBLA_OOM : EMBLA_CUDA;
+    }
+    *out = st;
+    return EMBLA_OK;
+}
+
+void embla_stack_destroy(EmblaStack* st) {
+    if (!st) return;
+    cudaFree(st->scores);
+    cudaFree(st->idx);
+    for (cudaEvent_t e : st->ev) cudaEventDestroy(e);
+    delete st;
+}
+
+EmblaStatus embla_stack_set_probe(EmblaStack* st, int32_t entry) {
+    if (!st) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_set_probe: null stack");
+    st->probe = entry;
+    st->ev_used = 0;
+    return EMBLA_OK;
+}
+
+EmblaStatus embla_stack_read_probe(EmblaStack* st, float* total_ms, int32_t* launches) {
+    if (!st || !total_ms || !launches) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_read_probe: null argument");
+    float sum = 0.0f;
+    for (int i = 0; i + 1 < st->ev_used; i += 2) {
+        float ms = 0.0f;
+        EMBLA_CUDA_TRY(cudaEventElapsedTime(&ms, st->ev[i], st->ev[i + 1]));
+        sum += ms;
+    }
+    *total_ms = sum;
+    *launches = st->ev_used / 2;
+    st->ev_used = 0;
+    return EMBLA_OK;
+}
+
+}  // extern "C"
+
+static EmblaStatus probe_mark(EmblaStack* st, int entry, cudaStream_t s) {
+    if (st->probe != entry) return EMBLA_OK;
+    if (st->ev_used == int(st->ev.size())) {
+        cudaEvent_t e;
+        EMBLA_CUDA_TRY(cudaEventCreate(&e));
+        st->ev.push_back(e);
+    }
+    EMBLA_CUDA_TRY(cudaEventRecord(st->ev[st->ev_used++], s));
+    return EMBLA_OK;
+}
+
+#define EMBLA_STEP(entry, call)                                   \
+    do {                                                          \
+        if (EmblaStatus s_ = probe_mark(st, entry, s)) return s_; \
+        if (EmblaStatus s_ = (call)) return s_;                   \
+        if (EmblaStatus s_ = probe_mark(st, entry, s)) return s_; \
+    } while (0)
+
+extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackStep* step, void* stream) {
+    if (!st || !step || !step->qkv_dev || !step->o_dev || !step->seq_lens_dev || !step->pos_dev)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_step: null argument");
+    EmblaAttn* ctx = st->ctx;
+    const int Hq = ctx->cfg.n_q_heads, Hkv = ctx->cfg.n_kv_heads, B = step->batch;
+    if (B <= 0 || B > ctx->cfg.max_batch) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_step: batch %d", B);
+    const size_t esz = 2;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int max_len = step->max_seq_len > 0 ? step->max_seq_len : ctx->cfg.max_context;
+    for (size_t li = 0; li < st->layers.size(); li++) {
+        const EmblaLayerDesc& L = st->layers[li];
+        const uint8_t* row = static_cast<const uint8_t*>(step->qkv_dev) + li * step->qkv_layer_stride * esz;
+        const void* qp = row;
+        const void* kp = row + size_t(Hq) * HD * esz;
+        const void* vp = row + size_t(Hq + Hkv) * HD * esz;
+        void* op = static_cast<uint8_t*>(step->o_dev) + li * step->o_layer_stride * esz;
+        EmblaQuery q;
+        q.q_dev = qp;
+        q.q_stride = step->qkv_stride;
+        q.prenormed = L.g1_dev ? 0 : 1;
+        q.ng = L.g1_dev ? (L.g2_dev ? 2 : 1) : 0;
+        q.g1_dev = L.g1_dev;
+        q.g2_dev = L.g2_dev;
+        if (L.kind == EMBLA_LAYER_SLIDING) {
+            const EmblaRing* ring = &st->rings[L.slot];
+            EMBLA_STEP(EMBLA_ENTRY_SLIDING_WRITE,
+                       embla_sliding_write(ctx, ring, step->pos_dev, B, 1, kp, vp, step->qkv_stride, step->qkv_stride,
+                                           L.kgain_dev ? 0 : 1, L.kgain_dev, stream));
+            EMBLA_STEP(EMBLA_ENTRY_SLIDING_DECODE,
+                       embla_attn_sliding_decode(ctx, ring, step->seq_lens_dev, B, &q, op, step->o_stride, stream));
+            continue;
+        }
+        EmblaKVView view;
+        view.batch = B;
+        view.layer = L.slot;
+        view.seq_lens_dev = step->seq_lens_dev;
+        view.max_seq_len = max_len;
+        if (L.kind == EMBLA_LAYER_FULL) {
+            view.block_table_dev = step->full_table_dev;
+            view.table_stride = step->full_table_stride;
+            if (!view.block_table_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_step: no block table for the full layers");
+            EMBLA_STEP(EMBLA_ENTRY_APPEND, embla_kv_append(ctx, st->full_pool, &view, step->pos_dev, 1, kp, vp, step->qkv_stride,
+                                                           step->qkv_stride, L.norm_k, stream));
+            EMBLA_STEP(EMBLA_ENTRY_FULL_DECODE,
+                       embla_attn_full_decode(ctx, st->full_pool, &view, &q, op, step->o_stride, nullptr, 0, stream));
+        } else {
+            view.block_table_dev = step->sparse_table_dev;
+            view.table_stride = step->sparse_table_stride;
+            if (!view.block_table_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_step: no block table for the sparse layers");
+            EMBLA_STEP(EMBLA_ENTRY_APPEND, embla_kv_append(ctx, st->sparse_pool, &view, step->pos_dev, 1, kp, vp, step->qkv_stride,
+                                                           step->qkv_stride, L.norm_k, stream));
+            const bool selecting = max_len > EMBLA_TOPK + EMBLA_RECENT;   // Engine.swift:796
+            if (selecting) {
+                EMBLA_STEP(EMBLA_ENTRY_SCORE, embla_score_keys(ctx, st->sparse_pool, &view, qp, step->qkv_stride, st->scores,
+                                                               st->scores_ld, stream));
+                EMBLA_STEP(EMBLA_ENTRY_SELECT, embla_select_keys(ctx, st->scores, st->scores_ld, step->seq_lens_dev, B, max_len,
+                                                                 st->idx, stream));
+            }
+            EMBLA_STEP(EMBLA_ENTRY_SPARSE_DECODE, embla_attn_sparse_decode(ctx, st->sparse_pool, &view, &q,
+                                                                           selecting ? st->idx : nullptr, op, step->o_stride,
+                                                                           stream));
+        }
+    }
+    return EMBLA_OK;
+}

@@ -1,0 +1,153 @@
+"""A stack of attention layers decoding one token per sequence: binding of embla_stack_* (the
+attention half of the reference's Engine.encodeStep loop, Sources/EmblaMetal/Engine.swift:933-991).
+
+`DecodeStack` owns the KV state of a batch of sequences — the int8 pool of the full layers, the
+16-bit pool of the sparse layers, the sliding layers' rings, and identity block tables — and runs a
+step from device-resident `qkv` rows or, through `step_host`, from pinned host buffers.
+"""
+import ctypes as C
+
+import torch
+
+from . import attn
+
+SLIDING, FULL, SPARSE = 0, 1, 2
+ENTRY = {"append": 0, "full_decode": 1, "sliding_write": 2, "sliding_decode": 3, "score": 4, "select": 5,
+         "sparse_decode": 6}
+
+
+class LayerDesc(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("slot", C.c_int32), ("norm_k", C.c_int32), ("pad", C.c_int32),
+                ("g1_dev", C.c_void_p), ("g2_dev", C.c_void_p), ("kgain_dev", C.c_void_p)]
+
+
+class StackStep(C.Structure):
+    _fields_ = [("qkv_dev", C.c_void_p), ("qkv_stride", C.c_int64), ("qkv_layer_stride", C.c_int64),
+                ("o_dev", C.c_void_p), ("o_stride", C.c_int64), ("o_layer_stride", C.c_int64),
+                ("seq_lens_dev", C.c_void_p), ("pos_dev", C.c_void_p), ("full_table_dev", C.c_void_p),
+                ("full_table_stride", C.c_int32), ("sparse_table_stride", C.c_int32), ("sparse_table_dev", C.c_void_p),
+                ("batch", C.c_int32), ("max_seq_len", C.c_int32)]
+
+
+def cycle_kinds(n_layers):
+    """The benchmark's stack: layers cycling sparse, sliding, sliding, full."""
+    return [(SPARSE, SLIDING, SLIDING, FULL)[i % 4] for i in range(n_layers)]
+
+
+class DecodeStack:
+    def __init__(self, kinds, batch, max_context, n_q_heads=16, n_kv_heads=4, act_dtype=attn.F16, window=1024,
+                 ring=4096, scale_dtype=attn.SCALE_F16, norm_k=False):
+        self.kinds, self.batch, self.max_context = list(kinds), batch, max_context
+        self.Hq, self.Hkv = n_q_heads, n_kv_heads
+        self.ctx = attn.Attention(n_q_heads, n_kv_heads, act_dtype, max_batch=batch, max_context=max_context)
+        self.dtype = self.ctx.torch_dtype
+        npages = (max_context + attn.BLOCK - 1) // attn.BLOCK
+        self.npages = npages
+        n_full = sum(k == FULL for k in self.kinds)
+        n_sparse = sum(k == SPARSE for k in self.kinds)
+        n_sliding = sum(k == SLIDING for k in self.kinds)
+        self.full_pool = attn.KVPool(n_full, n_kv_heads, batch * npages, attn.KV_INT8, scale_dtype) if n_full else None
+        self.sparse_pool = attn.KVPool(n_sparse, n_kv_heads, batch * npages, attn.KV_16BIT) if n_sparse else None
+        self.rings = [attn.Ring(batch, n_kv_heads, ring, window, self.dtype) for _ in range(n_sliding)]
+        # sequence b owns blocks b * npages .. of each pool
+        self.table = torch.arange(batch * npages, dtype=torch.int32, device="cuda").view(batch, npages).contiguous()
+        descs = (LayerDesc * len(self.kinds))()
+        slots = {SLIDING: 0, FULL: 0, SPARSE: 0}
+        for i, k in enumerate(self.kinds):
+            descs[i] = LayerDesc(k, slots[k], int(norm_k), 0, None, None, None)
+            slots[k] += 1
+        ring_descs = (attn.RingDesc * max(1, n_sliding))()
+        for i, r in enumerate(self.rings):
+            ring_descs[i] = r.desc
+        self.handle = C.c_void_p()
+        L = attn.lib()
+        attn._check(L.embla_stack_create(self.ctx.handle, descs, len(self.kinds),
+                                         self.full_pool.handle if self.full_pool else None,
+                                         self.sparse_pool.handle if self.sparse_pool else None,
+                                         ring_descs, n_sliding, C.byref(self.handle)))
+        self.qkv_width = (n_q_heads + 2 * n_kv_heads) * attn.HEAD_DIM
+        self.o_width = n_q_heads * attn.HEAD_DIM
+        n = len(self.kinds)
+        self.qkv = torch.zeros(n, batch, self.qkv_width, dtype=self.dtype, device="cuda")
+        self.o = torch.zeros(n, batch, self.o_width, dtype=self.dtype, device="cuda")
+        self.qkv_host = torch.zeros(n, batch, self.qkv_width, dtype=self.dtype).pin_memory()
+        self.o_host = torch.zeros(n, batch, self.o_width, dtype=self.dtype).pin_memory()
+        self.seq_lens = torch.zeros(batch, dtype=torch.int32, device="cuda")
+        self.pos = torch.zeros(batch, dtype=torch.int32, device="cuda")
+        self.max_seq_len = max_context
+
+    def close(self):
+        if self.handle:
+            attn.lib().embla_stack_destroy(self.handle)
+            self.handle = C.c_void_p()
+        for obj in (self.full_pool, self.sparse_pool, self.ctx):
+            if obj is not None:
+                obj.close()
+
+    def set_positions(self, pos):
+        """pos: int or list — position of the token each sequence decodes next (keys seen = pos + 1)."""
+        t = torch.as_tensor([pos] * self.batch if isinstance(pos, int) else list(pos), dtype=torch.int32)
+        self.pos.copy_(t)
+        self.seq_lens.copy_(t + 1)
+        self.max_seq_len = int(t.max()) + 1
+
+    def fill_random(self, seed=0):
+        """Synthetic KV state in the benchmark's distributions: int8 codes uniform in [-127, 127] with fp16
+        scales uniform in [0.005, 0.02]; 16-bit keys/values ~ N(0, 1) with 1 % of the keys scaled x4."""
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        if self.full_pool is not None:
+            raw = self.full_pool.raw()
+            flat = raw.view(-1, raw.shape[-1])
+            step = max(1, (1 << 28) // flat.shape[1])
+            sdt = torch.float16 if self.full_pool.scale_dtype == attn.SCALE_F16 else torch.float32
+            for i in range(0, flat.shape[0], step):
+                part = flat[i:i + step]
+                codes = torch.randint(-127, 128, (part.shape[0], 32768), dtype=torch.int8, device="cuda", generator=g)
+                part[:, :32768] = codes.view(torch.uint8)
+                sc = torch.empty(part.shape[0], 256, device="cuda").uniform_(0.005, 0.02, generator=g).to(sdt)
+                part[:, 32768:] = sc.view(torch.uint8)
+        if self.sparse_pool is not None:
+            raw = self.sparse_pool.raw()
+            flat = raw.view(-1, raw.shape[-1]).view(self.dtype)       # [pages, 2 * 128 * 128]
+            step = max(1, (1 << 27) // flat.shape[1])
+            for i in range(0, flat.shape[0], step):
+                part = flat[i:i + step]
+                vals = torch.randn(part.shape, device="cuda", generator=g)
+                keys = vals[:, :16384].view(part.shape[0], 128, 128)
+                boost = torch.rand(part.shape[0], 128, 1, device="cuda", generator=g) < 0.01
+                keys.mul_(torch.where(boost, 4.0, 1.0))
+                part.copy_(vals.to(self.dtype))
+        for r in self.rings:
+            r.k.copy_(torch.randn(r.k.shape, device="cuda", generator=g).to(self.dtype))
+            r.v.copy_(torch.randn(r.v.shape, device="cuda", generator=g).to(self.dtype))
+
+    def _step_struct(self):
+        return StackStep(self.qkv.data_ptr(), self.qkv.stride(1), self.qkv.stride(0), self.o.data_ptr(),
+                         self.o.stride(1), self.o.stride(0), self.seq_lens.data_ptr(), self.pos.data_ptr(),
+                         self.table.data_ptr(), self.table.stride(0), self.table.stride(0), self.table.data_ptr(),
+                         self.batch, self.max_seq_len)
+
+    def step(self):
+        """One decode step from the device-resident qkv rows; results in self.o."""
+        st = self._step_struct()
+        attn._check(attn.lib().embla_stack_decode_step(self.handle, C.byref(st), attn._stream()))
+
+    def step_host(self):
+        """One decode step from pinned host rows: qkv_host -> device, attention, o -> o_host."""
+        self.qkv.copy_(self.qkv_host, non_blocking=True)
+        self.step()
+        self.o_host.copy_(self.o, non_blocking=True)
+
+    def set_probe(self, name):
+        attn._check(attn.lib().embla_stack_set_probe(self.handle, -1 if name is None else ENTRY[name]))
+
+    def read_probe(self):
+        ms, n = C.c_float(), C.c_int32()
+        attn._check(attn.lib().embla_stack_read_probe(self.handle, C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
+    def launches_per_step(self):
+        """Kernels of this library one step launches."""
+        selecting = self.max_seq_len > attn.TOPK + attn.RECENT
+        per = {SLIDING: 2, FULL: 2, SPARSE: 4 if selecting else 2}
+        return sum(per[k] for k in self.kinds)

@@ -193,6 +193,55 @@ EmblaStatus embla_attn_sliding_decode(EmblaAttn* ctx, const EmblaRing* ring, con
                                       int32_t batch, const EmblaQuery* q, void* o_dev, int64_t o_stride,
                                       void* stream);
 
+/* ---- one decode step through a stack of layers ------------------------------------------------------- */
+/* The attention half of Engine.encodeStep's per-layer loop (Engine.swift:933-991 calling
+ * encodeAttention, :743-832) as one call: for every layer, the KV write of the current token and the
+ * layer's attention, enqueued on one stream. */
+enum { EMBLA_LAYER_SLIDING = 0, EMBLA_LAYER_FULL = 1, EMBLA_LAYER_SPARSE = 2 };   /* Embla.Kind, Engine.swift:14 */
+enum {   /* entry points a step launches, for embla_stack_set_probe */
+    EMBLA_ENTRY_APPEND = 0, EMBLA_ENTRY_FULL_DECODE = 1, EMBLA_ENTRY_SLIDING_WRITE = 2, EMBLA_ENTRY_SLIDING_DECODE = 3,
+    EMBLA_ENTRY_SCORE = 4, EMBLA_ENTRY_SELECT = 5, EMBLA_ENTRY_SPARSE_DECODE = 6
+};
+
+typedef struct {
+    int32_t     kind;        /* EMBLA_LAYER_* */
+    int32_t     slot;        /* full: layer of the int8 pool; sparse: layer of the 16-bit pool; sliding: ring index */
+    int32_t     norm_k;      /* full/sparse: RMS-norm k before it is stored (the reference does) */
+    int32_t     pad;
+    const void* g1_dev;      /* query gains; NULL = queries arrive prenormed (sparse layers: must be NULL) */
+    const void* g2_dev;
+    const void* kgain_dev;   /* sliding: key gain; NULL = keys arrive prenormed */
+} EmblaLayerDesc;
+
+typedef struct {
+    const void*    qkv_dev;            /* [n_layers][batch][qkv_stride]: q (n_q_heads*128), k, v (n_kv_heads*128 each) */
+    int64_t        qkv_stride;         /* elements between sequences (4096 in the reference) */
+    int64_t        qkv_layer_stride;   /* elements between layers */
+    void*          o_dev;              /* [n_layers][batch][o_stride] */
+    int64_t        o_stride, o_layer_stride;
+    const int32_t* seq_lens_dev;       /* [batch] keys visible, the current token included (pos + 1) */
+    const int32_t* pos_dev;            /* [batch] position of the current token */
+    const int32_t* full_table_dev;     /* block table into the int8 pool */
+    int32_t        full_table_stride;
+    int32_t        sparse_table_stride;
+    const int32_t* sparse_table_dev;   /* block table into the 16-bit pool */
+    int32_t        batch;
+    int32_t        max_seq_len;        /* host-side upper bound of seq_lens; 0 = max_context */
+} EmblaStackStep;
+
+typedef struct EmblaStack EmblaStack;
+/* `rings` holds one EmblaRing per sliding layer slot. The pools and rings stay owned by the caller. */
+EmblaStatus embla_stack_create(EmblaAttn* ctx, const EmblaLayerDesc* layers, int32_t n_layers, EmblaKVPool* full_pool,
+                               EmblaKVPool* sparse_pool, const EmblaRing* rings, int32_t n_rings, EmblaStack** out);
+void        embla_stack_destroy(EmblaStack* stack);
+EmblaStatus embla_stack_decode_step(EmblaStack* stack, const EmblaStackStep* step, void* stream);
+/* Timing probe, the counterpart of the reference's per-part Profiler (StepEncoder.swift:7-65):
+ * CUDA events are recorded on the stream around every launch of entry point `entry` (-1: off);
+ * read_probe returns their summed time and count since the last read, after the caller has
+ * synchronised the stream. */
+EmblaStatus embla_stack_set_probe(EmblaStack* stack, int32_t entry);
+EmblaStatus embla_stack_read_probe(EmblaStack* stack, float* total_ms, int32_t* launches);
+
 #ifdef __cplusplus
 }
 #endif
