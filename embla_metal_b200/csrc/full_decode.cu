@@ -481,3 +481,130 @@ extern "C" EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool*
     return s4 ? EMBLA_FD(EMBLA_F16, 4, false) : EMBLA_FD(EMBLA_F16, 2, false);
 #undef EMBLA_FD
 }
+
+// ---- full-layer decode for callers that must not allocate ---------------------------------------------
+// Some hosts of this library cannot call cudaMalloc at the point where they run attention: a serving
+// loop that has handed all device memory to its own arena at start-up, or a latency-critical thread
+// in which an allocation (and the device-wide synchronisation it can imply) is forbidden. For them
+// this entry point runs the same kernel as embla_attn_full_decode without any context object: the
+// split-K partial sums, the arrival counters and the error word live in the fixed array below, which
+// every GPU that loads the library holds from load to exit.
+namespace embla {
+
+constexpr int NOALLOC_MAX_PAIRS = 256;     // batch x kv heads
+constexpr int NOALLOC_MAX_SLOTS = 1024;    // (pair, key range) partials
+constexpr size_t NOALLOC_COUNTER_BYTES = NOALLOC_MAX_PAIRS * sizeof(int);          // 1 KiB
+constexpr size_t NOALLOC_ERR_OFFSET = NOALLOC_COUNTER_BYTES;                        // one int, own 256-byte line
+constexpr size_t NOALLOC_PART_OFFSET = NOALLOC_COUNTER_BYTES + 256;
+constexpr size_t NOALLOC_BYTES = NOALLOC_PART_OFFSET + size_t(NOALLOC_MAX_SLOTS) * 8 * FD_PART * sizeof(float);   // ~4.1 MiB
+
+// In host code this name is only a handle for the runtime, not a device address: the address the
+// kernel gets comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
+
+struct NoAllocDevice {
+    bool ready;
+    unsigned char* scratch;
+    int sm_count;
+};
+static NoAllocDevice g_noalloc[64];
+
+// Once per device, with that device current: resolve the array's device address and let the kernel
+// variants use their dynamic shared memory. Nothing here allocates.
+template <int DT, int SB>
+static EmblaStatus noalloc_setup_kernel() {
+    constexpr size_t smem = fd_smem_bytes<3, false>();
+    EMBLA_CUDA_TRY(cudaFuncSetAttribute(full_decode_kernel<DT, SB, 8, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        int(smem)));
+    return EMBLA_OK;
+}
+
+static EmblaStatus noalloc_setup(int device) {
+    NoAllocDevice& d = g_noalloc[device];
+    if (d.ready) return EMBLA_OK;
+    void* ptr = nullptr;
+    EMBLA_CUDA_TRY(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    EMBLA_CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
+    if (EmblaStatus s = noalloc_setup_kernel<EMBLA_BF16, 4>()) return s;
+    if (EmblaStatus s = noalloc_setup_kernel<EMBLA_BF16, 2>()) return s;
+    if (EmblaStatus s = noalloc_setup_kernel<EMBLA_F16, 4>()) return s;
+    if (EmblaStatus s = noalloc_setup_kernel<EMBLA_F16, 2>()) return s;
+    d.scratch = static_cast<unsigned char*>(ptr);
+    d.ready = true;
+    return EMBLA_OK;
+}
+
+}  // namespace embla
+
+extern "C" EmblaStatus embla_attn_full_decode_noalloc(const EmblaKVPool* pool, const EmblaKVView* view, const EmblaQuery* q,
+                                                      int32_t n_q_heads, int32_t act_dtype, void* o_dev, int64_t o_stride,
+                                                      void* stream) {
+    if (!pool || !view || !q || !o_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode_noalloc: null argument");
+    if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_decode_noalloc: the pool is not int8");
+    if (act_dtype != EMBLA_BF16 && act_dtype != EMBLA_F16)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode_noalloc: act_dtype %d", act_dtype);
+    const int Hkv = pool->n_kv_heads;
+    if (n_q_heads <= 0 || n_q_heads % Hkv != 0 || n_q_heads / Hkv > 8)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode_noalloc: %d query heads on %d kv heads", n_q_heads, Hkv);
+    if (view->layer < 0 || view->layer >= pool->n_layers || !view->block_table_dev || !view->seq_lens_dev || !q->q_dev)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode_noalloc: bad view or query");
+    if (!q->prenormed && ((q->ng >= 1 && !q->g1_dev) || (q->ng >= 2 && !q->g2_dev) || q->ng < 0 || q->ng > 2))
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode_noalloc: ng %d without its gain vectors", q->ng);
+    if (view->batch <= 0 || long(view->batch) * Hkv > NOALLOC_MAX_PAIRS)
+        EMBLA_FAIL(EMBLA_BAD_ARG,
+                   "embla_attn_full_decode_noalloc: batch %d x %d kv heads is over the fixed scratch's limit of %d "
+                   "(sequence, kv head) pairs; use embla_attn_full_decode with a context sized for it",
+                   view->batch, Hkv, NOALLOC_MAX_PAIRS);
+    if (view->max_seq_len <= 0)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode_noalloc: max_seq_len must be given (there is no context to take it from)");
+    int device = 0;
+    EMBLA_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_decode_noalloc: device %d", device);
+    if (device != pool->device) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode_noalloc: the pool lives on device %d", pool->device);
+    if (EmblaStatus s = noalloc_setup(device)) return s;
+    const NoAllocDevice& d = g_noalloc[device];
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The array keeps what the last call left: counters and the error word must start at zero.
+    EMBLA_CUDA_TRY(cudaMemsetAsync(d.scratch, 0, NOALLOC_PART_OFFSET, s));
+
+    FullDecodeParams p;
+    p.pool = pool->base;
+    p.block_table = view->block_table_dev;
+    p.seq_lens = view->seq_lens_dev;
+    p.q = q->q_dev;
+    p.g1 = q->g1_dev;
+    p.g2 = q->g2_dev;
+    p.o = o_dev;
+    p.counters = reinterpret_cast<int*>(d.scratch);
+    p.err = reinterpret_cast<int*>(d.scratch + NOALLOC_ERR_OFFSET);
+    p.partials = reinterpret_cast<float*>(d.scratch + NOALLOC_PART_OFFSET);
+    p.scores = nullptr;
+    p.q_stride = q->q_stride;
+    p.o_stride = o_stride;
+    p.scores_stride = 0;
+    p.page_bytes = pool->page_bytes;
+    p.table_stride = view->table_stride;
+    p.layer = view->layer;
+    p.n_layers = pool->n_layers;
+    p.n_kv_heads = Hkv;
+    p.G = n_q_heads / Hkv;
+    p.scale_bytes = pool->scale_bytes;
+    p.rows_per_page = pool->rows_per_page;
+    p.prenormed = q->prenormed;
+    p.ng = q->ng;
+    const int pairs = view->batch * Hkv;
+    const int pages = (view->max_seq_len + BLK - 1) / BLK;
+    p.nsplit = choose_splits(pairs, pages, 2 * d.sm_count, NOALLOC_MAX_SLOTS);
+    constexpr size_t smem = fd_smem_bytes<3, false>();
+    dim3 grid(p.nsplit, Hkv, view->batch);
+    const bool s4 = pool->scale_bytes == 4;
+    if (act_dtype == EMBLA_BF16) {
+        if (s4) full_decode_kernel<EMBLA_BF16, 4, 8, 3, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
+        else full_decode_kernel<EMBLA_BF16, 2, 8, 3, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
+    } else {
+        if (s4) full_decode_kernel<EMBLA_F16, 4, 8, 3, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
+        else full_decode_kernel<EMBLA_F16, 2, 8, 3, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
+    }
+    EMBLA_CUDA_TRY(cudaGetLastError());
+    return EMBLA_OK;
+}

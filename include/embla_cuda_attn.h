@@ -142,6 +142,26 @@ EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, cons
                                    const EmblaQuery* q, void* o_dev, int64_t o_stride,
                                    float* scores_dev, int64_t scores_stride, void* stream);
 
+/* No counterpart in the reference (its engine owns every buffer and allocates them all at init).
+ * The same attention as embla_attn_full_decode (without scores) for callers that cannot allocate
+ * device memory where they run attention — a server that gave all device memory to its own arena at
+ * start-up, or a thread in which cudaMalloc and the synchronisation it may imply are forbidden. It
+ * takes no context: the split-K partial sums and arrival counters live in a fixed array inside the
+ * library (about 4.1 MiB, held by every GPU that loads the library until the process exits), and
+ * the call makes no cudaMalloc / cudaFree or any other allocating call.
+ *  - Limit: batch * n_kv_heads <= 256 (sequence, kv head) pairs; more is refused with EMBLA_BAD_ARG.
+ *    view->max_seq_len must be given. The model shape comes from `n_q_heads` (kv heads from the pool)
+ *    and `act_dtype`.
+ *  - The first call on a device resolves the array's address and configures the kernels; make that
+ *    call before any stream capture.
+ *  - All calls on a device share the array: two calls whose kernels may overlap on the GPU (different
+ *    streams) race on it. Calls on one stream are safe; each call clears the counters first.
+ *  - A bounded device-side wait that runs out is not reported by this variant (there is no context
+ *    to ask); use embla_attn_full_decode + embla_attn_check where that matters. */
+EmblaStatus embla_attn_full_decode_noalloc(const EmblaKVPool* pool, const EmblaKVView* view, const EmblaQuery* q,
+                                           int32_t n_q_heads, int32_t act_dtype, void* o_dev, int64_t o_stride,
+                                           void* stream);
+
 /* ---- key scoring and selection (sparse layers) --------------------------------------------------- */
 /* The SCORES by-product of attn_full (attention.metal:146, 189, 203-205) as a pass of its own, for
  * sparse layers that keep their own 16-bit keys in a EMBLA_KV_16BIT pool: scores[b][kv head][j] =
