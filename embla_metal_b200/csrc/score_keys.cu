@@ -7,8 +7,8 @@
 // HBM-bound in bytes (256 B a key) but heavy in issue slots (G x 128 FMAs + 128 converts a key):
 // a producer warp streams pages through a TMA ring (two 128-byte-wide swizzled boxes a page, dims
 // 0-63 and 64-127); each consumer thread owns one key of the page and reads its row 16 bytes at a
-// time, conflict-free under the swizzle; queries sit in shared memory as fp32 and are read as
-// broadcast float4s.
+// time, conflict-free under the swizzle; queries sit in shared memory as stored and are read as
+// broadcast loads. The multiply-adds take the 16-bit operands directly (fma.rn.f32.f16 / .bf16).
 #include "common.cuh"
 
 namespace embla {
@@ -28,19 +28,27 @@ struct ScoreParams {
     int table_stride, layer, n_layers, n_kv_heads, rows_per_page, nsplit;
 };
 
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+// acc = fma(q.lo, k.lo, acc); acc = fma(q.hi, k.hi, acc) on a packed pair of 16-bit values, the
+// products exact and each step rounded once to fp32: the same result as converting to fp32 and
+// calling fmaf, without the conversions (mixed-precision fma of sm_100).
 template <int DT>
-__device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]) {
-    const uint32_t v[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        if (DT == EMBLA_F16) {
-            const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&v[i]));
-            f[2 * i] = t.x;
-            f[2 * i + 1] = t.y;
-        } else {
-            f[2 * i] = __uint_as_float(v[i] << 16);
-            f[2 * i + 1] = __uint_as_float(v[i] & 0xffff0000u);
-        }
+__device__ __forceinline__ void fma_pair(float& acc, uint32_t k, uint32_t q) {
+    if (DT == EMBLA_F16) {
+        asm("{\n .reg .b16 kl, kh, ql, qh;\n mov.b32 {kl, kh}, %1;\n mov.b32 {ql, qh}, %2;\n"
+            " fma.rn.f32.f16 %0, ql, kl, %0;\n fma.rn.f32.f16 %0, qh, kh, %0;\n}\n"
+            : "+f"(acc)
+            : "r"(k), "r"(q));
+    } else {
+        asm("{\n .reg .b16 kl, kh, ql, qh;\n mov.b32 {kl, kh}, %1;\n mov.b32 {ql, qh}, %2;\n"
+            " fma.rn.f32.bf16 %0, ql, kl, %0;\n fma.rn.f32.bf16 %0, qh, kh, %0;\n}\n"
+            : "+f"(acc)
+            : "r"(k), "r"(q));
     }
 }
 
@@ -50,7 +58,7 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stages = smem;
-    float(*qf)[SK_QLD] = reinterpret_cast<float(*)[SK_QLD]>(smem + STAGES * SK_STAGE);
+    uint16_t* qs = reinterpret_cast<uint16_t*>(smem + STAGES * SK_STAGE);   // [G][128] in the activation dtype
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * SK_STAGE + G * SK_QLD * 4);
     uint64_t* empty = full + STAGES;
 
@@ -70,10 +78,8 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
         }
         fence_barrier_init();
     }
-    for (int i = tid; i < G * HD; i += SK_THREADS) {
-        const int hh = i >> 7, d = i & 127;
-        qf[hh][d] = Act<DT>::load(p.q, size_t(b) * p.q_stride + size_t(kvh * G + hh) * HD + d);
-    }
+    for (int i = tid; i < G * HD; i += SK_THREADS)
+        qs[i] = reinterpret_cast<const uint16_t*>(p.q)[size_t(b) * p.q_stride + size_t(kvh * G) * HD + i];
     __syncthreads();
 
     if (warp == SK_CONSUMERS) {
@@ -101,7 +107,7 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
             atomicExch(p.err, ERR_WAIT_FULL);
             return;
         }
-        const uint8_t* Kb = stages + st * SK_STAGE;
+        const uint32_t Kb = smem_u32(stages + st * SK_STAGE) + r * 128, qa = smem_u32(qs);
         float dot[G];
 #pragma unroll
         for (int h = 0; h < G; h++) dot[h] = 0.0f;
@@ -109,22 +115,15 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
         for (int half = 0; half < 2; half++) {
 #pragma unroll
             for (int ch = 0; ch < 8; ch++) {
-                const uint4 w = *reinterpret_cast<const uint4*>(Kb + half * (BLK * 128) + r * 128 + ((ch ^ (r & 7)) << 4));
-                float kf[8];
-                unpack8<DT>(w, kf);
+                const uint4 kw = lds128(Kb + half * (BLK * 128) + ((ch ^ (r & 7)) << 4));
                 const int d = half * 64 + ch * 8;
 #pragma unroll
                 for (int h = 0; h < G; h++) {
-                    const float4 qa = *reinterpret_cast<const float4*>(&qf[h][d]);
-                    const float4 qb = *reinterpret_cast<const float4*>(&qf[h][d + 4]);
-                    dot[h] = __fmaf_rn(qa.x, kf[0], dot[h]);
-                    dot[h] = __fmaf_rn(qa.y, kf[1], dot[h]);
-                    dot[h] = __fmaf_rn(qa.z, kf[2], dot[h]);
-                    dot[h] = __fmaf_rn(qa.w, kf[3], dot[h]);
-                    dot[h] = __fmaf_rn(qb.x, kf[4], dot[h]);
-                    dot[h] = __fmaf_rn(qb.y, kf[5], dot[h]);
-                    dot[h] = __fmaf_rn(qb.z, kf[6], dot[h]);
-                    dot[h] = __fmaf_rn(qb.w, kf[7], dot[h]);
+                    const uint4 qw = lds128(qa + (h * HD + d) * 2);   // one address a warp: a broadcast
+                    fma_pair<DT>(dot[h], kw.x, qw.x);
+                    fma_pair<DT>(dot[h], kw.y, qw.y);
+                    fma_pair<DT>(dot[h], kw.z, qw.z);
+                    fma_pair<DT>(dot[h], kw.w, qw.w);
                 }
             }
         }

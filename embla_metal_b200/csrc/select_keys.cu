@@ -5,8 +5,8 @@
 // Integer work on the scores' order-preserving bit patterns, so the result is exact by construction:
 // four 8-bit most-significant-digit-first histogram passes narrow down the 1024-th largest pattern,
 // then a compaction in key order takes every key above it and the first equal ones. One CTA of 1024
-// threads per (sequence, kv head); the patterns are kept in shared memory after the first read when
-// they fit, so HBM/L2 is read once. The output order is the reference's:
+// threads per (sequence, kv head); the patterns stay in registers after the one read of the scores.
+// The output order is the reference's:
 // [greater, ascending index][equal, ascending index][n .. n + 127].
 #include "common.cuh"
 
@@ -20,7 +20,7 @@ struct SelectParams {
     const int32_t* seq_lens;
     uint32_t* idx;
     int64_t scores_stride;   // floats between (sequence, kv head) rows
-    int n_kv_heads, cache_cap;
+    int n_kv_heads;
 };
 
 __device__ __forceinline__ uint32_t order_bits(float f) {   // attention.metal:657-660
@@ -28,40 +28,13 @@ __device__ __forceinline__ uint32_t order_bits(float f) {   // attention.metal:6
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-// Exclusive prefix sum of one value per thread over the CTA, and the total.
-__device__ __forceinline__ uint32_t block_scan_excl(uint32_t v, uint32_t* buf, int lane, int warp, uint32_t& total) {
-    uint32_t incl = v;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t y = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += y;
-    }
-    if (lane == 31) buf[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-        const uint32_t s = buf[lane];
-        uint32_t p = s;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t y = __shfl_up_sync(0xffffffffu, p, o);
-            if (lane >= o) p += y;
-        }
-        buf[lane] = p - s;
-        if (lane == 31) buf[32] = p;
-    }
-    __syncthreads();
-    const uint32_t r = buf[warp] + incl - v;
-    total = buf[32];
-    __syncthreads();
-    return r;
-}
-
-template <bool CACHED>
+// ITEMS: keys a lane holds in registers; warp w owns keys [w * 32 * ITEMS, (w + 1) * 32 * ITEMS), a
+// round i takes the 32 consecutive keys w * 32 * ITEMS + 32 i + lane. The scores are read from global
+// memory once, all loads in flight together; every pass after that runs on registers.
+template <int ITEMS>
 __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p) {
-    extern __shared__ uint32_t cache[];            // CACHED: the order bits of all n scores
     __shared__ uint32_t hist[SEL_WARPS][256];      // one histogram a warp: no contention across warps
     __shared__ uint32_t cum[256];
-    __shared__ uint32_t buf[33];
     __shared__ uint32_t sel[2];                    // digit, count above it
 
     const int kvh = blockIdx.x, b = blockIdx.y;
@@ -72,25 +45,42 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
     const float* sc = p.scores + (size_t(b) * p.n_kv_heads + kvh) * p.scores_stride;
     uint32_t* out = p.idx + (size_t(b) * p.n_kv_heads + kvh) * (EMBLA_TOPK + EMBLA_RECENT);
 
-    if (CACHED) {
-        for (int j = t; j < n; j += SEL_T) cache[j] = order_bits(sc[j]);
-        __syncthreads();
+    const int w0 = warp * 32 * ITEMS;
+    uint32_t v[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const int j = w0 + 32 * i + lane;
+        v[i] = j < n ? order_bits(__ldg(sc + j)) : 0u;
     }
-    auto bits_at = [&](int j) -> uint32_t { return CACHED ? cache[j] : order_bits(sc[j]); };
+    for (int i = t; i < SEL_WARPS * 256; i += SEL_T) (&hist[0][0])[i] = 0;
+    __syncthreads();
 
     uint32_t prefix = 0, mask = 0, k = EMBLA_TOPK;
     for (int shift = 24; shift >= 0; shift -= 8) {
-        for (int i = t; i < SEL_WARPS * 256; i += SEL_T) (&hist[0][0])[i] = 0;
-        __syncthreads();
-        for (int j = t; j < n; j += SEL_T) {
-            const uint32_t v = bits_at(j);
-            if ((v & mask) == prefix) atomicAdd(&hist[warp][(v >> shift) & 255u], 1u);
+#pragma unroll
+        for (int i = 0; i < ITEMS; i++) {
+            const bool in = w0 + 32 * i + lane < n && (v[i] & mask) == prefix;
+            const uint32_t active = __ballot_sync(0xffffffffu, in);
+            if (active == 0) continue;   // later passes: most rounds hold no candidate
+            const uint32_t digit = (v[i] >> shift) & 255u;
+            if (shift == 24) {
+                // scores share a handful of leading digits: lanes with the same digit add once
+                if (in) {
+                    const uint32_t peers = __match_any_sync(active, digit);
+                    if (lane == __ffs(peers) - 1) atomicAdd(&hist[warp][digit], uint32_t(__popc(peers)));
+                }
+            } else if (in) {
+                atomicAdd(&hist[warp][digit], 1u);
+            }
         }
         __syncthreads();
         if (t < 256) {
             uint32_t s = 0;
 #pragma unroll 8
-            for (int w = 0; w < SEL_WARPS; w++) s += hist[w][t];
+            for (int w = 0; w < SEL_WARPS; w++) {
+                s += hist[w][t];
+                hist[w][t] = 0;   // ready for the next pass
+            }
             cum[t] = s;
         }
         __syncthreads();
@@ -122,26 +112,50 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
         prefix |= sel[0] << shift;
         mask |= 255u << shift;
         k -= sel[1];
-        __syncthreads();
     }
     // prefix is the TOPK-th largest pattern; every key above it, then the first k equal to it, in key order
-    const int per = (n + SEL_T - 1) / SEL_T, j0 = t * per, j1 = min(n, j0 + per);
     uint32_t gt = 0, eq = 0;
-    for (int j = j0; j < j1; j++) {
-        const uint32_t v = bits_at(j);
-        gt += v > prefix;
-        eq += v == prefix;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const bool ok = w0 + 32 * i + lane < n;
+        gt += __popc(__ballot_sync(0xffffffffu, ok && v[i] > prefix));
+        eq += __popc(__ballot_sync(0xffffffffu, ok && v[i] == prefix));
     }
-    uint32_t ngt, neq;
-    uint32_t gpos = block_scan_excl(gt, buf, lane, warp, ngt);
-    uint32_t epos = block_scan_excl(eq, buf, lane, warp, neq);
-    for (int j = j0; j < j1; j++) {
-        const uint32_t v = bits_at(j);
-        if (v > prefix) out[gpos++] = uint32_t(j);
-        else if (v == prefix) {
-            if (epos < k) out[ngt + epos] = uint32_t(j);
-            epos++;
+    __syncthreads();   // warp 0 has read cum[] of the last pass
+    if (lane == 0) {
+        cum[warp] = gt;
+        cum[32 + warp] = eq;
+    }
+    __syncthreads();
+    if (warp == 0) {   // exclusive scans of the 32 warps' counts
+        uint32_t a = cum[lane], e = cum[32 + lane], ia = a, ie = e;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t ya = __shfl_up_sync(0xffffffffu, ia, o), ye = __shfl_up_sync(0xffffffffu, ie, o);
+            if (lane >= o) {
+                ia += ya;
+                ie += ye;
+            }
         }
+        cum[64 + lane] = ia - a;
+        cum[96 + lane] = ie - e;
+        if (lane == 31) cum[128] = ia;
+    }
+    __syncthreads();
+    uint32_t gpos = cum[64 + warp], epos = cum[96 + warp];
+    const uint32_t ngt = cum[128], lt_mask = (1u << lane) - 1u;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+        const int j = w0 + 32 * i + lane;
+        const bool g = j < n && v[i] > prefix, e = j < n && v[i] == prefix;
+        const uint32_t bg = __ballot_sync(0xffffffffu, g), be = __ballot_sync(0xffffffffu, e);
+        if (g) out[gpos + __popc(bg & lt_mask)] = uint32_t(j);
+        if (e) {
+            const uint32_t at = epos + __popc(be & lt_mask);
+            if (at < k) out[ngt + at] = uint32_t(j);
+        }
+        gpos += __popc(bg);
+        epos += __popc(be);
     }
     for (int j = t; j < EMBLA_RECENT; j += SEL_T) out[EMBLA_TOPK + j] = uint32_t(n + j);
 }
@@ -164,21 +178,14 @@ extern "C" EmblaStatus embla_select_keys(EmblaAttn* ctx, const float* scores_dev
     p.idx = idx_dev;
     p.scores_stride = scores_stride;
     p.n_kv_heads = ctx->cfg.n_kv_heads;
-    const size_t cache_bytes = size_t(max_len) * 4;
-    constexpr size_t kMaxCache = 180 * 1024;
     dim3 grid(p.n_kv_heads, batch);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (cache_bytes <= kMaxCache) {
-        static bool configured[64] = {};
-        if (!configured[ctx->device & 63]) {
-            EMBLA_CUDA_TRY(cudaFuncSetAttribute(select_keys_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                int(kMaxCache)));
-            configured[ctx->device & 63] = true;
-        }
-        select_keys_kernel<true><<<grid, SEL_T, cache_bytes, s>>>(p);
-    } else {
-        select_keys_kernel<false><<<grid, SEL_T, 0, s>>>(p);
-    }
+    const int n_max = max_len - EMBLA_RECENT;   // keys a CTA ranks: 1024 threads x ITEMS
+    if (n_max <= 1024 * 4) select_keys_kernel<4><<<grid, SEL_T, 0, s>>>(p);
+    else if (n_max <= 1024 * 8) select_keys_kernel<8><<<grid, SEL_T, 0, s>>>(p);
+    else if (n_max <= 1024 * 16) select_keys_kernel<16><<<grid, SEL_T, 0, s>>>(p);
+    else if (n_max <= 1024 * 32) select_keys_kernel<32><<<grid, SEL_T, 0, s>>>(p);
+    else EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_select_keys: %d keys (at most %d)", max_len, 1024 * 32 + EMBLA_RECENT);
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;
 }
