@@ -211,3 +211,16 @@ class Ring:
         self.k = torch.zeros(batch, n_kv_heads, ring, HEAD_DIM, dtype=torch_dtype, device="cuda")
         self.v = torch.zeros_like(self.k)
         self.desc = RingDesc(self.k.data_ptr(), self.v.data_ptr(), self.k.stride(0), ring, window)
+
+
+def full_prefill(ctx, pool, block_table, layer, pos0, q, o, gains=None):
+    """Causal ReLU² attention of a prefill chunk. q [batch, n_tokens, >= n_q_heads*128], o likewise
+    (token-major); pos0 int32 [batch]. The chunk's keys/values must already be appended."""
+    view = Attention.view(block_table, None, layer)
+    if gains is None:
+        qd = Query(q.data_ptr(), q.stride(0), 1, 0, None, None)
+    else:
+        qd = Query(q.data_ptr(), q.stride(0), 0, 2, gains[0].data_ptr(), gains[1].data_ptr())
+    _check(lib().embla_attn_full_prefill(ctx.handle, pool.handle, C.byref(view), _ptr(pos0), q.shape[1], C.byref(qd),
+                                         C.c_int64(q.stride(1)), _ptr(o), C.c_int64(o.stride(1)), C.c_int64(o.stride(0)),
+                                         _stream()))

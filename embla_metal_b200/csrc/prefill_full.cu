@@ -1,0 +1,476 @@
+// Prefill-chunk attention of the full layers: causal ReLU² of up to 2048 new tokens over the int8
+// paged cache (their own keys already appended). Replaces relu2_prefill_nax
+// (Sources/EmblaMetal/Kernels/attn_nax.metal:61-364) with q_prep_b
+// (Sources/EmblaMetal/Kernels/prefill.metal:408-426); dispatch Sources/EmblaMetal/Prefill.swift:378-407.
+//
+// This is the one dense contraction of the path, so it runs on the 5th-generation tensor cores:
+//   S = Q Kᵀ   tcgen05.mma kind::f16, M = 128 queries, N = 128 keys (one page), K = 128 dims, fp32 in TMEM
+//   O += P V   tcgen05.mma kind::f16, A = P read straight from TMEM, B = V from shared memory (MN-major)
+// One CTA owns 128 consecutive tokens of one query head and walks the sequence's pages:
+//   warp 8      TMA producer: the page's 256 int8 code rows (swizzled box) + its scales into a 2-stage ring
+//   warps 4-7   converters: int8 codes -> fp16 (exact) into the UMMA operand layout
+//               [dims 0-63 | 64-127][128 keys][128 B], 128-byte swizzle — the same layout serves K as the
+//               K-major B operand of Q Kᵀ and V as the MN-major B operand of P V; 3 buffers in rotation
+//   warp 9      MMA issuer (one thread): S(j) is issued before P V(j-1), so the tensor pipe works on the
+//               next page's scores while the ReLU² warps work on this page's
+//   warps 0-3   one query row a thread: tcgen05.ld S, p = max(s,0)² (kscale/√D)² · vscale masked causally,
+//               row sums in fp32, P as fp16 back into TMEM (tcgen05.st); at the end O / (√D + Σp)
+// TMEM (512 columns): S[2] 2x128, O 128, P[2] 2x64. q is converted to fp16 once (bf16 values are exact
+// in fp16 inside its normal range); int8 codes and their products are exact; accumulation is fp32.
+// Every wait is bounded; a wait that runs out sets the context's error word and the CTA winds down.
+#include "common.cuh"
+
+namespace embla {
+
+constexpr int PF_THREADS = 320;
+constexpr int PF_TILE16 = BLK * HD * 2;            // 32 KiB: 128 rows x 128 dims fp16
+constexpr int PF_RAW = 2 * CODE_BYTES + 1024;      // int8 page: codes + scales
+constexpr int PF_RAW_STAGES = 2;
+constexpr int PF_KVBUFS = 3;
+constexpr size_t PF_SMEM = 1024 + PF_TILE16 + PF_KVBUFS * PF_TILE16 + PF_RAW_STAGES * PF_RAW + 2 * 2 * BLK * 4 + 256;
+
+struct PrefillParams {
+    const uint8_t* pool;
+    const int32_t* block_table;
+    const int32_t* pos0;       // [batch] position of the chunk's first token
+    const void* q;
+    const void* g1;
+    const void* g2;
+    void* o;
+    int* err;
+    int64_t q_token_stride, q_seq_stride, o_token_stride, o_seq_stride;
+    size_t page_bytes;
+    int table_stride, layer, n_layers, n_kv_heads, G, scale_bytes, rows_per_page, n_tokens, prenormed;
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc),
+        "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc),
+        "r"(accumulate)
+        : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: 128-byte swizzle, version 1. Offsets in bytes.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(lbo >> 4) << 16) | (uint64_t(sbo >> 4) << 32) | (uint64_t(1) << 46) |
+           (uint64_t(2) << 61);
+}
+// kind::f16, A and B fp16, D fp32, M = 128, N = 128; B K-major (Q Kᵀ) or MN-major (P V)
+constexpr uint32_t PF_IDESC_QK = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t PF_IDESC_PV = PF_IDESC_QK | (1u << 16);
+
+// One side (K or V) of a raw int8 page -> fp16 in the UMMA layout. 128 converter threads; lanes of a
+// quarter warp take 8 consecutive rows of one 16-byte chunk, so reads and writes are conflict-free.
+__device__ __forceinline__ void convert_side(const uint8_t* raw, uint8_t* dst, int ctid) {
+    const int rl = ctid & 7, ch = (ctid >> 3) & 7, rg = ctid >> 6;
+#pragma unroll
+    for (int it = 0; it < 8; it++) {
+        const int row = it * 16 + rg * 8 + rl;
+        const uint4 w = *reinterpret_cast<const uint4*>(raw + row * 128 + ((ch ^ (row & 7)) << 4));
+        const uint32_t x[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+        uint4 lo, hi;   // dims 16ch..16ch+7 and 16ch+8..16ch+15
+        lo.x = h2_from_biased_bytes(x[0], 0x4140);
+        lo.y = h2_from_biased_bytes(x[0], 0x4342);
+        lo.z = h2_from_biased_bytes(x[1], 0x4140);
+        lo.w = h2_from_biased_bytes(x[1], 0x4342);
+        hi.x = h2_from_biased_bytes(x[2], 0x4140);
+        hi.y = h2_from_biased_bytes(x[2], 0x4342);
+        hi.z = h2_from_biased_bytes(x[3], 0x4140);
+        hi.w = h2_from_biased_bytes(x[3], 0x4342);
+        uint8_t* base = dst + (ch >> 2) * (BLK * 128) + row * 128;
+        const int c16 = (2 * ch) & 7;
+        *reinterpret_cast<uint4*>(base + ((c16 ^ (row & 7)) << 4)) = lo;
+        *reinterpret_cast<uint4*>(base + (((c16 + 1) ^ (row & 7)) << 4)) = hi;
+    }
+}
+
+template <int DT, int SB>
+__global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __grid_constant__ CUtensorMap tmap,
+                                                                     const PrefillParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* Qs = smem;
+    uint8_t* kvb = smem + PF_TILE16;                                  // [3][32 KiB]
+    uint8_t* raw = kvb + PF_KVBUFS * PF_TILE16;                       // [2][PF_RAW]
+    float* scA = reinterpret_cast<float*>(raw + PF_RAW_STAGES * PF_RAW);   // [2][128] (kscale/√D)²
+    float* scV = scA + 2 * BLK;                                       // [2][128] vscale
+    uint64_t* bars = reinterpret_cast<uint64_t*>(scV + 2 * BLK);
+    uint64_t* raw_full = bars;            // [2]
+    uint64_t* raw_empty = bars + 2;       // [2]
+    uint64_t* kv_ready = bars + 4;        // [3]
+    uint64_t* kv_free = bars + 7;         // [3]
+    uint64_t* s_full = bars + 10;         // [2]
+    uint64_t* sm_done = bars + 12;        // [2] S[b] and the scales of its page are free again
+    uint64_t* p_ready = bars + 14;        // [2]
+    uint64_t* p_free = bars + 16;         // [2]
+    uint64_t* o_done = bars + 18;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int kvh = h / p.G;
+    const int p0 = p.pos0[b];
+    const int t0 = qt * BLK;                                   // first token of the tile
+    const int rows = min(BLK, p.n_tokens - t0);                // valid query rows
+    const int last_pos = p0 + t0 + rows - 1;
+    const int n = last_pos / BLK + 1;                          // pages this tile sees
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&raw_full[i], 1);
+            mbar_init(&raw_empty[i], 4);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&sm_done[i], 4);
+            mbar_init(&p_ready[i], 4);
+            mbar_init(&p_free[i], 1);
+        }
+        for (int i = 0; i < 3; i++) {
+            mbar_init(&kv_ready[i], 4);
+            mbar_init(&kv_free[i], 1);
+        }
+        mbar_init(o_done, 1);
+        s_abort = 0;
+        fence_barrier_init();
+    }
+    if (warp == 9) tmem_alloc(&s_tmem, 512);
+
+    // ---- Q tile: [128 tokens][128 dims] of head h as fp16 in the K-major swizzled layout
+    if (p.prenormed) {
+        for (int i = tid; i < BLK * 16; i += PF_THREADS) {
+            const int r = i >> 4, c8 = i & 15;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < rows) {
+                const size_t off = size_t(b) * p.q_seq_stride + size_t(t0 + r) * p.q_token_stride + size_t(h) * HD + c8 * 8;
+                v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
+                if (DT == EMBLA_BF16) {
+                    uint32_t* w = &v.x;
+#pragma unroll
+                    for (int e = 0; e < 4; e++) w[e] = pack_h2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+                }
+            }
+            *reinterpret_cast<uint4*>(Qs + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v;
+        }
+    } else {
+        // q_prep_b: head norm with both gains in the oracle's operation order, rounded to the activation dtype
+        for (int r = warp; r < BLK; r += PF_THREADS / 32) {
+            float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (r < rows) {
+                const size_t off = size_t(b) * p.q_seq_stride + size_t(t0 + r) * p.q_token_stride + size_t(h) * HD;
+#pragma unroll
+                for (int i = 0; i < 4; i++) x[i] = Act<DT>::load(p.q, off + lane + 32 * i);
+                float ss = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 4; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
+                float tot = 0.0f;
+                for (int l = 0; l < 32; l++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, ss, l));
+                const float rr = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, float(HD)), EPS32)));
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int d = lane + 32 * i;
+                    float gn = __fmul_rn(rr, __fadd_rn(1.0f, Act<DT>::load(p.g1, d)));
+                    gn = __fmul_rn(gn, __fadd_rn(1.0f, Act<DT>::load(p.g2, d)));
+                    x[i] = Act<DT>::round(__fmul_rn(x[i], gn));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int d = lane + 32 * i, c8 = d >> 3;
+                *reinterpret_cast<__half*>(Qs + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4) + (d & 7) * 2) =
+                    __float2half_rn(x[i]);
+            }
+        }
+    }
+    fence_proxy_async();      // Q was written by ordinary stores; the tensor pipe reads it through the async proxy
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t tS = tmem, tO = tmem + 256, tP = tmem + 384;
+
+    if (warp == 8) {
+        // ---- TMA producer
+        if (lane == 0) {
+            const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * SB;
+            for (int j = 0; j < n; j++) {
+                const int st = j & 1, use = j >> 1;
+                if (use > 0 && !mbar_wait_bounded(&raw_empty[st], (use - 1) & 1)) {
+                    atomicExch(p.err, ERR_WAIT_EMPTY);
+                    break;
+                }
+                if (*reinterpret_cast<volatile int*>(&s_abort)) break;
+                const int block = p.block_table[size_t(b) * p.table_stride + j];
+                const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
+                uint8_t* dst = raw + st * PF_RAW;
+                mbar_expect_tx(&raw_full[st], tx);
+                tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &raw_full[st]);
+                bulk_load_1d(dst + 2 * CODE_BYTES, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB,
+                             &raw_full[st]);
+            }
+        }
+    } else if (warp == 9) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            const uint32_t qa = smem_u32(Qs);
+            bool ok = true;
+            for (int j = 0; j <= n && ok; j++) {
+                if (j < n) {
+                    const int sb = j & 1, ck = 2 * j, bk = ck % 3;
+                    ok = mbar_wait_bounded(&kv_ready[bk], (ck / 3) & 1);
+                    if (ok && j >= 2) ok = mbar_wait_bounded(&sm_done[sb], ((j >> 1) - 1) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t ka = smem_u32(kvb + bk * PF_TILE16);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++) {
+                        const uint32_t koff = (ks >> 2) * (BLK * 128) + (ks & 3) * 32;
+                        umma_ss(tS + 128 * sb, umma_desc(qa + koff, 16, 1024), umma_desc(ka + koff, 16, 1024), PF_IDESC_QK, ks > 0);
+                    }
+                    tc_commit(&s_full[sb]);
+                    tc_commit(&kv_free[bk]);
+                }
+                if (j >= 1) {
+                    const int i = j - 1, pb = i & 1, cv = 2 * i + 1, bv = cv % 3;
+                    ok = mbar_wait_bounded(&p_ready[pb], (i >> 1) & 1) && mbar_wait_bounded(&kv_ready[bv], (cv / 3) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t va = smem_u32(kvb + bv * PF_TILE16);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++)
+                        umma_ts(tO, tP + 64 * pb + 8 * ks, umma_desc(va + ks * 2048, BLK * 128, 1024), PF_IDESC_PV, (i > 0) | (ks > 0));
+                    tc_commit(&p_free[pb]);
+                    tc_commit(&kv_free[bv]);
+                }
+            }
+            if (!ok) {
+                atomicExch(p.err, ERR_WAIT_FULL);
+                *reinterpret_cast<volatile int*>(&s_abort) = 1;
+            }
+            tc_commit(o_done);
+        }
+    } else if (warp >= 4) {
+        // ---- converters
+        const int ctid = tid - 128;
+        for (int j = 0; j < n; j++) {
+            const int st = j & 1, sb = j & 1;
+            bool ok = mbar_wait_bounded(&raw_full[st], (j >> 1) & 1);
+            const uint8_t* page = raw + st * PF_RAW;
+            for (int side = 0; side < 2 && ok; side++) {
+                const int c = 2 * j + side, buf = c % 3;
+                if (c >= 3) ok = mbar_wait_bounded(&kv_free[buf], ((c / 3) - 1) & 1);
+                if (!ok) break;
+                if (side == 1) {
+                    // the page's scales as fp32 for the ReLU² warps: (kscale/√D)² and vscale
+                    if (j >= 2) ok = mbar_wait_bounded(&sm_done[sb], ((j >> 1) - 1) & 1);
+                    if (!ok) break;
+                    const uint8_t* sc = page + 2 * CODE_BYTES;
+                    const float ks = SB == 4 ? reinterpret_cast<const float*>(sc)[ctid] : __half2float(reinterpret_cast<const __half*>(sc)[ctid]);
+                    const float vs = SB == 4 ? reinterpret_cast<const float*>(sc + BLK * SB)[ctid]
+                                             : __half2float(reinterpret_cast<const __half*>(sc + BLK * SB)[ctid]);
+                    const float a = ks * rsqrtf(float(HD));
+                    scA[sb * BLK + ctid] = a * a;
+                    scV[sb * BLK + ctid] = vs;
+                }
+                convert_side(page + side * CODE_BYTES, kvb + buf * PF_TILE16, ctid);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&kv_ready[buf]);
+            }
+            if (!ok) {
+                atomicExch(p.err, ERR_WAIT_FULL);
+                *reinterpret_cast<volatile int*>(&s_abort) = 1;
+                break;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&raw_empty[st]);
+        }
+    } else {
+        // ---- ReLU² warps: thread = query row
+        const int r = tid;                              // TMEM lane
+        const uint32_t lane_sel = uint32_t(warp * 32) << 16;
+        const int pos_r = p0 + t0 + r;                  // this row's absolute position
+        float rowsum = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n; j++) {
+            const int sb = j & 1;
+            ok = mbar_wait_bounded(&s_full[sb], (j >> 1) & 1) && mbar_wait_bounded(&kv_ready[(2 * j + 1) % 3], ((2 * j + 1) / 3) & 1);
+            if (ok && j >= 2) ok = mbar_wait_bounded(&p_free[sb], ((j >> 1) - 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const bool diag = j * BLK + BLK - 1 > p0 + t0;      // some (row, key) of this page is masked
+            const float* A = scA + sb * BLK;
+            const float* V = scV + sb * BLK;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; cc++) {
+                uint32_t s[32];
+                tmem_ld32(tS + 128 * sb + 32 * cc + lane_sel, s);
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const int c0 = 32 * cc + e;
+                    const float m0 = fmaxf(__uint_as_float(s[e]), 0.0f), m1 = fmaxf(__uint_as_float(s[e + 1]), 0.0f);
+                    float w0 = m0 * m0 * A[c0], w1 = m1 * m1 * A[c0 + 1];
+                    if (diag) {
+                        if (j * BLK + c0 > pos_r) w0 = 0.0f;
+                        if (j * BLK + c0 + 1 > pos_r) w1 = 0.0f;
+                    }
+                    rowsum += w0 + w1;
+                    pk[e >> 1] = pack_h2(w0 * V[c0], w1 * V[c0 + 1]);
+                }
+                tmem_st16(tP + 64 * sb + 16 * cc + lane_sel, pk);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&p_ready[sb]);
+                mbar_arrive(&sm_done[sb]);
+            }
+        }
+        if (ok) ok = mbar_wait_bounded(o_done, 0);
+        if (!ok) {
+            atomicExch(p.err, ERR_WAIT_FULL);
+            *reinterpret_cast<volatile int*>(&s_abort) = 1;
+        } else {
+            tc_fence_after();
+            const float inv = 1.0f / (sqrtf(float(HD)) + rowsum);
+            uint16_t* orow = static_cast<uint16_t*>(p.o) + size_t(b) * p.o_seq_stride + size_t(t0 + r) * p.o_token_stride + size_t(h) * HD;
+#pragma unroll 1
+            for (int cc = 0; cc < 4; cc++) {
+                uint32_t acc[32];
+                tmem_ld32(tO + 32 * cc + lane_sel, acc);
+                if (r < rows) {
+                    uint32_t outw[16];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float a0 = __uint_as_float(acc[e]) * inv, a1 = __uint_as_float(acc[e + 1]) * inv;
+                        if (DT == EMBLA_F16) outw[e >> 1] = pack_h2(a0, a1);
+                        else {
+                            __nv_bfloat162 t = __floats2bfloat162_rn(a0, a1);
+                            outw[e >> 1] = *reinterpret_cast<uint32_t*>(&t);
+                        }
+                    }
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; v4++)
+                        *reinterpret_cast<uint4*>(orow + 32 * cc + 8 * v4) =
+                            make_uint4(outw[4 * v4], outw[4 * v4 + 1], outw[4 * v4 + 2], outw[4 * v4 + 3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+}  // namespace embla
+
+using namespace embla;
+
+template <int DT, int SB>
+static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, const PrefillParams& p, int batch, cudaStream_t s) {
+    auto kern = full_prefill_kernel<DT, SB>;
+    static bool configured[64] = {};
+    if (!configured[ctx->device & 63]) {
+        EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PF_SMEM)));
+        configured[ctx->device & 63] = true;
+    }
+    dim3 grid((p.n_tokens + BLK - 1) / BLK, ctx->cfg.n_q_heads, batch);
+    kern<<<grid, PF_THREADS, PF_SMEM, s>>>(pool->tmap_codes, p);
+    EMBLA_CUDA_TRY(cudaGetLastError());
+    return EMBLA_OK;
+}
+
+extern "C" EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                               const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
+                                               int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
+                                               int64_t o_seq_stride, void* stream) {
+    if (!ctx || !pool || !view || !pos0_dev || !q || !q->q_dev || !o_dev)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_prefill: null argument");
+    if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_prefill: the pool is not int8");
+    if (pool->n_kv_heads != ctx->cfg.n_kv_heads || view->layer < 0 || view->layer >= pool->n_layers)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_prefill: pool/layer mismatch");
+    if (view->batch <= 0 || !view->block_table_dev || n_tokens <= 0)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_prefill: batch %d, n_tokens %d", view->batch, n_tokens);
+    if (!q->prenormed && (q->ng != 2 || !q->g1_dev || !q->g2_dev))
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_prefill: the fused head norm takes both gain vectors (ng = 2)");
+    if ((q_token_stride % 8) || (q->q_stride % 8) || (o_token_stride % 8) || (o_seq_stride % 8))
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_prefill: strides must be multiples of 8 elements (16-byte rows)");
+    PrefillParams p;
+    p.pool = pool->base;
+    p.block_table = view->block_table_dev;
+    p.pos0 = pos0_dev;
+    p.q = q->q_dev;
+    p.g1 = q->g1_dev;
+    p.g2 = q->g2_dev;
+    p.o = o_dev;
+    p.err = ctx->err_dev;
+    p.q_token_stride = q_token_stride;
+    p.q_seq_stride = q->q_stride;
+    p.o_token_stride = o_token_stride;
+    p.o_seq_stride = o_seq_stride;
+    p.page_bytes = pool->page_bytes;
+    p.table_stride = view->table_stride;
+    p.layer = view->layer;
+    p.n_layers = pool->n_layers;
+    p.n_kv_heads = pool->n_kv_heads;
+    p.G = ctx->cfg.n_q_heads / ctx->cfg.n_kv_heads;
+    p.scale_bytes = pool->scale_bytes;
+    p.rows_per_page = pool->rows_per_page;
+    p.n_tokens = n_tokens;
+    p.prenormed = q->prenormed;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool bf = ctx->cfg.act_dtype == EMBLA_BF16, s4 = pool->scale_bytes == 4;
+    if (bf) return s4 ? launch_prefill<EMBLA_BF16, 4>(ctx, pool, p, view->batch, s) : launch_prefill<EMBLA_BF16, 2>(ctx, pool, p, view->batch, s);
+    return s4 ? launch_prefill<EMBLA_F16, 4>(ctx, pool, p, view->batch, s) : launch_prefill<EMBLA_F16, 2>(ctx, pool, p, view->batch, s);
+}

@@ -213,6 +213,19 @@ EmblaStatus embla_attn_sliding_decode(EmblaAttn* ctx, const EmblaRing* ring, con
                                       int32_t batch, const EmblaQuery* q, void* o_dev, int64_t o_stride,
                                       void* stream);
 
+/* ---- prefill chunk, full layers (causal ReLU²) -------------------------------------------------------- */
+/* Replaces q_prep_b + relu2_prefill_nax (prefill.metal:408-426, attn_nax.metal:61-364; dispatch
+ * Prefill.swift:378-407) and the fallback attn_full_b (prefill.metal:218-282): for each sequence, the
+ * n_tokens new tokens at positions pos0_dev[b] + t attend causally (keys <= their own position) over the
+ * int8 cache, which must already hold their own keys and values (embla_kv_append first, as the reference
+ * runs kv_append_b first). Token t's query head h is at q_dev[b * q->q_stride + t * q_token_stride +
+ * h * 128]; out is token-major, o_dev[b * o_seq_stride + t * o_token_stride + h * 128]. Strides are in
+ * elements and must be multiples of 8. Runs on tcgen05 tensor cores with fp32 accumulation in TMEM. */
+EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                    const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
+                                    int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
+                                    int64_t o_seq_stride, void* stream);
+
 /* ---- one decode step through a stack of layers ------------------------------------------------------- */
 /* The attention half of Engine.encodeStep's per-layer loop (Engine.swift:933-991 calling
  * encodeAttention, :743-832) as one call: for every layer, the KV write of the current token and the

@@ -1,0 +1,80 @@
+"""GPU parity of the tcgen05 prefill-chunk kernel (full layers, causal ReLU² over the int8 cache)
+against the CPU oracle, through the C ABI."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from tests import util
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attention_golden.npz")
+
+
+def _prefill(q_bits, k, ks, v, vs, p0, dtype, scale_f16, gains=None, rows=None, nthreads=8):
+    """Runs the CUDA kernel on dense caches [Hkv, p0 + T, 128]; returns (got, want) float arrays on `rows`."""
+    import torch
+    from embla_metal_b200 import attn
+    T, Hq = q_bits.shape[0], q_bits.shape[1]
+    Hkv, S = k.shape[0], k.shape[1]
+    assert S == p0 + T
+    npg = (S + 127) // 128
+    ctx = attn.Attention(Hq, Hkv, dtype, 1, npg * 128)
+    pool = attn.KVPool(2, Hkv, npg + 1, attn.KV_INT8, attn.SCALE_F16 if scale_f16 else attn.SCALE_F32)
+    ids = np.random.default_rng(p0 + T).permutation(npg + 1)[:npg].astype(np.int32)
+    util.fill_pool(pool, 1, ids, k, ks, v, vs)
+    tbl = torch.from_numpy(ids[None]).cuda()
+    qt = util.act_tensor(q_bits.reshape(1, T, Hq * 128), dtype)
+    ot = torch.zeros_like(qt)
+    gt = None if gains is None else tuple(util.act_tensor(x, dtype) for x in gains)
+    attn.full_prefill(ctx, pool, tbl, 1, torch.tensor([p0], dtype=torch.int32, device="cuda"), qt, ot, gains=gt)
+    ctx.check()
+    got = orc.from_bits(util.act_bits(ot), dtype).reshape(T, Hq, 128)
+    ot2 = torch.zeros_like(qt)
+    attn.full_prefill(ctx, pool, tbl, 1, torch.tensor([p0], dtype=torch.int32, device="cuda"), qt, ot2, gains=gt)
+    torch.cuda.synchronize()
+    assert torch.equal(ot.view(torch.int16), ot2.view(torch.int16)), "two runs differ"
+    r0, rstep = (0, 1) if rows is None else rows
+    want = orc.from_bits(orc.full_prefill(q_bits, dtype, k, ks, v, vs, p0, gains=gains, r0=r0, rstep=rstep, nthreads=nthreads), dtype)
+    pool.close()
+    ctx.close()
+    return got[r0::rstep], want[r0::rstep]
+
+
+def _case(T, p0, Hq, Hkv, dtype, scale_f16, seed, gains=False, rows=None):
+    rng = np.random.default_rng(seed)
+    q = orc.to_bits(rng.standard_normal((T, Hq, 128)), dtype)
+    k, ks, v, vs = util.int8_cache(rng, Hkv, p0 + T, scale_f16)
+    g = None
+    if gains:
+        g = (orc.to_bits(rng.standard_normal(128) * 0.1, dtype), orc.to_bits(rng.standard_normal(128) * 0.1, dtype))
+    got, want = _prefill(q, k, ks, v, vs, p0, dtype, scale_f16, gains=g, rows=rows)
+    ok, msg = util.close(got, want, out_ulp=util.BF16_STEP if dtype == orc.BF16 else 0.0)
+    assert ok, f"T={T} p0={p0}: {msg}"
+
+
+@pytest.mark.parametrize("T,p0", [(128, 0), (1, 0), (5, 123), (128, 128), (129, 127), (300, 1000), (257, 2047)])
+def test_prefill_shapes(T, p0):
+    _case(T, p0, 16, 4, orc.BF16, True, seed=T * 7 + p0)
+
+
+def test_prefill_reference_shape_gains_fp32_scales():
+    _case(200, 333, 16, 2, orc.BF16, False, seed=3, gains=True)
+
+
+def test_prefill_fp16_activations():
+    _case(140, 77, 16, 4, orc.F16, True, seed=5)
+
+
+def test_prefill_golden():
+    g = np.load(GOLD)
+    got, _ = _prefill(g["pre_q"], g["pre_k"], g["pre_ks"], g["pre_v"], g["pre_vs"], int(g["pre_p0"]), orc.BF16, True)
+    ok, msg = util.close(got, orc.from_bits(g["pre_o"], orc.BF16), out_ulp=util.BF16_STEP)
+    assert ok, msg
+
+
+def test_config3_prefill_2048_after_30720():
+    # BASELINE config 3: 2048-token chunk after 30720 cached positions, bf16 q, int8 KV + fp16 scales, seed 3.
+    # The oracle checks every 37th query row (the full 0.5 TFLOP on the CPU would take minutes).
+    _case(2048, 30720, 16, 4, orc.BF16, True, seed=3, rows=(5, 37))
