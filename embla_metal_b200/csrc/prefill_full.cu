@@ -7,14 +7,15 @@
 //   S = Q Kᵀ   tcgen05.mma kind::f16, M = 128 queries, N = 128 keys (one page), K = 128 dims, fp32 in TMEM
 //   O += P V   tcgen05.mma kind::f16, A = P read straight from TMEM, B = V from shared memory (MN-major)
 // One CTA owns 128 consecutive tokens of one query head and walks the sequence's pages:
-//   warp 8      TMA producer: the page's 256 int8 code rows (swizzled box) + its scales into a 2-stage ring
-//   warps 4-7   converters: int8 codes -> fp16 (exact) into the UMMA operand layout
+//   warp 12     TMA producer: the page's 256 int8 code rows (swizzled box) + its scales into a 2-stage ring
+//   warps 8-11  converters: int8 codes -> fp16 (exact) into the UMMA operand layout
 //               [dims 0-63 | 64-127][128 keys][128 B], 128-byte swizzle — the same layout serves K as the
 //               K-major B operand of Q Kᵀ and V as the MN-major B operand of P V; 3 buffers in rotation
-//   warp 9      MMA issuer (one thread): S(j) is issued before P V(j-1), so the tensor pipe works on the
+//   warp 13     MMA issuer (one thread): S(j) is issued before P V(j-1), so the tensor pipe works on the
 //               next page's scores while the ReLU² warps work on this page's
-//   warps 0-3   one query row a thread: tcgen05.ld S, p = max(s,0)² (kscale/√D)² · vscale masked causally,
-//               row sums in fp32, P as fp16 back into TMEM (tcgen05.st); at the end O / (√D + Σp)
+//   warps 0-7   two warpgroups, each thread one query row and half of the page's keys: tcgen05.ld S,
+//               p = max(s,0)² (kscale/√D)² · vscale masked causally, row sums in fp32, P as fp16 back
+//               into TMEM (tcgen05.st); at the end O / (√D + Σp)
 // TMEM (512 columns): S[2] 2x128, O 128, P[2] 2x64. q is converted to fp16 once (bf16 values are exact
 // in fp16 inside its normal range); int8 codes and their products are exact; accumulation is fp32.
 // Every wait is bounded; a wait that runs out sets the context's error word and the CTA winds down.
@@ -22,7 +23,7 @@
 
 namespace embla {
 
-constexpr int PF_THREADS = 320;
+constexpr int PF_THREADS = 448;   // 8 ReLU² warps, 4 converter warps, TMA producer, MMA issuer
 constexpr int PF_TILE16 = BLK * HD * 2;            // 32 KiB: 128 rows x 128 dims fp16
 constexpr int PF_RAW = 2 * CODE_BYTES + 1024;      // int8 page: codes + scales
 constexpr int PF_RAW_STAGES = 2;
@@ -153,6 +154,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     uint64_t* o_done = bars + 18;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
+    __shared__ float s_rowsum[2][BLK];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -168,8 +170,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             mbar_init(&raw_full[i], 1);
             mbar_init(&raw_empty[i], 4);
             mbar_init(&s_full[i], 1);
-            mbar_init(&sm_done[i], 4);
-            mbar_init(&p_ready[i], 4);
+            mbar_init(&sm_done[i], 8);
+            mbar_init(&p_ready[i], 8);
             mbar_init(&p_free[i], 1);
         }
         for (int i = 0; i < 3; i++) {
@@ -180,7 +182,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         s_abort = 0;
         fence_barrier_init();
     }
-    if (warp == 9) tmem_alloc(&s_tmem, 512);
+    if (warp == 13) tmem_alloc(&s_tmem, 512);
 
     // ---- Q tile: [128 tokens][128 dims] of head h as fp16 in the K-major swizzled layout
     if (p.prenormed) {
@@ -235,7 +237,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     const uint32_t tmem = s_tmem;
     const uint32_t tS = tmem, tO = tmem + 256, tP = tmem + 384;
 
-    if (warp == 8) {
+    if (warp == 12) {
         // ---- TMA producer
         if (lane == 0) {
             const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * SB;
@@ -255,7 +257,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                              &raw_full[st]);
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == 13) {
         // ---- MMA issuer
         if (lane == 0) {
             const uint32_t qa = smem_u32(Qs);
@@ -295,9 +297,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             }
             tc_commit(o_done);
         }
-    } else if (warp >= 4) {
+    } else if (warp >= 8) {
         // ---- converters
-        const int ctid = tid - 128;
+        const int ctid = tid - 256;
         for (int j = 0; j < n; j++) {
             const int st = j & 1, sb = j & 1;
             bool ok = mbar_wait_bounded(&raw_full[st], (j >> 1) & 1);
@@ -332,9 +334,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             if (lane == 0) mbar_arrive(&raw_empty[st]);
         }
     } else {
-        // ---- ReLU² warps: thread = query row
-        const int r = tid;                              // TMEM lane
-        const uint32_t lane_sel = uint32_t(warp * 32) << 16;
+        // ---- ReLU² warps: thread = (query row, half of the page's keys)
+        const int r = tid & 127, hf = tid >> 7;         // TMEM lane, key half
+        const uint32_t lane_sel = uint32_t((warp & 3) * 32) << 16;
         const int pos_r = p0 + t0 + r;                  // this row's absolute position
         float rowsum = 0.0f;
         bool ok = true;
@@ -345,26 +347,32 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             if (!ok) break;
             tc_fence_after();
             const bool diag = j * BLK + BLK - 1 > p0 + t0;      // some (row, key) of this page is masked
-            const float* A = scA + sb * BLK;
-            const float* V = scV + sb * BLK;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; cc++) {
+            const float4* A4 = reinterpret_cast<const float4*>(scA + sb * BLK + 64 * hf);
+            const float4* V4 = reinterpret_cast<const float4*>(scV + sb * BLK + 64 * hf);
+            const int key0 = j * BLK + 64 * hf;
+#pragma unroll
+            for (int cc = 0; cc < 2; cc++) {
                 uint32_t s[32];
-                tmem_ld32(tS + 128 * sb + 32 * cc + lane_sel, s);
+                tmem_ld32(tS + 128 * sb + 64 * hf + 32 * cc + lane_sel, s);
                 uint32_t pk[16];
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const int c0 = 32 * cc + e;
+                for (int e = 0; e < 32; e += 4) {
+                    const float4 a = A4[(32 * cc + e) >> 2], v = V4[(32 * cc + e) >> 2];
                     const float m0 = fmaxf(__uint_as_float(s[e]), 0.0f), m1 = fmaxf(__uint_as_float(s[e + 1]), 0.0f);
-                    float w0 = m0 * m0 * A[c0], w1 = m1 * m1 * A[c0 + 1];
+                    const float m2 = fmaxf(__uint_as_float(s[e + 2]), 0.0f), m3 = fmaxf(__uint_as_float(s[e + 3]), 0.0f);
+                    float w0 = m0 * m0 * a.x, w1 = m1 * m1 * a.y, w2 = m2 * m2 * a.z, w3 = m3 * m3 * a.w;
                     if (diag) {
-                        if (j * BLK + c0 > pos_r) w0 = 0.0f;
-                        if (j * BLK + c0 + 1 > pos_r) w1 = 0.0f;
+                        const int kb = key0 + 32 * cc + e;
+                        if (kb > pos_r) w0 = 0.0f;
+                        if (kb + 1 > pos_r) w1 = 0.0f;
+                        if (kb + 2 > pos_r) w2 = 0.0f;
+                        if (kb + 3 > pos_r) w3 = 0.0f;
                     }
-                    rowsum += w0 + w1;
-                    pk[e >> 1] = pack_h2(w0 * V[c0], w1 * V[c0 + 1]);
+                    rowsum += (w0 + w1) + (w2 + w3);
+                    pk[e >> 1] = pack_h2(w0 * v.x, w1 * v.y);
+                    pk[(e >> 1) + 1] = pack_h2(w2 * v.z, w3 * v.w);
                 }
-                tmem_st16(tP + 64 * sb + 16 * cc + lane_sel, pk);
+                tmem_st16(tP + 64 * sb + 32 * hf + 16 * cc + lane_sel, pk);
             }
             tmem_wait_st();
             tc_fence_before();
@@ -378,14 +386,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         if (!ok) {
             atomicExch(p.err, ERR_WAIT_FULL);
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
-        } else {
+        }
+        // the two halves' row sums meet in shared memory (named barrier of the 8 ReLU² warps), added in a fixed order
+        s_rowsum[hf][r] = rowsum;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (ok) {
             tc_fence_after();
-            const float inv = 1.0f / (sqrtf(float(HD)) + rowsum);
-            uint16_t* orow = static_cast<uint16_t*>(p.o) + size_t(b) * p.o_seq_stride + size_t(t0 + r) * p.o_token_stride + size_t(h) * HD;
+            const float inv = 1.0f / (sqrtf(float(HD)) + (s_rowsum[0][r] + s_rowsum[1][r]));
+            uint16_t* orow = static_cast<uint16_t*>(p.o) + size_t(b) * p.o_seq_stride + size_t(t0 + r) * p.o_token_stride +
+                             size_t(h) * HD + 64 * hf;
 #pragma unroll 1
-            for (int cc = 0; cc < 4; cc++) {
+            for (int cc = 0; cc < 2; cc++) {
                 uint32_t acc[32];
-                tmem_ld32(tO + 32 * cc + lane_sel, acc);
+                tmem_ld32(tO + 64 * hf + 32 * cc + lane_sel, acc);
                 if (r < rows) {
                     uint32_t outw[16];
 #pragma unroll
@@ -407,7 +420,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == 13) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
