@@ -14,8 +14,9 @@
 //   warp 13     MMA issuer (one thread): S(j) is issued before P V(j-1), so the tensor pipe works on the
 //               next page's scores while the ReLU² warps work on this page's
 //   warps 0-7   two warpgroups, each thread one query row and half of the page's keys: tcgen05.ld S,
-//               p = max(s,0)² (kscale/√D)² · vscale masked causally, row sums in fp32, P as fp16 back
-//               into TMEM (tcgen05.st); at the end O / (√D + Σp)
+//               p = max(s,0)² masked causally, row sums in fp32, P as fp16 back into TMEM (tcgen05.st);
+//               at the end O / (√D + Σp). (The converters fold kscale/√D into K and vscale into V as
+//               fp16 after the exact widening, so S arrives scaled and P needs no per-key factor.)
 // TMEM (512 columns): S[2] 2x128, O 128, P[2] 2x64. q is converted to fp16 once (bf16 values are exact
 // in fp16 inside its normal range); int8 codes and their products are exact; accumulation is fp32.
 // Every wait is bounded; a wait that runs out sets the context's error word and the CTA winds down.
@@ -28,7 +29,7 @@ constexpr int PF_TILE16 = BLK * HD * 2;            // 32 KiB: 128 rows x 128 dim
 constexpr int PF_RAW = 2 * CODE_BYTES + 1024;      // int8 page: codes + scales
 constexpr int PF_RAW_STAGES = 2;
 constexpr int PF_KVBUFS = 3;
-constexpr size_t PF_SMEM = 1024 + PF_TILE16 + PF_KVBUFS * PF_TILE16 + PF_RAW_STAGES * PF_RAW + 2 * 2 * BLK * 4 + 256;
+constexpr size_t PF_SMEM = 1024 + PF_TILE16 + PF_KVBUFS * PF_TILE16 + PF_RAW_STAGES * PF_RAW + 256;
 
 struct PrefillParams {
     const uint8_t* pool;
@@ -109,22 +110,33 @@ constexpr uint32_t PF_IDESC_PV = PF_IDESC_QK | (1u << 16);
 
 // One side (K or V) of a raw int8 page -> fp16 in the UMMA layout. 128 converter threads; lanes of a
 // quarter warp take 8 consecutive rows of one 16-byte chunk, so reads and writes are conflict-free.
-__device__ __forceinline__ void convert_side(const uint8_t* raw, uint8_t* dst, int ctid) {
+__device__ __forceinline__ uint32_t h2_scaled(uint32_t x, uint32_t sel, __half2 sc) {
+    const uint32_t v = h2_from_biased_bytes(x, sel);
+    const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&v), sc);
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// `scales[row] * mult`: the row's dequantisation factor (keys: kscale / sqrt(D); values: vscale), applied as
+// fp16 after the exact widening, so the ReLU² warps need no per-key factors.
+template <int SB>
+__device__ __forceinline__ void convert_side(const uint8_t* raw, uint8_t* dst, int ctid, const uint8_t* scales, float mult) {
     const int rl = ctid & 7, ch = (ctid >> 3) & 7, rg = ctid >> 6;
 #pragma unroll
     for (int it = 0; it < 8; it++) {
         const int row = it * 16 + rg * 8 + rl;
         const uint4 w = *reinterpret_cast<const uint4*>(raw + row * 128 + ((ch ^ (row & 7)) << 4));
+        const float f = SB == 4 ? reinterpret_cast<const float*>(scales)[row] : __half2float(reinterpret_cast<const __half*>(scales)[row]);
+        const __half2 sc = __float2half2_rn(f * mult);
         const uint32_t x[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
         uint4 lo, hi;   // dims 16ch..16ch+7 and 16ch+8..16ch+15
-        lo.x = h2_from_biased_bytes(x[0], 0x4140);
-        lo.y = h2_from_biased_bytes(x[0], 0x4342);
-        lo.z = h2_from_biased_bytes(x[1], 0x4140);
-        lo.w = h2_from_biased_bytes(x[1], 0x4342);
-        hi.x = h2_from_biased_bytes(x[2], 0x4140);
-        hi.y = h2_from_biased_bytes(x[2], 0x4342);
-        hi.z = h2_from_biased_bytes(x[3], 0x4140);
-        hi.w = h2_from_biased_bytes(x[3], 0x4342);
+        lo.x = h2_scaled(x[0], 0x4140, sc);
+        lo.y = h2_scaled(x[0], 0x4342, sc);
+        lo.z = h2_scaled(x[1], 0x4140, sc);
+        lo.w = h2_scaled(x[1], 0x4342, sc);
+        hi.x = h2_scaled(x[2], 0x4140, sc);
+        hi.y = h2_scaled(x[2], 0x4342, sc);
+        hi.z = h2_scaled(x[3], 0x4140, sc);
+        hi.w = h2_scaled(x[3], 0x4342, sc);
         uint8_t* base = dst + (ch >> 2) * (BLK * 128) + row * 128;
         const int c16 = (2 * ch) & 7;
         *reinterpret_cast<uint4*>(base + ((c16 ^ (row & 7)) << 4)) = lo;
@@ -140,9 +152,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     uint8_t* Qs = smem;
     uint8_t* kvb = smem + PF_TILE16;                                  // [3][32 KiB]
     uint8_t* raw = kvb + PF_KVBUFS * PF_TILE16;                       // [2][PF_RAW]
-    float* scA = reinterpret_cast<float*>(raw + PF_RAW_STAGES * PF_RAW);   // [2][128] (kscale/√D)²
-    float* scV = scA + 2 * BLK;                                       // [2][128] vscale
-    uint64_t* bars = reinterpret_cast<uint64_t*>(scV + 2 * BLK);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + PF_RAW_STAGES * PF_RAW);
     uint64_t* raw_full = bars;            // [2]
     uint64_t* raw_empty = bars + 2;       // [2]
     uint64_t* kv_ready = bars + 4;        // [3]
@@ -308,19 +318,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                 const int c = 2 * j + side, buf = c % 3;
                 if (c >= 3) ok = mbar_wait_bounded(&kv_free[buf], ((c / 3) - 1) & 1);
                 if (!ok) break;
-                if (side == 1) {
-                    // the page's scales as fp32 for the ReLU² warps: (kscale/√D)² and vscale
-                    if (j >= 2) ok = mbar_wait_bounded(&sm_done[sb], ((j >> 1) - 1) & 1);
-                    if (!ok) break;
-                    const uint8_t* sc = page + 2 * CODE_BYTES;
-                    const float ks = SB == 4 ? reinterpret_cast<const float*>(sc)[ctid] : __half2float(reinterpret_cast<const __half*>(sc)[ctid]);
-                    const float vs = SB == 4 ? reinterpret_cast<const float*>(sc + BLK * SB)[ctid]
-                                             : __half2float(reinterpret_cast<const __half*>(sc + BLK * SB)[ctid]);
-                    const float a = ks * rsqrtf(float(HD));
-                    scA[sb * BLK + ctid] = a * a;
-                    scV[sb * BLK + ctid] = vs;
-                }
-                convert_side(page + side * CODE_BYTES, kvb + buf * PF_TILE16, ctid);
+                convert_side<SB>(page + side * CODE_BYTES, kvb + buf * PF_TILE16, ctid, page + 2 * CODE_BYTES + side * BLK * SB,
+                                 side == 0 ? rsqrtf(float(HD)) : 1.0f);
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&kv_ready[buf]);
@@ -342,13 +341,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         bool ok = true;
         for (int j = 0; j < n; j++) {
             const int sb = j & 1;
-            ok = mbar_wait_bounded(&s_full[sb], (j >> 1) & 1) && mbar_wait_bounded(&kv_ready[(2 * j + 1) % 3], ((2 * j + 1) / 3) & 1);
+            ok = mbar_wait_bounded(&s_full[sb], (j >> 1) & 1);
             if (ok && j >= 2) ok = mbar_wait_bounded(&p_free[sb], ((j >> 1) - 1) & 1);
             if (!ok) break;
             tc_fence_after();
             const bool diag = j * BLK + BLK - 1 > p0 + t0;      // some (row, key) of this page is masked
-            const float4* A4 = reinterpret_cast<const float4*>(scA + sb * BLK + 64 * hf);
-            const float4* V4 = reinterpret_cast<const float4*>(scV + sb * BLK + 64 * hf);
             const int key0 = j * BLK + 64 * hf;
 #pragma unroll
             for (int cc = 0; cc < 2; cc++) {
@@ -356,21 +353,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                 tmem_ld32(tS + 128 * sb + 64 * hf + 32 * cc + lane_sel, s);
                 uint32_t pk[16];
 #pragma unroll
-                for (int e = 0; e < 32; e += 4) {
-                    const float4 a = A4[(32 * cc + e) >> 2], v = V4[(32 * cc + e) >> 2];
+                for (int e = 0; e < 32; e += 2) {
                     const float m0 = fmaxf(__uint_as_float(s[e]), 0.0f), m1 = fmaxf(__uint_as_float(s[e + 1]), 0.0f);
-                    const float m2 = fmaxf(__uint_as_float(s[e + 2]), 0.0f), m3 = fmaxf(__uint_as_float(s[e + 3]), 0.0f);
-                    float w0 = m0 * m0 * a.x, w1 = m1 * m1 * a.y, w2 = m2 * m2 * a.z, w3 = m3 * m3 * a.w;
+                    float w0 = m0 * m0, w1 = m1 * m1;
                     if (diag) {
                         const int kb = key0 + 32 * cc + e;
                         if (kb > pos_r) w0 = 0.0f;
                         if (kb + 1 > pos_r) w1 = 0.0f;
-                        if (kb + 2 > pos_r) w2 = 0.0f;
-                        if (kb + 3 > pos_r) w3 = 0.0f;
                     }
-                    rowsum += (w0 + w1) + (w2 + w3);
-                    pk[e >> 1] = pack_h2(w0 * v.x, w1 * v.y);
-                    pk[(e >> 1) + 1] = pack_h2(w2 * v.z, w3 * v.w);
+                    rowsum += w0 + w1;
+                    pk[e >> 1] = pack_h2(w0, w1);
                 }
                 tmem_st16(tP + 64 * sb + 32 * hf + 16 * cc + lane_sel, pk);
             }

@@ -365,11 +365,12 @@ void orc_sliding_attend(const uint16_t* q, int ld_tok, int T, int dtype, int pre
 // attn_full_b (prefill.metal:218-282) / relu2_prefill_nax (attn_nax.metal:228-270, 350-363) with
 // threshold 0 and sink sqrt(D) (Prefill.swift:396-397): query row r (absolute position p0 + r)
 // sees keys c <= p0 + r; out[r][h·128 + d] token-major. Rows r0, r0 + rstep, ... are computed
-// (the others are left untouched), so a full-size chunk can be checked on a subset.
+// (the others are left untouched), so a full-size chunk can be checked on a subset. `o_f32` (optional) receives
+// the unrounded fp32 results.
 void orc_full_prefill(const uint16_t* q, int ld_tok, int Tq, int dtype, int prenormed,
                       const uint16_t* g1, const uint16_t* g2,
                       int kv_kind, const void* kc, const float* ks, const void* vc, const float* vs,
-                      int Hq, int Hkv, int p0, int ldS, uint16_t* o, int r0, int rstep, int nthreads) {
+                      int Hq, int Hkv, int p0, int ldS, uint16_t* o, int r0, int rstep, int nthreads, float* o_f32) {
     const int G = Hq / Hkv;
     const float scale = 1.0f / std::sqrt(float(HD));
     std::vector<int> rows;
@@ -396,6 +397,8 @@ void orc_full_prefill(const uint16_t* q, int ld_tok, int Tq, int dtype, int pren
         const float den = std::sqrt(float(HD)) + psum;
         uint16_t* od = o + (size_t(r) * Hq + h) * HD;
         for (int d = 0; d < HD; d++) od[d] = store_act(acc[d] / den, dtype);
+        // the same quotient before it is rounded to the storage dtype, for tolerance checks on 16-bit outputs
+        if (o_f32) for (int d = 0; d < HD; d++) o_f32[(size_t(r) * Hq + h) * HD + d] = acc[d] / den;
     });
 }
 

@@ -91,8 +91,8 @@ def build():
     v = rng.integers(-127, 128, (4, p0 + Tq, 128)).astype(np.int8)
     ks = rng.uniform(0.005, 0.02, (4, p0 + Tq)).astype(np.float16).astype(np.float32)
     vs = rng.uniform(0.005, 0.02, (4, p0 + Tq)).astype(np.float16).astype(np.float32)
-    o = orc.full_prefill(q, orc.BF16, k, ks, v, vs, p0)
-    g.update(pre_q=q, pre_k=k, pre_v=v, pre_ks=ks, pre_vs=vs, pre_o=o, pre_p0=np.array(p0))
+    o, o32 = orc.full_prefill(q, orc.BF16, k, ks, v, vs, p0, want_f32=True)
+    g.update(pre_q=q, pre_k=k, pre_v=v, pre_ks=ks, pre_vs=vs, pre_o=o, pre_o_f32=o32, pre_p0=np.array(p0))
     return g
 
 

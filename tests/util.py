@@ -22,6 +22,18 @@ def close(got, want, max_abs=MAX_ABS, rel_rms=REL_RMS, out_ulp=0.0):
 BF16_STEP = 2.0 ** -7
 
 
+def close_stored(got, want_f32, out_step, max_abs=MAX_ABS, rel_rms=REL_RMS):
+    """`got` is a kernel's output after rounding to its 16-bit storage dtype, `want_f32` the oracle's fp32
+    accumulation before that rounding. Storing rounds by up to half a step (out_step * |x| bounds one step),
+    which is not the kernel's error: only what exceeds half a step is held against the fp32 tolerances."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want_f32, np.float64)
+    err = np.maximum(np.abs(got - want) - 0.5 * out_step * np.abs(want), 0.0)
+    rms = np.sqrt((err ** 2).mean() / max((want ** 2).mean(), 1e-30))
+    return err.max() <= max_abs and rms <= rel_rms, (f"beyond storage rounding: max-abs {err.max():.3e} (<= {max_abs}), "
+                                                     f"rel-rms {rms:.3e} (<= {rel_rms})")
+
+
 def int8_cache(rng, Hkv, S, scale_f16=True, lo=0.005, hi=0.02):
     """K/V int8 uniform in [-127, 127] with per-token per-head scales uniform in [lo, hi]."""
     k = rng.integers(-127, 128, (Hkv, S, 128)).astype(np.int8)
