@@ -1,0 +1,109 @@
+"""Single-kernel timing cases on synthetic data (CUDA events; also the commands profiled under ncu).
+
+    python -m embla_metal_b200.microbench full_decode --batch 8 [--scores]
+    python -m embla_metal_b200.microbench sparse --batch 8        # score, select, gather-attend, sliding attend
+    python -m embla_metal_b200.microbench prefill --tokens 2048 --cached 30720
+
+Each case prints one line per kernel with its time per launch and the bandwidth or FLOP rate that follows
+from the algorithmic bytes / FLOPs of the launch.
+"""
+import argparse
+
+import torch
+
+from . import attn, stack as stk
+
+HQ, HKV, CTX = 16, 4, 32768
+
+
+def _events(fn, reps=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+    ev[0].record()
+    for i in range(reps):
+        fn()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    return sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(reps))
+
+
+def full_decode(batch, scores):
+    npg = CTX // 128
+    ctx = attn.Attention(HQ, HKV, attn.F16, max_batch=batch, max_context=CTX)
+    pool = attn.KVPool(1, HKV, batch * npg, attn.KV_INT8, attn.SCALE_F16)
+    raw = pool.raw()
+    raw.view(-1).random_(0, 256)
+    raw[..., 32768:].view(torch.float16).fill_(0.01)
+    table = torch.randperm(batch * npg, device="cuda", dtype=torch.int32).view(batch, npg).contiguous()
+    lens = torch.full((batch,), CTX, dtype=torch.int32, device="cuda")
+    q = torch.randn(batch, HQ * 128, device="cuda", dtype=torch.float16)
+    o = torch.zeros_like(q)
+    sc = torch.zeros(batch, HKV, CTX, device="cuda") if scores else None
+    ts = _events(lambda: ctx.full_decode(pool, table, lens, 0, q, o, scores=sc, max_seq_len=CTX))
+    ctx.check()
+    nbytes = batch * HKV * CTX * 260
+    print(f"full_decode batch {batch} scores {bool(scores)}: {1e3 * ts[len(ts) // 2]:.1f} us/launch, "
+          f"{nbytes / ts[len(ts) // 2] / 1e6:.0f} GB/s (min {nbytes / ts[0] / 1e6:.0f})")
+
+
+def sparse(batch):
+    st = stk.DecodeStack([stk.SPARSE, stk.SLIDING], batch, CTX)
+    st.fill_random(1)
+    st.set_positions(CTX - 1)
+    st.qkv.copy_(torch.randn(st.qkv.shape, device="cuda").to(st.dtype))
+    for _ in range(3):
+        st.step()
+    torch.cuda.synchronize()
+    pairs = batch * HKV
+    nbytes = {"score": pairs * CTX * 256, "select": pairs * (CTX - 128) * 4, "sparse_decode": pairs * 1152 * 512,
+              "sliding_decode": pairs * 1024 * 512, "append": pairs * 512, "sliding_write": pairs * 512}
+    for name in ("score", "select", "sparse_decode", "sliding_decode", "append", "sliding_write"):
+        st.set_probe(name)
+        for _ in range(5):
+            st.step()
+        torch.cuda.synchronize()
+        ms, n = st.read_probe()
+        print(f"{name} batch {batch}: {1e3 * ms / n:.1f} us/launch, {nbytes[name] / (ms / n) / 1e6:.0f} GB/s")
+    st.ctx.check()
+
+
+def prefill(tokens, cached):
+    S = cached + tokens
+    npg = (S + 127) // 128
+    ctx = attn.Attention(HQ, HKV, attn.BF16, 1, npg * 128)
+    pool = attn.KVPool(1, HKV, npg, attn.KV_INT8, attn.SCALE_F16)
+    raw = pool.raw()
+    raw.view(-1).random_(0, 256)
+    raw[..., 32768:].view(torch.float16).fill_(0.01)
+    tbl = torch.arange(npg, dtype=torch.int32, device="cuda")[None].contiguous()
+    q = torch.randn(1, tokens, HQ * 128, device="cuda", dtype=torch.bfloat16)
+    o = torch.zeros_like(q)
+    pos0 = torch.tensor([cached], dtype=torch.int32, device="cuda")
+    ts = _events(lambda: attn.full_prefill(ctx, pool, tbl, 0, pos0, q, o))
+    ctx.check()
+    flop = 4 * HQ * 128 * sum(cached + i + 1 for i in range(tokens))
+    med = ts[len(ts) // 2]
+    print(f"full_prefill {tokens} tokens after {cached}: {med:.4f} ms, {flop / med / 1e9:.0f} TFLOP/s "
+          f"(min-time {flop / ts[0] / 1e9:.0f}), {tokens / med * 1e3:.0f} tok/s")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["full_decode", "sparse", "prefill"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--scores", action="store_true")
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--cached", type=int, default=30720)
+    a = ap.parse_args()
+    if a.case == "full_decode":
+        full_decode(a.batch, a.scores)
+    elif a.case == "sparse":
+        sparse(a.batch)
+    else:
+        prefill(a.tokens, a.cached)
+
+
+if __name__ == "__main__":
+    main()
