@@ -183,6 +183,9 @@ def run_gpu(args, rank, world):
 
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
+    # libraries (NCCL's version banner) may write to stdout; keep it for the one JSON line
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     if TOTAL_SEQS % world:
@@ -265,11 +268,82 @@ def run_gpu(args, rank, world):
         v, secs = cpu_tok_s(cores, 4 * cores)
         line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": f"{4 * cores} sequence-cycles of the 4-layer cycle at {CONTEXT} keys on {cores} threads, {secs:.2f} s"}
-    if rank == 0:
-        print(json.dumps(line), flush=True)
     st.close()
+    del st
+    torch.cuda.empty_cache()
+    line["prefill"] = prefill_leg(rank, world, barrier)
+    if rank == 0:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+PREFILL_T, PREFILL_CACHED = 2048, 30720
+PREFILL_FLOP = 4 * HQ * 128 * sum(PREFILL_CACHED + i + 1 for i in range(PREFILL_T))
+
+
+def prefill_leg(rank, world, barrier, reps=10):
+    """BASELINE.json config 3 on the same GPUs: a 2048-token causal chunk appended to 30720 cached positions of the
+    int8 cache, bf16 q. One GPU computes all heads; 2 or 4 GPUs shard by kv head, 8 GPUs by (kv head, half of the
+    chunk); the per-rank outputs are combined with an NCCL all-gather inside the timed region."""
+    import torch
+    import torch.distributed as dist
+    from embla_metal_b200 import attn
+    if world not in (1, 2, 4, 8):
+        return None
+    kv_shards = min(world, HKV)
+    tok_shards = world // kv_shards
+    hkv_l, hq_l, T_l = HKV // kv_shards, HQ // kv_shards, PREFILL_T // tok_shards
+    tok_part = rank % tok_shards
+    pos0 = PREFILL_CACHED + tok_part * T_l
+    S = pos0 + T_l
+    npg = (S + 127) // 128
+    ctx = attn.Attention(hq_l, hkv_l, attn.BF16, 1, npg * 128)
+    pool = attn.KVPool(1, hkv_l, npg, attn.KV_INT8, attn.SCALE_F16)
+    g = torch.Generator(device="cuda").manual_seed(3 + rank)
+    raw = pool.raw()
+    flat = raw.view(-1, raw.shape[-1])
+    flat[:, :32768] = torch.randint(-127, 128, (flat.shape[0], 32768), dtype=torch.int8, device="cuda", generator=g).view(torch.uint8)
+    flat[:, 32768:] = torch.empty(flat.shape[0], 256, device="cuda").uniform_(0.005, 0.02, generator=g).to(torch.float16).view(torch.uint8)
+    tbl = torch.arange(npg, dtype=torch.int32, device="cuda")[None].contiguous()
+    q = torch.randn(1, T_l, hq_l * 128, device="cuda", generator=g).to(torch.bfloat16)
+    o = torch.zeros_like(q)
+    gathered = torch.zeros(world, T_l, hq_l * 128, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    p0 = torch.tensor([pos0], dtype=torch.int32, device="cuda")
+
+    def step():
+        attn.full_prefill(ctx, pool, tbl, 0, p0, q, o)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, o[0])
+
+    for _ in range(3):
+        step()
+    ctx.check()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(reps):
+        step()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms.item())
+    ctx.check()
+    pool.close()
+    ctx.close()
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    burst, sustained = float(peaks.get("bf16_tflops", 1590.0)), float(peaks.get("bf16_tflops_sustained", 1400.0))
+    tflops = PREFILL_FLOP / (ms * 1e-3) / 1e12
+    return {"metric": "prefill attn tok/s", "workload": "config 3: 2048-token causal chunk after 30720 cached positions, int8 KV, bf16 q",
+            "value": PREFILL_T / (ms * 1e-3), "unit": "tok/s", "ms": ms, "tflops": tflops, "n_gpus": world,
+            "sharding": ("none" if world == 1 else f"{kv_shards} kv-head shards x {tok_shards} chunk halves, NCCL all-gather of per-head outputs"),
+            "allgather_bytes": 0 if world == 1 else PREFILL_T * HQ * 128 * 2,
+            "roofline": {"bound": "tensor", "achieved": tflops, "peak": burst * world, "unit": "TFLOP/s", "frac": tflops / (burst * world),
+                         "frac_of_sustained": tflops / (sustained * world)}}
 
 
 def main():
