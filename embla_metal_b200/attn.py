@@ -224,3 +224,15 @@ def full_prefill(ctx, pool, block_table, layer, pos0, q, o, gains=None):
     _check(lib().embla_attn_full_prefill(ctx.handle, pool.handle, C.byref(view), _ptr(pos0), q.shape[1], C.byref(qd),
                                          C.c_int64(q.stride(1)), _ptr(o), C.c_int64(o.stride(1)), C.c_int64(o.stride(0)),
                                          _stream()))
+
+
+def sliding_prefill(ctx, ring, pos0, q, o, qgain=None):
+    """Softmax attention of a prefill chunk over each token's window; q, o [batch, n_tokens, >= n_q_heads*128].
+    The chunk's keys/values must already be in the ring (Attention.sliding_write)."""
+    if qgain is None:
+        qd = Query(q.data_ptr(), q.stride(0), 1, 0, None, None)
+    else:
+        qd = Query(q.data_ptr(), q.stride(0), 0, 1, qgain.data_ptr(), None)
+    _check(lib().embla_attn_sliding_prefill(ctx.handle, C.byref(ring.desc), _ptr(pos0), q.shape[0], q.shape[1], C.byref(qd),
+                                            C.c_int64(q.stride(1)), _ptr(o), C.c_int64(o.stride(1)), C.c_int64(o.stride(0)),
+                                            _stream()))

@@ -213,6 +213,17 @@ EmblaStatus embla_attn_sliding_decode(EmblaAttn* ctx, const EmblaRing* ring, con
                                       int32_t batch, const EmblaQuery* q, void* o_dev, int64_t o_stride,
                                       void* stream);
 
+/* ---- prefill chunk, sliding layers ------------------------------------------------------------------- */
+/* Replaces attn_sliding_b / attn_sliding8_b (prefill.metal:129-180, 439-548; dispatch Prefill.swift:300-313):
+ * token t of sequence b, at position pos0_dev[b] + t, attends its last `window` positions with softmax. The
+ * chunk's keys and values must already be in the ring (embla_sliding_write with n_tokens first, as the
+ * reference runs kv_sliding_b first); the ring must hold window + n_tokens slots. Without `prenormed`, q is
+ * normed with gain g1 (ng = 1), rotated at its position and rounded. Layout of q and o as for
+ * embla_attn_full_prefill. */
+EmblaStatus embla_attn_sliding_prefill(EmblaAttn* ctx, const EmblaRing* ring, const int32_t* pos0_dev, int32_t batch,
+                                       int32_t n_tokens, const EmblaQuery* q, int64_t q_token_stride, void* o_dev,
+                                       int64_t o_token_stride, int64_t o_seq_stride, void* stream);
+
 /* ---- prefill chunk, full layers (causal ReLU²) -------------------------------------------------------- */
 /* Replaces q_prep_b + relu2_prefill_nax (prefill.metal:408-426, attn_nax.metal:61-364; dispatch
  * Prefill.swift:378-407) and the fallback attn_full_b (prefill.metal:218-282): for each sequence, the
