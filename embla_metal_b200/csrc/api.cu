@@ -158,6 +158,12 @@ EmblaStatus embla_kv_pool_create(int32_t n_layers, int32_t n_kv_heads, int32_t k
     CUresult r = enc(&p->tmap_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, p->base, dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) {
+        const cuuint32_t box_half[2] = {128, 128};
+        r = enc(&p->tmap_half, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, p->base, dims, strides, box_half, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     if (r != CUDA_SUCCESS) {
         cudaFree(p->base);
         delete p;

@@ -51,6 +51,7 @@ struct EmblaKVPool {
     size_t page_bytes, block_bytes, total_bytes;
     uint8_t* base;          // device
     CUtensorMap tmap_codes; // [total rows][128 B] uint8, box 256 rows, 128-byte swizzle
+    CUtensorMap tmap_half;  // the same rows through a 128-row box (one side, K or V, of an int8 page)
     int device;
 };
 

@@ -6,18 +6,19 @@
 // This is the one dense contraction of the path, so it runs on the 5th-generation tensor cores:
 //   S = Q Kᵀ   tcgen05.mma kind::f16, M = 128 queries, N = 128 keys (one page), K = 128 dims, fp32 in TMEM
 //   O += P V   tcgen05.mma kind::f16, A = P read straight from TMEM, B = V from shared memory (MN-major)
-// One CTA owns 128 consecutive tokens of one query head and walks the sequence's pages:
-//   warp 12     TMA producer: the page's 256 int8 code rows (swizzled box) + its scales into a 2-stage ring
-//   warps 8-11  converters: int8 codes -> fp16 (exact) into the UMMA operand layout
-//               [dims 0-63 | 64-127][128 keys][128 B], 128-byte swizzle — the same layout serves K as the
-//               K-major B operand of Q Kᵀ and V as the MN-major B operand of P V; 3 buffers in rotation
-//   warp 13     MMA issuer (one thread): S(j) is issued before P V(j-1), so the tensor pipe works on the
-//               next page's scores while the ReLU² warps work on this page's
-//   warps 0-7   two warpgroups, each thread one query row and half of the page's keys: tcgen05.ld S,
-//               p = max(s,0)² masked causally, row sums in fp32, P as fp16 back into TMEM (tcgen05.st);
-//               at the end O / (√D + Σp). (The converters fold kscale/√D into K and vscale into V as
-//               fp16 after the exact widening, so S arrives scaled and P needs no per-key factor.)
-// TMEM (512 columns): S[2] 2x128, O 128, P[2] 2x64. q is converted to fp16 once (bf16 values are exact
+// One CTA owns 256 consecutive tokens of one query head as two tiles of 128 and walks the sequence's pages;
+// both tiles use every converted page, which halves the conversion work per MMA:
+//   warp 12     TMA producer: one side (K or V: 128 int8 code rows, swizzled box) at a time into a 3-slot ring,
+//               the page's scales with its K side
+//   warps 8-11  converters: int8 codes -> fp16 (exact), times the row's factor (kscale/√D or vscale), into the
+//               UMMA operand layout [dims 0-63 | 64-127][128 keys][128 B], 128-byte swizzle — the same layout
+//               serves K as the K-major B operand of Q Kᵀ and V as the MN-major B operand of P V; 3 buffers
+//   warp 13     MMA issuer (one thread), per page: S0(j), P V1(j-1), S1(j), P V0(j) — while the ReLU² warps of
+//               one tile work on its scores the tensor pipe runs the other tile's products
+//   warps 0-7   two warpgroups, one per tile, one query row a thread: tcgen05.ld S, p = max(s,0)² masked
+//               causally, row sums in fp32, P as fp16 back into TMEM over the consumed S columns
+//               (tcgen05.st); at the end O / (√D + Σp)
+// TMEM (512 columns): per tile S 128 (P aliases its first 64) and O 128. q is converted to fp16 once (bf16 values are exact
 // in fp16 inside its normal range); int8 codes and their products are exact; accumulation is fp32.
 // Every wait is bounded; a wait that runs out sets the context's error word and the CTA winds down.
 #include "common.cuh"
@@ -26,10 +27,9 @@ namespace embla {
 
 constexpr int PF_THREADS = 448;   // 8 ReLU² warps, 4 converter warps, TMA producer, MMA issuer
 constexpr int PF_TILE16 = BLK * HD * 2;            // 32 KiB: 128 rows x 128 dims fp16
-constexpr int PF_RAW = 2 * CODE_BYTES + 1024;      // int8 page: codes + scales
-constexpr int PF_RAW_STAGES = 2;
 constexpr int PF_KVBUFS = 3;
-constexpr size_t PF_SMEM = 1024 + PF_TILE16 + PF_KVBUFS * PF_TILE16 + PF_RAW_STAGES * PF_RAW + 256;
+// alignment slack, 2 Q tiles, 3 converted sides, 3 raw int8 sides, 2 pages' scales, barriers
+constexpr size_t PF_SMEM = 1024 + 2 * PF_TILE16 + PF_KVBUFS * PF_TILE16 + PF_KVBUFS * CODE_BYTES + 2 * 1024 + 256;
 
 struct PrefillParams {
     const uint8_t* pool;
@@ -149,44 +149,45 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                                                                      const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* Qs = smem;
-    uint8_t* kvb = smem + PF_TILE16;                                  // [3][32 KiB]
-    uint8_t* raw = kvb + PF_KVBUFS * PF_TILE16;                       // [2][PF_RAW]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + PF_RAW_STAGES * PF_RAW);
-    uint64_t* raw_full = bars;            // [2]
-    uint64_t* raw_empty = bars + 2;       // [2]
-    uint64_t* kv_ready = bars + 4;        // [3]
-    uint64_t* kv_free = bars + 7;         // [3]
-    uint64_t* s_full = bars + 10;         // [2]
-    uint64_t* sm_done = bars + 12;        // [2] S[b] and the scales of its page are free again
-    uint64_t* p_ready = bars + 14;        // [2]
-    uint64_t* p_free = bars + 16;         // [2]
-    uint64_t* o_done = bars + 18;
+    uint8_t* Qs = smem;                                               // [2 tiles][32 KiB]
+    uint8_t* kvb = smem + 2 * PF_TILE16;                              // [3][32 KiB] converted K / V sides
+    uint8_t* raw = kvb + PF_KVBUFS * PF_TILE16;                       // [3][16 KiB] int8 sides as loaded
+    uint8_t* scl = raw + PF_KVBUFS * CODE_BYTES;                      // [2 pages][K scales | V scales], 1 KiB each
+    uint64_t* bars = reinterpret_cast<uint64_t*>(scl + 2 * 1024);
+    uint64_t* raw_full = bars;            // [3]
+    uint64_t* raw_empty = bars + 3;       // [3]
+    uint64_t* kv_ready = bars + 6;        // [3]
+    uint64_t* kv_free = bars + 9;         // [3]
+    uint64_t* s_full = bars + 12;         // [2 tiles]
+    uint64_t* p_ready = bars + 14;        // [2 tiles]
+    uint64_t* o_done = bars + 16;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
-    __shared__ float s_rowsum[2][BLK];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int h = blockIdx.y, b = blockIdx.z;
     const int kvh = h / p.G;
     const int p0 = p.pos0[b];
-    const int t0 = qt * BLK;                                   // first token of the tile
-    const int rows = min(BLK, p.n_tokens - t0);                // valid query rows
-    const int last_pos = p0 + t0 + rows - 1;
-    const int n = last_pos / BLK + 1;                          // pages this tile sees
+    // two query tiles of 128 consecutive tokens each share every converted page
+    int t0[2], rows[2], npg[2];
+#pragma unroll
+    for (int x = 0; x < 2; x++) {
+        t0[x] = (2 * blockIdx.x + x) * BLK;
+        rows[x] = max(0, min(BLK, p.n_tokens - t0[x]));
+        npg[x] = rows[x] > 0 ? (p0 + t0[x] + rows[x] - 1) / BLK + 1 : 0;
+    }
+    const int n = max(npg[0], npg[1]);
 
     if (tid == 0) {
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < 3; i++) {
             mbar_init(&raw_full[i], 1);
             mbar_init(&raw_empty[i], 4);
-            mbar_init(&s_full[i], 1);
-            mbar_init(&sm_done[i], 8);
-            mbar_init(&p_ready[i], 8);
-            mbar_init(&p_free[i], 1);
-        }
-        for (int i = 0; i < 3; i++) {
             mbar_init(&kv_ready[i], 4);
             mbar_init(&kv_free[i], 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_ready[i], 4);
         }
         mbar_init(o_done, 1);
         s_abort = 0;
@@ -194,49 +195,52 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     }
     if (warp == 13) tmem_alloc(&s_tmem, 512);
 
-    // ---- Q tile: [128 tokens][128 dims] of head h as fp16 in the K-major swizzled layout
-    if (p.prenormed) {
-        for (int i = tid; i < BLK * 16; i += PF_THREADS) {
-            const int r = i >> 4, c8 = i & 15;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < rows) {
-                const size_t off = size_t(b) * p.q_seq_stride + size_t(t0 + r) * p.q_token_stride + size_t(h) * HD + c8 * 8;
-                v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
-                if (DT == EMBLA_BF16) {
-                    uint32_t* w = &v.x;
+    // ---- Q tiles: [128 tokens][128 dims] of head h as fp16 in the K-major swizzled layout
+    for (int x = 0; x < 2; x++) {
+        uint8_t* Qx = Qs + x * PF_TILE16;
+        if (p.prenormed) {
+            for (int i = tid; i < BLK * 16; i += PF_THREADS) {
+                const int r = i >> 4, c8 = i & 15;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (r < rows[x]) {
+                    const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + r) * p.q_token_stride + size_t(h) * HD + c8 * 8;
+                    v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
+                    if (DT == EMBLA_BF16) {
+                        uint32_t* w = &v.x;
 #pragma unroll
-                    for (int e = 0; e < 4; e++) w[e] = pack_h2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+                        for (int e = 0; e < 4; e++) w[e] = pack_h2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+                    }
                 }
+                *reinterpret_cast<uint4*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v;
             }
-            *reinterpret_cast<uint4*>(Qs + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v;
-        }
-    } else {
-        // q_prep_b: head norm with both gains in the oracle's operation order, rounded to the activation dtype
-        for (int r = warp; r < BLK; r += PF_THREADS / 32) {
-            float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (r < rows) {
-                const size_t off = size_t(b) * p.q_seq_stride + size_t(t0 + r) * p.q_token_stride + size_t(h) * HD;
+        } else {
+            // q_prep_b: head norm with both gains in the oracle's operation order, rounded to the activation dtype
+            for (int r = warp; r < BLK; r += PF_THREADS / 32) {
+                float xq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (r < rows[x]) {
+                    const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + r) * p.q_token_stride + size_t(h) * HD;
 #pragma unroll
-                for (int i = 0; i < 4; i++) x[i] = Act<DT>::load(p.q, off + lane + 32 * i);
-                float ss = 0.0f;
+                    for (int i = 0; i < 4; i++) xq[i] = Act<DT>::load(p.q, off + lane + 32 * i);
+                    float ss = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 4; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
-                float tot = 0.0f;
-                for (int l = 0; l < 32; l++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, ss, l));
-                const float rr = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, float(HD)), EPS32)));
+                    for (int i = 0; i < 4; i++) ss = __fadd_rn(ss, __fmul_rn(xq[i], xq[i]));
+                    float tot = 0.0f;
+                    for (int l = 0; l < 32; l++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, ss, l));
+                    const float rr = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, float(HD)), EPS32)));
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int d = lane + 32 * i;
+                        float gn = __fmul_rn(rr, __fadd_rn(1.0f, Act<DT>::load(p.g1, d)));
+                        gn = __fmul_rn(gn, __fadd_rn(1.0f, Act<DT>::load(p.g2, d)));
+                        xq[i] = Act<DT>::round(__fmul_rn(xq[i], gn));
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const int d = lane + 32 * i;
-                    float gn = __fmul_rn(rr, __fadd_rn(1.0f, Act<DT>::load(p.g1, d)));
-                    gn = __fmul_rn(gn, __fadd_rn(1.0f, Act<DT>::load(p.g2, d)));
-                    x[i] = Act<DT>::round(__fmul_rn(x[i], gn));
+                    const int d = lane + 32 * i, c8 = d >> 3;
+                    *reinterpret_cast<__half*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4) + (d & 7) * 2) =
+                        __float2half_rn(xq[i]);
                 }
-            }
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int d = lane + 32 * i, c8 = d >> 3;
-                *reinterpret_cast<__half*>(Qs + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4) + (d & 7) * 2) =
-                    __float2half_rn(x[i]);
             }
         }
     }
@@ -245,60 +249,75 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    const uint32_t tS = tmem, tO = tmem + 256, tP = tmem + 384;
+    // TMEM columns: S/P of tile 0 at 0, of tile 1 at 128 (P overwrites the first 64 columns of its S); O at 256, 384
 
     if (warp == 12) {
-        // ---- TMA producer
+        // ---- TMA producer: conversion c = 2 j + side takes ring slot c % 3; page j's scales go to scl[j & 1]
         if (lane == 0) {
-            const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * SB;
-            for (int j = 0; j < n; j++) {
-                const int st = j & 1, use = j >> 1;
-                if (use > 0 && !mbar_wait_bounded(&raw_empty[st], (use - 1) & 1)) {
+            for (int c = 0; c < 2 * n; c++) {
+                const int j = c >> 1, side = c & 1, slot = c % 3;
+                if (c >= 3 && !mbar_wait_bounded(&raw_empty[slot], ((c / 3) - 1) & 1)) {
                     atomicExch(p.err, ERR_WAIT_EMPTY);
                     break;
                 }
                 if (*reinterpret_cast<volatile int*>(&s_abort)) break;
                 const int block = p.block_table[size_t(b) * p.table_stride + j];
                 const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
-                uint8_t* dst = raw + st * PF_RAW;
-                mbar_expect_tx(&raw_full[st], tx);
-                tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &raw_full[st]);
-                bulk_load_1d(dst + 2 * CODE_BYTES, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB,
-                             &raw_full[st]);
+                mbar_expect_tx(&raw_full[slot], CODE_BYTES + (side == 0 ? 2 * BLK * SB : 0));
+                tma_load_2d(raw + slot * CODE_BYTES, &tmap, 0, int(page * p.rows_per_page) + side * BLK, &raw_full[slot]);
+                if (side == 0)
+                    bulk_load_1d(scl + (j & 1) * 1024, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB,
+                                 &raw_full[slot]);
             }
         }
     } else if (warp == 13) {
-        // ---- MMA issuer
+        // ---- MMA issuer. Per page: S0(j), PV1(j-1), S1(j), PV0(j): while the ReLU² warps of one tile work on its
+        // scores, the tensor pipe runs the other tile's products. All MMAs of one thread execute in issue order,
+        // which is what lets P overwrite S and S(j+1) overwrite P(j).
         if (lane == 0) {
             const uint32_t qa = smem_u32(Qs);
             bool ok = true;
-            for (int j = 0; j <= n && ok; j++) {
-                if (j < n) {
-                    const int sb = j & 1, ck = 2 * j, bk = ck % 3;
-                    ok = mbar_wait_bounded(&kv_ready[bk], (ck / 3) & 1);
-                    if (ok && j >= 2) ok = mbar_wait_bounded(&sm_done[sb], ((j >> 1) - 1) & 1);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t ka = smem_u32(kvb + bk * PF_TILE16);
+            auto issue_s = [&](int x, int j) {
+                const uint32_t ka = smem_u32(kvb + ((2 * j) % 3) * PF_TILE16);
 #pragma unroll
-                    for (int ks = 0; ks < 8; ks++) {
-                        const uint32_t koff = (ks >> 2) * (BLK * 128) + (ks & 3) * 32;
-                        umma_ss(tS + 128 * sb, umma_desc(qa + koff, 16, 1024), umma_desc(ka + koff, 16, 1024), PF_IDESC_QK, ks > 0);
-                    }
-                    tc_commit(&s_full[sb]);
-                    tc_commit(&kv_free[bk]);
+                for (int ks = 0; ks < 8; ks++) {
+                    const uint32_t koff = (ks >> 2) * (BLK * 128) + (ks & 3) * 32;
+                    umma_ss(tmem + 128 * x, umma_desc(qa + x * PF_TILE16 + koff, 16, 1024), umma_desc(ka + koff, 16, 1024), PF_IDESC_QK, ks > 0);
                 }
-                if (j >= 1) {
-                    const int i = j - 1, pb = i & 1, cv = 2 * i + 1, bv = cv % 3;
-                    ok = mbar_wait_bounded(&p_ready[pb], (i >> 1) & 1) && mbar_wait_bounded(&kv_ready[bv], (cv / 3) & 1);
+                tc_commit(&s_full[x]);
+            };
+            auto issue_pv = [&](int x, int j) {
+                const uint32_t va = smem_u32(kvb + ((2 * j + 1) % 3) * PF_TILE16);
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++)
+                    umma_ts(tmem + 256 + 128 * x, tmem + 128 * x + 8 * ks, umma_desc(va + ks * 2048, BLK * 128, 1024), PF_IDESC_PV,
+                            (j > 0) | (ks > 0));
+            };
+            for (int j = 0; j <= n && ok; j++) {
+                const bool a0 = j < npg[0], a1 = j < npg[1];              // tiles active on page j
+                const bool b1 = j >= 1 && j - 1 < npg[1];                 // tile 1 had page j - 1
+                if (a0 || a1) {
+                    ok = mbar_wait_bounded(&kv_ready[(2 * j) % 3], ((2 * j) / 3) & 1);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t va = smem_u32(kvb + bv * PF_TILE16);
-#pragma unroll
-                    for (int ks = 0; ks < 8; ks++)
-                        umma_ts(tO, tP + 64 * pb + 8 * ks, umma_desc(va + ks * 2048, BLK * 128, 1024), PF_IDESC_PV, (i > 0) | (ks > 0));
-                    tc_commit(&p_free[pb]);
-                    tc_commit(&kv_free[bv]);
+                }
+                if (a0) issue_s(0, j);
+                if (b1) {
+                    const int cv = 2 * (j - 1) + 1;
+                    ok = mbar_wait_bounded(&p_ready[1], (j - 1) & 1) && mbar_wait_bounded(&kv_ready[cv % 3], (cv / 3) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(1, j - 1);
+                }
+                if (j >= 1) tc_commit(&kv_free[(2 * (j - 1) + 1) % 3]);   // V(j-1): both tiles' P V are issued
+                if (a1) issue_s(1, j);
+                if (a0 || a1) tc_commit(&kv_free[(2 * j) % 3]);           // K(j)
+                if (a0) {
+                    const int cv = 2 * j + 1;
+                    ok = mbar_wait_bounded(&p_ready[0], j & 1) && mbar_wait_bounded(&kv_ready[cv % 3], (cv / 3) & 1);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(0, j);
                 }
             }
             if (!ok) {
@@ -310,88 +329,77 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     } else if (warp >= 8) {
         // ---- converters
         const int ctid = tid - 256;
-        for (int j = 0; j < n; j++) {
-            const int st = j & 1, sb = j & 1;
-            bool ok = mbar_wait_bounded(&raw_full[st], (j >> 1) & 1);
-            const uint8_t* page = raw + st * PF_RAW;
-            for (int side = 0; side < 2 && ok; side++) {
-                const int c = 2 * j + side, buf = c % 3;
-                if (c >= 3) ok = mbar_wait_bounded(&kv_free[buf], ((c / 3) - 1) & 1);
-                if (!ok) break;
-                convert_side<SB>(page + side * CODE_BYTES, kvb + buf * PF_TILE16, ctid, page + 2 * CODE_BYTES + side * BLK * SB,
-                                 side == 0 ? rsqrtf(float(HD)) : 1.0f);
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&kv_ready[buf]);
-            }
-            if (!ok) {
-                atomicExch(p.err, ERR_WAIT_FULL);
-                *reinterpret_cast<volatile int*>(&s_abort) = 1;
-                break;
-            }
+        bool ok = true;
+        for (int c = 0; c < 2 * n && ok; c++) {
+            const int j = c >> 1, side = c & 1, slot = c % 3;
+            ok = mbar_wait_bounded(&raw_full[slot], (c / 3) & 1);
+            if (ok && c >= 3) ok = mbar_wait_bounded(&kv_free[slot], ((c / 3) - 1) & 1);
+            if (!ok) break;
+            convert_side<SB>(raw + slot * CODE_BYTES, kvb + slot * PF_TILE16, ctid, scl + (j & 1) * 1024 + side * BLK * SB,
+                             side == 0 ? rsqrtf(float(HD)) : 1.0f);
+            fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&raw_empty[st]);
+            if (lane == 0) {
+                mbar_arrive(&kv_ready[slot]);
+                mbar_arrive(&raw_empty[slot]);
+            }
+        }
+        if (!ok) {
+            atomicExch(p.err, ERR_WAIT_FULL);
+            *reinterpret_cast<volatile int*>(&s_abort) = 1;
         }
     } else {
-        // ---- ReLU² warps: thread = (query row, half of the page's keys)
-        const int r = tid & 127, hf = tid >> 7;         // TMEM lane, key half
+        // ---- ReLU² warps: warpgroup x (warps 4x .. 4x+3) owns tile x, one query row a thread
+        const int x = warp >> 2, r = tid & 127;
         const uint32_t lane_sel = uint32_t((warp & 3) * 32) << 16;
-        const int pos_r = p0 + t0 + r;                  // this row's absolute position
+        const uint32_t tS = tmem + 128 * x, tO = tmem + 256 + 128 * x;
+        const int pos_r = p0 + t0[x] + r;               // this row's absolute position
+        const int nx = npg[x];
         float rowsum = 0.0f;
         bool ok = true;
-        for (int j = 0; j < n; j++) {
-            const int sb = j & 1;
-            ok = mbar_wait_bounded(&s_full[sb], (j >> 1) & 1);
-            if (ok && j >= 2) ok = mbar_wait_bounded(&p_free[sb], ((j >> 1) - 1) & 1);
+        for (int j = 0; j < nx; j++) {
+            ok = mbar_wait_bounded(&s_full[x], j & 1);
             if (!ok) break;
             tc_fence_after();
-            const bool diag = j * BLK + BLK - 1 > p0 + t0;      // some (row, key) of this page is masked
-            const int key0 = j * BLK + 64 * hf;
+            const bool diag = j * BLK + BLK - 1 > p0 + t0[x];   // some (row, key) of this page is masked
 #pragma unroll
-            for (int cc = 0; cc < 2; cc++) {
+            for (int cc = 0; cc < 4; cc++) {
                 uint32_t s[32];
-                tmem_ld32(tS + 128 * sb + 64 * hf + 32 * cc + lane_sel, s);
+                tmem_ld32(tS + 32 * cc + lane_sel, s);
                 uint32_t pk[16];
 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
                     const float m0 = fmaxf(__uint_as_float(s[e]), 0.0f), m1 = fmaxf(__uint_as_float(s[e + 1]), 0.0f);
                     float w0 = m0 * m0, w1 = m1 * m1;
                     if (diag) {
-                        const int kb = key0 + 32 * cc + e;
+                        const int kb = j * BLK + 32 * cc + e;
                         if (kb > pos_r) w0 = 0.0f;
                         if (kb + 1 > pos_r) w1 = 0.0f;
                     }
                     rowsum += w0 + w1;
                     pk[e >> 1] = pack_h2(w0, w1);
                 }
-                tmem_st16(tP + 64 * sb + 32 * hf + 16 * cc + lane_sel, pk);
+                // P (fp16) goes over the S columns already consumed: chunk cc's 16 columns lie inside [0, 32 cc + 32)
+                tmem_st16(tS + 16 * cc + lane_sel, pk);
             }
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&p_ready[sb]);
-                mbar_arrive(&sm_done[sb]);
-            }
+            if (lane == 0) mbar_arrive(&p_ready[x]);
         }
         if (ok) ok = mbar_wait_bounded(o_done, 0);
         if (!ok) {
             atomicExch(p.err, ERR_WAIT_FULL);
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
-        }
-        // the two halves' row sums meet in shared memory (named barrier of the 8 ReLU² warps), added in a fixed order
-        s_rowsum[hf][r] = rowsum;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        if (ok) {
+        } else if (nx > 0) {
             tc_fence_after();
-            const float inv = 1.0f / (sqrtf(float(HD)) + (s_rowsum[0][r] + s_rowsum[1][r]));
-            uint16_t* orow = static_cast<uint16_t*>(p.o) + size_t(b) * p.o_seq_stride + size_t(t0 + r) * p.o_token_stride +
-                             size_t(h) * HD + 64 * hf;
+            const float inv = 1.0f / (sqrtf(float(HD)) + rowsum);
+            uint16_t* orow = static_cast<uint16_t*>(p.o) + size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
 #pragma unroll 1
-            for (int cc = 0; cc < 2; cc++) {
+            for (int cc = 0; cc < 4; cc++) {
                 uint32_t acc[32];
-                tmem_ld32(tO + 64 * hf + 32 * cc + lane_sel, acc);
-                if (r < rows) {
+                tmem_ld32(tO + 32 * cc + lane_sel, acc);
+                if (r < rows[x]) {
                     uint32_t outw[16];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
@@ -430,8 +438,8 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, const
         EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PF_SMEM)));
         configured[ctx->device & 63] = true;
     }
-    dim3 grid((p.n_tokens + BLK - 1) / BLK, ctx->cfg.n_q_heads, batch);
-    kern<<<grid, PF_THREADS, PF_SMEM, s>>>(pool->tmap_codes, p);
+    dim3 grid((p.n_tokens + 2 * BLK - 1) / (2 * BLK), ctx->cfg.n_q_heads, batch);
+    kern<<<grid, PF_THREADS, PF_SMEM, s>>>(pool->tmap_half, p);
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;
 }
