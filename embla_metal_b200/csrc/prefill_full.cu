@@ -367,17 +367,31 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                 uint32_t s[32];
                 tmem_ld32(tS + 32 * cc + lane_sel, s);
                 uint32_t pk[16];
+                if (diag) {
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    const float m0 = fmaxf(__uint_as_float(s[e]), 0.0f), m1 = fmaxf(__uint_as_float(s[e + 1]), 0.0f);
-                    float w0 = m0 * m0, w1 = m1 * m1;
-                    if (diag) {
+                    for (int e = 0; e < 32; e += 2) {
+                        const float m0 = fmaxf(__uint_as_float(s[e]), 0.0f), m1 = fmaxf(__uint_as_float(s[e + 1]), 0.0f);
+                        float w0 = m0 * m0, w1 = m1 * m1;
                         const int kb = j * BLK + 32 * cc + e;
                         if (kb > pos_r) w0 = 0.0f;
                         if (kb + 1 > pos_r) w1 = 0.0f;
+                        rowsum += w0 + w1;
+                        pk[e >> 1] = pack_h2(w0, w1);
                     }
-                    rowsum += w0 + w1;
-                    pk[e >> 1] = pack_h2(w0, w1);
+                } else {
+                    // unmasked pages (all but the last one or two of a tile): ReLU² on packed fp16 pairs. The 16
+                    // products a half accumulates stay far inside fp16; their sum joins the fp32 row sum once a chunk.
+                    const __half2 zero = __float2half2_rn(0.0f);
+                    __half2 part = zero;
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        __half2 hm = __hmax2(__floats2half2_rn(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), zero);
+                        hm = __hmul2(hm, hm);
+                        part = __hadd2(part, hm);
+                        pk[e >> 1] = *reinterpret_cast<uint32_t*>(&hm);
+                    }
+                    const float2 pf = __half22float2(part);
+                    rowsum += pf.x + pf.y;
                 }
                 // P (fp16) goes over the S columns already consumed: chunk cc's 16 columns lie inside [0, 32 cc + 32)
                 tmem_st16(tS + 16 * cc + lane_sel, pk);
