@@ -43,6 +43,9 @@ EmblaStatus embla_stack_create(EmblaAttn* ctx, const EmblaLayerDesc* layers, int
             if (L.g1_dev)
                 EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_stack_create: layer %d: a sparse layer that scores its own keys takes "
                                               "its queries prenormed", i);
+        } else if (L.kind == EMBLA_LAYER_SPARSE_SHARED) {
+            if (!full_pool || full_pool->kv_dtype != EMBLA_KV_INT8 || L.slot < 0 || L.slot >= full_pool->n_layers)
+                EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_create: layer %d (sparse, shared cache) needs slot %d of an int8 pool", i, L.slot);
         } else if (L.kind == EMBLA_LAYER_SLIDING) {
             if (!rings || L.slot < 0 || L.slot >= n_rings)
                 EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_create: layer %d (sliding) needs ring %d of %d", i, L.slot, n_rings);
@@ -64,7 +67,9 @@ EmblaStatus embla_stack_create(EmblaAttn* ctx, const EmblaLayerDesc* layers, int
     st->scores_ld = (ctx->cfg.max_context + BLK - 1) / BLK * BLK;
     const size_t pairs = size_t(ctx->cfg.max_batch) * ctx->cfg.n_kv_heads;
     cudaError_t e = cudaSuccess;
-    if (sparse_pool) {
+    bool need_scores = sparse_pool != nullptr;
+    for (int i = 0; i < n_layers; i++) need_scores |= layers[i].kind == EMBLA_LAYER_SPARSE_SHARED || layers[i].emit_scores != 0;
+    if (need_scores) {
         e = cudaMalloc(&st->scores, pairs * st->scores_ld * sizeof(float));
         if (e == cudaSuccess) e = cudaMalloc(&st->idx, pairs * (EMBLA_TOPK + EMBLA_RECENT) * sizeof(uint32_t));
     }
@@ -171,8 +176,23 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
             if (!view.block_table_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_step: no block table for the full layers");
             EMBLA_STEP(EMBLA_ENTRY_APPEND, embla_kv_append(ctx, st->full_pool, &view, step->pos_dev, 1, kp, vp, step->qkv_stride,
                                                            step->qkv_stride, L.norm_k, stream));
+            // past topk + recent keys, a full layer followed by sparse layers that share its cache also scores
+            // every key, and the selection runs right after it (Engine.swift:796-797, 819-827)
+            const bool scoring = L.emit_scores != 0 && max_len > EMBLA_TOPK + EMBLA_RECENT;
             EMBLA_STEP(EMBLA_ENTRY_FULL_DECODE,
-                       embla_attn_full_decode(ctx, st->full_pool, &view, &q, op, step->o_stride, nullptr, 0, stream));
+                       embla_attn_full_decode(ctx, st->full_pool, &view, &q, op, step->o_stride, scoring ? st->scores : nullptr,
+                                              st->scores_ld, stream));
+            if (scoring)
+                EMBLA_STEP(EMBLA_ENTRY_SELECT, embla_select_keys(ctx, st->scores, st->scores_ld, step->seq_lens_dev, B, max_len,
+                                                                 st->idx, stream));
+        } else if (L.kind == EMBLA_LAYER_SPARSE_SHARED) {
+            // a sparse layer over the preceding full layer's int8 cache (Engine.swift:461-462): no KV of its own
+            view.block_table_dev = step->full_table_dev;
+            view.table_stride = step->full_table_stride;
+            const bool selecting = max_len > EMBLA_TOPK + EMBLA_RECENT;
+            EMBLA_STEP(EMBLA_ENTRY_SPARSE_DECODE, embla_attn_sparse_decode_int8(ctx, st->full_pool, &view, &q,
+                                                                                selecting ? st->idx : nullptr, op,
+                                                                                step->o_stride, stream));
         } else {
             view.block_table_dev = step->sparse_table_dev;
             view.table_stride = step->sparse_table_stride;

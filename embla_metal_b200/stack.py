@@ -11,13 +11,13 @@ import torch
 
 from . import attn
 
-SLIDING, FULL, SPARSE = 0, 1, 2
+SLIDING, FULL, SPARSE, SPARSE_SHARED = 0, 1, 2, 3
 ENTRY = {"append": 0, "full_decode": 1, "sliding_write": 2, "sliding_decode": 3, "score": 4, "select": 5,
          "sparse_decode": 6}
 
 
 class LayerDesc(C.Structure):
-    _fields_ = [("kind", C.c_int32), ("slot", C.c_int32), ("norm_k", C.c_int32), ("pad", C.c_int32),
+    _fields_ = [("kind", C.c_int32), ("slot", C.c_int32), ("norm_k", C.c_int32), ("emit_scores", C.c_int32),
                 ("g1_dev", C.c_void_p), ("g2_dev", C.c_void_p), ("kgain_dev", C.c_void_p)]
 
 
@@ -54,7 +54,14 @@ class DecodeStack:
         descs = (LayerDesc * len(self.kinds))()
         slots = {SLIDING: 0, FULL: 0, SPARSE: 0}
         for i, k in enumerate(self.kinds):
-            descs[i] = LayerDesc(k, slots[k], int(norm_k), 0, None, None, None)
+            if k == SPARSE_SHARED:
+                # reads the cache of the closest preceding full layer (Embla.blockFull, Engine.swift:22)
+                if slots[FULL] == 0:
+                    raise ValueError("a sparse layer that shares a cache needs a full layer before it")
+                descs[i] = LayerDesc(k, slots[FULL] - 1, 0, 0, None, None, None)
+                continue
+            shared_next = k == FULL and i + 1 < len(self.kinds) and self.kinds[i + 1] == SPARSE_SHARED
+            descs[i] = LayerDesc(k, slots[k], int(norm_k), int(shared_next), None, None, None)
             slots[k] += 1
         ring_descs = (attn.RingDesc * max(1, n_sliding))()
         for i, r in enumerate(self.rings):
@@ -149,5 +156,8 @@ class DecodeStack:
     def launches_per_step(self):
         """Kernels of this library one step launches."""
         selecting = self.max_seq_len > attn.TOPK + attn.RECENT
-        per = {SLIDING: 2, FULL: 2, SPARSE: 4 if selecting else 2}
-        return sum(per[k] for k in self.kinds)
+        per = {SLIDING: 2, FULL: 2, SPARSE: 4 if selecting else 2, SPARSE_SHARED: 1}
+        n = sum(per[k] for k in self.kinds)
+        if selecting:   # a full layer followed by a shared-cache sparse layer also selects
+            n += sum(1 for i, k in enumerate(self.kinds[:-1]) if k == FULL and self.kinds[i + 1] == SPARSE_SHARED)
+        return n

@@ -188,6 +188,13 @@ EmblaStatus embla_attn_sparse_decode(EmblaAttn* ctx, const EmblaKVPool* pool, co
                                      const EmblaQuery* q, const uint32_t* idx_dev, void* o_dev, int64_t o_stride,
                                      void* stream);
 
+/* The same over the preceding full layer's int8 cache, as the reference's sparse layers run
+ * (Engine.swift:461-462; attn_sparse8 / attn_sparse_short, attention.metal:448-584, 593-645): the rows come
+ * from embla_select_keys applied to the scores embla_attn_full_decode wrote for that full layer. */
+EmblaStatus embla_attn_sparse_decode_int8(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                          const EmblaQuery* q, const uint32_t* idx_dev, void* o_dev, int64_t o_stride,
+                                          void* stream);
+
 /* ---- sliding layers ------------------------------------------------------------------------------------ */
 /* The sliding layers' rings (Engine.swift:269-276; RING = 4096, attention.metal:4-6): per sequence
  * [n_kv_heads][ring][128] keys and the same for values, in the activation dtype, owned by the caller. */
@@ -241,7 +248,10 @@ EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, con
 /* The attention half of Engine.encodeStep's per-layer loop (Engine.swift:933-991 calling
  * encodeAttention, :743-832) as one call: for every layer, the KV write of the current token and the
  * layer's attention, enqueued on one stream. */
-enum { EMBLA_LAYER_SLIDING = 0, EMBLA_LAYER_FULL = 1, EMBLA_LAYER_SPARSE = 2 };   /* Embla.Kind, Engine.swift:14 */
+enum {   /* Embla.Kind, Engine.swift:14; a sparse layer either owns 16-bit keys (SPARSE) or, as in the reference,
+            reads the preceding full layer's int8 cache (SPARSE_SHARED, Engine.swift:461-462) */
+    EMBLA_LAYER_SLIDING = 0, EMBLA_LAYER_FULL = 1, EMBLA_LAYER_SPARSE = 2, EMBLA_LAYER_SPARSE_SHARED = 3
+};
 enum {   /* entry points a step launches, for embla_stack_set_probe */
     EMBLA_ENTRY_APPEND = 0, EMBLA_ENTRY_FULL_DECODE = 1, EMBLA_ENTRY_SLIDING_WRITE = 2, EMBLA_ENTRY_SLIDING_DECODE = 3,
     EMBLA_ENTRY_SCORE = 4, EMBLA_ENTRY_SELECT = 5, EMBLA_ENTRY_SPARSE_DECODE = 6
@@ -249,9 +259,11 @@ enum {   /* entry points a step launches, for embla_stack_set_probe */
 
 typedef struct {
     int32_t     kind;        /* EMBLA_LAYER_* */
-    int32_t     slot;        /* full: layer of the int8 pool; sparse: layer of the 16-bit pool; sliding: ring index */
+    int32_t     slot;        /* full: layer of the int8 pool; sparse: layer of the 16-bit pool; sparse shared: the int8
+                                pool layer of the full layer whose cache it reads; sliding: ring index */
     int32_t     norm_k;      /* full/sparse: RMS-norm k before it is stored (the reference does) */
-    int32_t     pad;
+    int32_t     emit_scores; /* full: 1 = past 1152 keys also write key scores and select rows for the sparse layers
+                                that follow (Embla.selects, Engine.swift:24-26, 797) */
     const void* g1_dev;      /* query gains; NULL = queries arrive prenormed (sparse layers: must be NULL) */
     const void* g2_dev;
     const void* kgain_dev;   /* sliding: key gain; NULL = keys arrive prenormed */
