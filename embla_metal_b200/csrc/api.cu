@@ -55,6 +55,9 @@ EmblaStatus embla_attn_create(const EmblaAttnConfig* cfg, EmblaAttn** out) {
     ctx->partials = nullptr;
     ctx->counters = nullptr;
     ctx->err_dev = nullptr;
+    ctx->prefill_scratch = nullptr;
+    ctx->prefill_scratch_bytes = 0;
+    ctx->prefill_counter_units = -1;
     cudaError_t e = cudaGetDevice(&ctx->device);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, ctx->device);
     if (e != cudaSuccess) {
@@ -88,6 +91,7 @@ void embla_attn_destroy(EmblaAttn* ctx) {
     cudaFree(ctx->partials);
     cudaFree(ctx->counters);
     cudaFree(ctx->err_dev);
+    cudaFree(ctx->prefill_scratch);
     delete ctx;
 }
 

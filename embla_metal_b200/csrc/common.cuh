@@ -63,6 +63,9 @@ struct EmblaAttn {
     int* counters;          // one arrival counter per (sequence, kv head); zero between launches
     int* err_dev;           // device error word
     int partial_slots;      // (sequence, kv head, key range) partials the scratch holds
+    uint8_t* prefill_scratch;      // split-KV partials of the prefill kernel, sized on first need
+    size_t prefill_scratch_bytes;
+    int prefill_counter_units;     // which (units, splits) layout its counters were cleared for
 };
 
 namespace embla {

@@ -40,9 +40,11 @@ struct PrefillParams {
     const void* g2;
     void* o;
     int* err;
+    float* partials;      // split-KV: [unit][split][tile][128 rows][128 + 1] fp32 (unnormalised O, row sum)
+    int* counters;        // [unit] arrivals
     int64_t q_token_stride, q_seq_stride, o_token_stride, o_seq_stride;
     size_t page_bytes;
-    int table_stride, layer, n_layers, n_kv_heads, G, scale_bytes, rows_per_page, n_tokens, prenormed;
+    int table_stride, layer, n_layers, n_kv_heads, G, scale_bytes, rows_per_page, n_tokens, prenormed, nsplit;
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------------------
@@ -166,17 +168,22 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y, b = blockIdx.z;
+    const int pair_ix = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit;
     const int kvh = h / p.G;
     const int p0 = p.pos0[b];
     // two query tiles of 128 consecutive tokens each share every converted page
     int t0[2], rows[2], npg[2];
 #pragma unroll
     for (int x = 0; x < 2; x++) {
-        t0[x] = (2 * blockIdx.x + x) * BLK;
+        t0[x] = (2 * pair_ix + x) * BLK;
         rows[x] = max(0, min(BLK, p.n_tokens - t0[x]));
         npg[x] = rows[x] > 0 ? (p0 + t0[x] + rows[x] - 1) / BLK + 1 : 0;
     }
-    const int n = max(npg[0], npg[1]);
+    // this CTA's share of the pages (split-KV: ReLU² partial sums of page ranges just add)
+    const int n_all = max(npg[0], npg[1]);
+    const int pps = (n_all + p.nsplit - 1) / p.nsplit;
+    const int jb = split * pps, je = min(n_all, jb + pps);
+    const int n = max(0, je - jb);
 
     if (tid == 0) {
         for (int i = 0; i < 3; i++) {
@@ -255,7 +262,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         // ---- TMA producer: conversion c = 2 j + side takes ring slot c % 3; page j's scales go to scl[j & 1]
         if (lane == 0) {
             for (int c = 0; c < 2 * n; c++) {
-                const int j = c >> 1, side = c & 1, slot = c % 3;
+                const int j = jb + (c >> 1), side = c & 1, slot = c % 3;
                 if (c >= 3 && !mbar_wait_bounded(&raw_empty[slot], ((c / 3) - 1) & 1)) {
                     atomicExch(p.err, ERR_WAIT_EMPTY);
                     break;
@@ -266,7 +273,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                 mbar_expect_tx(&raw_full[slot], CODE_BYTES + (side == 0 ? 2 * BLK * SB : 0));
                 tma_load_2d(raw + slot * CODE_BYTES, &tmap, 0, int(page * p.rows_per_page) + side * BLK, &raw_full[slot]);
                 if (side == 0)
-                    bulk_load_1d(scl + (j & 1) * 1024, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB,
+                    bulk_load_1d(scl + ((c >> 1) & 1) * 1024, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB,
                                  &raw_full[slot]);
             }
         }
@@ -277,8 +284,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         if (lane == 0) {
             const uint32_t qa = smem_u32(Qs);
             bool ok = true;
-            auto issue_s = [&](int x, int j) {
-                const uint32_t ka = smem_u32(kvb + ((2 * j) % 3) * PF_TILE16);
+            // i = page index inside this CTA's range (buffers and barrier phases count from 0), jb + i = the page
+            auto issue_s = [&](int x, int i) {
+                const uint32_t ka = smem_u32(kvb + ((2 * i) % 3) * PF_TILE16);
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
                     const uint32_t koff = (ks >> 2) * (BLK * 128) + (ks & 3) * 32;
@@ -286,38 +294,38 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                 }
                 tc_commit(&s_full[x]);
             };
-            auto issue_pv = [&](int x, int j) {
-                const uint32_t va = smem_u32(kvb + ((2 * j + 1) % 3) * PF_TILE16);
+            auto issue_pv = [&](int x, int i) {
+                const uint32_t va = smem_u32(kvb + ((2 * i + 1) % 3) * PF_TILE16);
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++)
                     umma_ts(tmem + 256 + 128 * x, tmem + 128 * x + 8 * ks, umma_desc(va + ks * 2048, BLK * 128, 1024), PF_IDESC_PV,
-                            (j > 0) | (ks > 0));
+                            (i > 0) | (ks > 0));
             };
-            for (int j = 0; j <= n && ok; j++) {
-                const bool a0 = j < npg[0], a1 = j < npg[1];              // tiles active on page j
-                const bool b1 = j >= 1 && j - 1 < npg[1];                 // tile 1 had page j - 1
+            for (int i = 0; i <= n && ok; i++) {
+                const bool a0 = i < n && jb + i < npg[0], a1 = i < n && jb + i < npg[1];   // tiles active on this page
+                const bool b1 = i >= 1 && jb + i - 1 < npg[1];                              // tile 1 had the page before
                 if (a0 || a1) {
-                    ok = mbar_wait_bounded(&kv_ready[(2 * j) % 3], ((2 * j) / 3) & 1);
+                    ok = mbar_wait_bounded(&kv_ready[(2 * i) % 3], ((2 * i) / 3) & 1);
                     if (!ok) break;
                     tc_fence_after();
                 }
-                if (a0) issue_s(0, j);
+                if (a0) issue_s(0, i);
                 if (b1) {
-                    const int cv = 2 * (j - 1) + 1;
-                    ok = mbar_wait_bounded(&p_ready[1], (j - 1) & 1) && mbar_wait_bounded(&kv_ready[cv % 3], (cv / 3) & 1);
+                    const int cv = 2 * (i - 1) + 1;
+                    ok = mbar_wait_bounded(&p_ready[1], (i - 1) & 1) && mbar_wait_bounded(&kv_ready[cv % 3], (cv / 3) & 1);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_pv(1, j - 1);
+                    issue_pv(1, i - 1);
                 }
-                if (j >= 1) tc_commit(&kv_free[(2 * (j - 1) + 1) % 3]);   // V(j-1): both tiles' P V are issued
-                if (a1) issue_s(1, j);
-                if (a0 || a1) tc_commit(&kv_free[(2 * j) % 3]);           // K(j)
+                if (i >= 1) tc_commit(&kv_free[(2 * (i - 1) + 1) % 3]);   // V of the page before: both tiles' P V are issued
+                if (a1) issue_s(1, i);
+                if (a0 || a1) tc_commit(&kv_free[(2 * i) % 3]);           // K of this page
                 if (a0) {
-                    const int cv = 2 * j + 1;
-                    ok = mbar_wait_bounded(&p_ready[0], j & 1) && mbar_wait_bounded(&kv_ready[cv % 3], (cv / 3) & 1);
+                    const int cv = 2 * i + 1;
+                    ok = mbar_wait_bounded(&p_ready[0], i & 1) && mbar_wait_bounded(&kv_ready[cv % 3], (cv / 3) & 1);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_pv(0, j);
+                    issue_pv(0, i);
                 }
             }
             if (!ok) {
@@ -331,11 +339,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         const int ctid = tid - 256;
         bool ok = true;
         for (int c = 0; c < 2 * n && ok; c++) {
-            const int j = c >> 1, side = c & 1, slot = c % 3;
+            const int side = c & 1, slot = c % 3;
             ok = mbar_wait_bounded(&raw_full[slot], (c / 3) & 1);
             if (ok && c >= 3) ok = mbar_wait_bounded(&kv_free[slot], ((c / 3) - 1) & 1);
             if (!ok) break;
-            convert_side<SB>(raw + slot * CODE_BYTES, kvb + slot * PF_TILE16, ctid, scl + (j & 1) * 1024 + side * BLK * SB,
+            convert_side<SB>(raw + slot * CODE_BYTES, kvb + slot * PF_TILE16, ctid, scl + ((c >> 1) & 1) * 1024 + side * BLK * SB,
                              side == 0 ? rsqrtf(float(HD)) : 1.0f);
             fence_proxy_async();
             __syncwarp();
@@ -354,11 +362,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         const uint32_t lane_sel = uint32_t((warp & 3) * 32) << 16;
         const uint32_t tS = tmem + 128 * x, tO = tmem + 256 + 128 * x;
         const int pos_r = p0 + t0[x] + r;               // this row's absolute position
-        const int nx = npg[x];
+        const int nx = max(0, min(je, npg[x]) - jb);     // pages of this CTA's range that the tile sees
         float rowsum = 0.0f;
         bool ok = true;
-        for (int j = 0; j < nx; j++) {
-            ok = mbar_wait_bounded(&s_full[x], j & 1);
+        for (int i = 0; i < nx; i++) {
+            const int j = jb + i;
+            ok = mbar_wait_bounded(&s_full[x], i & 1);
             if (!ok) break;
             tc_fence_after();
             const bool diag = j * BLK + BLK - 1 > p0 + t0[x];   // some (row, key) of this page is masked
@@ -405,6 +414,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         if (!ok) {
             atomicExch(p.err, ERR_WAIT_FULL);
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
+        } else if (p.nsplit > 1) {
+            // unnormalised O and the row sum of this page range into the scratch (zeros if the tile saw no page here)
+            tc_fence_after();
+            const int unit = (b * gridDim.y + h) * (gridDim.x / p.nsplit) + pair_ix;
+            float* prow = p.partials + ((size_t(unit) * p.nsplit + split) * 2 + x) * (BLK * (HD + 1)) + size_t(r) * (HD + 1);
+#pragma unroll 1
+            for (int cc = 0; cc < 4; cc++) {
+                uint32_t acc[32];
+                if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, acc);
+#pragma unroll
+                for (int e = 0; e < 32; e++) prow[32 * cc + e] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
+            }
+            prow[HD] = rowsum;
         } else if (nx > 0) {
             tc_fence_after();
             const float inv = 1.0f / (sqrtf(float(HD)) + rowsum);
@@ -432,6 +454,40 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             }
         }
     }
+    if (p.nsplit > 1) {
+        // the last CTA of the unit to arrive adds the page ranges in order and writes the rows (common.metal:88-99)
+        __shared__ int s_last;
+        const int unit = (b * gridDim.y + h) * (gridDim.x / p.nsplit) + pair_ix;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int prev = atomicAdd(&p.counters[unit], 1);
+            s_last = prev == p.nsplit - 1;
+            if (s_last) p.counters[unit] = 0;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            // one row a warp at a time, lanes across the head dims: coalesced, and the splits' loads are independent
+            const size_t sstride = size_t(2) * BLK * (HD + 1);
+            for (int row = warp; row < 2 * BLK; row += PF_THREADS / 32) {
+                const int x = row >> 7, r = row & 127;
+                if (r >= rows[x]) continue;
+                const float* base = p.partials + (size_t(unit) * p.nsplit * 2 + x) * (BLK * (HD + 1)) + size_t(r) * (HD + 1);
+                float den = sqrtf(float(HD)), acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                for (int sp = 0; sp < p.nsplit; sp++) {
+                    const float* q2 = base + sp * sstride;
+                    den += __ldcg(q2 + HD);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) acc[i] += __ldcg(q2 + lane + 32 * i);
+                }
+                const float inv = 1.0f / den;
+                const size_t off = size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
+#pragma unroll
+                for (int i = 0; i < 4; i++) Act<DT>::store(p.o, off + lane + 32 * i, acc[i] * inv);
+            }
+        }
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 13) {
@@ -445,14 +501,42 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
 using namespace embla;
 
 template <int DT, int SB>
-static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, const PrefillParams& p, int batch, cudaStream_t s) {
+static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, PrefillParams& p, int batch, int max_pages, cudaStream_t s) {
     auto kern = full_prefill_kernel<DT, SB>;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
         EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PF_SMEM)));
         configured[ctx->device & 63] = true;
     }
-    dim3 grid((p.n_tokens + 2 * BLK - 1) / (2 * BLK), ctx->cfg.n_q_heads, batch);
+    // A unit = 256 tokens of one head. With fewer units than SMs (short chunks, few heads on this GPU) the pages of
+    // a unit are split over several CTAs whose partial sums the last one adds (ReLU² partials are additive).
+    const int pairs = (p.n_tokens + 2 * BLK - 1) / (2 * BLK);
+    const int units = pairs * ctx->cfg.n_q_heads * batch;
+    int nsplit = ctx->sm_count / units;
+    nsplit = nsplit < 1 ? 1 : nsplit > 16 ? 16 : nsplit;
+    while (nsplit > 1 && max_pages / nsplit < 8) nsplit--;
+    p.nsplit = nsplit;
+    p.partials = nullptr;
+    p.counters = nullptr;
+    if (nsplit > 1) {
+        const size_t need = size_t(units) * nsplit * 2 * BLK * (HD + 1) * sizeof(float) + size_t(units) * sizeof(int);
+        if (need > ctx->prefill_scratch_bytes) {
+            EMBLA_CUDA_TRY(cudaStreamSynchronize(s));
+            cudaFree(ctx->prefill_scratch);
+            ctx->prefill_scratch = nullptr;
+            ctx->prefill_scratch_bytes = 0;
+            EMBLA_CUDA_TRY(cudaMalloc(&ctx->prefill_scratch, need));
+            ctx->prefill_scratch_bytes = need;
+        }
+        // counters sit after the partials; they are left at zero by every launch, cleared when (re)sized
+        p.partials = reinterpret_cast<float*>(ctx->prefill_scratch);
+        p.counters = reinterpret_cast<int*>(ctx->prefill_scratch + (need - size_t(units) * sizeof(int)));
+        if (ctx->prefill_counter_units != units * 1000 + nsplit) {
+            EMBLA_CUDA_TRY(cudaMemsetAsync(p.counters, 0, size_t(units) * sizeof(int), s));
+            ctx->prefill_counter_units = units * 1000 + nsplit;
+        }
+    }
+    dim3 grid(pairs * nsplit, ctx->cfg.n_q_heads, batch);
     kern<<<grid, PF_THREADS, PF_SMEM, s>>>(pool->tmap_half, p);
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;
@@ -498,6 +582,8 @@ extern "C" EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool
     p.prenormed = q->prenormed;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16, s4 = pool->scale_bytes == 4;
-    if (bf) return s4 ? launch_prefill<EMBLA_BF16, 4>(ctx, pool, p, view->batch, s) : launch_prefill<EMBLA_BF16, 2>(ctx, pool, p, view->batch, s);
-    return s4 ? launch_prefill<EMBLA_F16, 4>(ctx, pool, p, view->batch, s) : launch_prefill<EMBLA_F16, 2>(ctx, pool, p, view->batch, s);
+    // pages a tile may see, from the caller's bound on pos0 + n_tokens (sizes the page split only)
+    const int max_pages = ((view->max_seq_len > 0 ? view->max_seq_len : ctx->cfg.max_context) + BLK - 1) / BLK;
+    if (bf) return s4 ? launch_prefill<EMBLA_BF16, 4>(ctx, pool, p, view->batch, max_pages, s) : launch_prefill<EMBLA_BF16, 2>(ctx, pool, p, view->batch, max_pages, s);
+    return s4 ? launch_prefill<EMBLA_F16, 4>(ctx, pool, p, view->batch, max_pages, s) : launch_prefill<EMBLA_F16, 2>(ctx, pool, p, view->batch, max_pages, s);
 }

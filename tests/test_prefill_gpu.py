@@ -60,6 +60,12 @@ def test_prefill_shapes(T, p0):
     _case(T, p0, 16, 4, orc.BF16, True, seed=T * 7 + p0)
 
 
+def test_prefill_pages_split_over_ctas():
+    # few (tile pair, head) units: each unit's pages are split over several CTAs and the last one adds the partials
+    _case(200, 12000, 16, 4, orc.BF16, True, seed=21, rows=(3, 5))
+    _case(300, 9000, 8, 2, orc.F16, True, seed=22, rows=(0, 7))
+
+
 def test_prefill_reference_shape_gains_fp32_scales():
     _case(200, 333, 16, 2, orc.BF16, False, seed=3, gains=True)
 
