@@ -36,6 +36,12 @@ struct Attn16Params {
     int64_t q_stride, o_stride, ring_stride;   // elements; ring_stride between sequences
     size_t page_bytes;
     int table_stride, layer, n_layers, n_kv_heads, G, prenormed, ng, ring, window, max_chunks;
+    // sliding layers, fused ring write of the current token (attention.metal:47-62): its raw k, v rows or NULL
+    const void* k_new;
+    const void* v_new;
+    const void* kgain;
+    int64_t kv_stride;
+    int k_prenormed;
     float rope_freq[32];
 };
 
@@ -97,6 +103,27 @@ __global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16
         for (int i = 0; i < 4; i++) Act<DT>::store(&qs[hh][0], lane + 32 * i, x[i]);
     }
     cp_async_wait_all();
+    if (MODE == A16_SLIDING && p.k_new != nullptr && chunk == 0 && warp == 0) {
+        // The current token's key and value (row 0 of this chunk) come from the qkv row, not from the ring: normed,
+        // rotated and rounded as attn_sliding does, stored to the ring slot for the steps to come and put in the tiles.
+        __syncwarp();
+        const size_t off = size_t(b) * p.kv_stride + size_t(kvh) * HD;
+        float x[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) x[i] = Act<DT>::load(p.k_new, off + lane + 32 * i);
+        if (!p.k_prenormed) norm_rope_round<DT>(x, p.kgain, p.kgain, 1, pos, p.rope_freq, lane);
+        const size_t slot_off = size_t(b) * p.ring_stride + (size_t(kvh) * p.ring + pos % p.ring) * HD;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int d = lane + 32 * i;
+            const int at = (d >> 6) * (BLK * 128) + (((d >> 3) & 7) << 4) + (d & 7) * 2;   // row 0: no swizzle offset
+            const uint16_t vbits = reinterpret_cast<const uint16_t*>(p.v_new)[off + d];
+            Act<DT>::store(Kt + at, 0, x[i]);
+            *reinterpret_cast<uint16_t*>(Vt + at) = vbits;
+            Act<DT>::store(const_cast<uint8_t*>(p.ring_k), slot_off + d, x[i]);
+            reinterpret_cast<uint16_t*>(const_cast<uint8_t*>(p.ring_v))[slot_off + d] = vbits;
+        }
+    }
     __syncthreads();
 
     const int g = lane >> 2, c = lane & 3;
@@ -407,9 +434,30 @@ extern "C" EmblaStatus embla_sliding_write(EmblaAttn* ctx, const EmblaRing* ring
     return EMBLA_OK;
 }
 
+static EmblaStatus sliding_decode_impl(EmblaAttn* ctx, const EmblaRing* ring, const int32_t* seq_lens_dev, int32_t batch,
+                                       const EmblaQuery* q, void* o_dev, int64_t o_stride, const void* k_new,
+                                       const void* v_new, int64_t kv_stride, int32_t k_prenormed, const void* kgain,
+                                       void* stream);
+
 extern "C" EmblaStatus embla_attn_sliding_decode(EmblaAttn* ctx, const EmblaRing* ring, const int32_t* seq_lens_dev,
                                                  int32_t batch, const EmblaQuery* q, void* o_dev, int64_t o_stride,
                                                  void* stream) {
+    return sliding_decode_impl(ctx, ring, seq_lens_dev, batch, q, o_dev, o_stride, nullptr, nullptr, 0, 1, nullptr, stream);
+}
+
+extern "C" EmblaStatus embla_attn_sliding_step(EmblaAttn* ctx, const EmblaRing* ring, const int32_t* seq_lens_dev,
+                                               int32_t batch, const EmblaQuery* q, const void* k_dev, const void* v_dev,
+                                               int64_t kv_stride, int32_t k_prenormed, const void* kgain_dev, void* o_dev,
+                                               int64_t o_stride, void* stream) {
+    if (!k_dev || !v_dev || (!k_prenormed && !kgain_dev)) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sliding_step: null k, v or key gain");
+    return sliding_decode_impl(ctx, ring, seq_lens_dev, batch, q, o_dev, o_stride, k_dev, v_dev, kv_stride, k_prenormed,
+                               kgain_dev, stream);
+}
+
+static EmblaStatus sliding_decode_impl(EmblaAttn* ctx, const EmblaRing* ring, const int32_t* seq_lens_dev, int32_t batch,
+                                       const EmblaQuery* q, void* o_dev, int64_t o_stride, const void* k_new,
+                                       const void* v_new, int64_t kv_stride, int32_t k_prenormed, const void* kgain,
+                                       void* stream) {
     if (!ctx || !ring || !ring->k_dev || !ring->v_dev || !seq_lens_dev || !o_dev)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sliding_decode: null argument");
     if (EmblaStatus st = check_query("embla_attn_sliding_decode", q)) return st;
@@ -430,5 +478,10 @@ extern "C" EmblaStatus embla_attn_sliding_decode(EmblaAttn* ctx, const EmblaRing
     p.q_stride = q->q_stride;
     p.o = o_dev;
     p.o_stride = o_stride;
+    p.k_new = k_new;
+    p.v_new = v_new;
+    p.kgain = kgain;
+    p.kv_stride = kv_stride;
+    p.k_prenormed = k_prenormed;
     return launch_attn16<A16_SLIDING>(ctx, p, batch, ring->window, static_cast<cudaStream_t>(stream));
 }

@@ -158,11 +158,10 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
         q.g2_dev = L.g2_dev;
         if (L.kind == EMBLA_LAYER_SLIDING) {
             const EmblaRing* ring = &st->rings[L.slot];
-            EMBLA_STEP(EMBLA_ENTRY_SLIDING_WRITE,
-                       embla_sliding_write(ctx, ring, step->pos_dev, B, 1, kp, vp, step->qkv_stride, step->qkv_stride,
-                                           L.kgain_dev ? 0 : 1, L.kgain_dev, stream));
+            // ring write + attention in one launch, as the reference's attn_sliding
             EMBLA_STEP(EMBLA_ENTRY_SLIDING_DECODE,
-                       embla_attn_sliding_decode(ctx, ring, step->seq_lens_dev, B, &q, op, step->o_stride, stream));
+                       embla_attn_sliding_step(ctx, ring, step->seq_lens_dev, B, &q, kp, vp, step->qkv_stride, L.kgain_dev ? 0 : 1,
+                                               L.kgain_dev, op, step->o_stride, stream));
             continue;
         }
         EmblaKVView view;

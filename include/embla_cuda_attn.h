@@ -220,6 +220,15 @@ EmblaStatus embla_attn_sliding_decode(EmblaAttn* ctx, const EmblaRing* ring, con
                                       int32_t batch, const EmblaQuery* q, void* o_dev, int64_t o_stride,
                                       void* stream);
 
+/* Replaces attn_sliding as the reference runs it (attention.metal:26-102; dispatch Engine.swift:771-780): the ring
+ * write of the current token and the attention in ONE launch. k_dev / v_dev are the current token's raw rows
+ * ([batch][kv_stride], kv head h at h * 128); the key is normed with kgain, rotated at position seq_len - 1 and rounded
+ * (or stored as given with k_prenormed), written to slot (seq_len - 1) % ring, and used from registers by the attention. */
+EmblaStatus embla_attn_sliding_step(EmblaAttn* ctx, const EmblaRing* ring, const int32_t* seq_lens_dev, int32_t batch,
+                                    const EmblaQuery* q, const void* k_dev, const void* v_dev, int64_t kv_stride,
+                                    int32_t k_prenormed, const void* kgain_dev, void* o_dev, int64_t o_stride,
+                                    void* stream);
+
 /* ---- prefill chunk, sliding layers ------------------------------------------------------------------- */
 /* Replaces attn_sliding_b / attn_sliding8_b (prefill.metal:129-180, 439-548; dispatch Prefill.swift:300-313):
  * token t of sequence b, at position pos0_dev[b] + t, attends its last `window` positions with softmax. The

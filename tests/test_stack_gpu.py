@@ -44,7 +44,7 @@ def test_reference_block_through_the_stack():
     assert torch.equal(o, got[4])
     st.ctx.sliding_decode(st.rings[0], st.seq_lens, q(0), o)
     assert torch.equal(o, got[0])
-    assert st.launches_per_step() == 2 + 3 + 1 + 1 + 4
+    assert st.launches_per_step() == 1 + 3 + 1 + 1 + 4
     st.close()
 
 
@@ -67,3 +67,39 @@ def test_step_host_round_trip_and_probe():
     assert torch.equal(a, st.o_host)          # same inputs, same position: bit-identical (appends are idempotent)
     assert torch.isfinite(a.float()).all() and a.float().abs().sum() > 0
     st.close()
+
+
+def test_fused_sliding_step_equals_write_then_attend():
+    """embla_attn_sliding_step (ring write + attention in one launch, the reference's attn_sliding) against
+    embla_sliding_write followed by embla_attn_sliding_decode: same ring contents, same outputs, bit for bit."""
+    import ctypes as C
+    import torch
+    from embla_metal_b200 import attn
+    torch.manual_seed(3)
+    B, Hq, Hkv, RING, W = 5, 16, 4, 1024, 256
+    for dtype, tdt in ((attn.F16, torch.float16), (attn.BF16, torch.bfloat16)):
+        ctx = attn.Attention(Hq, Hkv, dtype, B, RING)
+        r1, r2 = attn.Ring(B, Hkv, RING, W, tdt), attn.Ring(B, Hkv, RING, W, tdt)
+        hist = torch.randn(r1.k.shape, device="cuda").to(tdt)
+        r1.k.copy_(hist); r2.k.copy_(hist)
+        hv = torch.randn(r1.v.shape, device="cuda").to(tdt)
+        r1.v.copy_(hv); r2.v.copy_(hv)
+        pos = torch.tensor([0, 5, 255, 1023, 3000], dtype=torch.int32, device="cuda")
+        lens = pos + 1
+        q = torch.randn(B, Hq * 128, device="cuda").to(tdt)
+        k = torch.randn(B, 1, Hkv * 128, device="cuda").to(tdt)
+        v = torch.randn(B, 1, Hkv * 128, device="cuda").to(tdt)
+        qg = (torch.randn(128, device="cuda") * 0.1).to(tdt)
+        kg = (torch.randn(128, device="cuda") * 0.1).to(tdt)
+        o1, o2 = torch.zeros_like(q), torch.zeros_like(q)
+        ctx.sliding_write(r1, pos, k, v, kgain=kg)
+        ctx.sliding_decode(r1, lens, q, o1, qgain=qg)
+        qd = attn.Attention.query(q, (qg, None))
+        attn._check(attn.lib().embla_attn_sliding_step(ctx.handle, C.byref(r2.desc), C.c_void_p(lens.data_ptr()), B, C.byref(qd),
+                                                       C.c_void_p(k.data_ptr()), C.c_void_p(v.data_ptr()), C.c_int64(k.stride(0)), 0,
+                                                       C.c_void_p(kg.data_ptr()), C.c_void_p(o2.data_ptr()), C.c_int64(o2.stride(0)),
+                                                       attn._stream()))
+        ctx.check()
+        assert torch.equal(r1.k.view(torch.int16), r2.k.view(torch.int16)) and torch.equal(r1.v.view(torch.int16), r2.v.view(torch.int16))
+        assert torch.equal(o1.view(torch.int16), o2.view(torch.int16))
+        ctx.close()
