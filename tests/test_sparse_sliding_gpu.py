@@ -187,3 +187,26 @@ def test_sliding_ring_boundary_and_short():
 def test_sliding_reference_shape_norm_rope():
     # the reference's own window (128) with fused head norm + RoPE, bf16
     _sliding_case([0, 5, 200, 4095, 4096, 30000], 128, 4096, orc.BF16, seed=6, gains=True)
+
+
+def test_select_large_batch_single_cta_path():
+    """With many (sequence, kv head) pairs each pair is ranked by one CTA (small batches use a cluster of CTAs per pair)."""
+    import torch
+    from embla_metal_b200 import attn
+    rng = np.random.default_rng(77)
+    B, Hkv, ld = 40, 4, 2304
+    S_list = [int(x) for x in rng.integers(1100, ld + 1, B)]
+    ctx = attn.Attention(16, Hkv, orc.F16, max_batch=B, max_context=ld)
+    scores = (np.round(rng.standard_normal((B, Hkv, ld)) * 8) / 8).astype(np.float32)
+    st = torch.from_numpy(scores).cuda()
+    lens = torch.tensor(S_list, dtype=torch.int32, device="cuda")
+    idx = torch.full((B, Hkv, 1152), -1, dtype=torch.int32, device="cuda")
+    ctx.select_keys(st, lens, idx, max_seq_len=ld)
+    torch.cuda.synchronize()
+    got = idx.cpu().numpy()
+    for b, S in enumerate(S_list):
+        if S <= 1152:
+            assert (got[b] == -1).all()
+        else:
+            assert np.array_equal(got[b].view(np.uint32), orc.select_keys(scores[b], S)), f"sequence {b}"
+    ctx.close()
