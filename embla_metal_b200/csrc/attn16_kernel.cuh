@@ -1,0 +1,320 @@
+// The softmax decode kernel over 16-bit keys and values (sparse layers' gathered rows, sliding layers' rings).
+// A CTA walks a contiguous range of 64-row tiles of one (sequence, kv head) through a 3-stage cp.async ring
+// (16-byte gathers: row address from the index list / block table / ring slot), so rows are in flight while
+// the previous tile is computed; its 4 warps take 16 rows of every tile each. S^T = K Q^T and O^T = V^T P^T are
+// m16n8k16 tensor tiles on the data as stored; the softmax is online per warp (running max and sum per query
+// head, O rescaled when the max grows), the warps merge at the end, and when a pair is cut into several row
+// ranges their (max, sum, acc) partials are merged by the last CTA to arrive, in range order.
+#pragma once
+
+#include "attn16_common.cuh"
+
+namespace embla {
+
+constexpr int A16_THREADS = 128;
+constexpr int A16_ROWS = 64;                          // rows of a tile
+constexpr int A16_STAGES = 3;
+constexpr int A16_SIDE = A16_ROWS * HD * 2;           // bytes of one side (K or V) of a tile: 16 KiB
+constexpr int A16_STAGE = 2 * A16_SIDE;
+constexpr int A16_PART = HD + 4;                      // floats per (range, head): 128 sums, max, sum
+enum { A16_SPARSE = 0, A16_SLIDING = 1 };
+
+struct Attn16Params {
+    const uint8_t* pool;
+    const int32_t* block_table;
+    const uint32_t* idx;
+    const uint8_t* ring_k;
+    const uint8_t* ring_v;
+    const int32_t* seq_lens;
+    const void* q;
+    const void* g1;
+    const void* g2;
+    void* o;
+    float* partials;
+    int* counters;
+    int64_t q_stride, o_stride, ring_stride;   // elements; ring_stride between sequences
+    size_t page_bytes;
+    int table_stride, layer, n_layers, n_kv_heads, G, prenormed, ng, ring, window;
+    int max_chunks, tiles_per_cta;             // row ranges a pair is cut into, tiles in a range
+    // sliding layers, fused ring write of the current token (attention.metal:47-62): its raw k, v rows or NULL
+    const void* k_new;
+    const void* v_new;
+    const void* kgain;
+    int64_t kv_stride;
+    int k_prenormed;
+    float rope_freq[32];
+};
+
+template <int DT, int MODE>
+__global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint16_t(*qs)[HD] = reinterpret_cast<uint16_t(*)[HD]>(smem + A16_STAGES * A16_STAGE);   // [8][128] activation dtype
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int S = p.seq_lens[b];
+    const bool selecting = MODE == A16_SPARSE && S > EMBLA_TOPK + EMBLA_RECENT;
+    const int count = MODE == A16_SLIDING ? min(S, p.window) : (selecting ? EMBLA_TOPK + EMBLA_RECENT : S);
+    const int tiles = (count + A16_ROWS - 1) / A16_ROWS;
+    const int nch = (tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;     // ranges this sequence really has
+    if (chunk >= nch) return;
+    const int tile0 = chunk * p.tiles_per_cta, ntile = min(p.tiles_per_cta, tiles - tile0);
+    const int pos = S - 1;
+
+    // gathers of tile `t` (of this CTA's range) into stage t % STAGES; every thread copies 8 chunks of K and of V
+    auto issue_tile = [&](int t) {
+        uint8_t* Kt = smem + (t % A16_STAGES) * A16_STAGE;
+        uint8_t* Vt = Kt + A16_SIDE;
+        const int ch = tid & 15, half = ch >> 3, cc = ch & 7;
+        const int jbase = (tile0 + t) * A16_ROWS;
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+            const int key = it * 8 + (tid >> 4), j = jbase + key;
+            const bool valid = j < count;
+            const uint8_t *ksrc, *vsrc;
+            if (MODE == A16_SLIDING) {
+                const int slot = valid ? (pos - j) % p.ring : 0;
+                const size_t off = (size_t(b) * p.ring_stride + (size_t(kvh) * p.ring + slot) * HD) * 2 + ch * 16;
+                ksrc = p.ring_k + off;
+                vsrc = p.ring_v + off;
+            } else {
+                int row = valid ? j : 0;
+                if (selecting && valid) row = int(p.idx[(size_t(b) * p.n_kv_heads + kvh) * (EMBLA_TOPK + EMBLA_RECENT) + j]);
+                const int block = p.block_table[size_t(b) * p.table_stride + (row >> 7)];
+                const uint8_t* page = p.pool + ((size_t(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh) * p.page_bytes;
+                ksrc = page + (row & 127) * (HD * 2) + ch * 16;
+                vsrc = ksrc + BLK * HD * 2;
+            }
+            const int dst = half * (A16_ROWS * 128) + key * 128 + ((cc ^ (key & 7)) << 4);
+            cp_async16(Kt + dst, ksrc, valid);
+            cp_async16(Vt + dst, vsrc, valid);
+        }
+    };
+#pragma unroll
+    for (int t = 0; t < A16_STAGES - 1; t++) {
+        if (t < ntile) issue_tile(t);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    // ---- the kv head's queries (norm, RoPE for sliding layers) while the rows arrive
+    for (int hh = warp; hh < 8; hh += A16_THREADS / 32) {
+        float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (hh < p.G) {
+            const size_t off = size_t(b) * p.q_stride + size_t(kvh * p.G + hh) * HD;
+#pragma unroll
+            for (int i = 0; i < 4; i++) x[i] = Act<DT>::load(p.q, off + lane + 32 * i);
+            if (!p.prenormed) norm_rope_round<DT>(x, p.g1, p.g2, p.ng, MODE == A16_SLIDING ? pos : -1, p.rope_freq, lane);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) Act<DT>::store(&qs[hh][0], lane + 32 * i, x[i]);
+    }
+    __syncthreads();
+
+    const int g = lane >> 2, c = lane & 3;
+    const int rg = rho16(g), kA = rho16(2 * c), kB = kA ^ 4;
+    uint32_t qb0[8], qb1[8];
+#pragma unroll
+    for (int t = 0; t < 8; t++) {
+        const int m = t >> 1, e = t & 1;
+        const int d0 = 64 * (m >> 1) + 8 * (c + 4 * (m & 1)) + 4 * e;
+        qb0[t] = *reinterpret_cast<const uint32_t*>(&qs[g][d0]);
+        qb1[t] = *reinterpret_cast<const uint32_t*>(&qs[g][d0 + 2]);
+    }
+    const float scale = rsqrtf(float(HD));
+    float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;     // running max / sum of heads 2c, 2c + 1 over this warp's rows
+    float OT[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++) OT[i][0] = OT[i][1] = OT[i][2] = OT[i][3] = 0.0f;
+
+    for (int t = 0; t < ntile; t++) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(A16_STAGES - 2) : "memory");
+        uint8_t* Kt = smem + (t % A16_STAGES) * A16_STAGE;
+        uint8_t* Vt = Kt + A16_SIDE;
+        if (MODE == A16_SLIDING && p.k_new != nullptr && tile0 + t == 0 && warp == 0) {
+            // The current token's key and value (row 0) come from the qkv row, not from the ring: normed, rotated and
+            // rounded as attn_sliding does, stored to the ring slot for the steps to come and put into the tile.
+            __syncwarp();
+            const size_t off = size_t(b) * p.kv_stride + size_t(kvh) * HD;
+            float x[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) x[i] = Act<DT>::load(p.k_new, off + lane + 32 * i);
+            if (!p.k_prenormed) norm_rope_round<DT>(x, p.kgain, p.kgain, 1, pos, p.rope_freq, lane);
+            const size_t slot_off = size_t(b) * p.ring_stride + (size_t(kvh) * p.ring + pos % p.ring) * HD;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int d = lane + 32 * i;
+                const int at = (d >> 6) * (A16_ROWS * 128) + (((d >> 3) & 7) << 4) + (d & 7) * 2;   // row 0: no swizzle offset
+                const uint16_t vbits = reinterpret_cast<const uint16_t*>(p.v_new)[off + d];
+                Act<DT>::store(Kt + at, 0, x[i]);
+                *reinterpret_cast<uint16_t*>(Vt + at) = vbits;
+                Act<DT>::store(const_cast<uint8_t*>(p.ring_k), slot_off + d, x[i]);
+                reinterpret_cast<uint16_t*>(const_cast<uint8_t*>(p.ring_v))[slot_off + d] = vbits;
+            }
+        }
+        __syncthreads();
+
+        // S^T = K Q^T for the warp's 16 rows: lane holds rows r0 and r0 + 8, heads 2c and 2c + 1
+        const int R0 = warp * 16, r0 = R0 + rg;
+        const int jrow = (tile0 + t) * A16_ROWS + r0;
+        float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+            const uint8_t* base = Kt + (m >> 1) * (A16_ROWS * 128) + r0 * 128 + (((c + 4 * (m & 1)) ^ rg) << 4);
+            const uint4 x0 = *reinterpret_cast<const uint4*>(base);
+            const uint4 x1 = *reinterpret_cast<const uint4*>(base + 8 * 128);
+            mma16<DT>(s, x0.x, x1.x, x0.y, x1.y, qb0[2 * m], qb1[2 * m]);
+            mma16<DT>(s, x0.z, x1.z, x0.w, x1.w, qb0[2 * m + 1], qb1[2 * m + 1]);
+        }
+        const bool v0 = jrow < count, v1 = jrow + 8 < count;
+        s[0] = v0 ? s[0] * scale : NEG_BIG;
+        s[1] = v0 ? s[1] * scale : NEG_BIG;
+        s[2] = v1 ? s[2] * scale : NEG_BIG;
+        s[3] = v1 ? s[3] * scale : NEG_BIG;
+        float tm0 = fmaxf(s[0], s[2]), tm1 = fmaxf(s[1], s[3]);
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, o));
+            tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, o));
+        }
+        const float n0 = fmaxf(m0, tm0), n1 = fmaxf(m1, tm1);
+        const float f0 = __expf(m0 - n0), f1 = __expf(m1 - n1);
+        m0 = n0;
+        m1 = n1;
+        float pw[4];
+        pw[0] = v0 ? __expf(s[0] - m0) : 0.0f;
+        pw[1] = v0 ? __expf(s[1] - m1) : 0.0f;
+        pw[2] = v1 ? __expf(s[2] - m0) : 0.0f;
+        pw[3] = v1 ? __expf(s[3] - m1) : 0.0f;
+        l0 = l0 * f0 + pw[0] + pw[2];
+        l1 = l1 * f1 + pw[1] + pw[3];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            OT[i][0] *= f0;
+            OT[i][1] *= f1;
+            OT[i][2] *= f0;
+            OT[i][3] *= f1;
+        }
+        const uint8_t* vA = Vt + (R0 + kA) * 128 + ((g ^ kA) << 4);
+        const uint8_t* vB = Vt + (R0 + kB) * 128 + ((g ^ kB) << 4);
+        uint4 A[2], B[2], C[2], D[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            A[h] = *reinterpret_cast<const uint4*>(vA + h * (A16_ROWS * 128));
+            B[h] = *reinterpret_cast<const uint4*>(vB + h * (A16_ROWS * 128));
+            C[h] = *reinterpret_cast<const uint4*>(vA + h * (A16_ROWS * 128) + 8 * 128);
+            D[h] = *reinterpret_cast<const uint4*>(vB + h * (A16_ROWS * 128) + 8 * 128);
+        }
+        // P^T as B fragments; for bf16 P is split hi + lo so that its rounding stays below 2^-16
+        const uint32_t pb0 = movmatrix_trans16(pack_act2<DT>(pw[0], pw[1]));
+        const uint32_t pb1 = movmatrix_trans16(pack_act2<DT>(pw[2], pw[3]));
+        uint32_t pl0 = 0, pl1 = 0;
+        if (DT == EMBLA_BF16) {
+            float lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) lo[e] = pw[e] - Act<EMBLA_BF16>::round(pw[e]);
+            pl0 = movmatrix_trans16(pack_act2<DT>(lo[0], lo[1]));
+            pl1 = movmatrix_trans16(pack_act2<DT>(lo[2], lo[3]));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int wi = i >> 1;
+            const uint32_t sel = (i & 1) ? 0x7632 : 0x5410;
+            const uint32_t a0 = __byte_perm(word4(A[0], wi), word4(B[0], wi), sel);
+            const uint32_t a1 = __byte_perm(word4(A[1], wi), word4(B[1], wi), sel);
+            const uint32_t a2 = __byte_perm(word4(C[0], wi), word4(D[0], wi), sel);
+            const uint32_t a3 = __byte_perm(word4(C[1], wi), word4(D[1], wi), sel);
+            mma16<DT>(OT[i], a0, a1, a2, a3, pb0, pb1);
+            if (DT == EMBLA_BF16) mma16<DT>(OT[i], a0, a1, a2, a3, pl0, pl1);
+        }
+        __syncthreads();   // every warp is done with this stage: the tile STAGES - 1 ahead may overwrite it
+        if (t + A16_STAGES - 1 < ntile) issue_tile(t + A16_STAGES - 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+    // ---- merge the 4 warps (stage 0 is free: the loop ended with a barrier)
+    float(*red)[8][HD] = reinterpret_cast<float(*)[8][HD]>(smem);
+    float(*redm)[8] = reinterpret_cast<float(*)[8]>(smem + 4 * 8 * HD * 4);
+    float(*redl)[8] = redm + 4;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        red[warp][2 * c][8 * g + i] = OT[i][0];
+        red[warp][2 * c + 1][8 * g + i] = OT[i][1];
+        red[warp][2 * c][64 + 8 * g + i] = OT[i][2];
+        red[warp][2 * c + 1][64 + 8 * g + i] = OT[i][3];
+    }
+    if (g == 0) {
+        redm[warp][2 * c] = m0;
+        redm[warp][2 * c + 1] = m1;
+        redl[warp][2 * c] = l0;
+        redl[warp][2 * c + 1] = l1;
+    }
+    __syncthreads();
+    const int pair = b * p.n_kv_heads + kvh;
+    float* part = p.partials + (size_t(pair) * p.max_chunks + chunk) * p.G * A16_PART;
+    for (int idx = tid; idx < p.G * HD; idx += A16_THREADS) {
+        const int hh = idx >> 7, d = idx & 127;
+        float M = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < 4; w++) M = fmaxf(M, redm[w][hh]);
+        float L = 0.0f, num = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float f = __expf(redm[w][hh] - M);
+            L += redl[w][hh] * f;
+            num += red[w][hh][d] * f;
+        }
+        if (nch == 1) {
+            Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
+        } else {
+            part[hh * A16_PART + d] = num;
+            if (d == 0) {
+                part[hh * A16_PART + HD] = M;
+                part[hh * A16_PART + HD + 1] = L;
+            }
+        }
+    }
+    if (nch == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(&p.counters[pair], 1);
+        s_last = prev == nch - 1;
+        if (s_last) p.counters[pair] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* base = p.partials + size_t(pair) * p.max_chunks * p.G * A16_PART;
+    for (int idx = tid; idx < p.G * HD; idx += A16_THREADS) {
+        const int hh = idx >> 7, d = idx & 127;
+        // all ranges' values first (independent loads, at most 16 ranges), then the merge in range order
+        float mc[16], lc[16], ac[16];
+#pragma unroll
+        for (int cc = 0; cc < 16; cc++) {
+            const float* q2 = base + (size_t(cc < nch ? cc : 0) * p.G + hh) * A16_PART;
+            mc[cc] = cc < nch ? __ldcg(q2 + HD) : NEG_BIG;
+            lc[cc] = cc < nch ? __ldcg(q2 + HD + 1) : 0.0f;
+            ac[cc] = cc < nch ? __ldcg(q2 + d) : 0.0f;
+        }
+        float M = NEG_BIG;
+#pragma unroll
+        for (int cc = 0; cc < 16; cc++) M = fmaxf(M, mc[cc]);
+        float L = 0.0f, num = 0.0f;
+#pragma unroll
+        for (int cc = 0; cc < 16; cc++) {
+            const float f = __expf(mc[cc] - M);
+            L += lc[cc] * f;
+            num += ac[cc] * f;
+        }
+        Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
+    }
+}
+
+}  // namespace embla

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(S8_THREADS) sparse8_decode_kernel(const Sparse
     // ---- gather this chunk's code rows (8 chunks of 16 bytes a row and side) and their scales
     {
         const int ch = tid & 7;
-#pragma unroll 4
+#pragma unroll
         for (int it = 0; it < 8; it++) {
             const int key = it * 16 + (tid >> 3), j = j0 + key;
             const bool valid = j < count;
@@ -245,14 +245,24 @@ __global__ void __launch_bounds__(S8_THREADS) sparse8_decode_kernel(const Sparse
     const float* base = p.partials + size_t(pair) * p.max_chunks * p.G * S8_PART;
     for (int idx = tid; idx < p.G * HD; idx += S8_THREADS) {
         const int hh = idx >> 7, d = idx & 127;
+        // all chunks' values first (independent loads, at most 16 chunks), then the merge in chunk order
+        float mc[16], lc[16], ac[16];
+#pragma unroll
+        for (int cc = 0; cc < 16; cc++) {
+            const float* q2 = base + (size_t(cc < nch ? cc : 0) * p.G + hh) * S8_PART;
+            mc[cc] = cc < nch ? __ldcg(q2 + HD) : NEG_BIG;
+            lc[cc] = cc < nch ? __ldcg(q2 + HD + 1) : 0.0f;
+            ac[cc] = cc < nch ? __ldcg(q2 + d) : 0.0f;
+        }
         float M = NEG_BIG;
-        for (int cc = 0; cc < nch; cc++) M = fmaxf(M, __ldcg(base + (size_t(cc) * p.G + hh) * S8_PART + HD));
+#pragma unroll
+        for (int cc = 0; cc < 16; cc++) M = fmaxf(M, mc[cc]);
         float L = 0.0f, num = 0.0f;
-        for (int cc = 0; cc < nch; cc++) {
-            const float* q2 = base + (size_t(cc) * p.G + hh) * S8_PART;
-            const float f = __expf(__ldcg(q2 + HD) - M);
-            L += __ldcg(q2 + HD + 1) * f;
-            num += __ldcg(q2 + d) * f;
+#pragma unroll
+        for (int cc = 0; cc < 16; cc++) {
+            const float f = __expf(mc[cc] - M);
+            L += lc[cc] * f;
+            num += ac[cc] * f;
         }
         Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
     }
