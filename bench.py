@@ -5,7 +5,9 @@ Workload (BASELINE.json config 4): 64 independent sequences at 32768 context, la
 sparse, sliding(1024), sliding(1024), full(int8 KV); 16 query / 4 kv heads, head_dim 128, fp16
 activations; KV state synthetic in the configs' distributions (seeded). A "step" decodes one token
 for every sequence through all 24 layers' attention (KV write + attention per layer). Sequences are
-sharded across GPUs (strong scaling: 64 in total), no collective on the data path.
+sharded across GPUs with no collective on the data path. The headline line is weak-scaled: every GPU
+holds the configuration's 64 sequences (64 N in total); the same line carries, under "strong", the run
+with 64 sequences in total split over the N GPUs (64 / N each).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -24,15 +26,15 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-TOTAL_SEQS, CONTEXT, N_LAYERS, HQ, HKV, WINDOW, RING = 64, 32768, 24, 16, 4, 1024, 4096
+SEQS_PER_GPU, CONTEXT, N_LAYERS, HQ, HKV, WINDOW, RING = 64, 32768, 24, 16, 4, 1024, 4096
 METRIC, UNIT = "decode attn tok/s @32k ctx", "tok/s"
 
 
 def workload_config(n_gpus):
-    return {"workload": "config 4: batched decode, 64 seqs x 32768 ctx x 24 layers [sparse, sliding1024, sliding1024, full int8]",
-            "sequences": TOTAL_SEQS, "context": CONTEXT, "layers": N_LAYERS, "q_heads": HQ, "kv_heads": HKV, "head_dim": 128,
+    return {"workload": "config 4: batched decode, 64 seqs per GPU x 32768 ctx x 24 layers [sparse, sliding1024, sliding1024, full int8]",
+            "sequences": SEQS_PER_GPU * n_gpus, "sequences_per_gpu": SEQS_PER_GPU, "context": CONTEXT, "layers": N_LAYERS, "q_heads": HQ, "kv_heads": HKV, "head_dim": 128,
             "sparse_mode": "own fp16 K/V: score all keys, radix-select 1024 + 128 latest, attend",
-            "sharding": f"by sequence, {TOTAL_SEQS // n_gpus} per GPU, no collective",
+            "sharding": f"by sequence, {SEQS_PER_GPU} per GPU, no collective",
             "l2": "inputs larger than L2: each step streams the whole KV state (tens of GB) once"}
 
 
@@ -167,7 +169,7 @@ def run_reference(args, rank):
     sample = (f"{n_items} sequence-cycles (1 sequence x [sparse, sliding, sliding, full] at {CONTEXT} keys) on {cores} threads "
               f"in {secs:.2f} s; tok/s = items / (6 cycles x seconds)")
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals),
-            "warmup": args.warmup, "ms_per_step": 1000.0 * secs, "higher_is_better": True, "scaling": "strong",
+            "warmup": args.warmup, "ms_per_step": 1000.0 * secs, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus),
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -188,15 +190,6 @@ def run_gpu(args, rank, world):
     os.dup2(2, 1)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    if TOTAL_SEQS % world:
-        raise SystemExit(f"{TOTAL_SEQS} sequences do not divide over {world} GPUs")
-    batch = TOTAL_SEQS // world
-    st = stk.DecodeStack(stk.cycle_kinds(N_LAYERS), batch, CONTEXT, HQ, HKV, attn.F16, WINDOW, RING)
-    st.fill_random(seed=4 + rank)
-    st.set_positions(CONTEXT - 1)
-    g = torch.Generator(device="cuda").manual_seed(100 + rank)
-    st.qkv.copy_(torch.randn(st.qkv.shape, device="cuda", generator=g).to(st.dtype))
-    st.qkv_host.copy_(st.qkv)
 
     def barrier():
         torch.cuda.synchronize()
@@ -217,60 +210,80 @@ def run_gpu(args, rank, world):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    for _ in range(max(3, args.warmup)):
-        st.step()
-    st.ctx.check()
-    # per-entry device time of one step (explains the step; picks the dominant kernel)
-    per_entry = {}
-    for name in stk.ENTRY:
-        st.set_probe(name)
-        st.step()
-        torch.cuda.synchronize()
-        ms, n = st.read_probe()
-        if n:
-            per_entry[name] = {"launches": n, "ms": ms}
-    dominant = max(per_entry, key=lambda k: per_entry[k]["ms"])
-    st.set_probe(dominant)
-
-    sampler = ClockSampler(local)
-    sampler.start()
-    total_ms = timed(st.step, args.steps)
-    clocks = sampler.result()
-    dom_ms, dom_n = st.read_probe()
-    st.set_probe(None)
-    e2e_ms = timed(st.step_host, args.steps)
-    st.ctx.check()
-
-    ms_per_step = total_ms / args.steps
-    value = TOTAL_SEQS / (ms_per_step / 1e3)
-    e2e_value = TOTAL_SEQS / (e2e_ms / args.steps / 1e3)
     peak, peak_src = measured_peak()
-    achieved = algorithmic_bytes(batch, dominant) / (dom_ms / dom_n * 1e-3) / 1e9
-    step_bytes = sum(algorithmic_bytes(batch, k) * v["launches"] for k, v in per_entry.items())
+
+    def decode(batch, full):
+        """Times args.steps decode steps of `batch` sequences on every GPU. full: also the host-buffer run, the clocks and
+        the dominant kernel's roofline."""
+        st = stk.DecodeStack(stk.cycle_kinds(N_LAYERS), batch, CONTEXT, HQ, HKV, attn.F16, WINDOW, RING)
+        st.fill_random(seed=4 + rank)
+        st.set_positions(CONTEXT - 1)
+        g = torch.Generator(device="cuda").manual_seed(100 + rank)
+        st.qkv.copy_(torch.randn(st.qkv.shape, device="cuda", generator=g).to(st.dtype))
+        st.qkv_host.copy_(st.qkv)
+        for _ in range(max(3, args.warmup)):
+            st.step()
+        st.ctx.check()
+        # per-entry device time of one step (explains the step; picks the dominant kernel)
+        per_entry = {}
+        for name in stk.ENTRY:
+            st.set_probe(name)
+            st.step()
+            torch.cuda.synchronize()
+            ms, n = st.read_probe()
+            if n:
+                per_entry[name] = {"launches": n, "ms": ms}
+        dominant = max(per_entry, key=lambda k: per_entry[k]["ms"])
+        st.set_probe(dominant)
+        sampler = ClockSampler(local) if full else None
+        if sampler:
+            sampler.start()
+        total_ms = timed(st.step, args.steps)
+        clocks = sampler.result() if sampler else None
+        dom_ms, dom_n = st.read_probe()
+        st.set_probe(None)
+        e2e_ms = timed(st.step_host, args.steps)
+        st.ctx.check()
+        ms_per_step = total_ms / args.steps
+        step_bytes = sum(algorithmic_bytes(batch, k) * v["launches"] for k, v in per_entry.items())
+        achieved = algorithmic_bytes(batch, dominant) / (dom_ms / dom_n * 1e-3) / 1e9
+        out = {
+            "value": batch * world / (ms_per_step / 1e3), "ms_per_step": ms_per_step, "clocks": clocks,
+            "e2e": {"value": batch * world / (e2e_ms / args.steps / 1e3), "unit": UNIT,
+                    "h2d_bytes_per_step": st.qkv_host.numel() * 2 * world, "d2h_bytes_per_step": st.o_host.numel() * 2 * world},
+            "gpu_launches": st.launches_per_step() * args.steps,
+            "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_8000": achieved / 8000.0,
+                         "traffic": ncu_traffic(dominant, batch), "launches_timed": dom_n},
+            "step": {"algorithmic_gb": step_bytes / 1e9, "gbs": step_bytes / (ms_per_step * 1e-3) / 1e9,
+                     "frac_of_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
+                     "per_entry": {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
+                                       "gbs": round(algorithmic_bytes(batch, k) * v["launches"] / (v["ms"] * 1e-3) / 1e9, 1)}
+                                   for k, v in per_entry.items()}},
+        }
+        st.close()
+        del st
+        torch.cuda.empty_cache()
+        return out
+
+    r = decode(SEQS_PER_GPU, full=True)
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
-        "data": "synthetic", "config": workload_config(world), "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": st.qkv_host.numel() * 2 * world,
-                "d2h_bytes_per_step": st.o_host.numel() * 2 * world},
-        "gpu_launches": st.launches_per_step() * args.steps,
-        "roofline": {"bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_8000": achieved / 8000.0,
-                     "traffic": ncu_traffic(dominant, batch), "launches_timed": dom_n},
-        "step": {"algorithmic_gb": step_bytes / 1e9, "gbs": step_bytes / (ms_per_step * 1e-3) / 1e9,
-                 "frac_of_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak,
-                 "per_entry": {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
-                                   "gbs": round(algorithmic_bytes(batch, k) * v["launches"] / (v["ms"] * 1e-3) / 1e9, 1)}
-                               for k, v in per_entry.items()}},
+        "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "config": workload_config(world), "clocks": r["clocks"], "e2e": r["e2e"],
+        "gpu_launches": r["gpu_launches"], "roofline": r["roofline"], "step": r["step"],
     }
+    if world > 1 and SEQS_PER_GPU % world == 0:
+        # the same 64 sequences in total, split over the GPUs (per-GPU batch shrinks: launch and latency bound sooner)
+        q = decode(SEQS_PER_GPU // world, full=False)
+        line["strong"] = {"sequences": SEQS_PER_GPU, "sequences_per_gpu": SEQS_PER_GPU // world, "value": q["value"], "unit": UNIT,
+                          "ms_per_step": q["ms_per_step"], "e2e": q["e2e"]["value"], "step_gbs_per_gpu": q["step"]["gbs"],
+                          "per_entry_ms": {k: v["ms"] for k, v in q["step"]["per_entry"].items()}}
     if rank == 0 and world == 1:
         cores = os.cpu_count() or 1
         v, secs = cpu_tok_s(cores, 4 * cores)
         line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": f"{4 * cores} sequence-cycles of the 4-layer cycle at {CONTEXT} keys on {cores} threads, {secs:.2f} s"}
-    st.close()
-    del st
-    torch.cuda.empty_cache()
     line["prefill"] = prefill_leg(rank, world, barrier)
     if rank == 0:
         sys.stdout.flush()

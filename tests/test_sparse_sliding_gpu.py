@@ -210,3 +210,33 @@ def test_select_large_batch_single_cta_path():
         else:
             assert np.array_equal(got[b].view(np.uint32), orc.select_keys(scores[b], S)), f"sequence {b}"
     ctx.close()
+
+
+@pytest.mark.parametrize("B", [2, 40])
+def test_select_unaligned_rows_and_special_values(B):
+    """Score rows that do not start on 16 bytes take the lanes' own loads instead of bulk copies; infinities and
+    tiny/huge magnitudes rank by their order-preserving bit patterns as in the reference."""
+    import torch
+    from embla_metal_b200 import attn
+    rng = np.random.default_rng(5 + B)
+    Hkv, ld = 4, 4099                       # odd row stride: rows start at 4-byte offsets
+    S_list = [int(x) for x in rng.integers(1153, ld + 1, B)]
+    S_list[0] = ld
+    ctx = attn.Attention(16, Hkv, orc.F16, max_batch=B, max_context=ld)
+    scores = rng.standard_normal((B, Hkv, ld)).astype(np.float32) * np.float32(11.0)
+    scores[0, 0, 5::97] = np.inf
+    scores[0, 1, 3::89] = -np.inf
+    scores[0, 2, ::3] *= np.float32(1e-30)
+    scores[0, 3, ::5] *= np.float32(1e30)
+    flat = torch.zeros(B * Hkv * ld + 1, dtype=torch.float32, device="cuda")
+    st = flat[1:].view(B, Hkv, ld)          # 4 bytes past an aligned base
+    st.copy_(torch.from_numpy(scores))
+    assert st.data_ptr() % 16 == 4
+    lens = torch.tensor(S_list, dtype=torch.int32, device="cuda")
+    idx = torch.full((B, Hkv, 1152), -1, dtype=torch.int32, device="cuda")
+    ctx.select_keys(st, lens, idx, max_seq_len=ld)
+    ctx.check()
+    got = idx.cpu().numpy()
+    for b, S in enumerate(S_list):
+        assert np.array_equal(got[b].view(np.uint32), orc.select_keys(scores[b], S)), f"sequence {b}"
+    ctx.close()
