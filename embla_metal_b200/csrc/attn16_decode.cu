@@ -61,16 +61,51 @@ static EmblaStatus check_query(const char* fn, const EmblaQuery* q) {
     return EMBLA_OK;
 }
 
+// Tensor maps over a sliding layer's K and V rings for the ring-tile path: bytes [sequence][kv head x slot][256], boxes of
+// 64 rows x 128 bytes under the 128-byte swizzle. Encoded per call (a host-side computation of about a microsecond).
+static EmblaStatus ring_maps(const Attn16Params& p, int batch, CUtensorMap* mk, CUtensorMap* mv) {
+    TensorMapEncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) EMBLA_FAIL(EMBLA_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {HD * 2, cuuint64_t(p.n_kv_heads) * p.ring, cuuint64_t(batch)};
+    const cuuint64_t strides[2] = {HD * 2, cuuint64_t(p.ring_stride) * 2};
+    const cuuint32_t box[3] = {128, A16_ROWS, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    for (int side = 0; side < 2; side++) {
+        CUresult r = enc(side ? mv : mk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(side ? p.ring_v : p.ring_k), dims,
+                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) EMBLA_FAIL(EMBLA_CUDA, "cuTensorMapEncodeTiled failed for a ring (%d)", int(r));
+    }
+    return EMBLA_OK;
+}
+
+template <int DT, int MODE, bool TMA>
+static EmblaStatus launch_attn16_kernel(EmblaAttn* ctx, const Attn16Params& p, const CUtensorMap& mk, const CUtensorMap& mv,
+                                        dim3 grid, cudaStream_t s) {
+    constexpr size_t smem = 1024 + A16_STAGES * A16_STAGE + 8 * HD * 2;
+    static bool configured[64] = {};
+    if (!configured[ctx->device & 63]) {
+        EMBLA_CUDA_TRY(cudaFuncSetAttribute(attn16_decode_kernel<DT, MODE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        configured[ctx->device & 63] = true;
+    }
+    attn16_decode_kernel<DT, MODE, TMA><<<grid, A16_THREADS + (TMA ? 32 : 0), smem, s>>>(p, mk, mv);
+    EMBLA_CUDA_TRY(cudaGetLastError());
+    return EMBLA_OK;
+}
+
 template <int MODE>
 static EmblaStatus launch_attn16(EmblaAttn* ctx, Attn16Params& p, int batch, int max_rows, cudaStream_t s) {
-    constexpr size_t smem = 1024 + A16_STAGES * A16_STAGE + 8 * HD * 2;
     p.partials = ctx->partials;
     p.counters = ctx->counters;
+    p.err = ctx->err_dev;
     p.G = ctx->cfg.n_q_heads / ctx->cfg.n_kv_heads;
     p.n_kv_heads = ctx->cfg.n_kv_heads;
+    // Rings of a multiple of 64 slots are read as tiles of 64 consecutive slots (TMA); the window then spans one tile
+    // more unless it starts on a tile boundary.
+    const bool tma = MODE == A16_SLIDING && p.ring % A16_ROWS == 0;
     // Ranges per pair: the count that minimises (waves of CTAs over 2 CTAs per SM) x (tiles of a range + the fixed cost
     // of a CTA in tiles: query set-up, pipeline fill, merge), at most 16 ranges.
-    const int max_tiles = max_rows > 0 ? (max_rows + A16_ROWS - 1) / A16_ROWS : 1;
+    const int max_tiles = (max_rows > 0 ? (max_rows + A16_ROWS - 1) / A16_ROWS : 1) + (tma ? 1 : 0);
     const long pairs = long(batch) * p.n_kv_heads, slots = 2L * ctx->sm_count;
     long best_cost = -1;
     p.tiles_per_cta = max_tiles;
@@ -88,16 +123,15 @@ static EmblaStatus launch_attn16(EmblaAttn* ctx, Attn16Params& p, int batch, int
     }
     fill_rope_freq(p.rope_freq);
     dim3 grid(p.max_chunks, p.n_kv_heads, batch);
-    static bool configured[2][64] = {};
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
-    auto kern = bf ? attn16_decode_kernel<EMBLA_BF16, MODE> : attn16_decode_kernel<EMBLA_F16, MODE>;
-    if (!configured[bf][ctx->device & 63]) {
-        EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        configured[bf][ctx->device & 63] = true;
+    CUtensorMap mk = {}, mv = {};
+    if (tma) {
+        if (EmblaStatus st = ring_maps(p, batch, &mk, &mv)) return st;
+        return bf ? launch_attn16_kernel<EMBLA_BF16, MODE, MODE == A16_SLIDING>(ctx, p, mk, mv, grid, s)
+                  : launch_attn16_kernel<EMBLA_F16, MODE, MODE == A16_SLIDING>(ctx, p, mk, mv, grid, s);
     }
-    kern<<<grid, A16_THREADS, smem, s>>>(p);
-    EMBLA_CUDA_TRY(cudaGetLastError());
-    return EMBLA_OK;
+    return bf ? launch_attn16_kernel<EMBLA_BF16, MODE, false>(ctx, p, mk, mv, grid, s)
+              : launch_attn16_kernel<EMBLA_F16, MODE, false>(ctx, p, mk, mv, grid, s);
 }
 
 extern "C" EmblaStatus embla_attn_sparse_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
@@ -197,6 +231,10 @@ static EmblaStatus sliding_decode_impl(EmblaAttn* ctx, const EmblaRing* ring, co
     if (EmblaStatus st = check_query("embla_attn_sliding_decode", q)) return st;
     if (batch <= 0 || batch > ctx->cfg.max_batch || ring->window <= 0 || ring->window > ring->ring)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sliding_decode: batch %d, window %d, ring %d", batch, ring->window, ring->ring);
+    // ring rows are fetched 16 bytes (or whole tiles) at a time
+    if (reinterpret_cast<uintptr_t>(ring->k_dev) % 16 || reinterpret_cast<uintptr_t>(ring->v_dev) % 16 || ring->seq_stride % 8)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sliding_decode: rings must start on 16 bytes, seq_stride %lld a multiple of 8",
+                   (long long)ring->seq_stride);
     Attn16Params p = {};
     p.ring_k = static_cast<const uint8_t*>(ring->k_dev);
     p.ring_v = static_cast<const uint8_t*>(ring->v_dev);

@@ -1,23 +1,31 @@
 // The softmax decode kernel over 16-bit keys and values (sparse layers' gathered rows, sliding layers' rings).
-// A CTA walks a contiguous range of 64-row tiles of one (sequence, kv head) through a 3-stage cp.async ring
-// (16-byte gathers: row address from the index list / block table / ring slot), so rows are in flight while
-// the previous tile is computed; its 4 warps take 16 rows of every tile each. S^T = K Q^T and O^T = V^T P^T are
-// m16n8k16 tensor tiles on the data as stored; the softmax is online per warp (running max and sum per query
-// head, O rescaled when the max grows), the warps merge at the end, and when a pair is cut into several row
-// ranges their (max, sum, acc) partials are merged by the last CTA to arrive, in range order.
+// A CTA walks a contiguous range of 64-row tiles of one (sequence, kv head) through a 3-stage ring in shared
+// memory, so rows are in flight while the previous tile is computed; its 4 consumer warps take 16 rows of every
+// tile each. Two ways to fill a stage:
+//  * gathered rows (sparse layers; rings whose size is no multiple of 64): 16-byte cp.async by the consumer
+//    threads, row address from the index list / block table / ring slot;
+//  * ring tiles (sliding layers): the window is cut at 64-slot boundaries of the ring, so a tile is 64 consecutive
+//    ring rows and one producer thread fetches it with four TMA boxes (K and V, two 128-byte halves, 128-byte
+//    swizzle), completion on the stage's mbarrier, the stage handed back through a second one; the rows of the
+//    edge tiles that lie outside the window are masked. Every wait is bounded.
+// S^T = K Q^T and O^T = V^T P^T are m16n8k16 tensor tiles on the data as stored; the softmax is online per warp
+// (running max and sum per query head, O rescaled when the max grows), the warps merge at the end, and when a pair
+// is cut into several row ranges their (max, sum, acc) partials are merged by the last CTA to arrive, in range order.
 #pragma once
 
 #include "attn16_common.cuh"
 
 namespace embla {
 
-constexpr int A16_THREADS = 128;
+constexpr int A16_THREADS = 128;                       // consumer threads; ring tiles add a producer warp
 constexpr int A16_ROWS = 64;                          // rows of a tile
 constexpr int A16_STAGES = 3;
 constexpr int A16_SIDE = A16_ROWS * HD * 2;           // bytes of one side (K or V) of a tile: 16 KiB
 constexpr int A16_STAGE = 2 * A16_SIDE;
 constexpr int A16_PART = HD + 4;                      // floats per (range, head): 128 sums, max, sum
 enum { A16_SPARSE = 0, A16_SLIDING = 1 };
+
+__device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(A16_THREADS) : "memory"); }
 
 struct Attn16Params {
     const uint8_t* pool;
@@ -32,6 +40,7 @@ struct Attn16Params {
     void* o;
     float* partials;
     int* counters;
+    int* err;
     int64_t q_stride, o_stride, ring_stride;   // elements; ring_stride between sequences
     size_t page_bytes;
     int table_stride, layer, n_layers, n_kv_heads, G, prenormed, ng, ring, window;
@@ -45,11 +54,13 @@ struct Attn16Params {
     float rope_freq[32];
 };
 
-template <int DT, int MODE>
-__global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16Params p) {
+template <int DT, int MODE, bool TMA>
+__global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
+    attn16_decode_kernel(const Attn16Params p, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint16_t(*qs)[HD] = reinterpret_cast<uint16_t(*)[HD]>(smem + A16_STAGES * A16_STAGE);   // [8][128] activation dtype
+    __shared__ uint64_t full[A16_STAGES], empty[A16_STAGES];
     __shared__ int s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -57,11 +68,45 @@ __global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16
     const int S = p.seq_lens[b];
     const bool selecting = MODE == A16_SPARSE && S > EMBLA_TOPK + EMBLA_RECENT;
     const int count = MODE == A16_SLIDING ? min(S, p.window) : (selecting ? EMBLA_TOPK + EMBLA_RECENT : S);
-    const int tiles = (count + A16_ROWS - 1) / A16_ROWS;
+    const int pos = S - 1;
+    // Tiles: of the row list j = 0 .. count - 1 (j-th latest position for rings), or, for ring tiles, of the ring's
+    // slots pos - count + 1 .. pos cut at multiples of 64 (tbase: the first such tile).
+    const int tbase = TMA ? (pos - count + 1) >> 6 : 0;
+    const int tiles = TMA ? (pos >> 6) - tbase + 1 : (count + A16_ROWS - 1) / A16_ROWS;
     const int nch = (tiles + p.tiles_per_cta - 1) / p.tiles_per_cta;     // ranges this sequence really has
     if (chunk >= nch) return;
     const int tile0 = chunk * p.tiles_per_cta, ntile = min(p.tiles_per_cta, tiles - tile0);
-    const int pos = S - 1;
+
+    if (TMA) {
+        if (tid == 0) {
+#pragma unroll
+            for (int i = 0; i < A16_STAGES; i++) {
+                mbar_init(&full[i], 1);
+                mbar_init(&empty[i], A16_THREADS / 32);
+            }
+            fence_barrier_init();
+        }
+        __syncthreads();
+        if (warp == A16_THREADS / 32) {   // the producer
+            if (lane == 0) {
+                for (int t = 0; t < ntile; t++) {
+                    const int st = t % A16_STAGES;
+                    if (t >= A16_STAGES && !mbar_wait_bounded(&empty[st], ((t / A16_STAGES) - 1) & 1)) {
+                        atomicExch(p.err, ERR_WAIT_EMPTY);
+                        break;
+                    }
+                    uint8_t* Kt = smem + st * A16_STAGE;
+                    const int y = kvh * p.ring + ((tbase + tile0 + t) * A16_ROWS) % p.ring;
+                    mbar_expect_tx(&full[st], A16_STAGE);
+                    tma_load_3d(Kt, &map_k, 0, y, b, &full[st]);
+                    tma_load_3d(Kt + A16_ROWS * 128, &map_k, 128, y, b, &full[st]);
+                    tma_load_3d(Kt + A16_SIDE, &map_v, 0, y, b, &full[st]);
+                    tma_load_3d(Kt + A16_SIDE + A16_ROWS * 128, &map_v, 128, y, b, &full[st]);
+                }
+            }
+            return;
+        }
+    }
 
     // gathers of tile `t` (of this CTA's range) into stage t % STAGES; every thread copies 8 chunks of K and of V
     auto issue_tile = [&](int t) {
@@ -92,10 +137,12 @@ __global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16
             cp_async16(Vt + dst, vsrc, valid);
         }
     };
+    if (!TMA) {
 #pragma unroll
-    for (int t = 0; t < A16_STAGES - 1; t++) {
-        if (t < ntile) issue_tile(t);
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        for (int t = 0; t < A16_STAGES - 1; t++) {
+            if (t < ntile) issue_tile(t);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
     }
     // ---- the kv head's queries (norm, RoPE for sliding layers) while the rows arrive
     for (int hh = warp; hh < 8; hh += A16_THREADS / 32) {
@@ -109,7 +156,31 @@ __global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16
 #pragma unroll
         for (int i = 0; i < 4; i++) Act<DT>::store(&qs[hh][0], lane + 32 * i, x[i]);
     }
-    __syncthreads();
+    // Sliding layers, fused ring write (attention.metal:47-62): the current token's key (normed, rotated and rounded as
+    // attn_sliding does) and value come from the qkv row, not from the ring. The warp that owns the token's row of its
+    // tile prepares them here, stores them to the ring slot for the steps to come and puts them into the tile below.
+    // The token is row 0 of the row list, or slot pos of the last ring tile.
+    const int prow = TMA ? pos & (A16_ROWS - 1) : 0;
+    const int ptile = TMA ? tiles - 1 : 0;
+    const bool patch = MODE == A16_SLIDING && p.k_new != nullptr && ptile >= tile0 && ptile < tile0 + ntile && warp == prow >> 4;
+    float knew[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    uint16_t vnew[4] = {0, 0, 0, 0};
+    if (patch) {
+        const size_t off = size_t(b) * p.kv_stride + size_t(kvh) * HD;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            knew[i] = Act<DT>::load(p.k_new, off + lane + 32 * i);
+            vnew[i] = reinterpret_cast<const uint16_t*>(p.v_new)[off + lane + 32 * i];
+        }
+        if (!p.k_prenormed) norm_rope_round<DT>(knew, p.kgain, p.kgain, 1, pos, p.rope_freq, lane);
+        const size_t slot_off = size_t(b) * p.ring_stride + (size_t(kvh) * p.ring + pos % p.ring) * HD;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            Act<DT>::store(const_cast<uint8_t*>(p.ring_k), slot_off + lane + 32 * i, knew[i]);
+            reinterpret_cast<uint16_t*>(const_cast<uint8_t*>(p.ring_v))[slot_off + lane + 32 * i] = vnew[i];
+        }
+    }
+    cons_sync();
 
     const int g = lane >> 2, c = lane & 3;
     const int rg = rho16(g), kA = rho16(2 * c), kB = kA ^ 4;
@@ -128,35 +199,55 @@ __global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16
     for (int i = 0; i < 8; i++) OT[i][0] = OT[i][1] = OT[i][2] = OT[i][3] = 0.0f;
 
     for (int t = 0; t < ntile; t++) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(A16_STAGES - 2) : "memory");
-        uint8_t* Kt = smem + (t % A16_STAGES) * A16_STAGE;
+        const int st = t % A16_STAGES;
+        uint8_t* Kt = smem + st * A16_STAGE;
         uint8_t* Vt = Kt + A16_SIDE;
-        if (MODE == A16_SLIDING && p.k_new != nullptr && tile0 + t == 0 && warp == 0) {
-            // The current token's key and value (row 0) come from the qkv row, not from the ring: normed, rotated and
-            // rounded as attn_sliding does, stored to the ring slot for the steps to come and put into the tile.
-            __syncwarp();
-            const size_t off = size_t(b) * p.kv_stride + size_t(kvh) * HD;
-            float x[4];
+        if (TMA) {
+            if (!mbar_wait_bounded(&full[st], (t / A16_STAGES) & 1)) {
+                if (lane == 0) atomicExch(p.err, ERR_WAIT_FULL);
+                break;
+            }
+        } else {
+            asm volatile("cp.async.wait_group %0;" ::"n"(A16_STAGES - 2) : "memory");
+            cons_sync();
+        }
+        // the 16 rows of this warp: lane holds rows r0 and r0 + 8
+        const int R0 = warp * 16, r0 = R0 + rg;
+        bool v0, v1;
+        if (TMA) {
+            const int u = (tbase + tile0 + t) * A16_ROWS + r0;   // ring position of the row
+            v0 = u <= pos && u > pos - count;
+            v1 = u + 8 <= pos && u + 8 > pos - count;
+            // rows outside the window hold other positions or never-written memory: their weights are zero, but
+            // the value rows must be finite
+            const int ulo = (tbase + tile0 + t) * A16_ROWS + R0;
+            if (ulo + 15 > pos || ulo <= pos - count) {
+                const int zr = R0 + (lane >> 1), zu = ulo + (lane >> 1);
+                if (zu > pos || zu <= pos - count) {
+                    uint4* z = reinterpret_cast<uint4*>(Vt + (lane & 1) * (A16_ROWS * 128) + zr * 128);
 #pragma unroll
-            for (int i = 0; i < 4; i++) x[i] = Act<DT>::load(p.k_new, off + lane + 32 * i);
-            if (!p.k_prenormed) norm_rope_round<DT>(x, p.kgain, p.kgain, 1, pos, p.rope_freq, lane);
-            const size_t slot_off = size_t(b) * p.ring_stride + (size_t(kvh) * p.ring + pos % p.ring) * HD;
+                    for (int i = 0; i < 8; i++) z[i] = make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+            }
+        } else {
+            const int jrow = (tile0 + t) * A16_ROWS + r0;
+            v0 = jrow < count;
+            v1 = jrow + 8 < count;
+        }
+        if (patch && tile0 + t == ptile) {
+            // (only this warp reads the token's row: no other warp waits for these stores)
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int d = lane + 32 * i;
-                const int at = (d >> 6) * (A16_ROWS * 128) + (((d >> 3) & 7) << 4) + (d & 7) * 2;   // row 0: no swizzle offset
-                const uint16_t vbits = reinterpret_cast<const uint16_t*>(p.v_new)[off + d];
-                Act<DT>::store(Kt + at, 0, x[i]);
-                *reinterpret_cast<uint16_t*>(Vt + at) = vbits;
-                Act<DT>::store(const_cast<uint8_t*>(p.ring_k), slot_off + d, x[i]);
-                reinterpret_cast<uint16_t*>(const_cast<uint8_t*>(p.ring_v))[slot_off + d] = vbits;
+                const int at = (d >> 6) * (A16_ROWS * 128) + prow * 128 + ((((d >> 3) & 7) ^ (prow & 7)) << 4) + (d & 7) * 2;
+                Act<DT>::store(Kt + at, 0, knew[i]);
+                *reinterpret_cast<uint16_t*>(Vt + at) = vnew[i];
             }
+            __syncwarp();
         }
-        __syncthreads();
 
-        // S^T = K Q^T for the warp's 16 rows: lane holds rows r0 and r0 + 8, heads 2c and 2c + 1
-        const int R0 = warp * 16, r0 = R0 + rg;
-        const int jrow = (tile0 + t) * A16_ROWS + r0;
+        // S^T = K Q^T: lane holds heads 2c and 2c + 1 of its two rows
         float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int m = 0; m < 4; m++) {
@@ -166,7 +257,6 @@ __global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16
             mma16<DT>(s, x0.x, x1.x, x0.y, x1.y, qb0[2 * m], qb1[2 * m]);
             mma16<DT>(s, x0.z, x1.z, x0.w, x1.w, qb0[2 * m + 1], qb1[2 * m + 1]);
         }
-        const bool v0 = jrow < count, v1 = jrow + 8 < count;
         s[0] = v0 ? s[0] * scale : NEG_BIG;
         s[1] = v0 ? s[1] * scale : NEG_BIG;
         s[2] = v1 ? s[2] * scale : NEG_BIG;
@@ -227,18 +317,24 @@ __global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16
             mma16<DT>(OT[i], a0, a1, a2, a3, pb0, pb1);
             if (DT == EMBLA_BF16) mma16<DT>(OT[i], a0, a1, a2, a3, pl0, pl1);
         }
-        __syncthreads();   // every warp is done with this stage: the tile STAGES - 1 ahead may overwrite it
-        if (t + A16_STAGES - 1 < ntile) issue_tile(t + A16_STAGES - 1);
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (TMA) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[st]);   // this warp is done with the stage
+        } else {
+            cons_sync();   // every warp is done with this stage: the tile STAGES - 1 ahead may overwrite it
+            if (t + A16_STAGES - 1 < ntile) issue_tile(t + A16_STAGES - 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
     }
 #pragma unroll
     for (int o = 4; o < 32; o <<= 1) {
         l0 += __shfl_xor_sync(0xffffffffu, l0, o);
         l1 += __shfl_xor_sync(0xffffffffu, l1, o);
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    if (!TMA) asm volatile("cp.async.wait_group 0;" ::: "memory");
+    cons_sync();   // every consumer is past its last tile: the stages are free
 
-    // ---- merge the 4 warps (stage 0 is free: the loop ended with a barrier)
+    // ---- merge the 4 warps (in stage 0)
     float(*red)[8][HD] = reinterpret_cast<float(*)[8][HD]>(smem);
     float(*redm)[8] = reinterpret_cast<float(*)[8]>(smem + 4 * 8 * HD * 4);
     float(*redl)[8] = redm + 4;
@@ -255,7 +351,7 @@ __global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16
         redl[warp][2 * c] = l0;
         redl[warp][2 * c + 1] = l1;
     }
-    __syncthreads();
+    cons_sync();
     const int pair = b * p.n_kv_heads + kvh;
     float* part = p.partials + (size_t(pair) * p.max_chunks + chunk) * p.G * A16_PART;
     for (int idx = tid; idx < p.G * HD; idx += A16_THREADS) {
@@ -282,13 +378,13 @@ __global__ void __launch_bounds__(A16_THREADS) attn16_decode_kernel(const Attn16
     }
     if (nch == 1) return;
     __threadfence();
-    __syncthreads();
+    cons_sync();
     if (tid == 0) {
         const int prev = atomicAdd(&p.counters[pair], 1);
         s_last = prev == nch - 1;
         if (s_last) p.counters[pair] = 0;
     }
-    __syncthreads();
+    cons_sync();
     if (!s_last) return;
     __threadfence();
     const float* base = p.partials + size_t(pair) * p.max_chunks * p.G * A16_PART;

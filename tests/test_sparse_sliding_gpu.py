@@ -122,7 +122,7 @@ def test_select_ties_and_signed_zero():
     ctx.close()
 
 
-def _sliding_case(pos_list, W, RING, dtype, seed, gains):
+def _sliding_case(pos_list, W, RING, dtype, seed, gains, poison=False):
     import torch
     from embla_metal_b200 import attn
     rng = np.random.default_rng(seed)
@@ -135,8 +135,9 @@ def _sliding_case(pos_list, W, RING, dtype, seed, gains):
         qg = orc.to_bits(rng.standard_normal(128) * 0.1, dtype)
         kg = orc.to_bits(rng.standard_normal(128) * 0.1, dtype)
     want = []
-    rk_all = np.zeros((B, Hkv, RING, 128), np.uint16)
-    rv_all = np.zeros((B, Hkv, RING, 128), np.uint16)
+    # slots no token has been written to: zeros, or (poison) NaN bit patterns as uninitialised memory may hold
+    rk_all = np.full((B, Hkv, RING, 128), 0x7FFF if poison else 0, np.uint16)
+    rv_all = np.full((B, Hkv, RING, 128), 0x7FFF if poison else 0, np.uint16)
     q = orc.to_bits(rng.standard_normal((B, Hq, 128)), dtype)
     knew = orc.to_bits(rng.standard_normal((B, 1, Hkv, 128)), dtype)
     vnew = orc.to_bits(rng.standard_normal((B, 1, Hkv, 128)), dtype)
@@ -158,8 +159,9 @@ def _sliding_case(pos_list, W, RING, dtype, seed, gains):
                       kgain=None if kg is None else util.act_tensor(kg, dtype))
     torch.cuda.synchronize()
     # the ring write is elementwise arithmetic in the oracle's order: compare the stored rows closely
-    gk = orc.from_bits(util.act_bits(ring.k), dtype)
-    wk = orc.from_bits(rk_all, dtype)
+    written = rk_all != 0x7FFF if poison else np.ones(rk_all.shape, bool)
+    gk = np.where(written, orc.from_bits(util.act_bits(ring.k), dtype), 0.0)
+    wk = np.where(written, orc.from_bits(rk_all, dtype), 0.0)
     step = 2.0 ** -7 if dtype == orc.BF16 else 2.0 ** -10     # sin/cos may differ by an ulp: one storage step
     assert np.abs(gk - wk).max() <= step * max(1.0, np.abs(wk).max())
     assert np.array_equal(util.act_bits(ring.v), rv_all)
@@ -187,6 +189,17 @@ def test_sliding_ring_boundary_and_short():
 def test_sliding_reference_shape_norm_rope():
     # the reference's own window (128) with fused head norm + RoPE, bf16
     _sliding_case([0, 5, 200, 4095, 4096, 30000], 128, 4096, orc.BF16, seed=6, gains=True)
+
+
+def test_sliding_unwritten_slots_hold_nans():
+    # short sequences: most of the ring (and of the tiles the kernel fetches) was never written
+    _sliding_case([0, 5, 70, 1000, 1023, 1024], 1024, 4096, orc.F16, seed=8, gains=False, poison=True)
+    _sliding_case([3, 64, 127, 128, 129], 128, 4096, orc.BF16, seed=9, gains=True, poison=True)
+
+
+def test_sliding_ring_not_a_multiple_of_64():
+    # such rings are read row by row (gathered), not as 64-slot tiles
+    _sliding_case([0, 299, 300, 999, 1000, 2500], 300, 1000, orc.F16, seed=10, gains=False, poison=True)
 
 
 def test_select_large_batch_single_cta_path():
