@@ -307,6 +307,60 @@ EmblaStatus embla_stack_decode_step(EmblaStack* stack, const EmblaStackStep* ste
 EmblaStatus embla_stack_set_probe(EmblaStack* stack, int32_t entry);
 EmblaStatus embla_stack_read_probe(EmblaStack* stack, float* total_ms, int32_t* launches);
 
+/* ---- Prefix-cache store ---------------------------------------------------------------------------
+ * Replaces PrefixCache (Sources/EmblaMetal/PrefixCache.swift:24-145) and Engine.restoreFromStore /
+ * saveToStore with their span copies (PrefixCache.swift:150-286; resume rules Engine.swift:346-373).
+ * Same index: blocks of 128 positions known by an FNV-1a hash chained over every token before them,
+ * a parent/child tree, window checkpoints only at turn ends, least recently used leaves evicted
+ * first. A stored block is one contiguous copy of a physical block of the full layers' pool; a
+ * checkpoint is the 128 ring slots of every sliding layer (K and V, every kv head), gathered by one
+ * launch. The reference's checkpoint also holds 16 rows of engram conv history: not part of this
+ * library. All calls on one store must use one stream (a slot freed by an eviction may be refilled
+ * by the next save, ordered on that stream). Not thread-safe, as the reference's is not. */
+typedef struct EmblaPrefixStore EmblaPrefixStore;
+typedef struct {
+    int64_t limit_bytes;   /* PrefixCache.limit: most bytes to hold; 0 stores nothing */
+    int32_t turn_margin;   /* PrefixCache.turnMargin (16): a turn's checkpoint is at least this far before its end */
+    int32_t dry_run;       /* 1: the index only - no device memory, no copies (host-side tests) */
+} EmblaPrefixConfig;
+/* The caches of one sequence: its row of the full layers' block table (host copy) and its rings. */
+typedef struct {
+    const EmblaKVPool* pool;              /* the full layers' pool (NULL in a dry run) */
+    const int32_t*     block_table_host;  /* physical block of positions 128 i .. 128 i + 127 */
+    int32_t            table_len;
+    const EmblaRing*   rings;             /* one per sliding layer */
+    int32_t            n_rings;
+    int32_t            n_kv_heads;        /* of the rings */
+    int32_t            ring_slots;        /* Engine.ring: slots of every ring, a multiple of 128 */
+    int32_t            seq;               /* the sequence's index in the rings */
+} EmblaSeqCaches;
+
+/* PrefixCache.hash (PrefixCache.swift:69-79): FNV-1a over the 4 bytes of every token, little end first, from parent ^ basis. */
+uint64_t    embla_prefix_hash(uint64_t parent, const int32_t* tokens, int32_t n);
+/* full_block_bytes = embla_kv_block_bytes(pool); window_bytes = n_rings * 2 * n_kv_heads * 128 * 256. */
+EmblaStatus embla_prefix_store_create(const EmblaPrefixConfig* cfg, int64_t full_block_bytes, int64_t window_bytes,
+                                      EmblaPrefixStore** out);
+void        embla_prefix_store_destroy(EmblaPrefixStore* store);
+void        embla_prefix_store_remove_all(EmblaPrefixStore* store);
+EmblaStatus embla_prefix_store_stats(const EmblaPrefixStore* store, int64_t* bytes, int32_t* blocks, int32_t* checkpoints,
+                                     int64_t* evicted);
+/* PrefixCache.chain: how many stored blocks `tokens` starts with, covering at most up_to positions; the first
+ * `cap` of their hashes and checkpoint flags are written when the pointers are not NULL. */
+int32_t     embla_prefix_store_chain(const EmblaPrefixStore* store, const int32_t* tokens, int32_t n_tokens, int32_t up_to,
+                                     uint64_t* hashes_out, int32_t* has_window_out, int32_t cap);
+/* Engine.restoreFromStore: if the last checkpoint block the prompt starts with ends beyond `reuse` (where the live
+ * caches can resume), copies that checkpoint into the rings and the stored blocks ending beyond `live` into the
+ * physical blocks of dst's table, and returns its end in *start_out (and start - 128 in *ring_valid_from_out);
+ * else *start_out = -1. */
+EmblaStatus embla_prefix_store_restore(EmblaPrefixStore* store, const EmblaSeqCaches* dst, const int32_t* prompt,
+                                       int32_t n_prompt, int32_t live, int32_t reuse, int32_t* start_out,
+                                       int32_t* ring_valid_from_out, void* stream);
+/* Engine.saveToStore: stores the blocks of positions 0 .. position - 1 the store lacks, and for each turn end the
+ * checkpoint of the last block ending at least turn_margin before it, when the rings still hold it; then evicts. */
+EmblaStatus embla_prefix_store_save(EmblaPrefixStore* store, const EmblaSeqCaches* src, const int32_t* tokens,
+                                    int32_t position, const int32_t* turn_ends, int32_t n_turn_ends,
+                                    int32_t ring_valid_from, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
