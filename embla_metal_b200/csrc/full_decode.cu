@@ -70,10 +70,27 @@ __device__ __forceinline__ float f32_from_biased_byte(uint32_t x, int k) {
 
 constexpr int QF_LD = HD + 4;   // fp32 query rows padded so that two heads never share a bank
 
-template <int DT, int SB, int NCONS, int STAGES, bool SCORES>
-__global__ void __launch_bounds__((NCONS + 1) * 32) full_decode_kernel(const __grid_constant__ CUtensorMap tmap,
-                                                                      const FullDecodeParams p) {
-    constexpr int THREADS = (NCONS + 1) * 32;
+// acc = fma(q.lo, k.lo, acc); acc = fma(q.hi, k.hi, acc) on packed fp16 pairs: products exact, each step rounded
+// once to fp32 (the mixed-precision fma of sm_100).
+__device__ __forceinline__ void fma_pair_f16(float& acc, uint32_t k, uint32_t q) {
+    asm("{\n .reg .b16 kl, kh, ql, qh;\n mov.b32 {kl, kh}, %1;\n mov.b32 {ql, qh}, %2;\n"
+        " fma.rn.f32.f16 %0, ql, kl, %0;\n fma.rn.f32.f16 %0, qh, kh, %0;\n}\n"
+        : "+f"(acc)
+        : "r"(k), "r"(q));
+}
+
+// SG: 0 = no scores; 1, 2, 4, 8 = also the key scores, for that many query heads a kv head; 9 = scores for any
+// head count up to 8 (the count read at run time).
+// NCONS consumer warps share the keys of every page for the attention; with scores, 4 more warps (one key a thread)
+// compute the key scores from the same stage; the last warp is the producer.
+template <int DT, int SB, int NCONS, int STAGES, int SG>
+__global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
+    full_decode_kernel(const __grid_constant__ CUtensorMap tmap, const FullDecodeParams p) {
+    constexpr bool SCORES = SG != 0;
+    constexpr int GT = SG == 9 ? 8 : SG;
+    constexpr int NSC = SCORES ? 4 : 0;            // scoring warps
+    constexpr int NWORK = NCONS + NSC;             // warps that read the stages
+    constexpr int THREADS = (NWORK + 1) * 32;
     constexpr int KPW = BLK / NCONS;   // keys of a page per consumer warp
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -95,7 +112,7 @@ __global__ void __launch_bounds__((NCONS + 1) * 32) full_decode_kernel(const __g
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], NCONS);
+            mbar_init(&empty[s], NWORK);
         }
         s_failed = 0;
         s_issued = 0;
@@ -103,7 +120,7 @@ __global__ void __launch_bounds__((NCONS + 1) * 32) full_decode_kernel(const __g
     }
     // Heads of this kv head into shared memory as fp16 (and fp32 for the scoring chain): optional
     // head norm with gains in the oracle's operation order, rounded to the activation dtype.
-    for (int hh = warp; hh < 8; hh += NCONS + 1) {
+    for (int hh = warp; hh < 8; hh += NWORK + 1) {
         float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         if (hh < p.G) {
             const size_t off = size_t(b) * p.q_stride + size_t(kvh * p.G + hh) * HD;
@@ -142,7 +159,7 @@ __global__ void __launch_bounds__((NCONS + 1) * 32) full_decode_kernel(const __g
     for (int i = 0; i < 8; i++) OT[i][0] = OT[i][1] = OT[i][2] = OT[i][3] = 0.0f;
     float ps0 = 0.0f, ps1 = 0.0f;   // sums of weights of heads 2c, 2c + 1
 
-    if (warp == NCONS) {
+    if (warp == NWORK) {
         // ---- producer: one lane keeps the ring of stages full
         if (lane == 0) {
             const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * SB;
@@ -161,6 +178,84 @@ __global__ void __launch_bounds__((NCONS + 1) * 32) full_decode_kernel(const __g
                              &full[st]);
                 *reinterpret_cast<volatile int*>(&s_issued) = i + 1;
             }
+        }
+    } else if (SCORES && warp >= NCONS) {
+        // ---- scoring warps
+        for (int i = 0; i < n; i++) {
+            const int st = i % STAGES, use = i / STAGES;
+            if (!mbar_wait_bounded(&full[st], use & 1)) {
+                atomicExch(p.err, ERR_WAIT_FULL);
+                *reinterpret_cast<volatile int*>(&s_failed) = 1;
+                break;
+            }
+            const uint8_t* Kb = stages + st * FD_STAGE_BYTES;
+            const uint8_t* ksc = Kb + 2 * CODE_BYTES;
+            const int key_base = (pg0 + i) * BLK;
+            if (SCORES) {
+                // One key a thread: the dots of the kv head's heads, each ONE fp32 fma chain over d ascending
+                // (the order the CPU restatement fixes; the selection that follows compares index sets bit for bit).
+                const int r = (warp - NCONS) * 32 + lane;
+                if (key_base + r < S) {
+                    float dot[GT > 0 ? GT : 1];
+#pragma unroll
+                    for (int h = 0; h < GT; h++) dot[h] = 0.0f;
+                    const uint8_t* krow = Kb + r * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 8; ch++) {
+                        const uint4 w4 = *reinterpret_cast<const uint4*>(krow + ((ch ^ (r & 7)) << 4));
+                        const uint32_t w[4] = {w4.x ^ 0x80808080u, w4.y ^ 0x80808080u, w4.z ^ 0x80808080u, w4.w ^ 0x80808080u};
+                        if (DT == EMBLA_F16) {
+                            // codes widened exactly to fp16 pairs, queries as stored: the mixed-precision fma multiplies
+                            // exactly and rounds each step once to fp32, as fmaf on the converted values would
+#pragma unroll
+                            for (int h8 = 0; h8 < 2; h8++) {
+                                const uint32_t k01 = h2_from_biased_bytes(w[2 * h8], 0x4140), k23 = h2_from_biased_bytes(w[2 * h8], 0x4342);
+                                const uint32_t k45 = h2_from_biased_bytes(w[2 * h8 + 1], 0x4140), k67 = h2_from_biased_bytes(w[2 * h8 + 1], 0x4342);
+                                const int d = ch * 16 + h8 * 8;
+#pragma unroll
+                                for (int h = 0; h < GT; h++) {
+                                    if (SG != 9 || h < p.G) {
+                                        const uint4 q8 = *reinterpret_cast<const uint4*>(&qh[h][d]);   // one address a warp
+                                        fma_pair_f16(dot[h], k01, q8.x);
+                                        fma_pair_f16(dot[h], k23, q8.y);
+                                        fma_pair_f16(dot[h], k45, q8.z);
+                                        fma_pair_f16(dot[h], k67, q8.w);
+                                    }
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int e4 = 0; e4 < 4; e4++) {
+                                const float k0 = f32_from_biased_byte(w[e4], 0), k1 = f32_from_biased_byte(w[e4], 1);
+                                const float k2 = f32_from_biased_byte(w[e4], 2), k3 = f32_from_biased_byte(w[e4], 3);
+                                const int d = ch * 16 + e4 * 4;
+#pragma unroll
+                                for (int h = 0; h < GT; h++) {
+                                    if (SG != 9 || h < p.G) {
+                                        const float4 q4 = *reinterpret_cast<const float4*>(&qf[h][d]);
+                                        dot[h] = __fmaf_rn(q4.x, k0, dot[h]);
+                                        dot[h] = __fmaf_rn(q4.y, k1, dot[h]);
+                                        dot[h] = __fmaf_rn(q4.z, k2, dot[h]);
+                                        dot[h] = __fmaf_rn(q4.w, k3, dot[h]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    const float ks = ld_scale<SB>(ksc, r);
+                    float best = __fmul_rn(dot[0], ks);
+#pragma unroll
+                    for (int h = 1; h < GT; h++) {
+                        if (SG != 9 || h < p.G) {
+                            const float t = __fmul_rn(dot[h], ks);
+                            if (t > best) best = t;
+                        }
+                    }
+                    p.scores[(size_t(b) * p.n_kv_heads + kvh) * p.scores_stride + key_base + r] = best;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[st]);
         }
     } else {
         // ---- consumers
@@ -185,49 +280,6 @@ __global__ void __launch_bounds__((NCONS + 1) * 32) full_decode_kernel(const __g
             const uint8_t* ksc = Kb + 2 * CODE_BYTES;
             const uint8_t* vsc = ksc + BLK * SB;
             const int key_base = (pg0 + i) * BLK;
-
-            if (SCORES) {
-                // one key a thread (KPW = 32): the kv head's heads' dots, each one fmaf chain over d ascending
-                static_assert(!SCORES || KPW == 32, "scoring takes one key a thread");
-                const int r = warp * 32 + lane;
-                if (key_base + r < S) {
-                    float dot[8];
-#pragma unroll
-                    for (int h = 0; h < 8; h++) dot[h] = 0.0f;
-                    const uint8_t* krow = Kb + r * 128;
-#pragma unroll
-                    for (int ch = 0; ch < 8; ch++) {
-                        const uint4 w4 = *reinterpret_cast<const uint4*>(krow + ((ch ^ (r & 7)) << 4));
-                        const uint32_t w[4] = {w4.x ^ 0x80808080u, w4.y ^ 0x80808080u, w4.z ^ 0x80808080u, w4.w ^ 0x80808080u};
-#pragma unroll
-                        for (int e4 = 0; e4 < 4; e4++) {
-                            const float k0 = f32_from_biased_byte(w[e4], 0), k1 = f32_from_biased_byte(w[e4], 1);
-                            const float k2 = f32_from_biased_byte(w[e4], 2), k3 = f32_from_biased_byte(w[e4], 3);
-                            const int d = ch * 16 + e4 * 4;
-#pragma unroll
-                            for (int h = 0; h < 8; h++) {
-                                if (h < p.G) {
-                                    const float4 q4 = *reinterpret_cast<const float4*>(&qf[h][d]);
-                                    dot[h] = __fmaf_rn(q4.x, k0, dot[h]);
-                                    dot[h] = __fmaf_rn(q4.y, k1, dot[h]);
-                                    dot[h] = __fmaf_rn(q4.z, k2, dot[h]);
-                                    dot[h] = __fmaf_rn(q4.w, k3, dot[h]);
-                                }
-                            }
-                        }
-                    }
-                    const float ks = ld_scale<SB>(ksc, r);
-                    float best = __fmul_rn(dot[0], ks);
-#pragma unroll
-                    for (int h = 1; h < 8; h++) {
-                        if (h < p.G) {
-                            const float t = __fmul_rn(dot[h], ks);
-                            if (t > best) best = t;
-                        }
-                    }
-                    p.scores[(size_t(b) * p.n_kv_heads + kvh) * p.scores_stride + key_base + r] = best;
-                }
-            }
 
 #pragma unroll
             for (int step = 0; step < KPW / 16; step++) {
@@ -402,14 +454,15 @@ int choose_splits(int pairs, int pages, int slots, int max_slots) {
 
 using namespace embla;
 
-template <int DT, int SB, bool SCORES>
+template <int DT, int SB, int SG>
 static EmblaStatus launch_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const FullDecodeParams& p, int batch,
                                       cudaStream_t s) {
     constexpr int STAGES = 3;
+    constexpr bool SCORES = SG != 0;
     constexpr int NCONS = SCORES ? 4 : 8;
-    constexpr int FD_THREADS = (NCONS + 1) * 32;
+    constexpr int FD_THREADS = (NCONS + (SCORES ? 4 : 0) + 1) * 32;
     constexpr size_t smem = fd_smem_bytes<STAGES, SCORES>();
-    auto kern = full_decode_kernel<DT, SB, NCONS, STAGES, SCORES>;
+    auto kern = full_decode_kernel<DT, SB, NCONS, STAGES, SG>;
     static bool configured[64] = {};   // per instantiation and device
     if (!configured[ctx->device & 63]) {
         EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
@@ -473,12 +526,19 @@ extern "C" EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool*
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
     const bool s4 = pool->scale_bytes == 4;
 #define EMBLA_FD(DT, SB, SC) launch_full_decode<DT, SB, SC>(ctx, pool, p, view->batch, s)
-    if (scores_dev) {
-        if (bf) return s4 ? EMBLA_FD(EMBLA_BF16, 4, true) : EMBLA_FD(EMBLA_BF16, 2, true);
-        return s4 ? EMBLA_FD(EMBLA_F16, 4, true) : EMBLA_FD(EMBLA_F16, 2, true);
+#define EMBLA_FD_SG(SG) \
+    (bf ? (s4 ? EMBLA_FD(EMBLA_BF16, 4, SG) : EMBLA_FD(EMBLA_BF16, 2, SG)) : (s4 ? EMBLA_FD(EMBLA_F16, 4, SG) : EMBLA_FD(EMBLA_F16, 2, SG)))
+    if (scores_dev) {   // the head count compiled in for the usual groupings
+        switch (p.G) {
+            case 1: return EMBLA_FD_SG(1);
+            case 2: return EMBLA_FD_SG(2);
+            case 4: return EMBLA_FD_SG(4);
+            case 8: return EMBLA_FD_SG(8);
+            default: return EMBLA_FD_SG(9);
+        }
     }
-    if (bf) return s4 ? EMBLA_FD(EMBLA_BF16, 4, false) : EMBLA_FD(EMBLA_BF16, 2, false);
-    return s4 ? EMBLA_FD(EMBLA_F16, 4, false) : EMBLA_FD(EMBLA_F16, 2, false);
+    return EMBLA_FD_SG(0);
+#undef EMBLA_FD_SG
 #undef EMBLA_FD
 }
 
@@ -514,7 +574,7 @@ static NoAllocDevice g_noalloc[64];
 template <int DT, int SB>
 static EmblaStatus noalloc_setup_kernel() {
     constexpr size_t smem = fd_smem_bytes<3, false>();
-    EMBLA_CUDA_TRY(cudaFuncSetAttribute(full_decode_kernel<DT, SB, 8, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    EMBLA_CUDA_TRY(cudaFuncSetAttribute(full_decode_kernel<DT, SB, 8, 3, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         int(smem)));
     return EMBLA_OK;
 }
