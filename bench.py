@@ -212,10 +212,10 @@ def run_gpu(args, rank, world):
 
     peak, peak_src = measured_peak()
 
-    def decode(batch, full):
+    def decode(batch, full, kinds=None):
         """Times args.steps decode steps of `batch` sequences on every GPU. full: also the host-buffer run, the clocks and
         the dominant kernel's roofline."""
-        st = stk.DecodeStack(stk.cycle_kinds(N_LAYERS), batch, CONTEXT, HQ, HKV, attn.F16, WINDOW, RING)
+        st = stk.DecodeStack(kinds or stk.cycle_kinds(N_LAYERS), batch, CONTEXT, HQ, HKV, attn.F16, WINDOW, RING)
         st.fill_random(seed=4 + rank)
         st.set_positions(CONTEXT - 1)
         g = torch.Generator(device="cuda").manual_seed(100 + rank)
@@ -273,6 +273,13 @@ def run_gpu(args, rank, world):
         "data": "synthetic", "config": workload_config(world), "clocks": r["clocks"], "e2e": r["e2e"],
         "gpu_launches": r["gpu_launches"], "roofline": r["roofline"], "step": r["step"],
     }
+    # The reference's own arrangement of the same 24 layers (Engine.swift:461-462, 796-827): sparse layers hold no keys of
+    # their own but read the preceding full layer's int8 cache, and that full layer emits the key scores as a by-product.
+    shared = [(stk.FULL, stk.SPARSE_SHARED, stk.SLIDING, stk.SLIDING)[i % 4] for i in range(N_LAYERS)]
+    q = decode(SEQS_PER_GPU, full=False, kinds=shared)
+    line["shared_cache_mode"] = {"layers": "[full int8 + scores, sparse over that cache, sliding1024, sliding1024] x 6",
+                                 "value": q["value"], "unit": UNIT, "ms_per_step": q["ms_per_step"], "e2e": q["e2e"]["value"],
+                                 "per_entry_ms": {k: v["ms"] for k, v in q["step"]["per_entry"].items()}}
     if world > 1 and SEQS_PER_GPU % world == 0:
         # the same 64 sequences in total, split over the GPUs (per-GPU batch shrinks: launch and latency bound sooner)
         q = decode(SEQS_PER_GPU // world, full=False)
