@@ -88,7 +88,7 @@ static EmblaStatus launch_attn16_kernel(EmblaAttn* ctx, const Attn16Params& p, c
         EMBLA_CUDA_TRY(cudaFuncSetAttribute(attn16_decode_kernel<DT, MODE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         configured[ctx->device & 63] = true;
     }
-    attn16_decode_kernel<DT, MODE, TMA><<<grid, A16_THREADS + (TMA ? 32 : 0), smem, s>>>(p, mk, mv);
+    EMBLA_CUDA_TRY(launch_kernel(ctx->pdl, attn16_decode_kernel<DT, MODE, TMA>, grid, dim3(A16_THREADS + (TMA ? 32 : 0)), smem, s, p, mk, mv));
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;
 }

@@ -65,6 +65,8 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    pdl_wait();
+    pdl_launch_dependents();
     const int S = p.seq_lens[b];
     const bool selecting = MODE == A16_SPARSE && S > EMBLA_TOPK + EMBLA_RECENT;
     const int count = MODE == A16_SLIDING ? min(S, p.window) : (selecting ? EMBLA_TOPK + EMBLA_RECENT : S);

@@ -66,6 +66,7 @@ struct EmblaAttn {
     uint8_t* prefill_scratch;      // split-KV partials of the prefill kernel, sized on first need
     size_t prefill_scratch_bytes;
     int prefill_counter_units;     // which (units, splits) layout its counters were cleared for
+    int pdl;                       // launches may start before the preceding kernel of the stream has drained (set by the step driver)
 };
 
 namespace embla {
@@ -148,6 +149,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may become resident while the
+// kernel before it in the stream drains. Every kernel of the decode step calls pdl_wait() before its first access to
+// global memory (it returns once the preceding grid has completed and its writes are visible), then lets its own
+// successor be scheduled. Both are no-ops in a launch without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // 3-D tiled TMA load (no multicast): box at (x, y, z).
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
     asm volatile(
@@ -163,6 +171,22 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
         : "memory");
 }
 #endif  // __CUDACC__
+
+// Host: a kernel launch, with the programmatic-dependent-launch attribute when `pdl`.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(bool pdl, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 // Host: the driver's cuTensorMapEncodeTiled, fetched through the runtime (no link against libcuda).
 typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -103,6 +103,8 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    pdl_wait();
+    pdl_launch_dependents();
     const int S = p.seq_lens[b];
     const int npages = (S + BLK - 1) / BLK;
     const int pps = (npages + p.nsplit - 1) / p.nsplit;
@@ -469,7 +471,7 @@ static EmblaStatus launch_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, c
         configured[ctx->device & 63] = true;
     }
     dim3 grid(p.nsplit, p.n_kv_heads, batch);
-    kern<<<grid, FD_THREADS, smem, s>>>(pool->tmap_codes, p);
+    EMBLA_CUDA_TRY(launch_kernel(ctx->pdl, kern, grid, dim3(FD_THREADS), smem, s, pool->tmap_codes, p));
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;
 }

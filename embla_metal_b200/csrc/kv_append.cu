@@ -21,6 +21,8 @@ struct AppendParams {
 
 template <int DT>
 __global__ void __launch_bounds__(128) kv_append_kernel(const AppendParams p) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const long warp = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const long total = long(p.batch) * p.n_tokens * p.n_kv_heads * 2;
@@ -112,8 +114,8 @@ extern "C" EmblaStatus embla_kv_append(EmblaAttn* ctx, EmblaKVPool* pool, const 
     const long warps = long(p.batch) * n_tokens * p.n_kv_heads * 2;
     const unsigned blocks = unsigned((warps + 3) / 4);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (ctx->cfg.act_dtype == EMBLA_BF16) kv_append_kernel<EMBLA_BF16><<<blocks, 128, 0, s>>>(p);
-    else kv_append_kernel<EMBLA_F16><<<blocks, 128, 0, s>>>(p);
+    if (ctx->cfg.act_dtype == EMBLA_BF16) EMBLA_CUDA_TRY(launch_kernel(ctx->pdl, kv_append_kernel<EMBLA_BF16>, dim3(blocks), dim3(128), 0, s, p));
+    else EMBLA_CUDA_TRY(launch_kernel(ctx->pdl, kv_append_kernel<EMBLA_F16>, dim3(blocks), dim3(128), 0, s, p));
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;
 }

@@ -64,6 +64,8 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    pdl_wait();
+    pdl_launch_dependents();
     const int S = p.seq_lens[b];
     const int npages = (S + BLK - 1) / BLK;
     const int pps = (npages + p.nsplit - 1) / p.nsplit;
@@ -151,7 +153,7 @@ static EmblaStatus launch_score(EmblaAttn* ctx, const EmblaKVPool* pool, const S
         configured[ctx->device & 63] = true;
     }
     dim3 grid(p.nsplit, p.n_kv_heads, batch);
-    kern<<<grid, SK_THREADS, smem, s>>>(pool->tmap_codes, p);
+    EMBLA_CUDA_TRY(launch_kernel(ctx->pdl, kern, grid, dim3(SK_THREADS), smem, s, pool->tmap_codes, p));
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;
 }

@@ -59,6 +59,8 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
     const int CL = int(cluster.num_blocks()), rank = int(cluster.block_rank());
     const int kvh = blockIdx.x / CL, b = blockIdx.y;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    pdl_wait();
+    pdl_launch_dependents();
     const int S = p.seq_lens[b];
     // the reference does not select yet at or below 1152 keys (Engine.swift:796); uniform over the cluster, and
     // every CTA keeps taking the barriers
@@ -224,7 +226,7 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
 }
 
 template <int ITEMS, bool BULK>
-static cudaError_t launch_select(const SelectParams& p, int batch, int cl, int device, cudaStream_t s) {
+static cudaError_t launch_select(const SelectParams& p, int batch, int cl, int device, bool pdl, cudaStream_t s) {
     const size_t smem = BULK ? size_t(SEL_T) * ITEMS * 4 : 0;
     static bool configured[64] = {};
     if (smem > 0 && !configured[device & 63]) {
@@ -237,24 +239,26 @@ static cudaError_t launch_select(const SelectParams& p, int batch, int cl, int d
     cfg.blockDim = dim3(SEL_T);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute at[1];
+    cudaLaunchAttribute at[2];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = cl;
     at[0].val.clusterDim.y = 1;
     at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, select_keys_kernel<ITEMS, BULK>, p);
 }
 
 template <bool BULK>
-static cudaError_t launch_select_items(const SelectParams& p, int per_thread, int batch, int cl, int device, cudaStream_t s) {
-    if (per_thread <= 1) return launch_select<1, BULK>(p, batch, cl, device, s);
-    if (per_thread <= 2) return launch_select<2, BULK>(p, batch, cl, device, s);
-    if (per_thread <= 4) return launch_select<4, BULK>(p, batch, cl, device, s);
-    if (per_thread <= 8) return launch_select<8, BULK>(p, batch, cl, device, s);
-    if (per_thread <= 16) return launch_select<16, BULK>(p, batch, cl, device, s);
-    return launch_select<32, BULK>(p, batch, cl, device, s);
+static cudaError_t launch_select_items(const SelectParams& p, int per_thread, int batch, int cl, int device, bool pdl, cudaStream_t s) {
+    if (per_thread <= 1) return launch_select<1, BULK>(p, batch, cl, device, pdl, s);
+    if (per_thread <= 2) return launch_select<2, BULK>(p, batch, cl, device, pdl, s);
+    if (per_thread <= 4) return launch_select<4, BULK>(p, batch, cl, device, pdl, s);
+    if (per_thread <= 8) return launch_select<8, BULK>(p, batch, cl, device, pdl, s);
+    if (per_thread <= 16) return launch_select<16, BULK>(p, batch, cl, device, pdl, s);
+    return launch_select<32, BULK>(p, batch, cl, device, pdl, s);
 }
 
 }  // namespace embla
@@ -285,8 +289,8 @@ extern "C" EmblaStatus embla_select_keys(EmblaAttn* ctx, const float* scores_dev
     const int per_thread = (n_max + 1024 * cl - 1) / (1024 * cl);
     // bulk copies want 16-byte aligned rows; any other layout takes the lanes' own loads
     const bool bulk = reinterpret_cast<uintptr_t>(scores_dev) % 16 == 0 && scores_stride % 4 == 0;
-    const cudaError_t e = bulk ? launch_select_items<true>(p, per_thread, batch, cl, ctx->device, s)
-                               : launch_select_items<false>(p, per_thread, batch, cl, ctx->device, s);
+    const cudaError_t e = bulk ? launch_select_items<true>(p, per_thread, batch, cl, ctx->device, ctx->pdl != 0, s)
+                               : launch_select_items<false>(p, per_thread, batch, cl, ctx->device, ctx->pdl != 0, s);
     EMBLA_CUDA_TRY(e);
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;

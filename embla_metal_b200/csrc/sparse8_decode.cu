@@ -43,6 +43,8 @@ __global__ void __launch_bounds__(S8_THREADS) sparse8_decode_kernel(const Sparse
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    pdl_wait();
+    pdl_launch_dependents();
     const int S = p.seq_lens[b];
     const bool selecting = S > EMBLA_TOPK + EMBLA_RECENT;
     const int count = selecting ? EMBLA_TOPK + EMBLA_RECENT : S;
@@ -272,7 +274,7 @@ template <int DT, int SB>
 static EmblaStatus launch_sparse8(EmblaAttn* ctx, const Sparse8Params& p, int batch, cudaStream_t s) {
     constexpr size_t smem = 1024 + 2 * CODE_BYTES + 2 * BLK * 4 + 8 * HD * 2;
     dim3 grid(p.max_chunks, p.n_kv_heads, batch);
-    sparse8_decode_kernel<DT, SB><<<grid, S8_THREADS, smem, s>>>(p);
+    EMBLA_CUDA_TRY(launch_kernel(ctx->pdl, sparse8_decode_kernel<DT, SB>, grid, dim3(S8_THREADS), smem, s, p));
     EMBLA_CUDA_TRY(cudaGetLastError());
     (void)ctx;
     return EMBLA_OK;

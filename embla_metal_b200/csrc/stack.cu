@@ -7,6 +7,8 @@
 #include <new>
 #include <vector>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 struct EmblaStack {
@@ -142,6 +144,15 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
     const size_t esz = 2;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int max_len = step->max_seq_len > 0 ? step->max_seq_len : ctx->cfg.max_context;
+    // The step's launches depend on one another in stream order only; with programmatic dependent launch each becomes
+    // resident while the one before it drains (EMBLA_NO_PDL=1 in the environment turns it off).
+    static const bool use_pdl = []() { const char* e = getenv("EMBLA_NO_PDL"); return !(e && e[0] == '1'); }();
+    struct PdlScope {
+        EmblaAttn* c;
+        int old;
+        PdlScope(EmblaAttn* c_, int v) : c(c_), old(c_->pdl) { c->pdl = v; }
+        ~PdlScope() { c->pdl = old; }
+    } pdl_scope(ctx, use_pdl ? 1 : 0);
     for (size_t li = 0; li < st->layers.size(); li++) {
         const EmblaLayerDesc& L = st->layers[li];
         const uint8_t* row = static_cast<const uint8_t*>(step->qkv_dev) + li * step->qkv_layer_stride * esz;
