@@ -52,3 +52,16 @@ def test_product_does_not_import_the_oracle():
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.replace("the oracle", "").replace("CPU oracle", "").replace("oracle's", "").replace(
                     "oracle fixes", ""), f"{f} refers to oracle/"
+
+
+def test_c_caller_compiles_links_and_runs(tmp_path):
+    """A C99 program that includes only the public header, linked against the built library."""
+    import subprocess
+    from embla_metal_b200 import build
+    lib = build.build()
+    exe = str(tmp_path / "abi_check")
+    src = os.path.join(ROOT, "tests", "c_abi", "abi_check.c")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"), src, "-o", exe,
+                    lib, "-Wl,-rpath," + os.path.dirname(lib)], check=True)
+    out = subprocess.run([exe], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.strip() == "ok", out.stdout + out.stderr
