@@ -40,7 +40,7 @@ struct PrefillParams {
     const void* g2;
     void* o;
     int* err;
-    float* partials;      // split-KV: [unit][split][tile][128 rows][128 + 1] fp32 (unnormalised O, row sum)
+    float* partials;      // split-KV: [unit][split][tile][128 + 1 columns][128 rows] fp32 (unnormalised O, then the row sums)
     int* counters;        // [unit] arrivals
     int64_t q_token_stride, q_seq_stride, o_token_stride, o_seq_stride;
     size_t page_bytes;
@@ -418,15 +418,16 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             // unnormalised O and the row sum of this page range into the scratch (zeros if the tile saw no page here)
             tc_fence_after();
             const int unit = (b * gridDim.y + h) * (gridDim.x / p.nsplit) + pair_ix;
-            float* prow = p.partials + ((size_t(unit) * p.nsplit + split) * 2 + x) * (BLK * (HD + 1)) + size_t(r) * (HD + 1);
+            // column-major [128 + 1][128 rows]: the 32 rows of a warp write 32 consecutive floats of a column
+            float* pcol = p.partials + ((size_t(unit) * p.nsplit + split) * 2 + x) * (BLK * (HD + 1)) + r;
 #pragma unroll 1
             for (int cc = 0; cc < 4; cc++) {
                 uint32_t acc[32];
                 if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, acc);
 #pragma unroll
-                for (int e = 0; e < 32; e++) prow[32 * cc + e] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
+                for (int e = 0; e < 32; e++) pcol[size_t(32 * cc + e) * BLK] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
             }
-            prow[HD] = rowsum;
+            pcol[size_t(HD) * BLK] = rowsum;
         } else if (nx > 0) {
             tc_fence_after();
             const float inv = 1.0f / (sqrtf(float(HD)) + rowsum);
@@ -468,23 +469,34 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         __syncthreads();
         if (s_last) {
             __threadfence();
-            // one row a warp at a time, lanes across the head dims: coalesced, and the splits' loads are independent
+            // Per tile: the page ranges' columns are added with the lanes across rows (coalesced, the ranges' loads
+            // independent) into a padded tile in shared memory (the K/V buffers are free), then the rows are written with
+            // the lanes across head dims.
             const size_t sstride = size_t(2) * BLK * (HD + 1);
-            for (int row = warp; row < 2 * BLK; row += PF_THREADS / 32) {
-                const int x = row >> 7, r = row & 127;
-                if (r >= rows[x]) continue;
-                const float* base = p.partials + (size_t(unit) * p.nsplit * 2 + x) * (BLK * (HD + 1)) + size_t(r) * (HD + 1);
-                float den = sqrtf(float(HD)), acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                for (int sp = 0; sp < p.nsplit; sp++) {
-                    const float* q2 = base + sp * sstride;
-                    den += __ldcg(q2 + HD);
+            float* tile = reinterpret_cast<float*>(kvb);          // [128 rows][128 + 1]
+            float* den = tile + BLK * (HD + 1);                   // [128]
+            for (int x = 0; x < 2; x++) {
+                const float* base = p.partials + (size_t(unit) * p.nsplit * 2 + x) * (BLK * (HD + 1));
+                for (int c = warp; c <= HD; c += PF_THREADS / 32) {
+                    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    for (int sp = 0; sp < p.nsplit; sp++) {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) acc[i] += __ldcg(q2 + lane + 32 * i);
+                        for (int i = 0; i < 4; i++) acc[i] += __ldcg(base + sp * sstride + size_t(c) * BLK + lane + 32 * i);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        if (c < HD) tile[(lane + 32 * i) * (HD + 1) + c] = acc[i];
+                        else den[lane + 32 * i] = sqrtf(float(HD)) + acc[i];
+                    }
                 }
-                const float inv = 1.0f / den;
-                const size_t off = size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
+                __syncthreads();
+                for (int r = warp; r < rows[x]; r += PF_THREADS / 32) {
+                    const float inv = 1.0f / den[r];
+                    const size_t off = size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
 #pragma unroll
-                for (int i = 0; i < 4; i++) Act<DT>::store(p.o, off + lane + 32 * i, acc[i] * inv);
+                    for (int i = 0; i < 4; i++) Act<DT>::store(p.o, off + lane + 32 * i, tile[r * (HD + 1) + lane + 32 * i] * inv);
+                }
+                __syncthreads();
             }
         }
     }
@@ -512,9 +524,19 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     // a unit are split over several CTAs whose partial sums the last one adds (ReLU² partials are additive).
     const int pairs = (p.n_tokens + 2 * BLK - 1) / (2 * BLK);
     const int units = pairs * ctx->cfg.n_q_heads * batch;
-    int nsplit = ctx->sm_count / units;
-    nsplit = nsplit < 1 ? 1 : nsplit > 16 ? 16 : nsplit;
-    while (nsplit > 1 && max_pages / nsplit < 8) nsplit--;
+    // Page ranges per unit: the count that minimises (waves of CTAs over the SMs) x (pages of a range + the fixed cost
+    // of a CTA, measured at about 24 pages' worth: query load, TMEM set-up, 132 KB of partials written and added again
+    // by the unit's last CTA), ranges of at least 8 pages, at most 16. At 128 units on 148 SMs one range is best.
+    int nsplit = 1;
+    long best = -1;
+    for (int ns = 1; ns <= 16 && (ns == 1 || max_pages / ns >= 8); ns++) {
+        const long waves = (long(units) * ns + ctx->sm_count - 1) / ctx->sm_count;
+        const long cost = waves * ((max_pages + ns - 1) / ns + 24);
+        if (best < 0 || cost < best) {
+            best = cost;
+            nsplit = ns;
+        }
+    }
     p.nsplit = nsplit;
     p.partials = nullptr;
     p.counters = nullptr;
