@@ -525,13 +525,14 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     const int pairs = (p.n_tokens + 2 * BLK - 1) / (2 * BLK);
     const int units = pairs * ctx->cfg.n_q_heads * batch;
     // Page ranges per unit: the count that minimises (waves of CTAs over the SMs) x (pages of a range + the fixed cost
-    // of a CTA, measured at about 24 pages' worth: query load, TMEM set-up, 132 KB of partials written and added again
-    // by the unit's last CTA), ranges of at least 8 pages, at most 16. At 128 units on 148 SMs one range is best.
+    // of a CTA: about 2 pages' worth for the query load, TMEM set-up and pipeline fill, and when the unit is split about 9
+    // (132 KB of partials written, then added by the unit's last CTA)), ranges of at least 8 pages, at most 16. Measured at
+    // 128 units x 252 pages on 148 SMs: 1 range 0.53 ms, 2: 0.57, 4: 0.59, 8: 0.60 - one range is best there.
     int nsplit = 1;
     long best = -1;
     for (int ns = 1; ns <= 16 && (ns == 1 || max_pages / ns >= 8); ns++) {
         const long waves = (long(units) * ns + ctx->sm_count - 1) / ctx->sm_count;
-        const long cost = waves * ((max_pages + ns - 1) / ns + 24);
+        const long cost = waves * ((max_pages + ns - 1) / ns + (ns > 1 ? 9 : 2));
         if (best < 0 || cost < best) {
             best = cost;
             nsplit = ns;
