@@ -25,7 +25,10 @@
 
 namespace embla {
 
-constexpr int PF_THREADS = 448;   // 8 ReLU² warps, 4 converter warps, TMA producer, MMA issuer
+constexpr int PF_CONV_WARPS = 4;                          // converter warps (8 measured no faster)
+constexpr int PF_PRODUCER = 8 + PF_CONV_WARPS;            // warp roles: 0-7 ReLU², 8.. converters, then TMA producer, MMA issuer
+constexpr int PF_MMA = PF_PRODUCER + 1;
+constexpr int PF_THREADS = (PF_MMA + 1) * 32;
 constexpr int PF_TILE16 = BLK * HD * 2;            // 32 KiB: 128 rows x 128 dims fp16
 constexpr int PF_KVBUFS = 3;
 // alignment slack, 2 Q tiles, 3 converted sides, 3 raw int8 sides, 2 pages' scales, barriers
@@ -76,19 +79,32 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         "r"(accumulate)
         : "memory");
 }
-// 32 consecutive fp32 columns of this thread's TMEM lane
+#define PF_R32_OUT(r)                                                                                                      \
+    "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),  \
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), \
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), \
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+#define PF_R32_INOUT(r)                                                                                                    \
+    "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]),  \
+        "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), \
+        "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), \
+        "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+#define PF_LD32 \
+    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                              \
+    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                                              \
+    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+// 32 consecutive fp32 columns of this thread's TMEM lane, waited for (load and wait are one statement, so that no use
+// of the registers can be scheduled between them)
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    asm volatile(PF_LD32 "\n tcgen05.wait::ld.sync.aligned;" : PF_R32_OUT(r) : "r"(taddr) : "memory");
+}
+// The same load left in flight: the registers hold the data only after tmem_ld_arrived(r).
+__device__ __forceinline__ void tmem_ld32_async(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(PF_LD32 : PF_R32_OUT(r) : "r"(taddr) : "memory");
+}
+// Waits for the loads in flight; the registers pass through the statement, which orders their uses after the wait.
+__device__ __forceinline__ void tmem_ld_arrived(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : PF_R32_INOUT(r) : : "memory");
 }
 // 16 consecutive 32-bit columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -122,10 +138,11 @@ __device__ __forceinline__ uint32_t h2_scaled(uint32_t x, uint32_t sel, __half2 
 // fp16 after the exact widening, so the ReLU² warps need no per-key factors.
 template <int SB>
 __device__ __forceinline__ void convert_side(const uint8_t* raw, uint8_t* dst, int ctid, const uint8_t* scales, float mult) {
+    constexpr int RG = PF_CONV_WARPS / 2;   // groups of 8 rows the converter threads cover at once
     const int rl = ctid & 7, ch = (ctid >> 3) & 7, rg = ctid >> 6;
 #pragma unroll
-    for (int it = 0; it < 8; it++) {
-        const int row = it * 16 + rg * 8 + rl;
+    for (int it = 0; it < BLK / (8 * RG); it++) {
+        const int row = it * 8 * RG + rg * 8 + rl;
         const uint4 w = *reinterpret_cast<const uint4*>(raw + row * 128 + ((ch ^ (row & 7)) << 4));
         const float f = SB == 4 ? reinterpret_cast<const float*>(scales)[row] : __half2float(reinterpret_cast<const __half*>(scales)[row]);
         const __half2 sc = __float2half2_rn(f * mult);
@@ -188,8 +205,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     if (tid == 0) {
         for (int i = 0; i < 3; i++) {
             mbar_init(&raw_full[i], 1);
-            mbar_init(&raw_empty[i], 4);
-            mbar_init(&kv_ready[i], 4);
+            mbar_init(&raw_empty[i], PF_CONV_WARPS);
+            mbar_init(&kv_ready[i], PF_CONV_WARPS);
             mbar_init(&kv_free[i], 1);
         }
         for (int i = 0; i < 2; i++) {
@@ -200,7 +217,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         s_abort = 0;
         fence_barrier_init();
     }
-    if (warp == 13) tmem_alloc(&s_tmem, 512);
+    if (warp == PF_MMA) tmem_alloc(&s_tmem, 512);
 
     // ---- Q tiles: [128 tokens][128 dims] of head h as fp16 in the K-major swizzled layout
     for (int x = 0; x < 2; x++) {
@@ -258,7 +275,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     const uint32_t tmem = s_tmem;
     // TMEM columns: S/P of tile 0 at 0, of tile 1 at 128 (P overwrites the first 64 columns of its S); O at 256, 384
 
-    if (warp == 12) {
+    if (warp == PF_PRODUCER) {
         // ---- TMA producer: conversion c = 2 j + side takes ring slot c % 3; page j's scales go to scl[j & 1]
         if (lane == 0) {
             for (int c = 0; c < 2 * n; c++) {
@@ -277,7 +294,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                                  &raw_full[slot]);
             }
         }
-    } else if (warp == 13) {
+    } else if (warp == PF_MMA) {
         // ---- MMA issuer. Per page: S0(j), PV1(j-1), S1(j), PV0(j): while the ReLU² warps of one tile work on its
         // scores, the tensor pipe runs the other tile's products. All MMAs of one thread execute in issue order,
         // which is what lets P overwrite S and S(j+1) overwrite P(j).
@@ -371,10 +388,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             if (!ok) break;
             tc_fence_after();
             const bool diag = j * BLK + BLK - 1 > p0 + t0[x];   // some (row, key) of this page is masked
+            // chunk cc + 1 of the row is on its way from TMEM while chunk cc is squared and packed
+            uint32_t sbuf[2][32];
+            tmem_ld32(tS + lane_sel, sbuf[0]);
 #pragma unroll
             for (int cc = 0; cc < 4; cc++) {
-                uint32_t s[32];
-                tmem_ld32(tS + 32 * cc + lane_sel, s);
+                uint32_t(&s)[32] = sbuf[cc & 1];
+                if (cc < 3) tmem_ld32_async(tS + 32 * (cc + 1) + lane_sel, sbuf[(cc + 1) & 1]);
                 uint32_t pk[16];
                 if (diag) {
 #pragma unroll
@@ -404,6 +424,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                 }
                 // P (fp16) goes over the S columns already consumed: chunk cc's 16 columns lie inside [0, 32 cc + 32)
                 tmem_st16(tS + 16 * cc + lane_sel, pk);
+                if (cc < 3) tmem_ld_arrived(sbuf[(cc + 1) & 1]);
             }
             tmem_wait_st();
             tc_fence_before();
@@ -502,7 +523,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 13) {
+    if (warp == PF_MMA) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
