@@ -176,6 +176,20 @@ class Attention:
         _check(lib().embla_score_keys(self.handle, pool.handle, C.byref(view), _ptr(q), C.c_int64(q.stride(0)),
                                       _ptr(scores), C.c_int64(scores.stride(1)), _stream()))
 
+    def full_step(self, pool, block_table, seq_lens, layer, q, k, v, o, gains=None, scores=None, max_seq_len=0, norm_k=True):
+        """kv_append of the current token (k, v [batch, >= n_kv_heads * 128]) and full_decode in one launch."""
+        view = self.view(block_table, seq_lens, layer, max_seq_len)
+        qd = self.query(q, gains)
+        _check(lib().embla_attn_full_step(self.handle, pool.handle, C.byref(view), C.byref(qd), _ptr(k), _ptr(v),
+                                          C.c_int64(k.stride(0)), int(norm_k), _ptr(o), C.c_int64(o.stride(0)), _ptr(scores),
+                                          C.c_int64(0 if scores is None else scores.stride(1)), _stream()))
+
+    def score_keys_step(self, pool, block_table, seq_lens, layer, q, k, v, scores, max_seq_len=0, norm_k=True):
+        """kv_append of the current token into the 16-bit pool and score_keys in one launch."""
+        view = self.view(block_table, seq_lens, layer, max_seq_len)
+        _check(lib().embla_score_keys_step(self.handle, pool.handle, C.byref(view), _ptr(q), C.c_int64(q.stride(0)), _ptr(k), _ptr(v),
+                                           C.c_int64(k.stride(0)), int(norm_k), _ptr(scores), C.c_int64(scores.stride(1)), _stream()))
+
     def select_keys(self, scores, seq_lens, idx, max_seq_len=0):
         """idx [batch, n_kv_heads, 1152] uint32 (int32 tensor) <- top 1024 + 128 latest per kv head."""
         _check(lib().embla_select_keys(self.handle, _ptr(scores), C.c_int64(scores.stride(1)), _ptr(seq_lens),

@@ -16,7 +16,7 @@
 //  * SCORES: each consumer thread also takes one key of the page and computes the kv head's query
 //    heads' dots as one fp32 fmaf chain over d = 0..127 (the summation order the CPU oracle fixes),
 //    so the selection that follows is reproducible bit for bit.
-#include "common.cuh"
+#include "kv_row.cuh"
 
 namespace embla {
 
@@ -38,6 +38,11 @@ struct FullDecodeParams {
     int64_t q_stride, o_stride, scores_stride;
     size_t page_bytes;
     int table_stride, layer, n_layers, n_kv_heads, G, scale_bytes, rows_per_page, nsplit, prenormed, ng;
+    // the current token's raw k and v rows, or NULL: appended by this launch (kv_append fused, attention.metal:113-140)
+    const void* k_new;
+    const void* v_new;
+    int64_t kv_stride;
+    int norm_k;
 };
 
 // Row of the 8-key tile that MMA column g of S = Q Kᵀ stands for. Chosen so that both the K loads
@@ -100,6 +105,7 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
     uint64_t* empty = full + STAGES;
     float(*qf)[QF_LD] = reinterpret_cast<float(*)[QF_LD]>(empty + STAGES);   // SCORES only
     __shared__ int s_last, s_failed, s_issued;
+    __shared__ uint64_t patched;   // the appended row is in the staged copy of the last page
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -110,12 +116,17 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
     const int pps = (npages + p.nsplit - 1) / p.nsplit;
     const int pg0 = split * pps;
     const int n = max(0, min(npages, pg0 + pps) - pg0);
+    // The CTA whose range ends with the sequence's last page also appends the current token (position S - 1): its
+    // producer warp quantises the k and v rows, writes them to the page for the steps to come and, because the page
+    // may have been fetched before that write, puts them into the staged copy before the consumers read it.
+    const bool appends = p.k_new != nullptr && n > 0 && pg0 + n == npages;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], NWORK);
         }
+        mbar_init(&patched, 1);
         s_failed = 0;
         s_issued = 0;
         fence_barrier_init();
@@ -163,29 +174,84 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
 
     if (warp == NWORK) {
         // ---- producer: one lane keeps the ring of stages full
-        if (lane == 0) {
-            const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * SB;
-            for (int i = 0; i < n; i++) {
-                const int st = i % STAGES, use = i / STAGES;
-                if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
-                    atomicExch(p.err, ERR_WAIT_EMPTY);
-                    break;
-                }
-                const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
-                const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
-                uint8_t* dst = stages + st * FD_STAGE_BYTES;
-                mbar_expect_tx(&full[st], tx);
-                tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &full[st]);
-                bulk_load_1d(dst + 2 * CODE_BYTES, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB,
-                             &full[st]);
-                *reinterpret_cast<volatile int*>(&s_issued) = i + 1;
+        const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * SB;
+        auto issue = [&](int i) {
+            const int st = i % STAGES, use = i / STAGES;
+            if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
+                atomicExch(p.err, ERR_WAIT_EMPTY);
+                return false;
             }
+            const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
+            const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
+            uint8_t* dst = stages + st * FD_STAGE_BYTES;
+            mbar_expect_tx(&full[st], tx);
+            tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &full[st]);
+            bulk_load_1d(dst + 2 * CODE_BYTES, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB, &full[st]);
+            *reinterpret_cast<volatile int*>(&s_issued) = i + 1;
+            return true;
+        };
+        int next = 0;
+        bool issuing = true;
+        if (lane == 0)
+            for (; next < min(n, STAGES) && issuing; next++) issuing = issue(next);   // the stages start empty: no wait
+        int code[2][4];
+        float rscale[2] = {0.0f, 0.0f};
+        const int row = (S - 1) & (BLK - 1);
+        if (appends) {
+            // the whole warp, while the first pages are in flight
+            const int block = p.block_table[size_t(b) * p.table_stride + npages - 1];
+            uint8_t* page = const_cast<uint8_t*>(p.pool) + ((size_t(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh) * p.page_bytes;
+#pragma unroll
+            for (int side = 0; side < 2; side++) {
+                float x[4];
+                kv_row_load<DT>(side ? p.v_new : p.k_new, size_t(b) * p.kv_stride + size_t(kvh) * HD, side == 0 && p.norm_k != 0, lane, x);
+                kv_row_quantise<DT>(x, code[side], rscale[side]);
+                int8_t* codes = reinterpret_cast<int8_t*>(page) + side * CODE_BYTES + row * HD;
+#pragma unroll
+                for (int i = 0; i < 4; i++) codes[lane + 32 * i] = int8_t(code[side][i]);
+                if (lane == 0) {
+                    uint8_t* sc = page + 2 * CODE_BYTES + side * BLK * SB;
+                    if (SB == 4) reinterpret_cast<float*>(sc)[row] = rscale[side];
+                    else reinterpret_cast<__half*>(sc)[row] = __float2half_rn(rscale[side]);
+                }
+            }
+        }
+        if (lane == 0)
+            for (; next < n && issuing; next++) issuing = issue(next);
+        if (appends) {
+            __syncwarp();
+            const int il = n - 1;
+            uint8_t* Kb = stages + (il % STAGES) * FD_STAGE_BYTES;
+            if (mbar_wait_bounded(&full[il % STAGES], (il / STAGES) & 1)) {
+#pragma unroll
+                for (int side = 0; side < 2; side++) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int d = lane + 32 * i;
+                        Kb[side * CODE_BYTES + row * 128 + (((d >> 4) ^ (row & 7)) << 4) + (d & 15)] = uint8_t(int8_t(code[side][i]));
+                    }
+                    if (lane == 0) {
+                        uint8_t* sc = Kb + 2 * CODE_BYTES + side * BLK * SB;
+                        if (SB == 4) reinterpret_cast<float*>(sc)[row] = rscale[side];
+                        else reinterpret_cast<__half*>(sc)[row] = __float2half_rn(rscale[side]);
+                    }
+                }
+            } else if (lane == 0) {
+                atomicExch(p.err, ERR_WAIT_FULL);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&patched);
         }
     } else if (SCORES && warp >= NCONS) {
         // ---- scoring warps
         for (int i = 0; i < n; i++) {
             const int st = i % STAGES, use = i / STAGES;
             if (!mbar_wait_bounded(&full[st], use & 1)) {
+                atomicExch(p.err, ERR_WAIT_FULL);
+                *reinterpret_cast<volatile int*>(&s_failed) = 1;
+                break;
+            }
+            if (appends && i == n - 1 && !mbar_wait_bounded(&patched, 0)) {
                 atomicExch(p.err, ERR_WAIT_FULL);
                 *reinterpret_cast<volatile int*>(&s_failed) = 1;
                 break;
@@ -273,6 +339,11 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
         for (int i = 0; i < n; i++) {
             const int st = i % STAGES, use = i / STAGES;
             if (!mbar_wait_bounded(&full[st], use & 1)) {
+                atomicExch(p.err, ERR_WAIT_FULL);
+                *reinterpret_cast<volatile int*>(&s_failed) = 1;
+                break;
+            }
+            if (appends && i == n - 1 && !mbar_wait_bounded(&patched, 0)) {
                 atomicExch(p.err, ERR_WAIT_FULL);
                 *reinterpret_cast<volatile int*>(&s_failed) = 1;
                 break;
@@ -476,9 +547,9 @@ static EmblaStatus launch_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, c
     return EMBLA_OK;
 }
 
-extern "C" EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
-                                              const EmblaQuery* q, void* o_dev, int64_t o_stride,
-                                              float* scores_dev, int64_t scores_stride, void* stream) {
+static EmblaStatus full_decode_impl(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view, const EmblaQuery* q,
+                                    void* o_dev, int64_t o_stride, float* scores_dev, int64_t scores_stride, const void* k_new,
+                                    const void* v_new, int64_t kv_stride, int32_t norm_k, void* stream) {
     if (!ctx || !pool || !view || !q || !o_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode: null argument");
     if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_decode: the pool is not int8");
     if (pool->n_kv_heads != ctx->cfg.n_kv_heads)
@@ -496,7 +567,7 @@ extern "C" EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool*
     if (max_len > ctx->cfg.max_context)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode: max_seq_len %d over the context's %d", max_len, ctx->cfg.max_context);
 
-    FullDecodeParams p;
+    FullDecodeParams p = {};
     p.pool = pool->base;
     p.block_table = view->block_table_dev;
     p.seq_lens = view->seq_lens_dev;
@@ -521,6 +592,10 @@ extern "C" EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool*
     p.rows_per_page = pool->rows_per_page;
     p.prenormed = q->prenormed;
     p.ng = q->ng;
+    p.k_new = k_new;
+    p.v_new = v_new;
+    p.kv_stride = kv_stride;
+    p.norm_k = norm_k;
     const int pairs = view->batch * pool->n_kv_heads;
     const int pages = (max_len + BLK - 1) / BLK;
     p.nsplit = choose_splits(pairs, pages, 2 * ctx->sm_count, ctx->partial_slots);
@@ -542,6 +617,20 @@ extern "C" EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool*
     return EMBLA_FD_SG(0);
 #undef EMBLA_FD_SG
 #undef EMBLA_FD
+}
+
+extern "C" EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                              const EmblaQuery* q, void* o_dev, int64_t o_stride,
+                                              float* scores_dev, int64_t scores_stride, void* stream) {
+    return full_decode_impl(ctx, pool, view, q, o_dev, o_stride, scores_dev, scores_stride, nullptr, nullptr, 0, 0, stream);
+}
+
+extern "C" EmblaStatus embla_attn_full_step(EmblaAttn* ctx, EmblaKVPool* pool, const EmblaKVView* view, const EmblaQuery* q,
+                                            const void* k_dev, const void* v_dev, int64_t kv_stride, int32_t norm_k,
+                                            void* o_dev, int64_t o_stride, float* scores_dev, int64_t scores_stride,
+                                            void* stream) {
+    if (!k_dev || !v_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_step: null k or v");
+    return full_decode_impl(ctx, pool, view, q, o_dev, o_stride, scores_dev, scores_stride, k_dev, v_dev, kv_stride, norm_k, stream);
 }
 
 // ---- full-layer decode for callers that must not allocate ---------------------------------------------
@@ -629,7 +718,7 @@ extern "C" EmblaStatus embla_attn_full_decode_noalloc(const EmblaKVPool* pool, c
     // The array keeps what the last call left: counters and the error word must start at zero.
     EMBLA_CUDA_TRY(cudaMemsetAsync(d.scratch, 0, NOALLOC_PART_OFFSET, s));
 
-    FullDecodeParams p;
+    FullDecodeParams p = {};
     p.pool = pool->base;
     p.block_table = view->block_table_dev;
     p.seq_lens = view->seq_lens_dev;

@@ -4,7 +4,7 @@
 // lane + 32 i like the reference. Every fp32 operation is an explicit round-to-nearest intrinsic in
 // the order the CPU oracle uses, so codes and scales are bit-exact. A 16-bit pool (sparse layers that
 // keep their own keys) takes the rows as they are, rounded to the activation dtype.
-#include "common.cuh"
+#include "kv_row.cuh"
 
 namespace embla {
 
@@ -35,19 +35,7 @@ __global__ void __launch_bounds__(128) kv_append_kernel(const AppendParams p) {
     const size_t off = size_t(b) * p.seq_stride + size_t(t) * p.token_stride + size_t(h) * HD;
 
     float x[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) x[i] = Act<DT>::load(src, off + lane + 32 * i);
-    if (!is_v && p.norm_k) {
-        // head_norm without gains (common.metal:30-41): lane sums, then the 32 lanes in lane order
-        float ss = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 4; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
-        float tot = 0.0f;
-        for (int l = 0; l < 32; l++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, ss, l));
-        const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, float(HD)), EPS32)));
-#pragma unroll
-        for (int i = 0; i < 4; i++) x[i] = __fmul_rn(x[i], r);
-    }
+    kv_row_load<DT>(src, off, !is_v && p.norm_k, lane, x);
     const int pos = p.pos0[b] + t;
     const int block = p.block_table[size_t(b) * p.table_stride + pos / BLK];
     const int row = pos % BLK;
@@ -58,23 +46,16 @@ __global__ void __launch_bounds__(128) kv_append_kernel(const AppendParams p) {
         for (int i = 0; i < 4; i++) Act<DT>::store(dst, size_t(row) * HD + lane + 32 * i, x[i]);
         return;
     }
-    float a = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        x[i] = Act<DT>::round(x[i]);
-        a = fmaxf(a, fabsf(x[i]));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-    const float inv = a > 0.0f ? __fdiv_rn(127.0f, a) : 0.0f;
+    int code[4];
+    float scale;
+    kv_row_quantise<DT>(x, code, scale);
     int8_t* codes = reinterpret_cast<int8_t*>(page) + (is_v ? CODE_BYTES : 0) + row * HD;
 #pragma unroll
-    for (int i = 0; i < 4; i++) codes[lane + 32 * i] = int8_t(int(rintf(__fmul_rn(x[i], inv))));
+    for (int i = 0; i < 4; i++) codes[lane + 32 * i] = int8_t(code[i]);
     if (lane == 0) {
-        const float s = __fdiv_rn(a, 127.0f);
         uint8_t* sc = page + 2 * CODE_BYTES + (is_v ? BLK * p.scale_bytes : 0);
-        if (p.scale_bytes == 4) reinterpret_cast<float*>(sc)[row] = s;
-        else reinterpret_cast<__half*>(sc)[row] = __float2half_rn(s);
+        if (p.scale_bytes == 4) reinterpret_cast<float*>(sc)[row] = scale;
+        else reinterpret_cast<__half*>(sc)[row] = __float2half_rn(scale);
     }
 }
 

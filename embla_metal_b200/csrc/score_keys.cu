@@ -9,7 +9,7 @@
 // 0-63 and 64-127); each consumer thread owns one key of the page and reads its row 16 bytes at a
 // time, conflict-free under the swizzle; queries sit in shared memory as stored and are read as
 // broadcast loads. The multiply-adds take the 16-bit operands directly (fma.rn.f32.f16 / .bf16).
-#include "common.cuh"
+#include "kv_row.cuh"
 
 namespace embla {
 
@@ -26,6 +26,13 @@ struct ScoreParams {
     int* err;
     int64_t q_stride, scores_stride;
     int table_stride, layer, n_layers, n_kv_heads, rows_per_page, nsplit;
+    // the current token's raw k and v rows, or NULL: appended to the 16-bit page by this launch (kv_append fused)
+    uint8_t* pool;
+    size_t page_bytes;
+    const void* k_new;
+    const void* v_new;
+    int64_t kv_stride;
+    int norm_k;
 };
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -72,12 +79,18 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
     const int pg0 = split * pps;
     const int n = max(0, min(npages, pg0 + pps) - pg0);
     if (n == 0) return;
+    // The CTA whose range ends with the sequence's last page also appends the current token (position S - 1): its
+    // producer warp writes the k and v rows to the page for the kernels and steps to come and puts the k row into the
+    // staged copy of the page, which may have been fetched before that write.
+    const bool appends = p.k_new != nullptr && pg0 + n == npages;
+    __shared__ uint64_t patched;
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], SK_CONSUMERS);
         }
+        mbar_init(&patched, 1);
         fence_barrier_init();
     }
     for (int i = tid; i < G * HD; i += SK_THREADS)
@@ -85,27 +98,64 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
     __syncthreads();
 
     if (warp == SK_CONSUMERS) {
-        if (lane == 0) {
-            for (int i = 0; i < n; i++) {
-                const int st = i % STAGES, use = i / STAGES;
-                if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
-                    atomicExch(p.err, ERR_WAIT_EMPTY);
-                    break;
-                }
-                const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
-                const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
-                uint8_t* dst = stages + st * SK_STAGE;
-                mbar_expect_tx(&full[st], SK_STAGE);
-                tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &full[st]);
-                tma_load_2d(dst + BLK * 128, &tmap, 128, int(page * p.rows_per_page), &full[st]);
+        auto issue = [&](int i) {
+            const int st = i % STAGES, use = i / STAGES;
+            if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
+                atomicExch(p.err, ERR_WAIT_EMPTY);
+                return false;
             }
+            const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
+            const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
+            uint8_t* dst = stages + st * SK_STAGE;
+            mbar_expect_tx(&full[st], SK_STAGE);
+            tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &full[st]);
+            tma_load_2d(dst + BLK * 128, &tmap, 128, int(page * p.rows_per_page), &full[st]);
+            return true;
+        };
+        int next = 0;
+        bool issuing = true;
+        if (lane == 0)
+            for (; next < min(n, STAGES) && issuing; next++) issuing = issue(next);   // the stages start empty: no wait
+        float xk[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const int row = (S - 1) & (BLK - 1);
+        if (appends) {
+            // the whole warp, while the first pages are in flight: 16-bit pages take the rows rounded to the activation dtype
+            const int block = p.block_table[size_t(b) * p.table_stride + npages - 1];
+            uint8_t* page = p.pool + ((size_t(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh) * p.page_bytes;
+            const size_t off = size_t(b) * p.kv_stride + size_t(kvh) * HD;
+            float xv[4];
+            kv_row_load<DT>(p.k_new, off, p.norm_k != 0, lane, xk);
+            kv_row_load<DT>(p.v_new, off, false, lane, xv);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                Act<DT>::store(page, size_t(row) * HD + lane + 32 * i, xk[i]);
+                Act<DT>::store(page + BLK * HD * 2, size_t(row) * HD + lane + 32 * i, xv[i]);
+            }
+        }
+        if (lane == 0)
+            for (; next < n && issuing; next++) issuing = issue(next);
+        if (appends) {
+            __syncwarp();
+            const int il = n - 1;
+            uint8_t* Kt = stages + (il % STAGES) * SK_STAGE;
+            if (mbar_wait_bounded(&full[il % STAGES], (il / STAGES) & 1)) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int d = lane + 32 * i;
+                    Act<DT>::store(Kt + (d >> 6) * (BLK * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4) + (d & 7) * 2, 0, xk[i]);
+                }
+            } else if (lane == 0) {
+                atomicExch(p.err, ERR_WAIT_FULL);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&patched);
         }
         return;
     }
     const int r = warp * 32 + lane;   // this thread's key of every page
     for (int i = 0; i < n; i++) {
         const int st = i % STAGES, use = i / STAGES;
-        if (!mbar_wait_bounded(&full[st], use & 1)) {
+        if (!mbar_wait_bounded(&full[st], use & 1) || (appends && i == n - 1 && !mbar_wait_bounded(&patched, 0))) {
             atomicExch(p.err, ERR_WAIT_FULL);
             return;
         }
@@ -162,9 +212,9 @@ static EmblaStatus launch_score(EmblaAttn* ctx, const EmblaKVPool* pool, const S
 
 using namespace embla;
 
-extern "C" EmblaStatus embla_score_keys(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
-                                        const void* q_dev, int64_t q_stride, float* scores_dev, int64_t scores_stride,
-                                        void* stream) {
+static EmblaStatus score_keys_impl(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view, const void* q_dev,
+                                   int64_t q_stride, float* scores_dev, int64_t scores_stride, const void* k_new,
+                                   const void* v_new, int64_t kv_stride, int32_t norm_k, void* stream) {
     if (!ctx || !pool || !view || !q_dev || !scores_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_score_keys: null argument");
     if (pool->kv_dtype != EMBLA_KV_16BIT) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_score_keys: the pool is not 16-bit");
     if (pool->n_kv_heads != ctx->cfg.n_kv_heads || view->layer < 0 || view->layer >= pool->n_layers)
@@ -174,7 +224,7 @@ extern "C" EmblaStatus embla_score_keys(EmblaAttn* ctx, const EmblaKVPool* pool,
     const int max_len = view->max_seq_len > 0 ? view->max_seq_len : ctx->cfg.max_context;
     if (scores_stride < max_len)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_score_keys: scores_stride %lld under max_seq_len %d", (long long)scores_stride, max_len);
-    ScoreParams p;
+    ScoreParams p = {};
     p.block_table = view->block_table_dev;
     p.seq_lens = view->seq_lens_dev;
     p.q = q_dev;
@@ -187,6 +237,12 @@ extern "C" EmblaStatus embla_score_keys(EmblaAttn* ctx, const EmblaKVPool* pool,
     p.n_layers = pool->n_layers;
     p.n_kv_heads = pool->n_kv_heads;
     p.rows_per_page = pool->rows_per_page;
+    p.pool = pool->base;
+    p.page_bytes = pool->page_bytes;
+    p.k_new = k_new;
+    p.v_new = v_new;
+    p.kv_stride = kv_stride;
+    p.norm_k = norm_k;
     const int pages = (max_len + BLK - 1) / BLK;
     p.nsplit = choose_splits(view->batch * pool->n_kv_heads, pages, 2 * ctx->sm_count, 1 << 30);
     const int G = ctx->cfg.n_q_heads / ctx->cfg.n_kv_heads;
@@ -201,4 +257,17 @@ extern "C" EmblaStatus embla_score_keys(EmblaAttn* ctx, const EmblaKVPool* pool,
         default: EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_score_keys: %d query heads per kv head (1, 2, 4 or 8)", G);
     }
 #undef EMBLA_SK
+}
+
+extern "C" EmblaStatus embla_score_keys(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                        const void* q_dev, int64_t q_stride, float* scores_dev, int64_t scores_stride,
+                                        void* stream) {
+    return score_keys_impl(ctx, pool, view, q_dev, q_stride, scores_dev, scores_stride, nullptr, nullptr, 0, 0, stream);
+}
+
+extern "C" EmblaStatus embla_score_keys_step(EmblaAttn* ctx, EmblaKVPool* pool, const EmblaKVView* view, const void* q_dev,
+                                             int64_t q_stride, const void* k_dev, const void* v_dev, int64_t kv_stride,
+                                             int32_t norm_k, float* scores_dev, int64_t scores_stride, void* stream) {
+    if (!k_dev || !v_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_score_keys_step: null k or v");
+    return score_keys_impl(ctx, pool, view, q_dev, q_stride, scores_dev, scores_stride, k_dev, v_dev, kv_stride, norm_k, stream);
 }

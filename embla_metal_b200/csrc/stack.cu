@@ -184,14 +184,13 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
             view.block_table_dev = step->full_table_dev;
             view.table_stride = step->full_table_stride;
             if (!view.block_table_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_step: no block table for the full layers");
-            EMBLA_STEP(EMBLA_ENTRY_APPEND, embla_kv_append(ctx, st->full_pool, &view, step->pos_dev, 1, kp, vp, step->qkv_stride,
-                                                           step->qkv_stride, L.norm_k, stream));
             // past topk + recent keys, a full layer followed by sparse layers that share its cache also scores
-            // every key, and the selection runs right after it (Engine.swift:796-797, 819-827)
+            // every key, and the selection runs right after it (Engine.swift:796-797, 819-827); the quantised append
+            // of the current token (Engine.swift:756-762) rides in the same launch
             const bool scoring = L.emit_scores != 0 && max_len > EMBLA_TOPK + EMBLA_RECENT;
             EMBLA_STEP(EMBLA_ENTRY_FULL_DECODE,
-                       embla_attn_full_decode(ctx, st->full_pool, &view, &q, op, step->o_stride, scoring ? st->scores : nullptr,
-                                              st->scores_ld, stream));
+                       embla_attn_full_step(ctx, st->full_pool, &view, &q, kp, vp, step->qkv_stride, L.norm_k, op, step->o_stride,
+                                            scoring ? st->scores : nullptr, st->scores_ld, stream));
             if (scoring)
                 EMBLA_STEP(EMBLA_ENTRY_SELECT, embla_select_keys(ctx, st->scores, st->scores_ld, step->seq_lens_dev, B, max_len,
                                                                  st->idx, stream));
@@ -207,14 +206,16 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
             view.block_table_dev = step->sparse_table_dev;
             view.table_stride = step->sparse_table_stride;
             if (!view.block_table_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_step: no block table for the sparse layers");
-            EMBLA_STEP(EMBLA_ENTRY_APPEND, embla_kv_append(ctx, st->sparse_pool, &view, step->pos_dev, 1, kp, vp, step->qkv_stride,
-                                                           step->qkv_stride, L.norm_k, stream));
             const bool selecting = max_len > EMBLA_TOPK + EMBLA_RECENT;   // Engine.swift:796
             if (selecting) {
-                EMBLA_STEP(EMBLA_ENTRY_SCORE, embla_score_keys(ctx, st->sparse_pool, &view, qp, step->qkv_stride, st->scores,
-                                                               st->scores_ld, stream));
+                // the append of the current token rides in the scoring launch
+                EMBLA_STEP(EMBLA_ENTRY_SCORE, embla_score_keys_step(ctx, st->sparse_pool, &view, qp, step->qkv_stride, kp, vp,
+                                                                    step->qkv_stride, L.norm_k, st->scores, st->scores_ld, stream));
                 EMBLA_STEP(EMBLA_ENTRY_SELECT, embla_select_keys(ctx, st->scores, st->scores_ld, step->seq_lens_dev, B, max_len,
                                                                  st->idx, stream));
+            } else {
+                EMBLA_STEP(EMBLA_ENTRY_APPEND, embla_kv_append(ctx, st->sparse_pool, &view, step->pos_dev, 1, kp, vp, step->qkv_stride,
+                                                               step->qkv_stride, L.norm_k, stream));
             }
             EMBLA_STEP(EMBLA_ENTRY_SPARSE_DECODE, embla_attn_sparse_decode(ctx, st->sparse_pool, &view, &q,
                                                                            selecting ? st->idx : nullptr, op, step->o_stride,

@@ -156,7 +156,7 @@ class DecodeStack:
     def launches_per_step(self):
         """Kernels of this library one step launches."""
         selecting = self.max_seq_len > attn.TOPK + attn.RECENT
-        per = {SLIDING: 1, FULL: 2, SPARSE: 4 if selecting else 2, SPARSE_SHARED: 1}
+        per = {SLIDING: 1, FULL: 1, SPARSE: 3 if selecting else 2, SPARSE_SHARED: 1}
         n = sum(per[k] for k in self.kinds)
         if selecting:   # a full layer followed by a shared-cache sparse layer also selects
             n += sum(1 for i, k in enumerate(self.kinds[:-1]) if k == FULL and self.kinds[i + 1] == SPARSE_SHARED)

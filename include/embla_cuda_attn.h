@@ -142,6 +142,14 @@ EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, cons
                                    const EmblaQuery* q, void* o_dev, int64_t o_stride,
                                    float* scores_dev, int64_t scores_stride, void* stream);
 
+/* The reference's per-layer pair kv_append + attn_full8 (Engine.swift:756-762, 796-818) in one launch: the current
+ * token of every sequence (position seq_lens_dev[b] - 1) is quantised from its raw k and v rows (k_dev, v_dev:
+ * [batch][kv_stride] elements, kv head h at h * 128; `norm_k` as embla_kv_append) into the view's layer, and the
+ * attention sees it. Same result as embla_kv_append followed by embla_attn_full_decode. */
+EmblaStatus embla_attn_full_step(EmblaAttn* ctx, EmblaKVPool* pool, const EmblaKVView* view, const EmblaQuery* q,
+                                 const void* k_dev, const void* v_dev, int64_t kv_stride, int32_t norm_k,
+                                 void* o_dev, int64_t o_stride, float* scores_dev, int64_t scores_stride, void* stream);
+
 /* No counterpart in the reference (its engine owns every buffer and allocates them all at init).
  * The same attention as embla_attn_full_decode (without scores) for callers that cannot allocate
  * device memory where they run attention — a server that gave all device memory to its own arena at
@@ -170,6 +178,13 @@ EmblaStatus embla_attn_full_decode_noalloc(const EmblaKVPool* pool, const EmblaK
 EmblaStatus embla_score_keys(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
                              const void* q_dev, int64_t q_stride, float* scores_dev, int64_t scores_stride,
                              void* stream);
+
+/* embla_kv_append of the current token (position seq_lens_dev[b] - 1; raw rows k_dev, v_dev: [batch][kv_stride]
+ * elements, kv head h at h * 128; `norm_k` as embla_kv_append) into the 16-bit pool and embla_score_keys in one launch;
+ * the appended key is scored too, and the row is in the pool for the attention that follows. */
+EmblaStatus embla_score_keys_step(EmblaAttn* ctx, EmblaKVPool* pool, const EmblaKVView* view, const void* q_dev,
+                                  int64_t q_stride, const void* k_dev, const void* v_dev, int64_t kv_stride,
+                                  int32_t norm_k, float* scores_dev, int64_t scores_stride, void* stream);
 
 /* Replaces select_keys (attention.metal:655-744; dispatch Engine.swift:819-827): for every sequence
  * with seq_len > 1152 and every kv head, idx[b][kv head][0..1151] = the 1024 highest-scoring keys among

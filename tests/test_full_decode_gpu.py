@@ -123,3 +123,45 @@ def test_kv_append_bit_exact():
                     assert np.float32(gks) == ksc[0] and np.float32(gvs) == vsc[0]
         pool.close()
         ctx.close()
+
+
+@pytest.mark.parametrize("dtype,scale_f16,Hkv,norm_k", [(orc.F16, True, 4, False), (orc.BF16, False, 2, True)])
+def test_fused_append_equals_append_then_decode(dtype, scale_f16, Hkv, norm_k):
+    """embla_attn_full_step writes the same page bytes and outputs as embla_kv_append + embla_attn_full_decode, with and
+    without scores, for positions at the start, inside and at the end of a page and for split and unsplit key ranges."""
+    import torch
+    from embla_metal_b200 import attn
+    rng = np.random.default_rng(31)
+    S_list = [1, 2, 128, 129, 300, 1024, 4097, 9000]
+    B, Hq = len(S_list), 16
+    npg = (max(S_list) + 127) // 128
+    ctx = attn.Attention(Hq, Hkv, dtype, max_batch=B, max_context=npg * 128)
+    pools = [attn.KVPool(1, Hkv, B * npg, attn.KV_INT8, attn.SCALE_F16 if scale_f16 else attn.SCALE_F32) for _ in range(2)]
+    table = torch.from_numpy(rng.permutation(B * npg).reshape(B, npg).astype(np.int32)).cuda()
+    fill = torch.from_numpy(rng.integers(0, 256, pools[0].raw().shape, dtype=np.uint8)).cuda()
+    for pool in pools:
+        raw = pool.raw()
+        raw.copy_(fill)
+        sc = raw[..., 32768:].view(torch.float16 if scale_f16 else torch.float32)
+        sc.copy_(torch.rand(sc.shape, device="cuda") * 0.015 + 0.005)
+    pools[1].raw().copy_(pools[0].raw())
+    lens = torch.tensor(S_list, dtype=torch.int32, device="cuda")
+    q = util.act_tensor(orc.to_bits(rng.standard_normal((B, Hq * 128)), dtype), dtype)
+    k = util.act_tensor(orc.to_bits(rng.standard_normal((B, Hkv * 128)) * 2, dtype), dtype)
+    v = util.act_tensor(orc.to_bits(rng.standard_normal((B, Hkv * 128)), dtype), dtype)
+    for want_scores in (False, True):
+        o0, o1 = torch.zeros_like(q), torch.zeros_like(q)
+        sc0 = torch.zeros(B, Hkv, npg * 128, device="cuda") if want_scores else None
+        sc1 = torch.zeros_like(sc0) if want_scores else None
+        ctx.kv_append(pools[0], table, 0, lens - 1, k.view(B, 1, -1), v.view(B, 1, -1), norm_k=norm_k)
+        ctx.full_decode(pools[0], table, lens, 0, q, o0, scores=sc0, max_seq_len=max(S_list))
+        ctx.full_step(pools[1], table, lens, 0, q, k, v, o1, scores=sc1, max_seq_len=max(S_list), norm_k=norm_k)
+        ctx.check()
+        assert torch.equal(pools[0].raw(), pools[1].raw()), "the fused append wrote other bytes"
+        assert torch.equal(o0.view(torch.int16), o1.view(torch.int16)), "outputs differ"
+        if want_scores:
+            for b, S in enumerate(S_list):
+                assert torch.equal(sc0[b, :, :S], sc1[b, :, :S]), f"scores of sequence {b} differ"
+    for pool in pools:
+        pool.close()
+    ctx.close()

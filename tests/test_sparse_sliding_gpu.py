@@ -253,3 +253,36 @@ def test_select_unaligned_rows_and_special_values(B):
     for b, S in enumerate(S_list):
         assert np.array_equal(got[b].view(np.uint32), orc.select_keys(scores[b], S)), f"sequence {b}"
     ctx.close()
+
+
+@pytest.mark.parametrize("dtype,Hkv,norm_k", [(orc.F16, 4, False), (orc.BF16, 2, True)])
+def test_fused_append_in_scoring_equals_append_then_score(dtype, Hkv, norm_k):
+    """embla_score_keys_step writes the same 16-bit rows and the same scores as embla_kv_append + embla_score_keys."""
+    import torch
+    from embla_metal_b200 import attn
+    rng = np.random.default_rng(41)
+    S_list = [1, 128, 129, 1153, 2000, 4097]
+    B, Hq = len(S_list), 16
+    npg = (max(S_list) + 127) // 128
+    ctx = attn.Attention(Hq, Hkv, dtype, max_batch=B, max_context=npg * 128)
+    tdt = torch.bfloat16 if dtype == orc.BF16 else torch.float16
+    pools = [attn.KVPool(1, Hkv, B * npg, attn.KV_16BIT) for _ in range(2)]
+    table = torch.from_numpy(rng.permutation(B * npg).reshape(B, npg).astype(np.int32)).cuda()
+    pools[0].raw().view(tdt).copy_(torch.randn(pools[0].raw().view(tdt).shape, device="cuda").to(tdt))
+    pools[1].raw().copy_(pools[0].raw())
+    lens = torch.tensor(S_list, dtype=torch.int32, device="cuda")
+    q = util.act_tensor(orc.to_bits(rng.standard_normal((B, Hq * 128)), dtype), dtype)
+    k = util.act_tensor(orc.to_bits(rng.standard_normal((B, Hkv * 128)) * 2, dtype), dtype)
+    v = util.act_tensor(orc.to_bits(rng.standard_normal((B, Hkv * 128)), dtype), dtype)
+    sc0 = torch.zeros(B, Hkv, npg * 128, device="cuda")
+    sc1 = torch.zeros_like(sc0)
+    ctx.kv_append(pools[0], table, 0, lens - 1, k.view(B, 1, -1), v.view(B, 1, -1), norm_k=norm_k)
+    ctx.score_keys(pools[0], table, lens, 0, q, sc0, max_seq_len=max(S_list))
+    ctx.score_keys_step(pools[1], table, lens, 0, q, k, v, sc1, max_seq_len=max(S_list), norm_k=norm_k)
+    ctx.check()
+    assert torch.equal(pools[0].raw(), pools[1].raw()), "the fused append wrote other bytes"
+    for b, S in enumerate(S_list):
+        assert torch.equal(sc0[b, :, :S], sc1[b, :, :S]), f"scores of sequence {b} differ"
+    for pool in pools:
+        pool.close()
+    ctx.close()

@@ -44,7 +44,7 @@ def test_reference_block_through_the_stack():
     assert torch.equal(o, got[4])
     st.ctx.sliding_decode(st.rings[0], st.seq_lens, q(0), o)
     assert torch.equal(o, got[0])
-    assert st.launches_per_step() == 1 + 3 + 1 + 1 + 4
+    assert st.launches_per_step() == 1 + 2 + 1 + 1 + 3   # sliding; full (append fused) + select; shared x 2; score (append fused) + select + attend
     st.close()
 
 
