@@ -46,7 +46,9 @@ __device__ __forceinline__ uint32_t warp_incl_scan(uint32_t x, int lane) {
 // ITEMS: keys a lane holds in registers. CTA `rank` of the cluster owns 1024 * ITEMS contiguous keys, its warp w
 // the keys [w0, w0 + 32 * ITEMS), and round i takes the 32 consecutive keys w0 + 32 i + lane. The scores are read
 // from global memory once, all loads in flight together; every pass after that runs on registers.
-template <int ITEMS, bool BULK>
+// SINGLE: one CTA per pair (launched without a cluster) - block barriers and plain shared-memory loads take the place of
+// the cluster barriers and of the loads through the cluster's shared-memory window.
+template <int ITEMS, bool BULK, bool SINGLE>
 __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
@@ -56,7 +58,11 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
     __shared__ uint32_t wcnt[2][SEL_WARPS];        // this CTA's per-warp counts of greater / equal keys
     __shared__ uint32_t base[2][SEL_WARPS + 1];
 
-    const int CL = int(cluster.num_blocks()), rank = int(cluster.block_rank());
+    const int CL = SINGLE ? 1 : int(cluster.num_blocks()), rank = SINGLE ? 0 : int(cluster.block_rank());
+    auto csync = [&]() {
+        if (SINGLE) __syncthreads();
+        else cluster.sync();
+    };
     const int kvh = blockIdx.x / CL, b = blockIdx.y;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     pdl_wait();
@@ -129,15 +135,20 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
             }
             if (in) atomicAdd(&h[digit], 1u);
         }
-        cluster.sync();
+        csync();
         // counts above each digit, from the top, over the cluster: the digit whose bucket holds the k-th largest.
         // Thread t takes digits nb - 1 - 2t and nb - 2 - 2t.
         uint32_t c0 = 0, c1 = 0;
         if (2 * t < nb) {
-            for (int r = 0; r < CL; r++) {
-                const uint32_t* hr = cluster.map_shared_rank(h, r);
-                c0 += hr[nb - 1 - 2 * t];
-                c1 += hr[nb - 2 - 2 * t];
+            if (SINGLE) {
+                c0 = h[nb - 1 - 2 * t];
+                c1 = h[nb - 2 - 2 * t];
+            } else {
+                for (int r = 0; r < CL; r++) {
+                    const uint32_t* hr = cluster.map_shared_rank(h, r);
+                    c0 += hr[nb - 1 - 2 * t];
+                    c1 += hr[nb - 2 - 2 * t];
+                }
             }
         }
         const uint32_t s = c0 + c1, incl = warp_incl_scan(s, lane);
@@ -187,12 +198,12 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
         wcnt[0][warp] = cg_incl;
         wcnt[1][warp] = ce_incl;
     }
-    cluster.sync();
+    csync();
     // offsets of this CTA's warps: everything counted by lower ranks, then this CTA's lower warps
     if (warp < 2) {
         uint32_t before = 0, all = 0;
         for (int r = 0; r < CL; r++) {
-            uint32_t sum = cluster.map_shared_rank(&wcnt[warp][0], r)[lane];
+            uint32_t sum = SINGLE ? wcnt[warp][lane] : cluster.map_shared_rank(&wcnt[warp][0], r)[lane];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             if (r < rank) before += sum;
@@ -222,15 +233,15 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
         if (rank == 0)
             for (int j = t; j < EMBLA_RECENT; j += SEL_T) out[EMBLA_TOPK + j] = uint32_t(n + j);
     }
-    cluster.sync();   // no CTA leaves while another may still read its shared memory
+    if (!SINGLE) cluster.sync();   // no CTA leaves while another may still read its shared memory
 }
 
-template <int ITEMS, bool BULK>
-static cudaError_t launch_select(const SelectParams& p, int batch, int cl, int device, bool pdl, cudaStream_t s) {
+template <int ITEMS, bool BULK, bool SINGLE>
+static cudaError_t launch_select_kernel(const SelectParams& p, int batch, int cl, int device, bool pdl, cudaStream_t s) {
     const size_t smem = BULK ? size_t(SEL_T) * ITEMS * 4 : 0;
     static bool configured[64] = {};
     if (smem > 0 && !configured[device & 63]) {
-        cudaError_t e = cudaFuncSetAttribute(select_keys_kernel<ITEMS, BULK>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        cudaError_t e = cudaFuncSetAttribute(select_keys_kernel<ITEMS, BULK, SINGLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
         configured[device & 63] = true;
     }
@@ -246,9 +257,16 @@ static cudaError_t launch_select(const SelectParams& p, int batch, int cl, int d
     at[0].val.clusterDim.z = 1;
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at;
-    cfg.numAttrs = pdl ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, select_keys_kernel<ITEMS, BULK>, p);
+    // without a cluster only the dependent-launch attribute (the second entry) applies
+    cfg.attrs = SINGLE ? at + 1 : at;
+    cfg.numAttrs = (SINGLE ? 0 : 1) + (pdl ? 1 : 0);
+    return cudaLaunchKernelEx(&cfg, select_keys_kernel<ITEMS, BULK, SINGLE>, p);
+}
+
+template <int ITEMS, bool BULK>
+static cudaError_t launch_select(const SelectParams& p, int batch, int cl, int device, bool pdl, cudaStream_t s) {
+    return cl == 1 ? launch_select_kernel<ITEMS, BULK, true>(p, batch, cl, device, pdl, s)
+                   : launch_select_kernel<ITEMS, BULK, false>(p, batch, cl, device, pdl, s);
 }
 
 template <bool BULK>

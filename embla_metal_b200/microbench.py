@@ -91,9 +91,28 @@ def prefill(tokens, cached):
           f"(min-time {flop / ts[0] / 1e9:.0f}), {tokens / med * 1e3:.0f} tok/s")
 
 
+def sliding_prefill(tokens, cached, window):
+    """BASELINE config 1 (b): a chunk of `tokens` appended after `cached` positions of a sliding layer."""
+    ring_slots = 4096
+    ctx = attn.Attention(HQ, HKV, attn.F16, 1, ring_slots)
+    ring = attn.Ring(1, HKV, ring_slots, window, torch.float16)
+    ring.k.copy_(torch.randn(ring.k.shape, device="cuda").half())
+    ring.v.copy_(torch.randn(ring.v.shape, device="cuda").half())
+    q = torch.randn(1, tokens, HQ * 128, device="cuda", dtype=torch.float16)
+    o = torch.zeros_like(q)
+    pos0 = torch.tensor([cached], dtype=torch.int32, device="cuda")
+    ts = _events(lambda: attn.sliding_prefill(ctx, ring, pos0, q, o))
+    ctx.check()
+    flop = 4 * HQ * 128 * sum(min(cached + i + 1, window) for i in range(tokens))
+    med = ts[len(ts) // 2]
+    print(f"sliding_prefill {tokens} tokens after {cached}, window {window}: {med:.4f} ms, {flop / med / 1e9:.1f} TFLOP/s, "
+          f"{tokens / med * 1e3:.0f} tok/s")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["full_decode", "sparse", "prefill"])
+    ap.add_argument("case", choices=["full_decode", "sparse", "prefill", "sliding_prefill"])
+    ap.add_argument("--window", type=int, default=1024)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--scores", action="store_true")
     ap.add_argument("--tokens", type=int, default=2048)
@@ -103,6 +122,8 @@ def main():
         full_decode(a.batch, a.scores)
     elif a.case == "sparse":
         sparse(a.batch)
+    elif a.case == "sliding_prefill":
+        sliding_prefill(a.tokens, a.cached if a.cached != 30720 else 2048, a.window)
     else:
         prefill(a.tokens, a.cached)
 
