@@ -133,10 +133,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Waits for the barrier's phase `parity`; gives up after WAIT_LIMIT tries and returns false.
+// Waits for the barrier's phase `parity`; gives up after WAIT_LIMIT tries or WAIT_CYCLES clocks (about half a second:
+// one try may itself suspend the thread for a while), whichever comes first, and returns false.
+constexpr long long WAIT_CYCLES = 1ll << 30;
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > WAIT_CYCLES) return false;
+    }
     return false;
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }

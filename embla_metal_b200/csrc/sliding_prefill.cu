@@ -11,6 +11,7 @@
 // This version re-reads the window for every 8 rows (it lives in L2); a tcgen05 variant with 128-token
 // tiles is the follow-up.
 #include "attn16_common.cuh"
+#include "sliding_prefill_tc.cuh"
 
 namespace embla {
 
@@ -262,6 +263,31 @@ extern "C" EmblaStatus embla_attn_sliding_prefill(EmblaAttn* ctx, const EmblaRin
     p.ring = ring->ring;
     p.window = ring->window;
     fill_rope_freq(p.rope_freq);
+    // Whole chunks of fp16 activations over rings of a multiple of 128 slots run on the tcgen05 kernel
+    // (sliding_prefill_tc.cu); short chunks, bf16 and other rings take the kernel below.
+    if (ctx->cfg.act_dtype == EMBLA_F16 && n_tokens >= 64 && ring->ring % BLK == 0 && ring->seq_stride % 8 == 0 &&
+        reinterpret_cast<uintptr_t>(ring->k_dev) % 16 == 0 && reinterpret_cast<uintptr_t>(ring->v_dev) % 16 == 0 &&
+        q_token_stride % 8 == 0 && o_token_stride % 8 == 0 && o_seq_stride % 8 == 0 &&
+        reinterpret_cast<uintptr_t>(o_dev) % 16 == 0) {
+        SlidingTcParams t = {};
+        t.pos0 = pos0_dev;
+        t.q = q->q_dev;
+        t.g1 = q->g1_dev;
+        t.o = o_dev;
+        t.err = ctx->err_dev;
+        t.q_token_stride = q_token_stride;
+        t.q_seq_stride = q->q_stride;
+        t.o_token_stride = o_token_stride;
+        t.o_seq_stride = o_seq_stride;
+        t.n_tokens = n_tokens;
+        t.n_kv_heads = ctx->cfg.n_kv_heads;
+        t.G = G;
+        t.prenormed = q->prenormed;
+        t.ring = ring->ring;
+        t.window = ring->window;
+        fill_rope_freq(t.rope_freq);
+        return launch_sliding_prefill_tc(ctx, ring, t, batch, static_cast<cudaStream_t>(stream));
+    }
     constexpr size_t smem = 1024 + 2 * SP_TILE + 8 * HD * 2;
     const int tpc = 8 / G;
     dim3 grid((n_tokens + tpc - 1) / tpc, p.n_kv_heads, batch);

@@ -9,7 +9,7 @@ from tests import util
 pytestmark = pytest.mark.gpu
 
 
-def _case(T, p0, W, RING, Hq, Hkv, dtype, seed, gains=False, rows=None):
+def _case(T, p0, W, RING, Hq, Hkv, dtype, seed, gains=False, rows=None, poison=False):
     import torch
     from embla_metal_b200 import attn
     rng = np.random.default_rng(seed)
@@ -20,8 +20,9 @@ def _case(T, p0, W, RING, Hq, Hkv, dtype, seed, gains=False, rows=None):
     if gains:
         qg = orc.to_bits(rng.standard_normal(128) * 0.1, dtype)
         kg = orc.to_bits(rng.standard_normal(128) * 0.1, dtype)
-    rk = np.zeros((Hkv, RING, 128), np.uint16)
-    rv = np.zeros((Hkv, RING, 128), np.uint16)
+    # slots no token was written to: zeros, or (poison) NaN bit patterns as uninitialised memory may hold
+    rk = np.full((Hkv, RING, 128), 0x7FFF if poison else 0, np.uint16)
+    rv = np.full((Hkv, RING, 128), 0x7FFF if poison else 0, np.uint16)
     n_hist = min(p0, W)                          # the cached positions the chunk can still see
     if n_hist:
         hk = orc.to_bits(rng.standard_normal((n_hist, Hkv, 128)), dtype)
@@ -62,3 +63,14 @@ def test_sliding_prefill_reference_shape_norm_rope():
     # the reference's window (128), bf16, fused head norm + RoPE, ring wrap inside the chunk
     _case(300, 3900, 128, 4096, 16, 4, orc.BF16, seed=8, gains=True)
     _case(70, 10, 128, 4096, 8, 1, orc.BF16, seed=9, gains=True)      # 8 query heads on one kv head: one token a CTA
+
+
+def test_sliding_prefill_tensor_core_path_edges():
+    """fp16 chunks of 64 tokens or more over rings of a multiple of 128 slots run on tcgen05: chunk ends inside a block
+    with never-written (NaN) slots after it, windows shorter and longer than a block, fused head norm + RoPE, one and
+    eight query heads a kv head, a chunk that wraps the ring."""
+    _case(130, 0, 256, 1024, 16, 4, orc.F16, seed=11, poison=True)
+    _case(200, 70, 100, 1024, 16, 4, orc.F16, seed=12, poison=True)
+    _case(333, 900, 1024, 4096, 16, 4, orc.F16, seed=13, gains=True, poison=True)
+    _case(96, 5000, 300, 1024, 8, 1, orc.F16, seed=14, gains=True)
+    _case(128, 8100, 512, 2048, 4, 4, orc.F16, seed=15)
