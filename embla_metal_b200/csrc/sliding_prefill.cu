@@ -263,9 +263,9 @@ extern "C" EmblaStatus embla_attn_sliding_prefill(EmblaAttn* ctx, const EmblaRin
     p.ring = ring->ring;
     p.window = ring->window;
     fill_rope_freq(p.rope_freq);
-    // Whole chunks of fp16 activations over rings of a multiple of 128 slots run on the tcgen05 kernel
-    // (sliding_prefill_tc.cu); short chunks, bf16 and other rings take the kernel below.
-    if (ctx->cfg.act_dtype == EMBLA_F16 && n_tokens >= 64 && ring->ring % BLK == 0 && ring->seq_stride % 8 == 0 &&
+    // Whole chunks over rings of a multiple of 128 slots run on the tcgen05 kernel (sliding_prefill_tc.cu); short chunks
+    // and other rings take the kernel below.
+    if (n_tokens >= 64 && ring->ring % BLK == 0 && ring->seq_stride % 8 == 0 &&
         reinterpret_cast<uintptr_t>(ring->k_dev) % 16 == 0 && reinterpret_cast<uintptr_t>(ring->v_dev) % 16 == 0 &&
         q_token_stride % 8 == 0 && o_token_stride % 8 == 0 && o_seq_stride % 8 == 0 &&
         reinterpret_cast<uintptr_t>(o_dev) % 16 == 0) {

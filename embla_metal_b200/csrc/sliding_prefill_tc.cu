@@ -1,6 +1,6 @@
-// Prefill-chunk attention of the sliding layers on the tensor cores (fp16 activations, rings of a multiple of 128
+// Prefill-chunk attention of the sliding layers on the tensor cores (rings of a multiple of 128
 // slots): every new token attends its last `window` positions, all already in the ring. Replaces attn_sliding_b /
-// attn_sliding8_b (Sources/EmblaMetal/Kernels/prefill.metal:129-180, 439-548) for whole chunks; short chunks, bf16
+// attn_sliding8_b (Sources/EmblaMetal/Kernels/prefill.metal:129-180, 439-548) for whole chunks; short chunks
 // and odd rings take the mma.sync kernel of sliding_prefill.cu.
 //
 //   S = Q Kᵀ   tcgen05.mma kind::f16, M = 128 query rows, N = 128 keys (one 128-slot block of the ring), K = 128 dims
@@ -13,7 +13,8 @@
 //
 // The softmax takes two passes over the blocks instead of rescaling O in TMEM: pass A runs only S = Q Kᵀ and the
 // softmax warps keep each row's maximum over its window; pass B runs S again, p = exp(s - max) (masked to the row's own
-// window), P as fp16 over the consumed S columns, O += P V; at the end O / Σp. A window is at most ten blocks, so
+// window), P in the activation dtype over the consumed S columns (bfloat16: P = hi + lo, two products, so that its
+// rounding stays below 2^-16), O += P V; at the end O / Σp. A window is at most ten blocks, so
 // the second Q Kᵀ costs half as much again as one pass and keeps the tensor pipe's work free of read-modify-write on O.
 //   warps 0-7   two warpgroups, one per tile, one query row a thread
 //   warp 8      TMA producer (3 buffers of 32 KiB: K blocks in pass A, K and V blocks in pass B)
@@ -161,12 +162,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
                 if (!mbar_wait_bounded(&kv_ready[cc % ST_BUFS], (cc / ST_BUFS) & 1)) return false;
                 return !(clean_v && cc == 3 * nblk - 1) || mbar_wait_bounded(v_clean, 0);
             };
+            // bfloat16 operands: formats of A and B in the instruction descriptor (bits 7-9 and 10-12)
+            constexpr uint32_t fmt = DT == EMBLA_BF16 ? (1u << 7) | (1u << 10) : 0u;
             auto issue_s = [&](int x, int cc) {
                 const uint32_t ka = smem_u32(kvb + (cc % ST_BUFS) * ST_TILE);
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
                     const uint32_t koff = (ks >> 2) * (BLK * 128) + (ks & 3) * 32;
-                    umma_ss(tmem + 128 * x, umma_desc(qa + x * ST_TILE + koff, 16, 1024), umma_desc(ka + koff, 16, 1024), PF_IDESC_QK, ks > 0);
+                    umma_ss(tmem + 128 * x, umma_desc(qa + x * ST_TILE + koff, 16, 1024), umma_desc(ka + koff, 16, 1024), PF_IDESC_QK | fmt, ks > 0);
                 }
                 tc_commit(&s_full[x]);
                 us[x]++;
@@ -174,9 +177,16 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
             auto issue_pv = [&](int x, int cc, bool first) {
                 const uint32_t va = smem_u32(kvb + (cc % ST_BUFS) * ST_TILE);
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++)
-                    umma_ts(tmem + 256 + 128 * x, tmem + 128 * x + 8 * ks, umma_desc(va + ks * 2048, BLK * 128, 1024), PF_IDESC_PV,
-                            (!first) | (ks > 0));
+                for (int ks = 0; ks < 8; ks++) {
+                    const uint64_t vd = umma_desc(va + ks * 2048, BLK * 128, 1024);
+                    if (DT == EMBLA_F16) {
+                        umma_ts(tmem + 256 + 128 * x, tmem + 128 * x + 8 * ks, vd, PF_IDESC_PV, (!first) | (ks > 0));
+                    } else {   // keys 64 h .. 64 h + 63: P hi at columns 64 h, P lo at 64 h + 32
+                        const uint32_t pa = tmem + 128 * x + 64 * (ks >> 2) + 8 * (ks & 3);
+                        umma_ts(tmem + 256 + 128 * x, pa, vd, PF_IDESC_PV | fmt, (!first) | (ks > 0));
+                        umma_ts(tmem + 256 + 128 * x, pa + 32, vd, PF_IDESC_PV | fmt, 1);
+                    }
+                }
             };
             // the tile's warps are done with the S product before its us[x]-th (they arrive once per product)
             auto wait_tile = [&](int x) { return us[x] == 0 || mbar_wait_bounded(&p_ready[x], (us[x] - 1) & 1); };
@@ -277,30 +287,54 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
                 ok = __all_sync(0xffffffffu, mbar_wait_bounded(&s_full[x], u & 1));
                 if (!ok) break;   // (warp-uniform: the TMEM loads below are warp-collective)
                 tc_fence_after();
+                // weights of 32 keys from kb on: exp(s - max) masked to the row's window, summed in fp32, packed in pairs
+                auto weights = [&](const uint32_t (&sv)[32], int kb, uint32_t (&hi)[16], uint32_t (&lo)[16]) {
 #pragma unroll
-                for (int cc = 0; cc < 4; cc++) {
-                    uint32_t s[32];
-                    tmem_ld32(tS + 32 * cc + lane_sel, s);
-                    const int kb = j * BLK + 32 * cc;
-                    if (pass == 0) {
+                    for (int e = 0; e < 32; e += 2) {
+                        const int kp = kb + e;
+                        float w0 = exp2f(fmaf(__uint_as_float(sv[e]), c2, -mc)), w1 = exp2f(fmaf(__uint_as_float(sv[e + 1]), c2, -mc));
+                        if (!(row_ok && kp <= pos_r && kp > pos_r - p.window)) w0 = 0.0f;
+                        if (!(row_ok && kp + 1 <= pos_r && kp + 1 > pos_r - p.window)) w1 = 0.0f;
+                        rowsum += w0 + w1;
+                        hi[e >> 1] = pack_act2<DT>(w0, w1);
+                        if (DT == EMBLA_BF16) lo[e >> 1] = pack_act2<DT>(w0 - Act<EMBLA_BF16>::round(w0), w1 - Act<EMBLA_BF16>::round(w1));
+                    }
+                };
+                if (pass == 0) {
+#pragma unroll
+                    for (int cc = 0; cc < 4; cc++) {
+                        uint32_t s[32];
+                        tmem_ld32(tS + 32 * cc + lane_sel, s);
+                        const int kb = j * BLK + 32 * cc;
 #pragma unroll
                         for (int e = 0; e < 32; e++) {
                             const int kp = kb + e;
                             if (kp <= pos_r && kp > pos_r - p.window) mrow = fmaxf(mrow, __uint_as_float(s[e]));
                         }
-                    } else {
-                        uint32_t pk[16];
+                    }
+                } else if (DT == EMBLA_F16) {
 #pragma unroll
-                        for (int e = 0; e < 32; e += 2) {
-                            const int kp = kb + e;
-                            float w0 = exp2f(fmaf(__uint_as_float(s[e]), c2, -mc)), w1 = exp2f(fmaf(__uint_as_float(s[e + 1]), c2, -mc));
-                            if (!(row_ok && kp <= pos_r && kp > pos_r - p.window)) w0 = 0.0f;
-                            if (!(row_ok && kp + 1 <= pos_r && kp + 1 > pos_r - p.window)) w1 = 0.0f;
-                            rowsum += w0 + w1;
-                            pk[e >> 1] = pack_h2(w0, w1);
-                        }
-                        // P (fp16) goes over the S columns already consumed: chunk cc's 16 columns lie inside [0, 32 cc + 32)
+                    for (int cc = 0; cc < 4; cc++) {
+                        uint32_t s[32], pk[16], unused[16];
+                        tmem_ld32(tS + 32 * cc + lane_sel, s);
+                        weights(s, j * BLK + 32 * cc, pk, unused);
+                        // P goes over the S columns already consumed: chunk cc's 16 columns lie inside [0, 32 cc + 32)
                         tmem_st16(tS + 16 * cc + lane_sel, pk);
+                    }
+                } else {
+                    // bfloat16: per 64 keys both S chunks are read before P hi (32 columns) and P lo (32 columns) overwrite them
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        uint32_t sa[32], ha[16], la[16];
+                        tmem_ld32(tS + 64 * h + lane_sel, sa);
+                        weights(sa, j * BLK + 64 * h, ha, la);
+                        uint32_t sb[32], hb[16], lb[16];
+                        tmem_ld32(tS + 64 * h + 32 + lane_sel, sb);
+                        tmem_st16(tS + 64 * h + lane_sel, ha);
+                        tmem_st16(tS + 64 * h + 32 + lane_sel, la);
+                        weights(sb, j * BLK + 64 * h + 32, hb, lb);
+                        tmem_st16(tS + 64 * h + 16 + lane_sel, hb);
+                        tmem_st16(tS + 64 * h + 48 + lane_sel, lb);
                     }
                 }
                 if (pass == 1) tmem_wait_st();
@@ -361,11 +395,12 @@ EmblaStatus launch_sliding_prefill_tc(EmblaAttn* ctx, const EmblaRing* ring, con
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) EMBLA_FAIL(EMBLA_CUDA, "cuTensorMapEncodeTiled failed for a ring (%d)", int(r));
     }
-    auto kern = sliding_prefill_tc_kernel<EMBLA_F16>;
-    static bool configured[64] = {};
-    if (!configured[ctx->device & 63]) {
+    const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
+    auto kern = bf ? sliding_prefill_tc_kernel<EMBLA_BF16> : sliding_prefill_tc_kernel<EMBLA_F16>;
+    static bool configured[2][64] = {};
+    if (!configured[bf][ctx->device & 63]) {
         EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ST_SMEM)));
-        configured[ctx->device & 63] = true;
+        configured[bf][ctx->device & 63] = true;
     }
     const int tpt = BLK / p.G;
     dim3 grid((p.n_tokens + 2 * tpt - 1) / (2 * tpt), p.n_kv_heads, batch);

@@ -74,3 +74,6 @@ def test_sliding_prefill_tensor_core_path_edges():
     _case(333, 900, 1024, 4096, 16, 4, orc.F16, seed=13, gains=True, poison=True)
     _case(96, 5000, 300, 1024, 8, 1, orc.F16, seed=14, gains=True)
     _case(128, 8100, 512, 2048, 4, 4, orc.F16, seed=15)
+    # bfloat16 (P = hi + lo): the reference's window and a long one, never-written slots after the chunk
+    _case(333, 900, 1024, 4096, 16, 4, orc.BF16, seed=16, gains=True, poison=True)
+    _case(2048, 2048, 1024, 4096, 16, 4, orc.BF16, seed=17)
