@@ -358,12 +358,45 @@ def prefill_leg(rank, world, barrier, reps=10):
     peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
     burst, sustained = float(peaks.get("bf16_tflops", 1590.0)), float(peaks.get("bf16_tflops_sustained", 1400.0))
     tflops = PREFILL_FLOP / (ms * 1e-3) / 1e12
-    return {"metric": "prefill attn tok/s", "workload": "config 3: 2048-token causal chunk after 30720 cached positions, int8 KV, bf16 q",
+    sliding = sliding_prefill_case(rank, reps) if world == 1 else None
+    return {"sliding_config_1b": sliding, "metric": "prefill attn tok/s", "workload": "config 3: 2048-token causal chunk after 30720 cached positions, int8 KV, bf16 q",
             "value": PREFILL_T / (ms * 1e-3), "unit": "tok/s", "ms": ms, "tflops": tflops, "n_gpus": world,
             "sharding": ("none" if world == 1 else f"{kv_shards} kv-head shards x {tok_shards} chunk halves, NCCL all-gather of per-head outputs"),
             "allgather_bytes": 0 if world == 1 else PREFILL_T * HQ * 128 * 2,
             "roofline": {"bound": "tensor", "achieved": tflops, "peak": burst * world, "unit": "TFLOP/s", "frac": tflops / (burst * world),
                          "frac_of_sustained": tflops / (sustained * world)}}
+
+
+def sliding_prefill_case(rank, reps):
+    """BASELINE.json config 1 (b) on one GPU: a 2048-token chunk of a sliding layer (window 1024, ring 4096, fp16) appended
+    after 2048 cached positions; FLOP = 4 x 16 heads x 128 x the keys every token sees."""
+    import torch
+    from embla_metal_b200 import attn
+    T, cached, window, ring_slots = 2048, 2048, 1024, 4096
+    ctx = attn.Attention(HQ, HKV, attn.F16, 1, ring_slots)
+    ring = attn.Ring(1, HKV, ring_slots, window, torch.float16)
+    g = torch.Generator(device="cuda").manual_seed(1 + rank)
+    ring.k.copy_(torch.randn(ring.k.shape, device="cuda", generator=g).half())
+    ring.v.copy_(torch.randn(ring.v.shape, device="cuda", generator=g).half())
+    q = torch.randn(1, T, HQ * 128, device="cuda", generator=g).half()
+    o = torch.zeros_like(q)
+    pos0 = torch.tensor([cached], dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        attn.sliding_prefill(ctx, ring, pos0, q, o)
+    ctx.check()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        attn.sliding_prefill(ctx, ring, pos0, q, o)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    ctx.check()
+    ctx.close()
+    flop = 4 * HQ * 128 * sum(min(cached + i + 1, window) for i in range(T))
+    return {"workload": "config 1 (b): 2048-token chunk after 2048 positions, window 1024, ring 4096, fp16", "ms": ms,
+            "value": T / (ms * 1e-3), "unit": "tok/s", "tflops": flop / (ms * 1e-3) / 1e12}
 
 
 def main():
