@@ -39,7 +39,8 @@ def workload_config(n_gpus):
 
 
 def algorithmic_bytes(batch, entry):
-    """Bytes one launch of `entry` must move for `batch` sequences at CONTEXT keys ('bytes per unit')."""
+    """Bytes one launch of `entry` must move for `batch` sequences at CONTEXT keys: the bytes of the rows it streams
+    (int8 K and V rows with their scales, 16-bit K rows, gathered 16-bit K + V rows, fp32 scores)."""
     pairs = batch * HKV
     return {
         "full_decode": pairs * CONTEXT * (2 * 128 + 2 * 2),          # int8 K, V rows + fp16 scales
