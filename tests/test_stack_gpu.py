@@ -103,3 +103,83 @@ def test_fused_sliding_step_equals_write_then_attend():
         assert torch.equal(r1.k.view(torch.int16), r2.k.view(torch.int16)) and torch.equal(r1.v.view(torch.int16), r2.v.view(torch.int16))
         assert torch.equal(o1.view(torch.int16), o2.view(torch.int16))
         ctx.close()
+
+
+def test_config4_full_size_step():
+    """BASELINE config 4 at full size: 64 sequences x 32768 context x 24 layers [sparse, sliding 1024, sliding 1024,
+    full int8], seed 4 (a few sequences shorter, one below the selection threshold). The step run twice from the same
+    inputs is bit-identical (appends are idempotent, every combine is ordered); for sampled (sequence, layer) pairs the
+    step's rows agree with the CPU restatement fed the very pages and rings the step left behind, and the sparse
+    layer's selection - recomputed through the single entry points - equals the restatement's bit for bit."""
+    import torch
+    from oracle import oracle as orc
+    from tests import util
+    from embla_metal_b200 import attn, stack as stk
+    B, CTX, Hq, Hkv = 64, 32768, 16, 4
+    st = stk.DecodeStack(stk.cycle_kinds(24), B, CTX, Hq, Hkv, attn.F16, 1024, 4096)
+    st.fill_random(seed=4)
+    pos = [CTX - 1] * B
+    pos[3], pos[7], pos[11] = 20000, 1100, 4095
+    st.set_positions(pos)
+    g = torch.Generator(device="cuda").manual_seed(104)
+    st.qkv.copy_(torch.randn(st.qkv.shape, device="cuda", generator=g).to(st.dtype))
+    st.step()
+    st.ctx.check()
+    first = st.o.clone()
+    st.step()
+    st.ctx.check()
+    assert torch.equal(first.view(torch.int16), st.o.view(torch.int16)), "two steps from the same inputs differ"
+    assert torch.isfinite(first.float()).all()
+    npg = CTX // 128
+    qrow = lambda li, b: st.qkv[li, b, :Hq * 128].view(torch.int16).cpu().numpy().view(np.uint16).reshape(Hq, 128)
+    got = lambda li, b: orc.from_bits(first[li, b].view(torch.int16).cpu().numpy().view(np.uint16), orc.F16).reshape(Hq, 128)
+
+    # full layer (layer 3 = slot 0 of the int8 pool) of sequences 5 (32768 keys) and 3 (20001 keys)
+    raw = st.full_pool.raw()
+    for b in (5, 3):
+        S = pos[b] + 1
+        pages = raw[st.table[b].long(), 0].cpu().numpy()                      # [npg, Hkv, page_bytes]
+        k = pages[:, :, :16384].reshape(npg, Hkv, 128, 128).transpose(1, 0, 2, 3).reshape(Hkv, npg * 128, 128).view(np.int8)
+        v = pages[:, :, 16384:32768].reshape(npg, Hkv, 128, 128).transpose(1, 0, 2, 3).reshape(Hkv, npg * 128, 128).view(np.int8)
+        sc = np.ascontiguousarray(pages[:, :, 32768:]).view(np.float16).reshape(npg, Hkv, 2, 128).astype(np.float32)
+        ks = sc[:, :, 0].transpose(1, 0, 2).reshape(Hkv, npg * 128)
+        vs = sc[:, :, 1].transpose(1, 0, 2).reshape(Hkv, npg * 128)
+        want = orc.from_bits(orc.full_decode(qrow(3, b), orc.F16, np.ascontiguousarray(k[:, :S]), np.ascontiguousarray(ks[:, :S]),
+                                             np.ascontiguousarray(v[:, :S]), np.ascontiguousarray(vs[:, :S]), S)[0], orc.F16)
+        ok, msg = util.close(got(3, b), want)
+        assert ok, f"full layer, sequence {b}: {msg}"
+
+    # sparse layer (layer 0 = slot 0 of the 16-bit pool) of sequences 5 (selects) and 7 (1101 keys: attends them all)
+    raw16 = st.sparse_pool.raw()
+    for b in (5, 7):
+        S = pos[b] + 1
+        n = (S + 127) // 128
+        pages = raw16[st.table[b, :n].long(), 0].cpu().numpy().view(np.uint16)   # [n, Hkv, 2 * 128 * 128]
+        k = pages[:, :, :16384].reshape(n, Hkv, 128, 128).transpose(1, 0, 2, 3).reshape(Hkv, n * 128, 128)[:, :S]
+        v = pages[:, :, 16384:].reshape(n, Hkv, 128, 128).transpose(1, 0, 2, 3).reshape(Hkv, n * 128, 128)[:, :S]
+        k, v = np.ascontiguousarray(k), np.ascontiguousarray(v)
+        want_idx = None
+        if S > 1152:
+            want_sc = orc.score_keys(qrow(0, b), orc.F16, k, S, nthreads=8)
+            want_idx = orc.select_keys(want_sc, S)
+            scores = torch.zeros(1, Hkv, CTX, device="cuda")
+            idx = torch.zeros(1, Hkv, 1152, dtype=torch.int32, device="cuda")
+            lens = st.seq_lens[b:b + 1]
+            st.ctx.score_keys(st.sparse_pool, st.table[b:b + 1], lens, 0, st.qkv[0, b:b + 1, :Hq * 128], scores, max_seq_len=S)
+            st.ctx.select_keys(scores, lens, idx, max_seq_len=S)
+            st.ctx.check()
+            assert np.array_equal(scores[0, :, :S].cpu().numpy().view(np.uint32), want_sc[:, :S].view(np.uint32))
+            assert np.array_equal(idx[0].cpu().numpy().view(np.uint32), want_idx), "selection differs"
+            assert orc.verify_selection(want_sc, want_idx, S) == 0
+        want = orc.from_bits(orc.sparse_decode(qrow(0, b), orc.F16, k, None, v, None, S, idx=want_idx, kv_kind=1), orc.F16)
+        ok, msg = util.close(got(0, b), want)
+        assert ok, f"sparse layer, sequence {b}: {msg}"
+
+    # sliding layer (layer 1 = ring 0) of sequences 5 and 11 (position 4095: the ring's last slot)
+    for b in (5, 11):
+        rk = st.rings[0].k[b].view(torch.int16).cpu().numpy().view(np.uint16)
+        rv = st.rings[0].v[b].view(torch.int16).cpu().numpy().view(np.uint16)
+        want = orc.from_bits(orc.sliding_attend(qrow(1, b)[None], orc.F16, rk, rv, pos[b], 1024), orc.F16)[0]
+        ok, msg = util.close(got(1, b), want)
+        assert ok, f"sliding layer, sequence {b}: {msg}"
+    st.close()
