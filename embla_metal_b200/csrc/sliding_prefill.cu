@@ -267,7 +267,7 @@ extern "C" EmblaStatus embla_attn_sliding_prefill(EmblaAttn* ctx, const EmblaRin
     // and other rings take the kernel below.
     if (n_tokens >= 64 && ring->ring % BLK == 0 && ring->seq_stride % 8 == 0 &&
         reinterpret_cast<uintptr_t>(ring->k_dev) % 16 == 0 && reinterpret_cast<uintptr_t>(ring->v_dev) % 16 == 0 &&
-        q_token_stride % 8 == 0 && o_token_stride % 8 == 0 && o_seq_stride % 8 == 0 &&
+        q_token_stride % 8 == 0 && q->q_stride % 8 == 0 && reinterpret_cast<uintptr_t>(q->q_dev) % 16 == 0 && o_token_stride % 8 == 0 && o_seq_stride % 8 == 0 &&
         reinterpret_cast<uintptr_t>(o_dev) % 16 == 0) {
         SlidingTcParams t = {};
         t.pos0 = pos0_dev;

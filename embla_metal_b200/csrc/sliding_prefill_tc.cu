@@ -92,6 +92,20 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
     // position when the queries arrive raw, as attn_sliding_b does)
     for (int x = 0; x < 2; x++) {
         uint8_t* Qx = Qs + x * ST_TILE;
+        if (p.prenormed) {
+            // rows as they are: 16 bytes a thread and trip, many loads in flight
+#pragma unroll 4
+            for (int i = tid; i < BLK * 16; i += ST_THREADS) {
+                const int r = i >> 4, c8 = i & 15, t = r / p.G, hh = r % p.G;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (t < ntok[x]) {
+                    const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + t) * p.q_token_stride + size_t(kvh * p.G + hh) * HD + c8 * 8;
+                    v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
+                }
+                *reinterpret_cast<uint4*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v;
+            }
+            continue;
+        }
         for (int r = warp; r < BLK; r += ST_THREADS / 32) {
             const int t = r / p.G, hh = r % p.G;
             float xq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -99,7 +113,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
                 const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + t) * p.q_token_stride + size_t(kvh * p.G + hh) * HD;
 #pragma unroll
                 for (int i = 0; i < 4; i++) xq[i] = Act<DT>::load(p.q, off + lane + 32 * i);
-                if (!p.prenormed) norm_rope_round<DT>(xq, p.g1, p.g1, 1, p0 + t0[x] + t, p.rope_freq, lane);
+                norm_rope_round<DT>(xq, p.g1, p.g1, 1, p0 + t0[x] + t, p.rope_freq, lane);
             }
 #pragma unroll
             for (int i = 0; i < 4; i++) {
