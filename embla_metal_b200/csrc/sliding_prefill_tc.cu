@@ -106,19 +106,25 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
             }
             continue;
         }
-        for (int r = warp; r < BLK; r += ST_THREADS / 32) {
-            const int t = r / p.G, hh = r % p.G;
-            float xq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            if (t < ntok[x]) {
+        // raw queries: four rows a warp and trip, their loads in flight together before the norms
+        for (int r4 = warp * 4; r4 < BLK; r4 += 4 * (ST_THREADS / 32)) {
+            float xq[4][4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int r = r4 + k, t = r / p.G, hh = r % p.G;
                 const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + t) * p.q_token_stride + size_t(kvh * p.G + hh) * HD;
 #pragma unroll
-                for (int i = 0; i < 4; i++) xq[i] = Act<DT>::load(p.q, off + lane + 32 * i);
-                norm_rope_round<DT>(xq, p.g1, p.g1, 1, p0 + t0[x] + t, p.rope_freq, lane);
+                for (int i = 0; i < 4; i++) xq[k][i] = t < ntok[x] ? Act<DT>::load(p.q, off + lane + 32 * i) : 0.0f;
             }
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int d = lane + 32 * i, c8 = d >> 3;
-                Act<DT>::store(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4) + (d & 7) * 2, 0, xq[i]);
+            for (int k = 0; k < 4; k++) {
+                const int r = r4 + k, t = r / p.G;
+                if (t < ntok[x]) norm_rope_round<DT>(xq[k], p.g1, p.g1, 1, p0 + t0[x] + t, p.rope_freq, lane);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int d = lane + 32 * i, c8 = d >> 3;
+                    Act<DT>::store(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4) + (d & 7) * 2, 0, xq[k][i]);
+                }
             }
         }
     }

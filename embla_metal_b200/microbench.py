@@ -91,7 +91,7 @@ def prefill(tokens, cached):
           f"(min-time {flop / ts[0] / 1e9:.0f}), {tokens / med * 1e3:.0f} tok/s")
 
 
-def sliding_prefill(tokens, cached, window):
+def sliding_prefill(tokens, cached, window, raw=False):
     """BASELINE config 1 (b): a chunk of `tokens` appended after `cached` positions of a sliding layer."""
     ring_slots = 4096
     ctx = attn.Attention(HQ, HKV, attn.F16, 1, ring_slots)
@@ -101,7 +101,8 @@ def sliding_prefill(tokens, cached, window):
     q = torch.randn(1, tokens, HQ * 128, device="cuda", dtype=torch.float16)
     o = torch.zeros_like(q)
     pos0 = torch.tensor([cached], dtype=torch.int32, device="cuda")
-    ts = _events(lambda: attn.sliding_prefill(ctx, ring, pos0, q, o))
+    gain = (torch.randn(128, device="cuda") * 0.1).half() if raw else None   # raw queries: fused head norm + RoPE
+    ts = _events(lambda: attn.sliding_prefill(ctx, ring, pos0, q, o, qgain=gain))
     ctx.check()
     flop = 4 * HQ * 128 * sum(min(cached + i + 1, window) for i in range(tokens))
     med = ts[len(ts) // 2]
@@ -113,6 +114,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=["full_decode", "sparse", "prefill", "sliding_prefill"])
     ap.add_argument("--window", type=int, default=1024)
+    ap.add_argument("--raw", action="store_true", help="sliding_prefill: queries arrive raw (fused head norm + RoPE)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--scores", action="store_true")
     ap.add_argument("--tokens", type=int, default=2048)
@@ -123,7 +125,7 @@ def main():
     elif a.case == "sparse":
         sparse(a.batch)
     elif a.case == "sliding_prefill":
-        sliding_prefill(a.tokens, a.cached if a.cached != 30720 else 2048, a.window)
+        sliding_prefill(a.tokens, a.cached if a.cached != 30720 else 2048, a.window, a.raw)
     else:
         prefill(a.tokens, a.cached)
 
