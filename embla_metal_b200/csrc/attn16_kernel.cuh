@@ -110,40 +110,53 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
         }
     }
 
-    // gathers of tile `t` (of this CTA's range) into stage t % STAGES; every thread copies 8 chunks of K and of V
-    auto issue_tile = [&](int t) {
-        uint8_t* Kt = smem + (t % A16_STAGES) * A16_STAGE;
-        uint8_t* Vt = Kt + A16_SIDE;
-        const int ch = tid & 15, half = ch >> 3, cc = ch & 7;
+    // Gathers of tile `t` (of this CTA's range) into stage t % STAGES; every thread copies 8 chunks of K and of V. The
+    // rows' addresses (index list -> block table -> page: two dependent loads) are resolved one tile ahead of their
+    // use, so that those loads fly while the tile before is computed instead of stalling every warp at the issue.
+    const uint8_t* const base_k = MODE == A16_SLIDING ? p.ring_k : p.pool;
+    const uint8_t* const base_v = MODE == A16_SLIDING ? p.ring_v : p.pool + BLK * HD * 2;
+    size_t roff[8];      // byte offsets of this thread's 8 rows of the resolved tile (this thread's 16-byte chunk included)
+    uint32_t rvalid = 0;
+    auto resolve_tile = [&](int t) {
+        const int ch = tid & 15;
         const int jbase = (tile0 + t) * A16_ROWS;
+        rvalid = 0;
 #pragma unroll
         for (int it = 0; it < 8; it++) {
             const int key = it * 8 + (tid >> 4), j = jbase + key;
-            const bool valid = j < count;
-            const uint8_t *ksrc, *vsrc;
+            const bool valid = t < ntile && j < count;
+            rvalid |= uint32_t(valid) << it;
             if (MODE == A16_SLIDING) {
                 const int slot = valid ? (pos - j) % p.ring : 0;
-                const size_t off = (size_t(b) * p.ring_stride + (size_t(kvh) * p.ring + slot) * HD) * 2 + ch * 16;
-                ksrc = p.ring_k + off;
-                vsrc = p.ring_v + off;
+                roff[it] = (size_t(b) * p.ring_stride + (size_t(kvh) * p.ring + slot) * HD) * 2 + ch * 16;
             } else {
                 int row = valid ? j : 0;
                 if (selecting && valid) row = int(p.idx[(size_t(b) * p.n_kv_heads + kvh) * (EMBLA_TOPK + EMBLA_RECENT) + j]);
                 const int block = p.block_table[size_t(b) * p.table_stride + (row >> 7)];
-                const uint8_t* page = p.pool + ((size_t(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh) * p.page_bytes;
-                ksrc = page + (row & 127) * (HD * 2) + ch * 16;
-                vsrc = ksrc + BLK * HD * 2;
+                roff[it] = ((size_t(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh) * p.page_bytes + (row & 127) * (HD * 2) + ch * 16;
             }
+        }
+    };
+    auto issue_tile = [&](int t) {   // the tile resolved last
+        uint8_t* Kt = smem + (t % A16_STAGES) * A16_STAGE;
+        uint8_t* Vt = Kt + A16_SIDE;
+        const int ch = tid & 15, half = ch >> 3, cc = ch & 7;
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+            const int key = it * 8 + (tid >> 4);
+            const bool valid = (rvalid >> it) & 1;
             const int dst = half * (A16_ROWS * 128) + key * 128 + ((cc ^ (key & 7)) << 4);
-            cp_async16(Kt + dst, ksrc, valid);
-            cp_async16(Vt + dst, vsrc, valid);
+            cp_async16(Kt + dst, base_k + roff[it], valid);
+            cp_async16(Vt + dst, base_v + roff[it], valid);
         }
     };
     if (!TMA) {
+        resolve_tile(0);
 #pragma unroll
         for (int t = 0; t < A16_STAGES - 1; t++) {
             if (t < ntile) issue_tile(t);
             asm volatile("cp.async.commit_group;" ::: "memory");
+            resolve_tile(t + 1);
         }
     }
     // ---- the kv head's queries (norm, RoPE for sliding layers) while the rows arrive
@@ -326,6 +339,7 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             cons_sync();   // every warp is done with this stage: the tile STAGES - 1 ahead may overwrite it
             if (t + A16_STAGES - 1 < ntile) issue_tile(t + A16_STAGES - 1);
             asm volatile("cp.async.commit_group;" ::: "memory");
+            resolve_tile(t + A16_STAGES);   // its loads fly during the next tile's wait and compute
         }
     }
 #pragma unroll
