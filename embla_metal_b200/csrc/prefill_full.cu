@@ -162,32 +162,41 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                 *reinterpret_cast<uint4*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v;
             }
         } else {
-            // q_prep_b: head norm with both gains in the oracle's operation order, rounded to the activation dtype
-            for (int r = warp; r < BLK; r += PF_THREADS / 32) {
-                float xq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                if (r < rows[x]) {
+            // q_prep_b: head norm with both gains in the oracle's operation order, rounded to the activation dtype; four
+            // rows a warp and trip, their loads in flight together before the norms
+            for (int r4 = warp * 4; r4 < BLK; r4 += 4 * (PF_THREADS / 32)) {
+                float xq[4][4];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const int r = r4 + k;
                     const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + r) * p.q_token_stride + size_t(h) * HD;
 #pragma unroll
-                    for (int i = 0; i < 4; i++) xq[i] = Act<DT>::load(p.q, off + lane + 32 * i);
-                    float ss = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < 4; i++) ss = __fadd_rn(ss, __fmul_rn(xq[i], xq[i]));
-                    float tot = 0.0f;
-                    for (int l = 0; l < 32; l++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, ss, l));
-                    const float rr = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, float(HD)), EPS32)));
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int d = lane + 32 * i;
-                        float gn = __fmul_rn(rr, __fadd_rn(1.0f, Act<DT>::load(p.g1, d)));
-                        gn = __fmul_rn(gn, __fadd_rn(1.0f, Act<DT>::load(p.g2, d)));
-                        xq[i] = Act<DT>::round(__fmul_rn(xq[i], gn));
-                    }
+                    for (int i = 0; i < 4; i++) xq[k][i] = r < rows[x] ? Act<DT>::load(p.q, off + lane + 32 * i) : 0.0f;
                 }
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int d = lane + 32 * i, c8 = d >> 3;
-                    *reinterpret_cast<__half*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4) + (d & 7) * 2) =
-                        __float2half_rn(xq[i]);
+                for (int k = 0; k < 4; k++) {
+                    const int r = r4 + k;
+                    if (r < rows[x]) {
+                        float ss = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) ss = __fadd_rn(ss, __fmul_rn(xq[k][i], xq[k][i]));
+                        float tot = 0.0f;
+                        for (int l = 0; l < 32; l++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, ss, l));
+                        const float rr = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, float(HD)), EPS32)));
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int d = lane + 32 * i;
+                            float gn = __fmul_rn(rr, __fadd_rn(1.0f, Act<DT>::load(p.g1, d)));
+                            gn = __fmul_rn(gn, __fadd_rn(1.0f, Act<DT>::load(p.g2, d)));
+                            xq[k][i] = Act<DT>::round(__fmul_rn(xq[k][i], gn));
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int d = lane + 32 * i, c8 = d >> 3;
+                        *reinterpret_cast<__half*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4) + (d & 7) * 2) =
+                            __float2half_rn(xq[k][i]);
+                    }
                 }
             }
         }
