@@ -183,3 +183,30 @@ def test_config4_full_size_step():
         ok, msg = util.close(got(1, b), want)
         assert ok, f"sliding layer, sequence {b}: {msg}"
     st.close()
+
+
+def test_dependent_launch_overlap_changes_nothing():
+    """The step's launches overlap through programmatic dependent launch unless EMBLA_NO_PDL=1 is in the environment (read
+    once per process): both ways the same inputs give the same bits."""
+    import hashlib
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, hashlib, torch; sys.path.insert(0, %r)\n"
+        "from embla_metal_b200 import stack as stk\n"
+        "st = stk.DecodeStack(stk.cycle_kinds(8) + [stk.FULL, stk.SPARSE_SHARED], 6, 4096, window=256, ring=1024)\n"
+        "st.fill_random(9); st.set_positions([4095, 3000, 1500, 1151, 1152, 200])\n"
+        "g = torch.Generator(device='cuda').manual_seed(1)\n"
+        "st.qkv.copy_(torch.randn(st.qkv.shape, device='cuda', generator=g).to(st.dtype))\n"
+        "for _ in range(3): st.step()\n"
+        "st.ctx.check()\n"
+        "print(hashlib.sha256(st.o.view(torch.int16).cpu().numpy().tobytes()).hexdigest())\n" % root)
+    digests = []
+    for no_pdl in ("0", "1"):
+        env = dict(os.environ, EMBLA_NO_PDL=no_pdl)
+        out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+        assert out.returncode == 0, out.stderr[-800:]
+        digests.append(out.stdout.strip().splitlines()[-1])
+    assert digests[0] == digests[1] and len(digests[0]) == 64
