@@ -143,6 +143,27 @@ class Attention:
     def check(self):
         _check(lib().embla_attn_check(self.handle, _stream()))
 
+    def set_wait_limit(self, cycles):
+        """Bound of the device-side waits of this context's launches, in SM clocks."""
+        _check(lib().embla_attn_set_wait_limit(self.handle, C.c_int64(cycles)))
+
+    def inject_stall(self, item):
+        """Diagnostic: producers stop requesting data at `item` of their range (None or -1: off)."""
+        _check(lib().embla_attn_inject_stall(self.handle, -1 if item is None else int(item)))
+
+    def trace_begin(self, max_launches=256):
+        _check(lib().embla_attn_trace_begin(self.handle, max_launches, _stream()))
+        self._trace_cap = max_launches
+
+    def trace_end(self):
+        """[(entry, first_enter_ns, first_ready_ns, last_loop_end_ns, last_exit_ns)] of the launches since trace_begin."""
+        cap = self._trace_cap
+        stamps = (C.c_uint64 * (4 * cap))()
+        entries = (C.c_int32 * cap)()
+        n = C.c_int32()
+        _check(lib().embla_attn_trace_end(self.handle, _stream(), stamps, entries, cap, C.byref(n)))
+        return [(entries[i], *[stamps[4 * i + k] for k in range(4)]) for i in range(n.value)]
+
     @staticmethod
     def view(block_table, seq_lens, layer, max_seq_len=0):
         return KVView(block_table.data_ptr(), block_table.stride(0), None if seq_lens is None else seq_lens.data_ptr(),
@@ -235,6 +256,9 @@ def full_prefill(ctx, pool, block_table, layer, pos0, q, o, gains=None):
         qd = Query(q.data_ptr(), q.stride(0), 1, 0, None, None)
     else:
         qd = Query(q.data_ptr(), q.stride(0), 0, 2, gains[0].data_ptr(), gains[1].data_ptr())
+    if not getattr(ctx, "_prefill_reserved", False):   # set-up, once per context: the split-KV scratch
+        _check(lib().embla_attn_reserve_prefill(ctx.handle, _stream()))
+        ctx._prefill_reserved = True
     _check(lib().embla_attn_full_prefill(ctx.handle, pool.handle, C.byref(view), _ptr(pos0), q.shape[1], C.byref(qd),
                                          C.c_int64(q.stride(1)), _ptr(o), C.c_int64(o.stride(1)), C.c_int64(o.stride(0)),
                                          _stream()))

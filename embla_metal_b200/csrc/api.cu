@@ -57,7 +57,16 @@ EmblaStatus embla_attn_create(const EmblaAttnConfig* cfg, EmblaAttn** out) {
     ctx->err_dev = nullptr;
     ctx->prefill_scratch = nullptr;
     ctx->prefill_scratch_bytes = 0;
-    ctx->prefill_counter_units = -1;
+    ctx->prefill_counters = 0;
+    ctx->pdl = 0;
+    ctx->early = 0;
+    ctx->wait_cycles = WAIT_CYCLES;
+    ctx->stall_at = -1;
+    ctx->trace_dev = nullptr;
+    ctx->trace_entry = nullptr;
+    ctx->trace_cap = ctx->trace_next = ctx->trace_on = 0;
+    ctx->trace_tag = -1;
+    ctx->ring_maps_used = ctx->ring_maps_next = 0;
     cudaError_t e = cudaGetDevice(&ctx->device);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&ctx->sm_count, cudaDevAttrMultiProcessorCount, ctx->device);
     if (e != cudaSuccess) {
@@ -92,7 +101,63 @@ void embla_attn_destroy(EmblaAttn* ctx) {
     cudaFree(ctx->counters);
     cudaFree(ctx->err_dev);
     cudaFree(ctx->prefill_scratch);
+    cudaFree(ctx->trace_dev);
+    delete[] ctx->trace_entry;
     delete ctx;
+}
+
+EmblaStatus embla_attn_set_wait_limit(EmblaAttn* ctx, int64_t cycles) {
+    if (!ctx || cycles <= 0) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_set_wait_limit: null context or limit %lld", (long long)cycles);
+    ctx->wait_cycles = cycles;
+    return EMBLA_OK;
+}
+
+EmblaStatus embla_attn_inject_stall(EmblaAttn* ctx, int32_t item) {
+    if (!ctx) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_inject_stall: null context");
+    ctx->stall_at = item < 0 ? -1 : item;
+    return EMBLA_OK;
+}
+
+EmblaStatus embla_attn_trace_begin(EmblaAttn* ctx, int32_t max_launches, void* stream) {
+    if (!ctx || max_launches <= 0) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_trace_begin: null context or %d launches", max_launches);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (max_launches > ctx->trace_cap) {
+        EMBLA_CUDA_TRY(cudaStreamSynchronize(s));
+        cudaFree(ctx->trace_dev);
+        delete[] ctx->trace_entry;
+        ctx->trace_dev = nullptr;
+        ctx->trace_entry = nullptr;
+        ctx->trace_cap = 0;
+        EMBLA_CUDA_TRY(cudaMalloc(&ctx->trace_dev, size_t(max_launches) * 4 * sizeof(unsigned long long)));
+        ctx->trace_entry = new (std::nothrow) int[max_launches];
+        if (!ctx->trace_entry) EMBLA_FAIL(EMBLA_OOM, "embla_attn_trace_begin: host allocation failed");
+        ctx->trace_cap = max_launches;
+    }
+    EMBLA_CUDA_TRY(cudaMemsetAsync(ctx->trace_dev, 0xff, size_t(ctx->trace_cap) * 4 * sizeof(unsigned long long), s));
+    ctx->trace_next = 0;
+    ctx->trace_on = 1;
+    return EMBLA_OK;
+}
+
+EmblaStatus embla_attn_trace_end(EmblaAttn* ctx, void* stream, uint64_t* stamps, int32_t* entries, int32_t cap, int32_t* n_out) {
+    if (!ctx || !stamps || !entries || !n_out) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_trace_end: null argument");
+    ctx->trace_on = 0;
+    const int n = ctx->trace_next < cap ? ctx->trace_next : cap;
+    *n_out = n;
+    if (n == 0) return EMBLA_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    EMBLA_CUDA_TRY(cudaMemcpyAsync(stamps, ctx->trace_dev, size_t(n) * 4 * sizeof(uint64_t), cudaMemcpyDeviceToHost, s));
+    EMBLA_CUDA_TRY(cudaStreamSynchronize(s));
+    for (int i = 0; i < n; i++) {
+        entries[i] = ctx->trace_entry[i];
+        // slots 2 and 3 are kept as complements on the device; a slot no CTA stamped reads 0
+        for (int k = 0; k < 4; k++) {
+            uint64_t& v = stamps[4 * i + k];
+            if (k >= 2) v = ~v;
+            else if (v == ~uint64_t(0)) v = 0;
+        }
+    }
+    return EMBLA_OK;
 }
 
 EmblaStatus embla_attn_check(EmblaAttn* ctx, void* stream) {

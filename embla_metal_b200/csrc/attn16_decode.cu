@@ -62,20 +62,43 @@ static EmblaStatus check_query(const char* fn, const EmblaQuery* q) {
 }
 
 // Tensor maps over a sliding layer's K and V rings for the ring-tile path: bytes [sequence][kv head x slot][256], boxes of
-// 64 rows x 128 bytes under the 128-byte swizzle. Encoded per call (a host-side computation of about a microsecond).
-static EmblaStatus ring_maps(const Attn16Params& p, int batch, CUtensorMap* mk, CUtensorMap* mv) {
+// 64 rows x 128 bytes under the 128-byte swizzle. Encoded once per (ring, batch) and kept in the context.
+static EmblaStatus ring_maps(EmblaAttn* ctx, const Attn16Params& p, int batch, const CUtensorMap** mk, const CUtensorMap** mv) {
+    for (int i = 0; i < ctx->ring_maps_used; i++) {
+        const EmblaAttn::RingMaps& m = ctx->ring_maps[i];
+        if (m.k == p.ring_k && m.v == p.ring_v && m.seq_stride == p.ring_stride && m.ring == p.ring &&
+            m.n_kv_heads == p.n_kv_heads && m.batch == batch) {
+            *mk = &m.mk;
+            *mv = &m.mv;
+            return EMBLA_OK;
+        }
+    }
     TensorMapEncodeTiledFn enc = tensor_map_encoder();
     if (!enc) EMBLA_FAIL(EMBLA_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    EmblaAttn::RingMaps& m = ctx->ring_maps[ctx->ring_maps_next];
     const cuuint64_t dims[3] = {HD * 2, cuuint64_t(p.n_kv_heads) * p.ring, cuuint64_t(batch)};
     const cuuint64_t strides[2] = {HD * 2, cuuint64_t(p.ring_stride) * 2};
     const cuuint32_t box[3] = {128, A16_ROWS, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     for (int side = 0; side < 2; side++) {
-        CUresult r = enc(side ? mv : mk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(side ? p.ring_v : p.ring_k), dims,
+        CUresult r = enc(side ? &m.mv : &m.mk, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(side ? p.ring_v : p.ring_k), dims,
                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) EMBLA_FAIL(EMBLA_CUDA, "cuTensorMapEncodeTiled failed for a ring (%d)", int(r));
+        if (r != CUDA_SUCCESS) {
+            m.k = nullptr;
+            EMBLA_FAIL(EMBLA_CUDA, "cuTensorMapEncodeTiled failed for a ring (%d)", int(r));
+        }
     }
+    m.k = p.ring_k;
+    m.v = p.ring_v;
+    m.seq_stride = p.ring_stride;
+    m.ring = p.ring;
+    m.n_kv_heads = p.n_kv_heads;
+    m.batch = batch;
+    ctx->ring_maps_next = (ctx->ring_maps_next + 1) % EmblaAttn::RING_MAP_SLOTS;
+    if (ctx->ring_maps_used < EmblaAttn::RING_MAP_SLOTS) ctx->ring_maps_used++;
+    *mk = &m.mk;
+    *mv = &m.mv;
     return EMBLA_OK;
 }
 
@@ -97,7 +120,7 @@ template <int MODE>
 static EmblaStatus launch_attn16(EmblaAttn* ctx, Attn16Params& p, int batch, int max_rows, cudaStream_t s) {
     p.partials = ctx->partials;
     p.counters = ctx->counters;
-    p.err = ctx->err_dev;
+    p.ctl = kernel_ctl(ctx);
     p.G = ctx->cfg.n_q_heads / ctx->cfg.n_kv_heads;
     p.n_kv_heads = ctx->cfg.n_kv_heads;
     // Rings of a multiple of 64 slots are read as tiles of 64 consecutive slots (TMA); the window then spans one tile
@@ -124,14 +147,15 @@ static EmblaStatus launch_attn16(EmblaAttn* ctx, Attn16Params& p, int batch, int
     fill_rope_freq(p.rope_freq);
     dim3 grid(p.max_chunks, p.n_kv_heads, batch);
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
-    CUtensorMap mk = {}, mv = {};
     if (tma) {
-        if (EmblaStatus st = ring_maps(p, batch, &mk, &mv)) return st;
-        return bf ? launch_attn16_kernel<EMBLA_BF16, MODE, MODE == A16_SLIDING>(ctx, p, mk, mv, grid, s)
-                  : launch_attn16_kernel<EMBLA_F16, MODE, MODE == A16_SLIDING>(ctx, p, mk, mv, grid, s);
+        const CUtensorMap *mk = nullptr, *mv = nullptr;
+        if (EmblaStatus st = ring_maps(ctx, p, batch, &mk, &mv)) return st;
+        return bf ? launch_attn16_kernel<EMBLA_BF16, MODE, MODE == A16_SLIDING>(ctx, p, *mk, *mv, grid, s)
+                  : launch_attn16_kernel<EMBLA_F16, MODE, MODE == A16_SLIDING>(ctx, p, *mk, *mv, grid, s);
     }
-    return bf ? launch_attn16_kernel<EMBLA_BF16, MODE, false>(ctx, p, mk, mv, grid, s)
-              : launch_attn16_kernel<EMBLA_F16, MODE, false>(ctx, p, mk, mv, grid, s);
+    static const CUtensorMap none = {};
+    return bf ? launch_attn16_kernel<EMBLA_BF16, MODE, false>(ctx, p, none, none, grid, s)
+              : launch_attn16_kernel<EMBLA_F16, MODE, false>(ctx, p, none, none, grid, s);
 }
 
 extern "C" EmblaStatus embla_attn_sparse_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
@@ -229,6 +253,9 @@ static EmblaStatus sliding_decode_impl(EmblaAttn* ctx, const EmblaRing* ring, co
     if (!ctx || !ring || !ring->k_dev || !ring->v_dev || !seq_lens_dev || !o_dev)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sliding_decode: null argument");
     if (EmblaStatus st = check_query("embla_attn_sliding_decode", q)) return st;
+    // sliding layers norm q with ONE gain vector whatever ng says (attention.metal:47-48): it must be there
+    if (!q->prenormed && !q->g1_dev)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sliding_decode: q is not prenormed and g1_dev (the q gain) is null");
     if (batch <= 0 || batch > ctx->cfg.max_batch || ring->window <= 0 || ring->window > ring->ring)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sliding_decode: batch %d, window %d, ring %d", batch, ring->window, ring->ring);
     // ring rows are fetched 16 bytes (or whole tiles) at a time

@@ -40,7 +40,7 @@ struct Attn16Params {
     void* o;
     float* partials;
     int* counters;
-    int* err;
+    KernelCtl ctl;
     int64_t q_stride, o_stride, ring_stride;   // elements; ring_stride between sequences
     size_t page_bytes;
     int table_stride, layer, n_layers, n_kv_heads, G, prenormed, ng, ring, window;
@@ -61,12 +61,18 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint16_t(*qs)[HD] = reinterpret_cast<uint16_t(*)[HD]>(smem + A16_STAGES * A16_STAGE);   // [8][128] activation dtype
     __shared__ uint64_t full[A16_STAGES], empty[A16_STAGES];
-    __shared__ int s_last;
+    __shared__ int s_last, s_failed, s_issued;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    pdl_wait();
-    pdl_launch_dependents();
+    trace_first(p.ctl.trace, 0);
+    // Ring tiles of an "early" launch (the kernel ahead of it in the stream does not write this ring) are requested before
+    // the wait for that kernel; seq_lens is an input of the whole step.
+    const bool early = TMA && p.ctl.early != 0;
+    if (!early) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
     const int S = p.seq_lens[b];
     const bool selecting = MODE == A16_SPARSE && S > EMBLA_TOPK + EMBLA_RECENT;
     const int count = MODE == A16_SLIDING ? min(S, p.window) : (selecting ? EMBLA_TOPK + EMBLA_RECENT : S);
@@ -80,35 +86,51 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
     const int tile0 = chunk * p.tiles_per_cta, ntile = min(p.tiles_per_cta, tiles - tile0);
 
     if (TMA) {
-        if (tid == 0) {
+        auto issue = [&](int t) {
+            const int st = t % A16_STAGES;
+            if (t == p.ctl.stall_at) return false;   // diagnostic stall: the consumers' wait for this tile runs out
+            if (t >= A16_STAGES && !mbar_wait_bounded(p.ctl.wait_cycles, &empty[st], ((t / A16_STAGES) - 1) & 1)) {
+                atomicExch(p.ctl.err, ERR_WAIT_EMPTY);
+                return false;
+            }
+            uint8_t* Kt = smem + st * A16_STAGE;
+            const int y = kvh * p.ring + ((tbase + tile0 + t) * A16_ROWS) % p.ring;
+            mbar_expect_tx(&full[st], A16_STAGE);
+            tma_load_3d(Kt, &map_k, 0, y, b, &full[st]);
+            tma_load_3d(Kt + A16_ROWS * 128, &map_k, 128, y, b, &full[st]);
+            tma_load_3d(Kt + A16_SIDE, &map_v, 0, y, b, &full[st]);
+            tma_load_3d(Kt + A16_SIDE + A16_ROWS * 128, &map_v, 128, y, b, &full[st]);
+            *reinterpret_cast<volatile int*>(&s_issued) = t + 1;
+            return true;
+        };
+        int next = 0;
+        bool issuing = true;
+        if (tid == A16_THREADS) {   // the producer lane sets the barriers up itself, so that it can start before anyone else
 #pragma unroll
             for (int i = 0; i < A16_STAGES; i++) {
                 mbar_init(&full[i], 1);
                 mbar_init(&empty[i], A16_THREADS / 32);
             }
+            s_failed = 0;
+            s_issued = 0;
             fence_barrier_init();
+            for (; next < min(ntile, A16_STAGES) && issuing; next++) issuing = issue(next);   // the stages start empty
+        }
+        if (early) {
+            pdl_wait();
+            pdl_launch_dependents();
         }
         __syncthreads();
         if (warp == A16_THREADS / 32) {   // the producer
-            if (lane == 0) {
-                for (int t = 0; t < ntile; t++) {
-                    const int st = t % A16_STAGES;
-                    if (t >= A16_STAGES && !mbar_wait_bounded(&empty[st], ((t / A16_STAGES) - 1) & 1)) {
-                        atomicExch(p.err, ERR_WAIT_EMPTY);
-                        break;
-                    }
-                    uint8_t* Kt = smem + st * A16_STAGE;
-                    const int y = kvh * p.ring + ((tbase + tile0 + t) * A16_ROWS) % p.ring;
-                    mbar_expect_tx(&full[st], A16_STAGE);
-                    tma_load_3d(Kt, &map_k, 0, y, b, &full[st]);
-                    tma_load_3d(Kt + A16_ROWS * 128, &map_k, 128, y, b, &full[st]);
-                    tma_load_3d(Kt + A16_SIDE, &map_v, 0, y, b, &full[st]);
-                    tma_load_3d(Kt + A16_SIDE + A16_ROWS * 128, &map_v, 128, y, b, &full[st]);
-                }
-            }
+            if (lane == 0)
+                for (; next < ntile && issuing; next++) issuing = issue(next);
+            __syncwarp();
+            // (a consumer that gave up a wait meets the producer here before it drains the copies in flight)
+            asm volatile("bar.arrive 2, %0;" ::"n"(A16_THREADS + 32) : "memory");
             return;
         }
     }
+    trace_first(p.ctl.trace, 1);
 
     // Gathers of tile `t` (of this CTA's range) into stage t % STAGES; every thread copies 8 chunks of K and of V. The
     // rows' addresses (index list -> block table -> page: two dependent loads) are resolved one tile ahead of their
@@ -218,8 +240,11 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
         uint8_t* Kt = smem + st * A16_STAGE;
         uint8_t* Vt = Kt + A16_SIDE;
         if (TMA) {
-            if (!mbar_wait_bounded(&full[st], (t / A16_STAGES) & 1)) {
-                if (lane == 0) atomicExch(p.err, ERR_WAIT_FULL);
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &full[st], (t / A16_STAGES) & 1))) {
+                if (lane == 0) {
+                    atomicExch(p.ctl.err, ERR_WAIT_FULL);
+                    *reinterpret_cast<volatile int*>(&s_failed) = 1;
+                }
                 break;
             }
         } else {
@@ -342,6 +367,7 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             resolve_tile(t + A16_STAGES);   // its loads fly during the next tile's wait and compute
         }
     }
+    trace_last(p.ctl.trace, 2);
 #pragma unroll
     for (int o = 4; o < 32; o <<= 1) {
         l0 += __shfl_xor_sync(0xffffffffu, l0, o);
@@ -349,6 +375,16 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
     }
     if (!TMA) asm volatile("cp.async.wait_group 0;" ::: "memory");
     cons_sync();   // every consumer is past its last tile: the stages are free
+    if (TMA && *reinterpret_cast<volatile int*>(&s_failed)) {
+        // a wait gave up: once the producer has stopped, wait (bounded) for the copies still on their way into the stages
+        asm volatile("bar.sync 2, %0;" ::"n"(A16_THREADS + 32) : "memory");
+        if (tid == 0) {
+            const int issued = *reinterpret_cast<volatile int*>(&s_issued);
+            for (int i = max(0, issued - A16_STAGES); i < issued; i++)
+                if (!mbar_wait_bounded(p.ctl.wait_cycles, &full[i % A16_STAGES], (i / A16_STAGES) & 1)) atomicExch(p.ctl.err, ERR_WAIT_DRAIN);
+        }
+        cons_sync();
+    }
 
     // ---- merge the 4 warps (in stage 0)
     float(*red)[8][HD] = reinterpret_cast<float(*)[8][HD]>(smem);
@@ -392,7 +428,10 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             }
         }
     }
-    if (nch == 1) return;
+    if (nch == 1) {
+        trace_last(p.ctl.trace, 3);
+        return;
+    }
     __threadfence();
     cons_sync();
     if (tid == 0) {
@@ -401,7 +440,10 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
         if (s_last) p.counters[pair] = 0;
     }
     cons_sync();
-    if (!s_last) return;
+    if (!s_last) {
+        trace_last(p.ctl.trace, 3);
+        return;
+    }
     __threadfence();
     const float* base = p.partials + size_t(pair) * p.max_chunks * p.G * A16_PART;
     for (int idx = tid; idx < p.G * HD; idx += A16_THREADS) {
@@ -427,6 +469,7 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
         }
         Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
     }
+    trace_last(p.ctl.trace, 3);
 }
 
 }  // namespace embla

@@ -22,8 +22,22 @@ constexpr float NEG_BIG = -1e30f;        // "-inf" of the running maxima (common
 
 // Device-side error word values (EmblaAttn::err_dev).
 constexpr int ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_WAIT_DRAIN = 3;
-// Bounded waits: tries before a kernel gives up, records an error and leaves.
+// Bounded waits: tries before a kernel gives up, records an error and leaves; and the default bound in SM clocks
+// (about half a second: one try may itself suspend the thread for a while). The clock bound is a launch
+// parameter (KernelCtl::wait_cycles, embla_attn_set_wait_limit).
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
+constexpr long long WAIT_CYCLES = 1ll << 30;
+
+// What every launch takes from its context besides its operands.
+struct KernelCtl {
+    int* err;                    // device error word
+    unsigned long long* trace;   // 4 device timestamps of this launch (trace_* below), or nullptr
+    long long wait_cycles;       // bound of every device-side wait
+    int stall_at;                // diagnostic (embla_attn_inject_stall): the producer stops issuing at this item of
+                                 // its range, so that the consumers' bounded wait runs out; -1: never
+    int early;                   // the launch may fetch its cache rows before the kernel ahead of it in the stream
+                                 // has finished (that kernel writes none of them; set by the step driver)
+};
 
 // ---- host-side error plumbing -------------------------------------------------------------------
 void set_error(const char* fmt, ...);
@@ -63,11 +77,46 @@ struct EmblaAttn {
     int* counters;          // one arrival counter per (sequence, kv head); zero between launches
     int* err_dev;           // device error word
     int partial_slots;      // (sequence, kv head, key range) partials the scratch holds
-    uint8_t* prefill_scratch;      // split-KV partials of the prefill kernel, sized on first need
-    size_t prefill_scratch_bytes;
-    int prefill_counter_units;     // which (units, splits) layout its counters were cleared for
+    uint8_t* prefill_scratch;      // split-KV partials of the prefill kernel (embla_attn_reserve_prefill), then its arrival counters
+    size_t prefill_scratch_bytes;  // bytes of the partials
+    int prefill_counters;          // arrival counters behind them
     int pdl;                       // launches may start before the preceding kernel of the stream has drained (set by the step driver)
+    int early;                     // the next launch may read its cache ahead of the kernel before it (set by the step driver per launch)
+    long long wait_cycles;         // bound of the device-side waits of this context's launches
+    int stall_at;                  // diagnostic stall of the next launches' producers (-1: off)
+    // device-timestamp profiler (embla_attn_trace_*): 4 timestamps a launch, the entry point of each launch
+    unsigned long long* trace_dev;
+    int* trace_entry;              // host
+    int trace_cap, trace_next, trace_on, trace_tag;
+    // tensor maps of the sliding layers' rings seen so far (encoding two of them costs a few microseconds of host time a launch)
+    struct RingMaps {
+        const void* k;
+        const void* v;
+        long long seq_stride;
+        int ring, n_kv_heads, batch;
+        CUtensorMap mk, mv;
+    };
+    enum { RING_MAP_SLOTS = 32 };
+    RingMaps ring_maps[RING_MAP_SLOTS];
+    int ring_maps_used, ring_maps_next;
 };
+
+namespace embla {
+// The control block of the context's next launch; takes the launch's trace slot when the profiler is on.
+inline KernelCtl kernel_ctl(EmblaAttn* ctx) {
+    KernelCtl c;
+    c.err = ctx->err_dev;
+    c.trace = nullptr;
+    if (ctx->trace_on && ctx->trace_next < ctx->trace_cap) {
+        ctx->trace_entry[ctx->trace_next] = ctx->trace_tag;
+        c.trace = ctx->trace_dev + 4 * size_t(ctx->trace_next++);
+    }
+    c.wait_cycles = ctx->wait_cycles;
+    c.stall_at = ctx->stall_at;
+    c.early = ctx->pdl ? ctx->early : 0;
+    return c;
+}
+}  // namespace embla
 
 namespace embla {
 
@@ -133,17 +182,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Waits for the barrier's phase `parity`; gives up after WAIT_LIMIT tries or WAIT_CYCLES clocks (about half a second:
-// one try may itself suspend the thread for a while), whichever comes first, and returns false.
-constexpr long long WAIT_CYCLES = 1ll << 30;
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+// Waits for the barrier's phase `parity`; gives up after WAIT_LIMIT tries or `limit` clocks, whichever comes first,
+// and returns false.
+__device__ __forceinline__ bool mbar_wait_bounded(long long limit, uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > WAIT_CYCLES) return false;
+        if (clock64() - t0 > limit) return false;
     }
     return false;
+}
+
+// ---- device-timestamp profiler: per launch, when the first CTA entered (0), when the first CTA was past its
+// dependency wait (1), when the last CTA left its main loop (2) and when the last CTA finished (3), in nanoseconds of
+// the GPU's global timer. Slots 2 and 3 hold the complement, so that one atomicMin serves all four; the host
+// presets every slot to all ones. Thread 0 of every CTA stamps; a launch without a slot (the usual case) pays one
+// predictable branch.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void trace_first(unsigned long long* tr, int slot) {
+    if (tr != nullptr && threadIdx.x == 0) atomicMin(tr + slot, global_ns());
+}
+__device__ __forceinline__ void trace_last(unsigned long long* tr, int slot) {
+    if (tr != nullptr && threadIdx.x == 0) atomicMin(tr + slot, ~global_ns());
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

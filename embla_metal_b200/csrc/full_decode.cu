@@ -33,7 +33,7 @@ struct FullDecodeParams {
     void* o;
     float* partials;
     int* counters;
-    int* err;
+    KernelCtl ctl;
     float* scores;
     int64_t q_stride, o_stride, scores_stride;
     size_t page_bytes;
@@ -109,8 +109,14 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    pdl_wait();
-    pdl_launch_dependents();
+    trace_first(p.ctl.trace, 0);
+    // Launched with the dependent-launch attribute, the kernel ahead of this one in the stream may still be running
+    // here. An "early" launch (the step driver knows that kernel writes none of this layer's pages) starts its first
+    // pages before it waits for that kernel; seq_lens and the block table are inputs of the whole step.
+    if (!p.ctl.early) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
     const int S = p.seq_lens[b];
     const int npages = (S + BLK - 1) / BLK;
     const int pps = (npages + p.nsplit - 1) / p.nsplit;
@@ -121,7 +127,27 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
     // may have been fetched before that write, puts them into the staged copy before the consumers read it.
     const bool appends = p.k_new != nullptr && n > 0 && pg0 + n == npages;
 
-    if (tid == 0) {
+    // ---- producer: one lane keeps the ring of stages full
+    const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * SB;
+    auto issue = [&](int i) {
+        const int st = i % STAGES, use = i / STAGES;
+        if (i == p.ctl.stall_at) return false;   // diagnostic stall: the consumers' wait for this page runs out
+        if (use > 0 && !mbar_wait_bounded(p.ctl.wait_cycles, &empty[st], (use - 1) & 1)) {
+            atomicExch(p.ctl.err, ERR_WAIT_EMPTY);
+            return false;
+        }
+        const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
+        const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
+        uint8_t* dst = stages + st * FD_STAGE_BYTES;
+        mbar_expect_tx(&full[st], tx);
+        tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &full[st]);
+        bulk_load_1d(dst + 2 * CODE_BYTES, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB, &full[st]);
+        *reinterpret_cast<volatile int*>(&s_issued) = i + 1;
+        return true;
+    };
+    int next = 0;
+    bool issuing = true;
+    if (tid == NWORK * 32) {   // the producer lane sets the barriers up itself, so that it can start before anyone else
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], NWORK);
@@ -130,7 +156,13 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
         s_failed = 0;
         s_issued = 0;
         fence_barrier_init();
+        for (; next < min(n, STAGES) && issuing; next++) issuing = issue(next);   // the stages start empty: no wait
     }
+    if (p.ctl.early) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
+    trace_first(p.ctl.trace, 1);
     // Heads of this kv head into shared memory as fp16 (and fp32 for the scoring chain): optional
     // head norm with gains in the oracle's operation order, rounded to the activation dtype.
     for (int hh = warp; hh < 8; hh += NWORK + 1) {
@@ -173,27 +205,7 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
     float ps0 = 0.0f, ps1 = 0.0f;   // sums of weights of heads 2c, 2c + 1
 
     if (warp == NWORK) {
-        // ---- producer: one lane keeps the ring of stages full
-        const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * SB;
-        auto issue = [&](int i) {
-            const int st = i % STAGES, use = i / STAGES;
-            if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
-                atomicExch(p.err, ERR_WAIT_EMPTY);
-                return false;
-            }
-            const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
-            const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
-            uint8_t* dst = stages + st * FD_STAGE_BYTES;
-            mbar_expect_tx(&full[st], tx);
-            tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &full[st]);
-            bulk_load_1d(dst + 2 * CODE_BYTES, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB, &full[st]);
-            *reinterpret_cast<volatile int*>(&s_issued) = i + 1;
-            return true;
-        };
-        int next = 0;
-        bool issuing = true;
-        if (lane == 0)
-            for (; next < min(n, STAGES) && issuing; next++) issuing = issue(next);   // the stages start empty: no wait
+        // ---- producer, after the first pages
         int code[2][4];
         float rscale[2] = {0.0f, 0.0f};
         const int row = (S - 1) & (BLK - 1);
@@ -222,7 +234,7 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
             __syncwarp();
             const int il = n - 1;
             uint8_t* Kb = stages + (il % STAGES) * FD_STAGE_BYTES;
-            if (mbar_wait_bounded(&full[il % STAGES], (il / STAGES) & 1)) {
+            if (mbar_wait_bounded(p.ctl.wait_cycles, &full[il % STAGES], (il / STAGES) & 1)) {
 #pragma unroll
                 for (int side = 0; side < 2; side++) {
 #pragma unroll
@@ -237,7 +249,7 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
                     }
                 }
             } else if (lane == 0) {
-                atomicExch(p.err, ERR_WAIT_FULL);
+                atomicExch(p.ctl.err, ERR_WAIT_FULL);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&patched);
@@ -246,13 +258,10 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
         // ---- scoring warps
         for (int i = 0; i < n; i++) {
             const int st = i % STAGES, use = i / STAGES;
-            if (!mbar_wait_bounded(&full[st], use & 1)) {
-                atomicExch(p.err, ERR_WAIT_FULL);
-                *reinterpret_cast<volatile int*>(&s_failed) = 1;
-                break;
-            }
-            if (appends && i == n - 1 && !mbar_wait_bounded(&patched, 0)) {
-                atomicExch(p.err, ERR_WAIT_FULL);
+            // (the decision is the warp's: a warp that leaves the loop leaves it whole)
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &full[st], use & 1) &&
+                                             (!(appends && i == n - 1) || mbar_wait_bounded(p.ctl.wait_cycles, &patched, 0)))) {
+                atomicExch(p.ctl.err, ERR_WAIT_FULL);
                 *reinterpret_cast<volatile int*>(&s_failed) = 1;
                 break;
             }
@@ -338,13 +347,10 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
         const float scale = rsqrtf(float(HD));
         for (int i = 0; i < n; i++) {
             const int st = i % STAGES, use = i / STAGES;
-            if (!mbar_wait_bounded(&full[st], use & 1)) {
-                atomicExch(p.err, ERR_WAIT_FULL);
-                *reinterpret_cast<volatile int*>(&s_failed) = 1;
-                break;
-            }
-            if (appends && i == n - 1 && !mbar_wait_bounded(&patched, 0)) {
-                atomicExch(p.err, ERR_WAIT_FULL);
+            // (the decision is the warp's: a warp that leaves the loop leaves it whole)
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &full[st], use & 1) &&
+                                             (!(appends && i == n - 1) || mbar_wait_bounded(p.ctl.wait_cycles, &patched, 0)))) {
+                atomicExch(p.ctl.err, ERR_WAIT_FULL);
                 *reinterpret_cast<volatile int*>(&s_failed) = 1;
                 break;
             }
@@ -423,6 +429,7 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
         }
     }
 
+    trace_last(p.ctl.trace, 2);
     // ---- the consumer warps' sums into one partial. The stage ring is free now: every page that
     // was requested has been waited for, unless a wait gave up — then wait (bounded) for what is
     // still in flight first.
@@ -430,7 +437,7 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
     if (s_failed) {
         if (tid == 0) {
             for (int i = max(0, s_issued - STAGES); i < s_issued; i++)
-                if (!mbar_wait_bounded(&full[i % STAGES], (i / STAGES) & 1)) atomicExch(p.err, ERR_WAIT_DRAIN);
+                if (!mbar_wait_bounded(p.ctl.wait_cycles, &full[i % STAGES], (i / STAGES) & 1)) atomicExch(p.ctl.err, ERR_WAIT_DRAIN);
         }
         __syncthreads();
     }
@@ -474,7 +481,10 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
             if (d == 0) part[hh * FD_PART + HD] = den;
         }
     }
-    if (p.nsplit == 1) return;
+    if (p.nsplit == 1) {
+        trace_last(p.ctl.trace, 3);
+        return;
+    }
     // last CTA of the pair to arrive adds the splits in order (arrive_last, common.metal:88-99)
     __threadfence();
     __syncthreads();
@@ -484,7 +494,10 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
         if (s_last) p.counters[pair] = 0;
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) {
+        trace_last(p.ctl.trace, 3);
+        return;
+    }
     __threadfence();
     const float* base = p.partials + size_t(pair) * p.nsplit * p.G * FD_PART;
     for (int idx = tid; idx < p.G * HD; idx += THREADS) {
@@ -497,6 +510,7 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
         }
         Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / den);
     }
+    trace_last(p.ctl.trace, 3);
 }
 
 template <int STAGES, bool SCORES>
@@ -577,7 +591,7 @@ static EmblaStatus full_decode_impl(EmblaAttn* ctx, const EmblaKVPool* pool, con
     p.o = o_dev;
     p.partials = ctx->partials;
     p.counters = ctx->counters;
-    p.err = ctx->err_dev;
+    p.ctl = kernel_ctl(ctx);
     p.scores = scores_dev;
     p.q_stride = q->q_stride;
     p.o_stride = o_stride;
@@ -727,7 +741,11 @@ extern "C" EmblaStatus embla_attn_full_decode_noalloc(const EmblaKVPool* pool, c
     p.g2 = q->g2_dev;
     p.o = o_dev;
     p.counters = reinterpret_cast<int*>(d.scratch);
-    p.err = reinterpret_cast<int*>(d.scratch + NOALLOC_ERR_OFFSET);
+    p.ctl.err = reinterpret_cast<int*>(d.scratch + NOALLOC_ERR_OFFSET);
+    p.ctl.trace = nullptr;
+    p.ctl.wait_cycles = WAIT_CYCLES;
+    p.ctl.stall_at = -1;
+    p.ctl.early = 0;
     p.partials = reinterpret_cast<float*>(d.scratch + NOALLOC_PART_OFFSET);
     p.scores = nullptr;
     p.q_stride = q->q_stride;

@@ -31,6 +31,11 @@ constexpr int PF_MMA = PF_PRODUCER + 1;
 constexpr int PF_THREADS = (PF_MMA + 1) * 32;
 constexpr int PF_TILE16 = BLK * HD * 2;            // 32 KiB: 128 rows x 128 dims fp16
 constexpr int PF_KVBUFS = 3;
+// The queries enter the tensor cores scaled by 2^-3 (exact), so the weights p = relu(s)^2, which the kernel keeps as
+// fp16 (P in TMEM, packed row sums), come out scaled by 2^-6: a score of 2047 still squares inside fp16's range (the
+// reference keeps P in fp32, attn_nax.metal:11), and fp16's gradual underflow keeps the small weights to 2^-24 of the
+// scaled unit. The sink of the denominator takes the same factor, so O / (sink + sum p) is unchanged.
+constexpr float PF_QSCALE = 0.125f, PF_PSCALE = PF_QSCALE * PF_QSCALE;
 // alignment slack, 2 Q tiles, 3 converted sides, 3 raw int8 sides, 2 pages' scales, barriers
 constexpr size_t PF_SMEM = 1024 + 2 * PF_TILE16 + PF_KVBUFS * PF_TILE16 + PF_KVBUFS * CODE_BYTES + 2 * 1024 + 256;
 
@@ -42,7 +47,7 @@ struct PrefillParams {
     const void* g1;
     const void* g2;
     void* o;
-    int* err;
+    KernelCtl ctl;
     float* partials;      // split-KV: [unit][split][tile][128 + 1 columns][128 rows] fp32 (unnormalised O, then the row sums)
     int* counters;        // [unit] arrivals
     int64_t q_token_stride, q_seq_stride, o_token_stride, o_seq_stride;
@@ -153,10 +158,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                 if (r < rows[x]) {
                     const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + r) * p.q_token_stride + size_t(h) * HD + c8 * 8;
                     v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
+                    uint32_t* w = &v.x;
                     if (DT == EMBLA_BF16) {
-                        uint32_t* w = &v.x;
 #pragma unroll
-                        for (int e = 0; e < 4; e++) w[e] = pack_h2(__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xffff0000u));
+                        for (int e = 0; e < 4; e++)
+                            w[e] = pack_h2(__uint_as_float(w[e] << 16) * PF_QSCALE, __uint_as_float(w[e] & 0xffff0000u) * PF_QSCALE);
+                    } else {
+                        const __half2 qs2 = __float2half2_rn(PF_QSCALE);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const __half2 t = __hmul2(*reinterpret_cast<const __half2*>(&w[e]), qs2);
+                            w[e] = *reinterpret_cast<const uint32_t*>(&t);
+                        }
                     }
                 }
                 *reinterpret_cast<uint4*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v;
@@ -195,7 +208,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                     for (int i = 0; i < 4; i++) {
                         const int d = lane + 32 * i, c8 = d >> 3;
                         *reinterpret_cast<__half*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4) + (d & 7) * 2) =
-                            __float2half_rn(xq[k][i]);
+                            __float2half_rn(xq[k][i] * PF_QSCALE);
                     }
                 }
             }
@@ -213,8 +226,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         if (lane == 0) {
             for (int c = 0; c < 2 * n; c++) {
                 const int j = jb + (c >> 1), side = c & 1, slot = c % 3;
-                if (c >= 3 && !mbar_wait_bounded(&raw_empty[slot], ((c / 3) - 1) & 1)) {
-                    atomicExch(p.err, ERR_WAIT_EMPTY);
+                if (c == p.ctl.stall_at) break;   // diagnostic stall: the converters' wait for this side runs out
+                if (c >= 3 && !mbar_wait_bounded(p.ctl.wait_cycles, &raw_empty[slot], ((c / 3) - 1) & 1)) {
+                    atomicExch(p.ctl.err, ERR_WAIT_EMPTY);
                     break;
                 }
                 if (*reinterpret_cast<volatile int*>(&s_abort)) break;
@@ -255,14 +269,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                 const bool a0 = i < n && jb + i < npg[0], a1 = i < n && jb + i < npg[1];   // tiles active on this page
                 const bool b1 = i >= 1 && jb + i - 1 < npg[1];                              // tile 1 had the page before
                 if (a0 || a1) {
-                    ok = mbar_wait_bounded(&kv_ready[(2 * i) % 3], ((2 * i) / 3) & 1);
+                    ok = mbar_wait_bounded(p.ctl.wait_cycles, &kv_ready[(2 * i) % 3], ((2 * i) / 3) & 1);
                     if (!ok) break;
                     tc_fence_after();
                 }
                 if (a0) issue_s(0, i);
                 if (b1) {
                     const int cv = 2 * (i - 1) + 1;
-                    ok = mbar_wait_bounded(&p_ready[1], (i - 1) & 1) && mbar_wait_bounded(&kv_ready[cv % 3], (cv / 3) & 1);
+                    ok = mbar_wait_bounded(p.ctl.wait_cycles, &p_ready[1], (i - 1) & 1) && mbar_wait_bounded(p.ctl.wait_cycles, &kv_ready[cv % 3], (cv / 3) & 1);
                     if (!ok) break;
                     tc_fence_after();
                     issue_pv(1, i - 1);
@@ -272,14 +286,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                 if (a0 || a1) tc_commit(&kv_free[(2 * i) % 3]);           // K of this page
                 if (a0) {
                     const int cv = 2 * i + 1;
-                    ok = mbar_wait_bounded(&p_ready[0], i & 1) && mbar_wait_bounded(&kv_ready[cv % 3], (cv / 3) & 1);
+                    ok = mbar_wait_bounded(p.ctl.wait_cycles, &p_ready[0], i & 1) && mbar_wait_bounded(p.ctl.wait_cycles, &kv_ready[cv % 3], (cv / 3) & 1);
                     if (!ok) break;
                     tc_fence_after();
                     issue_pv(0, i);
                 }
             }
             if (!ok) {
-                atomicExch(p.err, ERR_WAIT_FULL);
+                atomicExch(p.ctl.err, ERR_WAIT_FULL);
                 *reinterpret_cast<volatile int*>(&s_abort) = 1;
             }
             tc_commit(o_done);
@@ -290,8 +304,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         bool ok = true;
         for (int c = 0; c < 2 * n && ok; c++) {
             const int side = c & 1, slot = c % 3;
-            ok = mbar_wait_bounded(&raw_full[slot], (c / 3) & 1);
-            if (ok && c >= 3) ok = mbar_wait_bounded(&kv_free[slot], ((c / 3) - 1) & 1);
+            ok = mbar_wait_bounded(p.ctl.wait_cycles, &raw_full[slot], (c / 3) & 1);
+            if (ok && c >= 3) ok = mbar_wait_bounded(p.ctl.wait_cycles, &kv_free[slot], ((c / 3) - 1) & 1);
             if (!ok) break;
             convert_side<SB>(raw + slot * CODE_BYTES, kvb + slot * PF_TILE16, ctid, scl + ((c >> 1) & 1) * 1024 + side * BLK * SB,
                              side == 0 ? rsqrtf(float(HD)) : 1.0f);
@@ -303,7 +317,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             }
         }
         if (!ok) {
-            atomicExch(p.err, ERR_WAIT_FULL);
+            atomicExch(p.ctl.err, ERR_WAIT_FULL);
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
         }
     } else {
@@ -317,7 +331,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         bool ok = true;
         for (int i = 0; i < nx; i++) {
             const int j = jb + i;
-            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&s_full[x], i & 1));
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &s_full[x], i & 1));
             if (!ok) break;   // (warp-uniform: the TMEM loads below are warp-collective)
             tc_fence_after();
             const bool diag = j * BLK + BLK - 1 > p0 + t0[x];   // some (row, key) of this page is masked
@@ -364,10 +378,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[x]);
         }
-        if (ok) ok = mbar_wait_bounded(o_done, 0);
+        if (ok) ok = mbar_wait_bounded(p.ctl.wait_cycles, o_done, 0);
         ok = __all_sync(0xffffffffu, ok);   // (warp-uniform: the TMEM loads below are warp-collective)
         if (!ok) {
-            atomicExch(p.err, ERR_WAIT_FULL);
+            atomicExch(p.ctl.err, ERR_WAIT_FULL);
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
         } else if (p.nsplit > 1) {
             // unnormalised O and the row sum of this page range into the scratch (zeros if the tile saw no page here)
@@ -385,7 +399,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             pcol[size_t(HD) * BLK] = rowsum;
         } else if (nx > 0) {
             tc_fence_after();
-            const float inv = 1.0f / (sqrtf(float(HD)) + rowsum);
+            const float inv = 1.0f / (sqrtf(float(HD)) * PF_PSCALE + rowsum);
             uint16_t* orow = static_cast<uint16_t*>(p.o) + size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
 #pragma unroll 1
             for (int cc = 0; cc < 4; cc++) {
@@ -441,7 +455,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         if (c < HD) tile[(lane + 32 * i) * (HD + 1) + c] = acc[i];
-                        else den[lane + 32 * i] = sqrtf(float(HD)) + acc[i];
+                        else den[lane + 32 * i] = sqrtf(float(HD)) * PF_PSCALE + acc[i];
                     }
                 }
                 __syncthreads();
@@ -467,6 +481,22 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
 
 using namespace embla;
 
+// bytes of one (unit, page range) slot of partial sums: two tiles of [128 + 1 columns][128 rows] fp32
+static constexpr size_t PF_SLOT_BYTES = size_t(2) * BLK * (HD + 1) * sizeof(float);
+
+extern "C" EmblaStatus embla_attn_reserve_prefill(EmblaAttn* ctx, void* stream) {
+    if (!ctx) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_reserve_prefill: null context");
+    if (ctx->prefill_scratch) return EMBLA_OK;
+    // A split pays only while the CTAs fit one wave or two: two slots an SM, one counter a unit.
+    const size_t slots = 2 * size_t(ctx->sm_count), counters = 2 * size_t(ctx->sm_count);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    EMBLA_CUDA_TRY(cudaMalloc(&ctx->prefill_scratch, slots * PF_SLOT_BYTES + counters * sizeof(int)));
+    EMBLA_CUDA_TRY(cudaMemsetAsync(ctx->prefill_scratch + slots * PF_SLOT_BYTES, 0, counters * sizeof(int), s));
+    ctx->prefill_scratch_bytes = slots * PF_SLOT_BYTES;
+    ctx->prefill_counters = int(counters);
+    return EMBLA_OK;
+}
+
 template <int DT, int SB>
 static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, PrefillParams& p, int batch, int max_pages, cudaStream_t s) {
     auto kern = full_prefill_kernel<DT, SB>;
@@ -483,9 +513,12 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     // of a CTA: about 2 pages' worth for the query load, TMEM set-up and pipeline fill, and when the unit is split about 9
     // (132 KB of partials written, then added by the unit's last CTA)), ranges of at least 8 pages, at most 16. Measured at
     // 128 units x 252 pages on 148 SMs: 1 range 0.53 ms, 2: 0.57, 4: 0.59, 8: 0.60 - one range is best there.
+    // The partial sums live in scratch that embla_attn_reserve_prefill allocated (this call never allocates or
+    // synchronises): a split is taken only as far as that scratch holds it; without a reserve every unit is one CTA.
+    const long slots = long(ctx->prefill_scratch_bytes / PF_SLOT_BYTES);
     int nsplit = 1;
     long best = -1;
-    for (int ns = 1; ns <= 16 && (ns == 1 || max_pages / ns >= 8); ns++) {
+    for (int ns = 1; ns <= 16 && (ns == 1 || (max_pages / ns >= 8 && long(units) * ns <= slots && units <= ctx->prefill_counters)); ns++) {
         const long waves = (long(units) * ns + ctx->sm_count - 1) / ctx->sm_count;
         const long cost = waves * ((max_pages + ns - 1) / ns + (ns > 1 ? 9 : 2));
         if (best < 0 || cost < best) {
@@ -497,22 +530,9 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     p.partials = nullptr;
     p.counters = nullptr;
     if (nsplit > 1) {
-        const size_t need = size_t(units) * nsplit * 2 * BLK * (HD + 1) * sizeof(float) + size_t(units) * sizeof(int);
-        if (need > ctx->prefill_scratch_bytes) {
-            EMBLA_CUDA_TRY(cudaStreamSynchronize(s));
-            cudaFree(ctx->prefill_scratch);
-            ctx->prefill_scratch = nullptr;
-            ctx->prefill_scratch_bytes = 0;
-            EMBLA_CUDA_TRY(cudaMalloc(&ctx->prefill_scratch, need));
-            ctx->prefill_scratch_bytes = need;
-        }
-        // counters sit after the partials; they are left at zero by every launch, cleared when (re)sized
+        // the counters sit after the partials and are left at zero by every launch
         p.partials = reinterpret_cast<float*>(ctx->prefill_scratch);
-        p.counters = reinterpret_cast<int*>(ctx->prefill_scratch + (need - size_t(units) * sizeof(int)));
-        if (ctx->prefill_counter_units != units * 1000 + nsplit) {
-            EMBLA_CUDA_TRY(cudaMemsetAsync(p.counters, 0, size_t(units) * sizeof(int), s));
-            ctx->prefill_counter_units = units * 1000 + nsplit;
-        }
+        p.counters = reinterpret_cast<int*>(ctx->prefill_scratch + ctx->prefill_scratch_bytes);
     }
     dim3 grid(pairs * nsplit, ctx->cfg.n_q_heads, batch);
     kern<<<grid, PF_THREADS, PF_SMEM, s>>>(pool->tmap_half, p);
@@ -543,7 +563,7 @@ extern "C" EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool
     p.g1 = q->g1_dev;
     p.g2 = q->g2_dev;
     p.o = o_dev;
-    p.err = ctx->err_dev;
+    p.ctl = kernel_ctl(ctx);
     p.q_token_stride = q_token_stride;
     p.q_seq_stride = q->q_stride;
     p.o_token_stride = o_token_stride;

@@ -23,7 +23,7 @@ struct ScoreParams {
     const int32_t* seq_lens;
     const void* q;
     float* scores;
-    int* err;
+    KernelCtl ctl;
     int64_t q_stride, scores_stride;
     int table_stride, layer, n_layers, n_kv_heads, rows_per_page, nsplit;
     // the current token's raw k and v rows, or NULL: appended to the 16-bit page by this launch (kv_append fused)
@@ -71,51 +71,71 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    pdl_wait();
-    pdl_launch_dependents();
+    trace_first(p.ctl.trace, 0);
+    // An "early" launch (the kernel ahead of it in the stream writes none of this layer's pages) starts its first pages
+    // before it waits for that kernel; seq_lens and the block table are inputs of the whole step.
+    if (!p.ctl.early) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
     const int S = p.seq_lens[b];
     const int npages = (S + BLK - 1) / BLK;
     const int pps = (npages + p.nsplit - 1) / p.nsplit;
     const int pg0 = split * pps;
     const int n = max(0, min(npages, pg0 + pps) - pg0);
-    if (n == 0) return;
+    if (n == 0) {
+        if (p.ctl.early) {
+            pdl_wait();
+            pdl_launch_dependents();
+        }
+        return;
+    }
     // The CTA whose range ends with the sequence's last page also appends the current token (position S - 1): its
     // producer warp writes the k and v rows to the page for the kernels and steps to come and puts the k row into the
     // staged copy of the page, which may have been fetched before that write.
     const bool appends = p.k_new != nullptr && pg0 + n == npages;
     __shared__ uint64_t patched;
+    __shared__ int s_failed, s_issued;
 
-    if (tid == 0) {
+    auto issue = [&](int i) {
+        const int st = i % STAGES, use = i / STAGES;
+        if (i == p.ctl.stall_at) return false;   // diagnostic stall: the consumers' wait for this page runs out
+        if (use > 0 && !mbar_wait_bounded(p.ctl.wait_cycles, &empty[st], (use - 1) & 1)) {
+            atomicExch(p.ctl.err, ERR_WAIT_EMPTY);
+            return false;
+        }
+        const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
+        const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
+        uint8_t* dst = stages + st * SK_STAGE;
+        mbar_expect_tx(&full[st], SK_STAGE);
+        tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &full[st]);
+        tma_load_2d(dst + BLK * 128, &tmap, 128, int(page * p.rows_per_page), &full[st]);
+        *reinterpret_cast<volatile int*>(&s_issued) = i + 1;
+        return true;
+    };
+    int next = 0;
+    bool issuing = true;
+    if (tid == SK_CONSUMERS * 32) {   // the producer lane sets the barriers up itself, so that it can start before anyone else
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], SK_CONSUMERS);
         }
         mbar_init(&patched, 1);
+        s_failed = 0;
+        s_issued = 0;
         fence_barrier_init();
+        for (; next < min(n, STAGES) && issuing; next++) issuing = issue(next);   // the stages start empty: no wait
     }
+    if (p.ctl.early) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
+    trace_first(p.ctl.trace, 1);
     for (int i = tid; i < G * HD; i += SK_THREADS)
         qs[i] = reinterpret_cast<const uint16_t*>(p.q)[size_t(b) * p.q_stride + size_t(kvh * G) * HD + i];
     __syncthreads();
 
     if (warp == SK_CONSUMERS) {
-        auto issue = [&](int i) {
-            const int st = i % STAGES, use = i / STAGES;
-            if (use > 0 && !mbar_wait_bounded(&empty[st], (use - 1) & 1)) {
-                atomicExch(p.err, ERR_WAIT_EMPTY);
-                return false;
-            }
-            const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
-            const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
-            uint8_t* dst = stages + st * SK_STAGE;
-            mbar_expect_tx(&full[st], SK_STAGE);
-            tma_load_2d(dst, &tmap, 0, int(page * p.rows_per_page), &full[st]);
-            tma_load_2d(dst + BLK * 128, &tmap, 128, int(page * p.rows_per_page), &full[st]);
-            return true;
-        };
-        int next = 0;
-        bool issuing = true;
-        if (lane == 0)
-            for (; next < min(n, STAGES) && issuing; next++) issuing = issue(next);   // the stages start empty: no wait
         float xk[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         const int row = (S - 1) & (BLK - 1);
         if (appends) {
@@ -138,56 +158,68 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
             __syncwarp();
             const int il = n - 1;
             uint8_t* Kt = stages + (il % STAGES) * SK_STAGE;
-            if (mbar_wait_bounded(&full[il % STAGES], (il / STAGES) & 1)) {
+            if (mbar_wait_bounded(p.ctl.wait_cycles, &full[il % STAGES], (il / STAGES) & 1)) {
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     const int d = lane + 32 * i;
                     Act<DT>::store(Kt + (d >> 6) * (BLK * 128) + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4) + (d & 7) * 2, 0, xk[i]);
                 }
             } else if (lane == 0) {
-                atomicExch(p.err, ERR_WAIT_FULL);
+                atomicExch(p.ctl.err, ERR_WAIT_FULL);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&patched);
         }
-        return;
     }
-    const int r = warp * 32 + lane;   // this thread's key of every page
-    for (int i = 0; i < n; i++) {
-        const int st = i % STAGES, use = i / STAGES;
-        if (!mbar_wait_bounded(&full[st], use & 1) || (appends && i == n - 1 && !mbar_wait_bounded(&patched, 0))) {
-            atomicExch(p.err, ERR_WAIT_FULL);
-            return;
-        }
-        const uint32_t Kb = smem_u32(stages + st * SK_STAGE) + r * 128, qa = smem_u32(qs);
-        float dot[G];
+    if (warp < SK_CONSUMERS) {
+        const int r = warp * 32 + lane;   // this thread's key of every page
+        for (int i = 0; i < n; i++) {
+            const int st = i % STAGES, use = i / STAGES;
+            // (the decision is the warp's: a warp that leaves the loop leaves it whole)
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &full[st], use & 1) &&
+                                             (!(appends && i == n - 1) || mbar_wait_bounded(p.ctl.wait_cycles, &patched, 0)))) {
+                atomicExch(p.ctl.err, ERR_WAIT_FULL);
+                *reinterpret_cast<volatile int*>(&s_failed) = 1;
+                break;
+            }
+            const uint32_t Kb = smem_u32(stages + st * SK_STAGE) + r * 128, qa = smem_u32(qs);
+            float dot[G];
 #pragma unroll
-        for (int h = 0; h < G; h++) dot[h] = 0.0f;
+            for (int h = 0; h < G; h++) dot[h] = 0.0f;
 #pragma unroll
-        for (int half = 0; half < 2; half++) {
+            for (int half = 0; half < 2; half++) {
 #pragma unroll
-            for (int ch = 0; ch < 8; ch++) {
-                const uint4 kw = lds128(Kb + half * (BLK * 128) + ((ch ^ (r & 7)) << 4));
-                const int d = half * 64 + ch * 8;
+                for (int ch = 0; ch < 8; ch++) {
+                    const uint4 kw = lds128(Kb + half * (BLK * 128) + ((ch ^ (r & 7)) << 4));
+                    const int d = half * 64 + ch * 8;
 #pragma unroll
-                for (int h = 0; h < G; h++) {
-                    const uint4 qw = lds128(qa + (h * HD + d) * 2);   // one address a warp: a broadcast
-                    fma_pair<DT>(dot[h], kw.x, qw.x);
-                    fma_pair<DT>(dot[h], kw.y, qw.y);
-                    fma_pair<DT>(dot[h], kw.z, qw.z);
-                    fma_pair<DT>(dot[h], kw.w, qw.w);
+                    for (int h = 0; h < G; h++) {
+                        const uint4 qw = lds128(qa + (h * HD + d) * 2);   // one address a warp: a broadcast
+                        fma_pair<DT>(dot[h], kw.x, qw.x);
+                        fma_pair<DT>(dot[h], kw.y, qw.y);
+                        fma_pair<DT>(dot[h], kw.z, qw.z);
+                        fma_pair<DT>(dot[h], kw.w, qw.w);
+                    }
                 }
             }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[st]);
-        float best = dot[0];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[st]);
+            float best = dot[0];
 #pragma unroll
-        for (int h = 1; h < G; h++)
-            if (dot[h] > best) best = dot[h];
-        const int key = (pg0 + i) * BLK + r;
-        if (key < S) p.scores[(size_t(b) * p.n_kv_heads + kvh) * p.scores_stride + key] = best;
+            for (int h = 1; h < G; h++)
+                if (dot[h] > best) best = dot[h];
+            const int key = (pg0 + i) * BLK + r;
+            if (key < S) p.scores[(size_t(b) * p.n_kv_heads + kvh) * p.scores_stride + key] = best;
+        }
     }
+    trace_last(p.ctl.trace, 2);
+    // A wait that gave up: no thread leaves while a copy may still be on its way into this CTA's stages.
+    __syncthreads();
+    if (s_failed && tid == 0) {
+        for (int i = max(0, s_issued - STAGES); i < s_issued; i++)
+            if (!mbar_wait_bounded(p.ctl.wait_cycles, &full[i % STAGES], (i / STAGES) & 1)) atomicExch(p.ctl.err, ERR_WAIT_DRAIN);
+    }
+    trace_last(p.ctl.trace, 3);
 }
 
 int choose_splits(int pairs, int pages, int slots, int max_slots);
@@ -229,7 +261,7 @@ static EmblaStatus score_keys_impl(EmblaAttn* ctx, const EmblaKVPool* pool, cons
     p.seq_lens = view->seq_lens_dev;
     p.q = q_dev;
     p.scores = scores_dev;
-    p.err = ctx->err_dev;
+    p.ctl = kernel_ctl(ctx);
     p.q_stride = q_stride;
     p.scores_stride = scores_stride;
     p.table_stride = view->table_stride;

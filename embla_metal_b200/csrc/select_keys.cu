@@ -26,7 +26,7 @@ struct SelectParams {
     uint32_t* idx;
     int64_t scores_stride;   // floats between (sequence, kv head) rows
     int n_kv_heads;
-    int* err;
+    KernelCtl ctl;
 };
 
 __device__ __forceinline__ uint32_t order_bits(float f) {   // attention.metal:657-660
@@ -65,8 +65,10 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
     };
     const int kvh = blockIdx.x / CL, b = blockIdx.y;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    trace_first(p.ctl.trace, 0);
     pdl_wait();
     pdl_launch_dependents();
+    trace_first(p.ctl.trace, 1);
     const int S = p.seq_lens[b];
     // the reference does not select yet at or below 1152 keys (Engine.swift:796); uniform over the cluster, and
     // every CTA keeps taking the barriers
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
         }
         for (int i = t; i < 2 * SEL_BINS; i += SEL_T) (&hist[0][0])[i] = 0;
         __syncthreads();
-        if (bytes && !mbar_wait_bounded(&bar, 0) && lane == 0) atomicExch(p.err, ERR_WAIT_FULL);
+        if (bytes && !mbar_wait_bounded(p.ctl.wait_cycles, &bar, 0) && lane == 0) atomicExch(p.ctl.err, ERR_WAIT_FULL);
 #pragma unroll
         for (int i = 0; i < ITEMS; i++) v[i] = 32 * i < lim ? order_bits(staged[warp * 32 * ITEMS + 32 * i + lane]) : 0u;
     } else {
@@ -179,6 +181,7 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
             k -= sel[1];
         }
     }
+    trace_last(p.ctl.trace, 2);
     // prefix is the TOPK-th largest pattern; every key above it, then the first k equal to it, in key order.
     // Lane i keeps round i's ballots, so the counts and the writes below cost a few instructions a warp.
     uint32_t mybg = 0, mybe = 0;
@@ -234,6 +237,7 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
             for (int j = t; j < EMBLA_RECENT; j += SEL_T) out[EMBLA_TOPK + j] = uint32_t(n + j);
     }
     if (!SINGLE) cluster.sync();   // no CTA leaves while another may still read its shared memory
+    trace_last(p.ctl.trace, 3);
 }
 
 template <int ITEMS, bool BULK, bool SINGLE>
@@ -297,12 +301,16 @@ extern "C" EmblaStatus embla_select_keys(EmblaAttn* ctx, const float* scores_dev
     p.idx = idx_dev;
     p.scores_stride = scores_stride;
     p.n_kv_heads = ctx->cfg.n_kv_heads;
-    p.err = ctx->err_dev;
+    p.ctl = kernel_ctl(ctx);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int n_max = max_len - EMBLA_RECENT;   // keys a pair ranks: CL CTAs x 1024 threads x ITEMS
-    if (n_max > 1024 * 32) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_select_keys: %d keys (at most %d)", max_len, 1024 * 32 + EMBLA_RECENT);
-    // small batches: a cluster of 2, 4 or 8 CTAs per (sequence, kv head), as many as keep the GPU busy
+    if (n_max > EMBLA_SELECT_MAX_KEYS - EMBLA_RECENT)
+        EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_select_keys: %d keys (at most %d: 8 CTAs x 1024 threads x 32 keys + the %d latest)", max_len,
+                   EMBLA_SELECT_MAX_KEYS, EMBLA_RECENT);
+    // long rows: as many CTAs a pair as it takes to hold its keys in registers (32 a lane); small batches: a cluster of
+    // 2, 4 or 8 CTAs per (sequence, kv head), as many as keep the GPU busy
     int cl = 1;
+    while (cl < 8 && n_max > 1024 * 32 * cl) cl *= 2;
     while (cl < 8 && 2 * cl * p.n_kv_heads * batch <= ctx->sm_count && n_max > 1024 * cl) cl *= 2;
     const int per_thread = (n_max + 1024 * cl - 1) / (1024 * cl);
     // bulk copies want 16-byte aligned rows; any other layout takes the lanes' own loads

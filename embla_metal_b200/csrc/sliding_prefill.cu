@@ -274,7 +274,7 @@ extern "C" EmblaStatus embla_attn_sliding_prefill(EmblaAttn* ctx, const EmblaRin
         t.q = q->q_dev;
         t.g1 = q->g1_dev;
         t.o = o_dev;
-        t.err = ctx->err_dev;
+        t.ctl = kernel_ctl(ctx);
         t.q_token_stride = q_token_stride;
         t.q_seq_stride = q->q_stride;
         t.o_token_stride = o_token_stride;

@@ -142,8 +142,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
                 const int j = jb + (c < nblk ? c : (c - nblk) >> 1);
                 const bool is_v = c >= nblk && ((c - nblk) & 1);
                 const int slot = c % ST_BUFS;
-                if (c >= ST_BUFS && !mbar_wait_bounded(&kv_free[slot], ((c / ST_BUFS) - 1) & 1)) {
-                    atomicCAS(p.err, 0, 1000 + c);
+                if (c >= ST_BUFS && !mbar_wait_bounded(p.ctl.wait_cycles, &kv_free[slot], ((c / ST_BUFS) - 1) & 1)) {
+                    atomicCAS(p.ctl.err, 0, 1000 + c);
                     break;
                 }
                 if (*reinterpret_cast<volatile int*>(&s_abort)) break;
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
             __syncwarp();
             const int cl = 3 * nblk - 1;                   // the last load: V of block je
             uint8_t* vb = kvb + (cl % ST_BUFS) * ST_TILE;
-            if (mbar_wait_bounded(&kv_ready[cl % ST_BUFS], (cl / ST_BUFS) & 1)) {
+            if (mbar_wait_bounded(p.ctl.wait_cycles, &kv_ready[cl % ST_BUFS], (cl / ST_BUFS) & 1)) {
                 const int first = (chunk_end & (BLK - 1)) + 1;
                 for (int i = first * 16 + lane; i < BLK * 16; i += 32) {      // 16 x 16 bytes a row: 8 in each half
                     const int row = i >> 4, q16 = i & 15;
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
                 }
                 fence_proxy_async();
             } else if (lane == 0) {
-                atomicCAS(p.err, 0, 1900);
+                atomicCAS(p.ctl.err, 0, 1900);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(v_clean);
@@ -179,8 +179,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
             int site = 0;              // where a wait gave up: 100 pass + 10 step + ..., reported in the error word
             int us[2] = {0, 0};        // S products issued per tile (the phase counters of s_full / p_ready)
             auto wait_load = [&](int cc) {
-                if (!mbar_wait_bounded(&kv_ready[cc % ST_BUFS], (cc / ST_BUFS) & 1)) return false;
-                return !(clean_v && cc == 3 * nblk - 1) || mbar_wait_bounded(v_clean, 0);
+                if (!mbar_wait_bounded(p.ctl.wait_cycles, &kv_ready[cc % ST_BUFS], (cc / ST_BUFS) & 1)) return false;
+                return !(clean_v && cc == 3 * nblk - 1) || mbar_wait_bounded(p.ctl.wait_cycles, v_clean, 0);
             };
             // bfloat16 operands: formats of A and B in the instruction descriptor (bits 7-9 and 10-12)
             constexpr uint32_t fmt = DT == EMBLA_BF16 ? (1u << 7) | (1u << 10) : 0u;
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
                 }
             };
             // the tile's warps are done with the S product before its us[x]-th (they arrive once per product)
-            auto wait_tile = [&](int x) { return us[x] == 0 || mbar_wait_bounded(&p_ready[x], (us[x] - 1) & 1); };
+            auto wait_tile = [&](int x) { return us[x] == 0 || mbar_wait_bounded(p.ctl.wait_cycles, &p_ready[x], (us[x] - 1) & 1); };
             // ---- pass A: row maxima
             for (int i = 0; i < nblk && ok; i++, c++) {
                 const int j = jb + i;
@@ -250,7 +250,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
                 }
                 if (pv1_load >= 0) {
                     site = 500 + i;
-                    ok = mbar_wait_bounded(&p_ready[1], (us[1] - 1) & 1) && wait_load(pv1_load);
+                    ok = mbar_wait_bounded(p.ctl.wait_cycles, &p_ready[1], (us[1] - 1) & 1) && wait_load(pv1_load);
                     if (!ok) break;
                     tc_fence_after();
                     issue_pv(1, pv1_load, first_pv[1]);
@@ -272,7 +272,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
                 if (i < nblk) tc_commit(&kv_free[ck % ST_BUFS]);   // K of this block
                 if (a0) {
                     site = 700 + i;
-                    ok = mbar_wait_bounded(&p_ready[0], (us[0] - 1) & 1) && wait_load(cv);
+                    ok = mbar_wait_bounded(p.ctl.wait_cycles, &p_ready[0], (us[0] - 1) & 1) && wait_load(cv);
                     if (!ok) break;
                     tc_fence_after();
                     issue_pv(0, cv, first_pv[0]);
@@ -282,7 +282,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
                 if (i < nblk) c += 2;
             }
             if (!ok) {
-                atomicCAS(p.err, 0, 2000 + site);
+                atomicCAS(p.ctl.err, 0, 2000 + site);
                 *reinterpret_cast<volatile int*>(&s_abort) = 1;
             }
             tc_commit(o_done);
@@ -304,7 +304,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
             const float mc = mrow * c2;
             for (int i = 0; i < nx && ok; i++, u++) {
                 const int j = jlo[x] + i;
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&s_full[x], u & 1));
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &s_full[x], u & 1));
                 if (!ok) break;   // (warp-uniform: the TMEM loads below are warp-collective)
                 tc_fence_after();
                 // weights of 32 keys from kb on: exp(s - max) masked to the row's window, summed in fp32, packed in pairs
@@ -364,12 +364,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
             }
         }
         if (ok) {
-            ok = mbar_wait_bounded(o_done, 0);
+            ok = mbar_wait_bounded(p.ctl.wait_cycles, o_done, 0);
             if (!ok) u = 99;
         }
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
-            atomicCAS(p.err, 0, 3000 + 100 * x + u);
+            atomicCAS(p.ctl.err, 0, 3000 + 100 * x + u);
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
         } else if (ntok[x] > 0) {
             // (the TMEM loads are warp-collective: every thread of the warpgroup takes them, rows past the chunk only skip the stores)

@@ -11,7 +11,7 @@ struct SlidingTcParams {
     const void* q;
     const void* g1;
     void* o;
-    int* err;
+    KernelCtl ctl;
     int64_t q_token_stride, q_seq_stride, o_token_stride, o_seq_stride;
     int n_tokens, n_kv_heads, G, prenormed, ring, window;
     float rope_freq[32];

@@ -25,6 +25,7 @@ struct Sparse8Params {
     void* o;
     float* partials;
     int* counters;
+    KernelCtl ctl;
     int64_t q_stride, o_stride;
     size_t page_bytes;
     int table_stride, layer, n_layers, n_kv_heads, G, prenormed, ng, max_chunks;
@@ -43,8 +44,10 @@ __global__ void __launch_bounds__(S8_THREADS) sparse8_decode_kernel(const Sparse
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    trace_first(p.ctl.trace, 0);
     pdl_wait();
     pdl_launch_dependents();
+    trace_first(p.ctl.trace, 1);
     const int S = p.seq_lens[b];
     const bool selecting = S > EMBLA_TOPK + EMBLA_RECENT;
     const int count = selecting ? EMBLA_TOPK + EMBLA_RECENT : S;
@@ -233,7 +236,11 @@ __global__ void __launch_bounds__(S8_THREADS) sparse8_decode_kernel(const Sparse
             }
         }
     }
-    if (nch == 1) return;
+    trace_last(p.ctl.trace, 2);
+    if (nch == 1) {
+        trace_last(p.ctl.trace, 3);
+        return;
+    }
     __threadfence();
     __syncthreads();
     if (tid == 0) {
@@ -242,7 +249,10 @@ __global__ void __launch_bounds__(S8_THREADS) sparse8_decode_kernel(const Sparse
         if (s_last) p.counters[pair] = 0;
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) {
+        trace_last(p.ctl.trace, 3);
+        return;
+    }
     __threadfence();
     const float* base = p.partials + size_t(pair) * p.max_chunks * p.G * S8_PART;
     for (int idx = tid; idx < p.G * HD; idx += S8_THREADS) {
@@ -268,6 +278,7 @@ __global__ void __launch_bounds__(S8_THREADS) sparse8_decode_kernel(const Sparse
         }
         Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
     }
+    trace_last(p.ctl.trace, 3);
 }
 
 template <int DT, int SB>
@@ -310,6 +321,7 @@ extern "C" EmblaStatus embla_attn_sparse_decode_int8(EmblaAttn* ctx, const Embla
     p.o = o_dev;
     p.partials = ctx->partials;
     p.counters = ctx->counters;
+    p.ctl = kernel_ctl(ctx);
     p.q_stride = q->q_stride;
     p.o_stride = o_stride;
     p.page_bytes = pool->page_bytes;

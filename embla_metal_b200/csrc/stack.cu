@@ -24,7 +24,13 @@ struct EmblaStack {
     int probe;
     std::vector<cudaEvent_t> ev;
     int ev_used;
+    int early_ok;         // launches may fetch their cache ahead of the preceding kernel (EMBLA_NO_EARLY=1 turns it off)
 };
+
+// What a launch of the step writes / streams, for the "early" rule: a launch may request its cache rows before the
+// kernel ahead of it in the stream has finished only if that kernel writes none of them (it appends the current token
+// to its own layer's cache, nothing else), and never as the first launch of a step (what ran before is not ours).
+enum { TOUCH_NONE = -1, TOUCH_FULL = 1000, TOUCH_SPARSE = 2000, TOUCH_RING = 3000 };
 
 using namespace embla;
 
@@ -55,6 +61,12 @@ EmblaStatus embla_stack_create(EmblaAttn* ctx, const EmblaLayerDesc* layers, int
             EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_create: layer %d has kind %d", i, L.kind);
         }
     }
+    bool selects = false;
+    for (int i = 0; i < n_layers; i++)
+        selects |= layers[i].kind == EMBLA_LAYER_SPARSE || layers[i].kind == EMBLA_LAYER_SPARSE_SHARED || layers[i].emit_scores != 0;
+    if (selects && ctx->cfg.max_context > EMBLA_SELECT_MAX_KEYS)
+        EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_stack_create: max_context %d is over the %d keys embla_select_keys ranks",
+                   ctx->cfg.max_context, EMBLA_SELECT_MAX_KEYS);
     EmblaStack* st = new (std::nothrow) EmblaStack();
     if (!st) EMBLA_FAIL(EMBLA_OOM, "embla_stack_create: host allocation failed");
     st->ctx = ctx;
@@ -66,6 +78,10 @@ EmblaStatus embla_stack_create(EmblaAttn* ctx, const EmblaLayerDesc* layers, int
     st->idx = nullptr;
     st->probe = -1;
     st->ev_used = 0;
+    {
+        const char* e = getenv("EMBLA_NO_EARLY");
+        st->early_ok = !(e && e[0] == '1');
+    }
     st->scores_ld = (ctx->cfg.max_context + BLK - 1) / BLK * BLK;
     const size_t pairs = size_t(ctx->cfg.max_batch) * ctx->cfg.n_kv_heads;
     cudaError_t e = cudaSuccess;
@@ -128,11 +144,15 @@ static EmblaStatus probe_mark(EmblaStack* st, int entry, cudaStream_t s) {
     return EMBLA_OK;
 }
 
-#define EMBLA_STEP(entry, call)                                   \
-    do {                                                          \
-        if (EmblaStatus s_ = probe_mark(st, entry, s)) return s_; \
-        if (EmblaStatus s_ = (call)) return s_;                   \
-        if (EmblaStatus s_ = probe_mark(st, entry, s)) return s_; \
+// One launch of the step: `reads` is the cache it streams (TOUCH_*, for the early rule), `writes` the cache it appends to.
+#define EMBLA_STEP(entry, reads, writes, call)                                                        \
+    do {                                                                                              \
+        if (EmblaStatus s_ = probe_mark(st, entry, s)) return s_;                                     \
+        ctx->trace_tag = entry;                                                                       \
+        ctx->early = st->early_ok && last_write != -2 && (reads) != TOUCH_NONE && last_write != (reads); \
+        if (EmblaStatus s_ = (call)) return s_;                                                       \
+        last_write = (writes);                                                                        \
+        if (EmblaStatus s_ = probe_mark(st, entry, s)) return s_;                                     \
     } while (0)
 
 extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackStep* step, void* stream) {
@@ -151,8 +171,13 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
         EmblaAttn* c;
         int old;
         PdlScope(EmblaAttn* c_, int v) : c(c_), old(c_->pdl) { c->pdl = v; }
-        ~PdlScope() { c->pdl = old; }
+        ~PdlScope() {
+            c->pdl = old;
+            c->early = 0;
+            c->trace_tag = -1;
+        }
     } pdl_scope(ctx, use_pdl ? 1 : 0);
+    int last_write = -2;   // -2: nothing of this step launched yet
     for (size_t li = 0; li < st->layers.size(); li++) {
         const EmblaLayerDesc& L = st->layers[li];
         const uint8_t* row = static_cast<const uint8_t*>(step->qkv_dev) + li * step->qkv_layer_stride * esz;
@@ -170,7 +195,7 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
         if (L.kind == EMBLA_LAYER_SLIDING) {
             const EmblaRing* ring = &st->rings[L.slot];
             // ring write + attention in one launch, as the reference's attn_sliding
-            EMBLA_STEP(EMBLA_ENTRY_SLIDING_DECODE,
+            EMBLA_STEP(EMBLA_ENTRY_SLIDING_DECODE, TOUCH_RING + L.slot, TOUCH_RING + L.slot,
                        embla_attn_sliding_step(ctx, ring, step->seq_lens_dev, B, &q, kp, vp, step->qkv_stride, L.kgain_dev ? 0 : 1,
                                                L.kgain_dev, op, step->o_stride, stream));
             continue;
@@ -188,20 +213,20 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
             // every key, and the selection runs right after it (Engine.swift:796-797, 819-827); the quantised append
             // of the current token (Engine.swift:756-762) rides in the same launch
             const bool scoring = L.emit_scores != 0 && max_len > EMBLA_TOPK + EMBLA_RECENT;
-            EMBLA_STEP(EMBLA_ENTRY_FULL_DECODE,
+            EMBLA_STEP(EMBLA_ENTRY_FULL_DECODE, TOUCH_FULL + L.slot, TOUCH_FULL + L.slot,
                        embla_attn_full_step(ctx, st->full_pool, &view, &q, kp, vp, step->qkv_stride, L.norm_k, op, step->o_stride,
                                             scoring ? st->scores : nullptr, st->scores_ld, stream));
             if (scoring)
-                EMBLA_STEP(EMBLA_ENTRY_SELECT, embla_select_keys(ctx, st->scores, st->scores_ld, step->seq_lens_dev, B, max_len,
-                                                                 st->idx, stream));
+                EMBLA_STEP(EMBLA_ENTRY_SELECT, TOUCH_NONE, TOUCH_NONE,
+                           embla_select_keys(ctx, st->scores, st->scores_ld, step->seq_lens_dev, B, max_len, st->idx, stream));
         } else if (L.kind == EMBLA_LAYER_SPARSE_SHARED) {
             // a sparse layer over the preceding full layer's int8 cache (Engine.swift:461-462): no KV of its own
             view.block_table_dev = step->full_table_dev;
             view.table_stride = step->full_table_stride;
             const bool selecting = max_len > EMBLA_TOPK + EMBLA_RECENT;
-            EMBLA_STEP(EMBLA_ENTRY_SPARSE_DECODE, embla_attn_sparse_decode_int8(ctx, st->full_pool, &view, &q,
-                                                                                selecting ? st->idx : nullptr, op,
-                                                                                step->o_stride, stream));
+            EMBLA_STEP(EMBLA_ENTRY_SPARSE_DECODE, TOUCH_NONE, TOUCH_NONE,
+                       embla_attn_sparse_decode_int8(ctx, st->full_pool, &view, &q, selecting ? st->idx : nullptr, op,
+                                                     step->o_stride, stream));
         } else {
             view.block_table_dev = step->sparse_table_dev;
             view.table_stride = step->sparse_table_stride;
@@ -209,17 +234,19 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
             const bool selecting = max_len > EMBLA_TOPK + EMBLA_RECENT;   // Engine.swift:796
             if (selecting) {
                 // the append of the current token rides in the scoring launch
-                EMBLA_STEP(EMBLA_ENTRY_SCORE, embla_score_keys_step(ctx, st->sparse_pool, &view, qp, step->qkv_stride, kp, vp,
-                                                                    step->qkv_stride, L.norm_k, st->scores, st->scores_ld, stream));
-                EMBLA_STEP(EMBLA_ENTRY_SELECT, embla_select_keys(ctx, st->scores, st->scores_ld, step->seq_lens_dev, B, max_len,
-                                                                 st->idx, stream));
+                EMBLA_STEP(EMBLA_ENTRY_SCORE, TOUCH_SPARSE + L.slot, TOUCH_SPARSE + L.slot,
+                           embla_score_keys_step(ctx, st->sparse_pool, &view, qp, step->qkv_stride, kp, vp, step->qkv_stride,
+                                                 L.norm_k, st->scores, st->scores_ld, stream));
+                EMBLA_STEP(EMBLA_ENTRY_SELECT, TOUCH_NONE, TOUCH_NONE,
+                           embla_select_keys(ctx, st->scores, st->scores_ld, step->seq_lens_dev, B, max_len, st->idx, stream));
             } else {
-                EMBLA_STEP(EMBLA_ENTRY_APPEND, embla_kv_append(ctx, st->sparse_pool, &view, step->pos_dev, 1, kp, vp, step->qkv_stride,
-                                                               step->qkv_stride, L.norm_k, stream));
+                EMBLA_STEP(EMBLA_ENTRY_APPEND, TOUCH_NONE, TOUCH_SPARSE + L.slot,
+                           embla_kv_append(ctx, st->sparse_pool, &view, step->pos_dev, 1, kp, vp, step->qkv_stride,
+                                           step->qkv_stride, L.norm_k, stream));
             }
-            EMBLA_STEP(EMBLA_ENTRY_SPARSE_DECODE, embla_attn_sparse_decode(ctx, st->sparse_pool, &view, &q,
-                                                                           selecting ? st->idx : nullptr, op, step->o_stride,
-                                                                           stream));
+            EMBLA_STEP(EMBLA_ENTRY_SPARSE_DECODE, TOUCH_NONE, TOUCH_NONE,
+                       embla_attn_sparse_decode(ctx, st->sparse_pool, &view, &q, selecting ? st->idx : nullptr, op,
+                                                step->o_stride, stream));
         }
     }
     return EMBLA_OK;

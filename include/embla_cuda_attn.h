@@ -6,7 +6,7 @@
  * Engine.swift:743-832) and Prefill.encode / encodeFullNAX (Sources/EmblaMetal/Prefill.swift:265-407),
  * which bind buffers and dispatch Metal kernels. This header gives one entry point per kernel
  * dispatch of those methods, with the same operands, so that a Swift caller can replace each
- * `dispatchThreadgroups` with one C call (a module map + wrapper are shown in INTEGRATION.md).
+ * `dispatchThreadgroups` with one C call through a module map and a thin Swift wrapper.
  *
  * Conventions
  *  - Every function returns an EmblaStatus (0 = ok) and never aborts or throws; a message for the
@@ -55,6 +55,10 @@ enum { EMBLA_BF16 = 0, EMBLA_F16 = 1 };                       /* activation dtyp
 enum { EMBLA_KV_INT8 = 0, EMBLA_KV_16BIT = 1 };               /* cache element type (16BIT = activation dtype) */
 enum { EMBLA_SCALE_F32 = 0, EMBLA_SCALE_F16 = 1 };            /* int8 row scale dtype */
 enum { EMBLA_HEAD_DIM = 128, EMBLA_BLOCK = 128, EMBLA_TOPK = 1024, EMBLA_RECENT = 128 };
+/* Longest sequence embla_select_keys ranks: a (sequence, kv head) pair's keys are held in the registers of a
+ * cluster of at most 8 CTAs x 1024 threads x 32 keys, plus the 128 latest. (The reference's loop takes any
+ * length, attention.metal:701; its engine is built for 32768.) */
+enum { EMBLA_SELECT_MAX_KEYS = 8 * 1024 * 32 + 128 };
 
 typedef struct EmblaAttn EmblaAttn;       /* context: device, scratch (split-K partials, counters) */
 typedef struct EmblaKVPool EmblaKVPool;   /* paged KV pool */
@@ -103,6 +107,28 @@ void        embla_attn_destroy(EmblaAttn* ctx);
 /* Reads (and clears) the device-side error word: EMBLA_TIMEOUT if a bounded wait of an earlier
  * kernel ran out. Synchronises the stream. */
 EmblaStatus embla_attn_check(EmblaAttn* ctx, void* stream);
+/* Every device-side wait of this library's kernels (on a shared-memory barrier that a TMA copy or
+ * another warp completes) is bounded; a wait that runs out makes the kernel record an error code, wait
+ * (bounded again) for its own copies in flight and return, and embla_attn_check reports EMBLA_TIMEOUT.
+ * `cycles` is that bound in SM clocks for the launches this context makes from now on (default 2^30,
+ * about half a second). The counterpart of the reference's trap on a failed command buffer
+ * (Engine.swift:1070, 1170), without losing the context. */
+EmblaStatus embla_attn_set_wait_limit(EmblaAttn* ctx, int64_t cycles);
+/* Diagnostic, for testing the path above without any fault: the producer warps of the launches this
+ * context makes from now on stop requesting data at item `item` of their range (page of a key range,
+ * tile of a window), so that the consumers' wait for it runs out. -1 turns it off. */
+EmblaStatus embla_attn_inject_stall(EmblaAttn* ctx, int32_t item);
+
+/* Device-timestamp profiler, the counterpart of the reference's per-part Profiler (StepEncoder.swift:7-65)
+ * that does not serialise the launches it measures: between trace_begin and trace_end every launch
+ * of this context (at most max_launches of them) records four times of the GPU's global nanosecond
+ * timer - the first CTA entering, the first CTA past its wait for the preceding kernel, the last CTA
+ * leaving its main loop, the last CTA finishing. trace_begin allocates on first use or growth (it then
+ * synchronises the stream); trace_end synchronises the stream and writes stamps[launch][4] and the
+ * entry point of each launch (EMBLA_ENTRY_* inside embla_stack_decode_step, else -1). */
+EmblaStatus embla_attn_trace_begin(EmblaAttn* ctx, int32_t max_launches, void* stream);
+EmblaStatus embla_attn_trace_end(EmblaAttn* ctx, void* stream, uint64_t* stamps, int32_t* entries, int32_t cap,
+                                 int32_t* n_launches);
 
 /* Replaces the cache allocation of Engine.swift:269-284 for the full layers. */
 EmblaStatus embla_kv_pool_create(int32_t n_layers, int32_t n_kv_heads, int32_t kv_dtype, int32_t scale_dtype,
@@ -161,7 +187,8 @@ EmblaStatus embla_attn_full_step(EmblaAttn* ctx, EmblaKVPool* pool, const EmblaK
  *    view->max_seq_len must be given. The model shape comes from `n_q_heads` (kv heads from the pool)
  *    and `act_dtype`.
  *  - The first call on a device resolves the array's address and configures the kernels; make that
- *    call before any stream capture.
+ *    call before any stream capture, and from one thread: two threads making a device's first call at
+ *    the same moment race on that set-up.
  *  - All calls on a device share the array: two calls whose kernels may overlap on the GPU (different
  *    streams) race on it. Calls on one stream are safe; each call clears the counters first.
  *  - A bounded device-side wait that runs out is not reported by this variant (there is no context
@@ -190,7 +217,9 @@ EmblaStatus embla_score_keys_step(EmblaAttn* ctx, EmblaKVPool* pool, const Embla
  * with seq_len > 1152 and every kv head, idx[b][kv head][0..1151] = the 1024 highest-scoring keys among
  * j < seq_len - 128 (ties: lowest index; order: greater ascending, then equal ascending), then the 128
  * latest. Rows of shorter sequences are left untouched (the reference does not select yet,
- * Engine.swift:796). scores rows are scores_stride floats apart per (sequence, kv head). Exact. */
+ * Engine.swift:796). scores rows are scores_stride floats apart per (sequence, kv head). Exact.
+ * max_seq_len (or the context's max_context when 0) above EMBLA_SELECT_MAX_KEYS is refused with
+ * EMBLA_UNSUPPORTED; embla_stack_create refuses such a context for a stack with selecting layers. */
 EmblaStatus embla_select_keys(EmblaAttn* ctx, const float* scores_dev, int64_t scores_stride,
                               const int32_t* seq_lens_dev, int32_t batch, int32_t max_seq_len,
                               uint32_t* idx_dev, void* stream);
@@ -267,6 +296,12 @@ EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, con
                                     const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
                                     int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
                                     int64_t o_seq_stride, void* stream);
+/* Part of Engine.init's scratch set-up (`apart`, Engine.swift:242-258) that only prefill needs: about 39 MB of
+ * partial sums, with which embla_attn_full_prefill cuts the pages of a (256 tokens, head) unit over several CTAs
+ * when a chunk has fewer units than the GPU has SMs (short chunks, head-sharded prefill). Allocates once per
+ * context; without it embla_attn_full_prefill runs every unit as one CTA. Call it at set-up: the attention calls
+ * themselves never allocate or synchronise. */
+EmblaStatus embla_attn_reserve_prefill(EmblaAttn* ctx, void* stream);
 
 /* ---- one decode step through a stack of layers ------------------------------------------------------- */
 /* The attention half of Engine.encodeStep's per-layer loop (Engine.swift:933-991 calling
