@@ -1,13 +1,12 @@
 #!/usr/bin/env python
 """Benchmark of the attention hot path: batched decode at 32k context through a 24-layer stack.
 
-Workload (BASELINE.json config 4): 64 independent sequences at 32768 context, layers cycling
-sparse, sliding(1024), sliding(1024), full(int8 KV); 16 query / 4 kv heads, head_dim 128, fp16
-activations; KV state synthetic in the configs' distributions (seeded). A "step" decodes one token
-for every sequence through all 24 layers' attention (KV write + attention per layer). Sequences are
-sharded across GPUs with no collective on the data path. The headline line is weak-scaled: every GPU
-holds the configuration's 64 sequences (64 N in total); the same line carries, under "strong", the run
-with 64 sequences in total split over the N GPUs (64 / N each).
+Workload (the benchmark configuration "batched decode, 64 independent sequences at 32768 context"): layers
+cycling sparse, sliding(1024), sliding(1024), full(int8 KV); 16 query / 4 kv heads, head_dim 128, fp16
+activations; KV state synthetic in the configurations' distributions (seeded). A "step" decodes one token
+for every sequence through all 24 layers' attention (KV write + attention per layer). The 64 sequences are
+sharded across the GPUs (64 / N each) with no collective on the data path, so the headline is strong-scaled:
+the total work is fixed as N grows. The same line carries, under "weak", the run with 64 sequences on every GPU.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -26,16 +25,17 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-SEQS_PER_GPU, CONTEXT, N_LAYERS, HQ, HKV, WINDOW, RING = 64, 32768, 24, 16, 4, 1024, 4096
+SEQUENCES, CONTEXT, N_LAYERS, HQ, HKV, WINDOW, RING = 64, 32768, 24, 16, 4, 1024, 4096
 METRIC, UNIT = "decode attn tok/s @32k ctx", "tok/s"
 
 
 def workload_config(n_gpus):
-    return {"workload": "config 4: batched decode, 64 seqs per GPU x 32768 ctx x 24 layers [sparse, sliding1024, sliding1024, full int8]",
-            "sequences": SEQS_PER_GPU * n_gpus, "sequences_per_gpu": SEQS_PER_GPU, "context": CONTEXT, "layers": N_LAYERS, "q_heads": HQ, "kv_heads": HKV, "head_dim": 128,
+    per = SEQUENCES // n_gpus
+    return {"workload": "config 4: batched decode, 64 seqs x 32768 ctx x 24 layers [sparse, sliding1024, sliding1024, full int8]",
+            "sequences": SEQUENCES, "sequences_per_gpu": per, "context": CONTEXT, "layers": N_LAYERS, "q_heads": HQ, "kv_heads": HKV, "head_dim": 128,
             "sparse_mode": "own fp16 K/V: score all keys, radix-select 1024 + 128 latest, attend",
-            "sharding": f"by sequence, {SEQS_PER_GPU} per GPU, no collective",
-            "l2": "inputs larger than L2: each step streams the whole KV state (tens of GB) once"}
+            "sharding": f"by sequence, {per} per GPU, no collective",
+            "l2": "inputs larger than L2: each step streams the whole KV state (GBs per GPU) once"}
 
 
 def algorithmic_bytes(batch, entry):
@@ -154,6 +154,45 @@ def cpu_tok_s(n_threads, n_items):
     return n_items / (cycles_per_token * secs), secs
 
 
+def cpu_config0(n_threads, reps):
+    """The benchmark's CPU-path configuration (full-attention decode, 1 layer, batch 1, 16 query / 4 kv heads, context
+    1024, int8 K/V with fp16 scales, seed 0): seconds per decode step of the CPU oracle, `reps` steps, with `n_threads`
+    independent copies running side by side (1 = the scalar single-thread number)."""
+    import numpy as np
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import oracle as orc
+    rng = np.random.default_rng(0)
+    S = 1024
+    k8 = rng.integers(-127, 128, (HKV, S, 128), dtype=np.int8)
+    v8 = rng.integers(-127, 128, (HKV, S, 128), dtype=np.int8)
+    ks = rng.uniform(0.005, 0.02, (HKV, S)).astype(np.float16).astype(np.float32)
+    vs = rng.uniform(0.005, 0.02, (HKV, S)).astype(np.float16).astype(np.float32)
+    q = orc.to_bits(rng.standard_normal((HQ, 128)), orc.F16)
+
+    def item(_):
+        for _ in range(reps):
+            orc.full_decode(q, orc.F16, k8, ks, v8, vs, S)
+
+    item(0)
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(n_threads) as ex:
+        list(ex.map(item, range(n_threads)))
+    return (time.perf_counter() - t0) / reps
+
+
+def cpu_baseline():
+    cores = os.cpu_count() or 1
+    v, secs = cpu_tok_s(cores, 4 * cores)
+    one = cpu_config0(1, 200)
+    many = cpu_config0(cores, 200)
+    return {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{4 * cores} sequence-cycles of the 4-layer cycle at {CONTEXT} keys on {cores} threads, {secs:.2f} s",
+            "config0": {"workload": "config 0: full-attention decode, 1 layer, batch 1, context 1024, int8 K/V, fp16 scales",
+                        "one_thread": {"ms_per_step": 1e3 * one, "tok_s": 1.0 / one, "cores": 1},
+                        "all_cores": {"ms_per_step": 1e3 * many, "tok_s": cores / many, "cores": cores,
+                                      "note": "one independent sequence a thread"}}}
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -170,7 +209,7 @@ def run_reference(args, rank):
     sample = (f"{n_items} sequence-cycles (1 sequence x [sparse, sliding, sliding, full] at {CONTEXT} keys) on {cores} threads "
               f"in {secs:.2f} s; tok/s = items / (6 cycles x seconds)")
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals),
-            "warmup": args.warmup, "ms_per_step": 1000.0 * secs, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": 1000.0 * secs, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args.gpus),
             "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -267,31 +306,31 @@ def run_gpu(args, rank, world):
         torch.cuda.empty_cache()
         return out
 
-    r = decode(SEQS_PER_GPU, full=True)
+    if SEQUENCES % world:
+        raise SystemExit(f"{SEQUENCES} sequences do not divide over {world} GPUs")
+    per_gpu = SEQUENCES // world
+    r = decode(per_gpu, full=True)
     line = {
         "metric": METRIC, "value": r["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "config": workload_config(world), "clocks": r["clocks"], "e2e": r["e2e"],
         "gpu_launches": r["gpu_launches"], "roofline": r["roofline"], "step": r["step"],
     }
     # The reference's own arrangement of the same 24 layers (Engine.swift:461-462, 796-827): sparse layers hold no keys of
     # their own but read the preceding full layer's int8 cache, and that full layer emits the key scores as a by-product.
     shared = [(stk.FULL, stk.SPARSE_SHARED, stk.SLIDING, stk.SLIDING)[i % 4] for i in range(N_LAYERS)]
-    q = decode(SEQS_PER_GPU, full=False, kinds=shared)
+    q = decode(per_gpu, full=False, kinds=shared)
     line["shared_cache_mode"] = {"layers": "[full int8 + scores, sparse over that cache, sliding1024, sliding1024] x 6",
                                  "value": q["value"], "unit": UNIT, "ms_per_step": q["ms_per_step"], "e2e": q["e2e"]["value"],
                                  "per_entry_ms": {k: v["ms"] for k, v in q["step"]["per_entry"].items()}}
-    if world > 1 and SEQS_PER_GPU % world == 0:
-        # the same 64 sequences in total, split over the GPUs (per-GPU batch shrinks: launch and latency bound sooner)
-        q = decode(SEQS_PER_GPU // world, full=False)
-        line["strong"] = {"sequences": SEQS_PER_GPU, "sequences_per_gpu": SEQS_PER_GPU // world, "value": q["value"], "unit": UNIT,
-                          "ms_per_step": q["ms_per_step"], "e2e": q["e2e"]["value"], "step_gbs_per_gpu": q["step"]["gbs"],
-                          "per_entry_ms": {k: v["ms"] for k, v in q["step"]["per_entry"].items()}}
+    if world > 1:
+        # the deployment that grows with the box: 64 sequences on every GPU (64 N in total), the per-GPU work fixed
+        q = decode(SEQUENCES, full=False)
+        line["weak"] = {"sequences": SEQUENCES * world, "sequences_per_gpu": SEQUENCES, "value": q["value"], "unit": UNIT,
+                        "ms_per_step": q["ms_per_step"], "e2e": q["e2e"]["value"], "step_gbs_per_gpu": q["step"]["gbs"],
+                        "per_entry_ms": {k: v["ms"] for k, v in q["step"]["per_entry"].items()}}
     if rank == 0 and world == 1:
-        cores = os.cpu_count() or 1
-        v, secs = cpu_tok_s(cores, 4 * cores)
-        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                                "sample": f"{4 * cores} sequence-cycles of the 4-layer cycle at {CONTEXT} keys on {cores} threads, {secs:.2f} s"}
+        line["cpu_baseline"] = cpu_baseline()
     line["prefill"] = prefill_leg(rank, world, barrier)
     if rank == 0:
         sys.stdout.flush()
@@ -306,63 +345,58 @@ PREFILL_FLOP = 4 * HQ * 128 * sum(PREFILL_CACHED + i + 1 for i in range(PREFILL_
 
 
 def prefill_leg(rank, world, barrier, reps=10):
-    """BASELINE.json config 3 on the same GPUs: a 2048-token causal chunk appended to 30720 cached positions of the
-    int8 cache, bf16 q. One GPU computes all heads; 2 or 4 GPUs shard by kv head, 8 GPUs by (kv head, half of the
-    chunk); the per-rank outputs are combined with an NCCL all-gather inside the timed region."""
+    """The 2048-token causal chunk appended to 30720 cached positions of the int8 cache, bf16 q, on the same GPUs, through
+    embla_metal_b200.shard.HeadShardedPrefill: one GPU computes all heads; 2 or 4 GPUs shard by kv head, 8 GPUs by
+    (kv head, half of the chunk); the per-head outputs are combined with an NCCL all-gather and placed token-major
+    inside the timed region. The attention kernel and the combine are also timed on their own."""
     import torch
     import torch.distributed as dist
-    from embla_metal_b200 import attn
+    from embla_metal_b200 import attn, shard
     if world not in (1, 2, 4, 8):
         return None
-    kv_shards = min(world, HKV)
-    tok_shards = world // kv_shards
-    hkv_l, hq_l, T_l = HKV // kv_shards, HQ // kv_shards, PREFILL_T // tok_shards
-    tok_part = rank % tok_shards
-    pos0 = PREFILL_CACHED + tok_part * T_l
-    S = pos0 + T_l
-    npg = (S + 127) // 128
-    ctx = attn.Attention(hq_l, hkv_l, attn.BF16, 1, npg * 128)
-    pool = attn.KVPool(1, hkv_l, npg, attn.KV_INT8, attn.SCALE_F16)
+    hsp = shard.HeadShardedPrefill(HQ, HKV, attn.BF16, PREFILL_T, PREFILL_CACHED + PREFILL_T, world, rank)
+    sh = hsp.shard
+    pos0 = PREFILL_CACHED + sh.token0
+    npg = (pos0 + sh.n_tokens + 127) // 128
+    pool = attn.KVPool(1, sh.n_kv_heads, npg, attn.KV_INT8, attn.SCALE_F16)
     g = torch.Generator(device="cuda").manual_seed(3 + rank)
     raw = pool.raw()
     flat = raw.view(-1, raw.shape[-1])
     flat[:, :32768] = torch.randint(-127, 128, (flat.shape[0], 32768), dtype=torch.int8, device="cuda", generator=g).view(torch.uint8)
     flat[:, 32768:] = torch.empty(flat.shape[0], 256, device="cuda").uniform_(0.005, 0.02, generator=g).to(torch.float16).view(torch.uint8)
     tbl = torch.arange(npg, dtype=torch.int32, device="cuda")[None].contiguous()
-    q = torch.randn(1, T_l, hq_l * 128, device="cuda", generator=g).to(torch.bfloat16)
-    o = torch.zeros_like(q)
-    gathered = torch.zeros(world, T_l, hq_l * 128, dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    q = torch.randn(1, sh.n_tokens, sh.n_q_heads * 128, device="cuda", generator=g).to(torch.bfloat16)
     p0 = torch.tensor([pos0], dtype=torch.int32, device="cuda")
 
-    def step():
-        attn.full_prefill(ctx, pool, tbl, 0, p0, q, o)
+    def timed_ms(fn):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
         if world > 1:
-            dist.all_gather_into_tensor(gathered, o[0])
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
 
-    for _ in range(3):
-        step()
-    ctx.check()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(reps):
-        step()
-    e1.record()
-    barrier()
-    ms = torch.tensor([e0.elapsed_time(e1) / reps], device="cuda")
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms = float(ms.item())
-    ctx.check()
+    ms = timed_ms(lambda: hsp.run(pool, tbl, 0, p0, q))
+    hsp.ctx.check()
+    kernel_ms = timed_ms(lambda: hsp.attend(pool, tbl, 0, p0, q))
+    combine_ms = timed_ms(hsp.combine) if world > 1 else 0.0
     pool.close()
-    ctx.close()
+    hsp.close()
     peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
     burst, sustained = float(peaks.get("bf16_tflops", 1590.0)), float(peaks.get("bf16_tflops_sustained", 1400.0))
     tflops = PREFILL_FLOP / (ms * 1e-3) / 1e12
     sliding = sliding_prefill_case(rank, reps) if world == 1 else None
     return {"sliding_config_1b": sliding, "metric": "prefill attn tok/s", "workload": "config 3: 2048-token causal chunk after 30720 cached positions, int8 KV, bf16 q",
             "value": PREFILL_T / (ms * 1e-3), "unit": "tok/s", "ms": ms, "tflops": tflops, "n_gpus": world,
-            "sharding": ("none" if world == 1 else f"{kv_shards} kv-head shards x {tok_shards} chunk halves, NCCL all-gather of per-head outputs"),
+            "kernel_ms": kernel_ms, "allgather_and_placement_ms": combine_ms,
+            "sharding": ("none" if world == 1 else f"{sh.kv_shards} kv-head shards x {sh.tok_shards} chunk halves, NCCL all-gather of per-head outputs, token-major placement"),
             "allgather_bytes": 0 if world == 1 else PREFILL_T * HQ * 128 * 2,
             "roofline": {"bound": "tensor", "achieved": tflops, "peak": burst * world, "unit": "TFLOP/s", "frac": tflops / (burst * world),
                          "frac_of_sustained": tflops / (sustained * world)}}

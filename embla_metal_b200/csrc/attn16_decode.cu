@@ -9,6 +9,8 @@
 // The kernel (attn16_kernel.cuh) streams 64-row tiles of one (sequence, kv head) through a cp.async ring
 // with an online softmax; a pair's rows are cut into as many ranges as fill the device, merged through
 // (max, sum, acc) partials by the last CTA to arrive, in range order (attention.metal:428-440).
+#include <cstdlib>
+
 #include "attn16_kernel.cuh"
 
 namespace embla {
@@ -102,18 +104,26 @@ static EmblaStatus ring_maps(EmblaAttn* ctx, const Attn16Params& p, int batch, c
     return EMBLA_OK;
 }
 
-template <int DT, int MODE, bool TMA>
+template <int DT, int MODE, bool TMA, bool CL>
 static EmblaStatus launch_attn16_kernel(EmblaAttn* ctx, const Attn16Params& p, const CUtensorMap& mk, const CUtensorMap& mv,
                                         dim3 grid, cudaStream_t s) {
     constexpr size_t smem = 1024 + A16_STAGES * A16_STAGE + 8 * HD * 2;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        EMBLA_CUDA_TRY(cudaFuncSetAttribute(attn16_decode_kernel<DT, MODE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        EMBLA_CUDA_TRY(cudaFuncSetAttribute(attn16_decode_kernel<DT, MODE, TMA, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         configured[ctx->device & 63] = true;
     }
-    EMBLA_CUDA_TRY(launch_kernel(ctx->pdl, attn16_decode_kernel<DT, MODE, TMA>, grid, dim3(A16_THREADS + (TMA ? 32 : 0)), smem, s, p, mk, mv));
+    EMBLA_CUDA_TRY(launch_kernel_cluster(ctx->pdl, CL ? int(grid.x) : 1, attn16_decode_kernel<DT, MODE, TMA, CL>, grid,
+                                         dim3(A16_THREADS + (TMA ? 32 : 0)), smem, s, p, mk, mv));
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;
+}
+
+template <int DT, int MODE, bool TMA>
+static EmblaStatus launch_attn16_cl(EmblaAttn* ctx, const Attn16Params& p, const CUtensorMap& mk, const CUtensorMap& mv, dim3 grid,
+                                    bool cluster, cudaStream_t s) {
+    return cluster ? launch_attn16_kernel<DT, MODE, TMA, true>(ctx, p, mk, mv, grid, s)
+                   : launch_attn16_kernel<DT, MODE, TMA, false>(ctx, p, mk, mv, grid, s);
 }
 
 template <int MODE>
@@ -127,15 +137,19 @@ static EmblaStatus launch_attn16(EmblaAttn* ctx, Attn16Params& p, int batch, int
     // more unless it starts on a tile boundary.
     const bool tma = MODE == A16_SLIDING && p.ring % A16_ROWS == 0;
     // Ranges per pair: the count that minimises (waves of CTAs over 2 CTAs per SM) x (tiles of a range + the fixed cost
-    // of a CTA in tiles: query set-up, pipeline fill, merge), at most 16 ranges.
+    // of a CTA in tiles: query set-up, pipeline fill, merge). Up to 8 ranges run as one thread-block cluster a pair and
+    // merge through its shared memory (EMBLA_NO_CLUSTER=1: up to 16 ranges merged through global scratch by the last
+    // CTA to arrive, the path that also serves when a cluster cannot be had).
+    static const bool use_clusters = []() { const char* e = getenv("EMBLA_NO_CLUSTER"); return !(e && e[0] == '1'); }();
+    const int ns_max = use_clusters ? 8 : 16;
     const int max_tiles = (max_rows > 0 ? (max_rows + A16_ROWS - 1) / A16_ROWS : 1) + (tma ? 1 : 0);
     const long pairs = long(batch) * p.n_kv_heads, slots = 2L * ctx->sm_count;
     long best_cost = -1;
     p.tiles_per_cta = max_tiles;
     p.max_chunks = 1;
-    for (int ns = 1; ns <= 16 && ns <= max_tiles; ns++) {
+    for (int ns = 1; ns <= ns_max && ns <= max_tiles; ns++) {
         const int tp = (max_tiles + ns - 1) / ns, nsr = (max_tiles + tp - 1) / tp;
-        if (nsr > 16 || pairs * nsr > ctx->partial_slots) continue;
+        if (nsr > ns_max || (!use_clusters && pairs * nsr > ctx->partial_slots)) continue;
         const long waves = (pairs * nsr + slots - 1) / slots;
         const long cost = waves * (tp + 3 + (nsr > 1 ? 1 : 0));
         if (best_cost < 0 || cost < best_cost) {
@@ -144,18 +158,19 @@ static EmblaStatus launch_attn16(EmblaAttn* ctx, Attn16Params& p, int batch, int
             p.max_chunks = nsr;
         }
     }
+    const bool cluster = use_clusters && p.max_chunks > 1;
     fill_rope_freq(p.rope_freq);
     dim3 grid(p.max_chunks, p.n_kv_heads, batch);
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
     if (tma) {
         const CUtensorMap *mk = nullptr, *mv = nullptr;
         if (EmblaStatus st = ring_maps(ctx, p, batch, &mk, &mv)) return st;
-        return bf ? launch_attn16_kernel<EMBLA_BF16, MODE, MODE == A16_SLIDING>(ctx, p, *mk, *mv, grid, s)
-                  : launch_attn16_kernel<EMBLA_F16, MODE, MODE == A16_SLIDING>(ctx, p, *mk, *mv, grid, s);
+        return bf ? launch_attn16_cl<EMBLA_BF16, MODE, MODE == A16_SLIDING>(ctx, p, *mk, *mv, grid, cluster, s)
+                  : launch_attn16_cl<EMBLA_F16, MODE, MODE == A16_SLIDING>(ctx, p, *mk, *mv, grid, cluster, s);
     }
     static const CUtensorMap none = {};
-    return bf ? launch_attn16_kernel<EMBLA_BF16, MODE, false>(ctx, p, none, none, grid, s)
-              : launch_attn16_kernel<EMBLA_F16, MODE, false>(ctx, p, none, none, grid, s);
+    return bf ? launch_attn16_cl<EMBLA_BF16, MODE, false>(ctx, p, none, none, grid, cluster, s)
+              : launch_attn16_cl<EMBLA_F16, MODE, false>(ctx, p, none, none, grid, cluster, s);
 }
 
 extern "C" EmblaStatus embla_attn_sparse_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,

@@ -54,7 +54,10 @@ struct Attn16Params {
     float rope_freq[32];
 };
 
-template <int DT, int MODE, bool TMA>
+// CL: the ranges of a pair are the CTAs of one thread-block cluster (at most 8), launched as such; they merge their
+// partials through the cluster's shared memory, each CTA finishing a share of the heads, instead of through global
+// scratch and a last arriver.
+template <int DT, int MODE, bool TMA, bool CL>
 __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
     attn16_decode_kernel(const Attn16Params p, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ uint8_t smem_raw[];
@@ -405,7 +408,9 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
     }
     cons_sync();
     const int pair = b * p.n_kv_heads + kvh;
-    float* part = p.partials + (size_t(pair) * p.max_chunks + chunk) * p.G * A16_PART;
+    // this CTA's merged partial: to the global scratch, or (clusters) kept in shared memory behind the warps' partials
+    float* part = CL ? reinterpret_cast<float*>(smem + 4 * 8 * HD * 4 + 1024)
+                     : p.partials + (size_t(pair) * p.max_chunks + chunk) * p.G * A16_PART;
     for (int idx = tid; idx < p.G * HD; idx += A16_THREADS) {
         const int hh = idx >> 7, d = idx & 127;
         float M = NEG_BIG;
@@ -428,6 +433,40 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             }
         }
     }
+    if (CL && nch > 1) {
+        // Every range's partial is in its CTA's shared memory: one cluster barrier, then CTA `chunk` merges heads
+        // chunk, chunk + nch, ... in range order, reading the other CTAs' rows through the cluster's window (all loads in
+        // flight together); a second barrier keeps every CTA's shared memory alive until the others have read it.
+        cluster_arrive();
+        cluster_wait();
+        const uint32_t mine = smem_u32(part);
+        for (int hh = chunk; hh < p.G; hh += nch) {
+            const int d = tid;
+            float mc[8], lc[8], ac[8];
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                const uint32_t row = cluster_map(mine, uint32_t(r < nch ? r : 0)) + uint32_t(hh * A16_PART) * 4u;
+                mc[r] = r < nch ? cluster_ld_f32(row + HD * 4) : NEG_BIG;
+                lc[r] = r < nch ? cluster_ld_f32(row + (HD + 1) * 4) : 0.0f;
+                ac[r] = r < nch ? cluster_ld_f32(row + uint32_t(d) * 4u) : 0.0f;
+            }
+            float M = NEG_BIG;
+#pragma unroll
+            for (int r = 0; r < 8; r++) M = fmaxf(M, mc[r]);
+            float L = 0.0f, num = 0.0f;
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                const float f = __expf(mc[r] - M);
+                L += lc[r] * f;
+                num += ac[r] * f;
+            }
+            Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
+        }
+        cluster_arrive();
+        cluster_wait();
+        trace_last(p.ctl.trace, 3);
+        return;
+    }
     if (nch == 1) {
         trace_last(p.ctl.trace, 3);
         return;
@@ -445,27 +484,22 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
         return;
     }
     __threadfence();
-    const float* base = p.partials + size_t(pair) * p.max_chunks * p.G * A16_PART;
+    // the pair's partials (contiguous: [range][head][128 sums, max, sum]) into the free stages in one batch of loads,
+    // then the merge in range order from shared memory
+    const float* gbase = p.partials + size_t(pair) * p.max_chunks * p.G * A16_PART;
+    float* sbase = reinterpret_cast<float*>(smem);
+    stage_from_global<A16_THREADS>(reinterpret_cast<float4*>(sbase), reinterpret_cast<const float4*>(gbase), nch * p.G * (A16_PART / 4), tid);
+    cons_sync();
     for (int idx = tid; idx < p.G * HD; idx += A16_THREADS) {
         const int hh = idx >> 7, d = idx & 127;
-        // all ranges' values first (independent loads, at most 16 ranges), then the merge in range order
-        float mc[16], lc[16], ac[16];
-#pragma unroll
-        for (int cc = 0; cc < 16; cc++) {
-            const float* q2 = base + (size_t(cc < nch ? cc : 0) * p.G + hh) * A16_PART;
-            mc[cc] = cc < nch ? __ldcg(q2 + HD) : NEG_BIG;
-            lc[cc] = cc < nch ? __ldcg(q2 + HD + 1) : 0.0f;
-            ac[cc] = cc < nch ? __ldcg(q2 + d) : 0.0f;
-        }
         float M = NEG_BIG;
-#pragma unroll
-        for (int cc = 0; cc < 16; cc++) M = fmaxf(M, mc[cc]);
+        for (int cc = 0; cc < nch; cc++) M = fmaxf(M, sbase[(cc * p.G + hh) * A16_PART + HD]);
         float L = 0.0f, num = 0.0f;
-#pragma unroll
-        for (int cc = 0; cc < 16; cc++) {
-            const float f = __expf(mc[cc] - M);
-            L += lc[cc] * f;
-            num += ac[cc] * f;
+        for (int cc = 0; cc < nch; cc++) {
+            const float* q2 = sbase + (cc * p.G + hh) * A16_PART;
+            const float f = __expf(q2[HD] - M);
+            L += q2[HD + 1] * f;
+            num += q2[d] * f;
         }
         Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
     }

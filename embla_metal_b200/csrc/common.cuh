@@ -194,6 +194,42 @@ __device__ __forceinline__ bool mbar_wait_bounded(long long limit, uint64_t* bar
     return false;
 }
 
+// ---- thread-block clusters: the hardware barrier over all CTAs of a cluster (threads that have exited do not count) and
+// loads from another CTA's shared memory. No spinning: the barrier is a hardware wait like bar.sync.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// the address, in the cluster's shared-memory window, of this CTA's shared address `saddr` in CTA `rank`
+__device__ __forceinline__ uint32_t cluster_map(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float cluster_ld_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// Partial sums that other CTAs left in global memory -> shared memory, every load of a batch in flight together (the
+// last CTA of a split reads a few tens of KB once; read one dependent load at a time, that costs several microseconds).
+template <int THREADS>
+__device__ __forceinline__ void stage_from_global(float4* dst, const float4* src, int n4, int tid) {
+    constexpr int BATCH = 12;
+    for (int base = 0; base < n4; base += THREADS * BATCH) {
+        float4 v[BATCH];
+#pragma unroll
+        for (int k = 0; k < BATCH; k++) {
+            const int i = base + tid + THREADS * k;
+            if (i < n4) v[k] = __ldcg(src + i);
+        }
+#pragma unroll
+        for (int k = 0; k < BATCH; k++) {
+            const int i = base + tid + THREADS * k;
+            if (i < n4) dst[i] = v[k];
+        }
+    }
+}
+
 // ---- device-timestamp profiler: per launch, when the first CTA entered (0), when the first CTA was past its
 // dependency wait (1), when the last CTA left its main loop (2) and when the last CTA finished (3), in nanoseconds of
 // the GPU's global timer. Slots 2 and 3 hold the complement, so that one atomicMin serves all four; the host
@@ -243,20 +279,37 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
 }
 #endif  // __CUDACC__
 
-// Host: a kernel launch, with the programmatic-dependent-launch attribute when `pdl`.
+// Host: a kernel launch, with the programmatic-dependent-launch attribute when `pdl`, as thread-block clusters of
+// `cluster_x` CTAs along x when that is above 1.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_kernel(bool pdl, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+inline cudaError_t launch_kernel_cluster(bool pdl, int cluster_x, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t s, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute at[2];
+    int n = 0;
+    if (pdl) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    if (cluster_x > 1) {
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = unsigned(cluster_x);
+        at[n].val.clusterDim.y = 1;
+        at[n].val.clusterDim.z = 1;
+        n++;
+    }
     cfg.attrs = at;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(bool pdl, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    return launch_kernel_cluster(pdl, 1, kern, grid, block, smem, s, static_cast<Args&&>(args)...);
 }
 
 // Host: the driver's cuTensorMapEncodeTiled, fetched through the runtime (no link against libcuda).

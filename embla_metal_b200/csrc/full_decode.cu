@@ -500,15 +500,34 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
     }
     __threadfence();
     const float* base = p.partials + size_t(pair) * p.nsplit * p.G * FD_PART;
-    for (int idx = tid; idx < p.G * HD; idx += THREADS) {
-        const int hh = idx >> 7, d = idx & 127;
-        float num = 0.0f, den = sink;
-        for (int s = 0; s < p.nsplit; s++) {
-            const float* q2 = base + (size_t(s) * p.G + hh) * FD_PART;
-            den += __ldcg(q2 + HD);
-            num += __ldcg(q2 + d);
+    const int n4 = p.nsplit * p.G * (FD_PART / 4);
+    if (n4 * 16 <= STAGES * FD_STAGE_BYTES) {
+        // the pair's partials (contiguous: [split][head][128 sums, sum of weights]) into the free stages in one batch of
+        // loads, then added in split order from shared memory
+        float* sbase = reinterpret_cast<float*>(stages);
+        stage_from_global<THREADS>(reinterpret_cast<float4*>(sbase), reinterpret_cast<const float4*>(base), n4, tid);
+        __syncthreads();
+        for (int idx = tid; idx < p.G * HD; idx += THREADS) {
+            const int hh = idx >> 7, d = idx & 127;
+            float num = 0.0f, den = sink;
+            for (int s = 0; s < p.nsplit; s++) {
+                const float* q2 = sbase + (s * p.G + hh) * FD_PART;
+                den += q2[HD];
+                num += q2[d];
+            }
+            Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / den);
         }
-        Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / den);
+    } else {
+        for (int idx = tid; idx < p.G * HD; idx += THREADS) {
+            const int hh = idx >> 7, d = idx & 127;
+            float num = 0.0f, den = sink;
+            for (int s = 0; s < p.nsplit; s++) {
+                const float* q2 = base + (size_t(s) * p.G + hh) * FD_PART;
+                den += __ldcg(q2 + HD);
+                num += __ldcg(q2 + d);
+            }
+            Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / den);
+        }
     }
     trace_last(p.ctl.trace, 3);
 }

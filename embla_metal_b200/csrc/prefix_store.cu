@@ -99,7 +99,8 @@ static uint64_t prefix_hash(uint64_t parent, const int32_t* tokens, int n) {   /
     return h;
 }
 
-// The stored blocks `tokens` starts with, in order, covering at most `limit` positions (PrefixCache.swift:82-96).
+// Walks the tree from the root along `tokens`, 128 at a time, while each next block is stored and ends inside the first
+// `limit` positions; returns the blocks it passed (the lookup of PrefixCache.swift:82-96).
 static std::vector<PrefixBlock*> chain_of(const EmblaPrefixStore* st, const int32_t* tokens, int limit) {
     std::vector<PrefixBlock*> out;
     PrefixBlock* parent = nullptr;
@@ -110,7 +111,8 @@ static std::vector<PrefixBlock*> chain_of(const EmblaPrefixStore* st, const int3
         auto it = st->blocks.find(h);
         if (it == st->blocks.end()) break;
         PrefixBlock* b = it->second.get();
-        // equal hashes are checked: the same parent and the same tokens
+        // a 64-bit hash can collide: the entry only counts if it hangs off the block we came from, at this depth, with
+        // exactly these 128 tokens
         if (b->parent != parent || b->index != j || std::memcmp(b->tokens.data(), slice, BLK * sizeof(int32_t)) != 0) break;
         out.push_back(b);
         parent = b;
@@ -136,9 +138,10 @@ static void remove_block(EmblaPrefixStore* st, PrefixBlock* b) {   // PrefixCach
     if (parent->children == 0 && parent->window == nullptr) remove_block(st, parent);
 }
 
-// Drops the least recently used blocks with nothing after them until within the limit, never one of `keep`
-// (PrefixCache.swift:121-131). Equal ages: the lower hash goes first (the reference iterates a dictionary, whose
-// order among equal ages is unspecified).
+// Over budget: leaves (blocks no stored block continues) are dropped oldest first until the bytes fit, sparing the
+// hashes in `keep`; dropping a leaf can expose its parent as the next candidate (the policy of PrefixCache.swift:121-131).
+// Among leaves of equal age the lower hash goes first, which makes the order reproducible (the reference walks a
+// dictionary there, in no stated order).
 static void evict(EmblaPrefixStore* st, const std::set<uint64_t>& keep) {
     while (st->bytes > st->cfg.limit_bytes) {
         PrefixBlock* lru = nullptr;

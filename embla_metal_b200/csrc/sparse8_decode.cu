@@ -254,27 +254,22 @@ __global__ void __launch_bounds__(S8_THREADS) sparse8_decode_kernel(const Sparse
         return;
     }
     __threadfence();
-    const float* base = p.partials + size_t(pair) * p.max_chunks * p.G * S8_PART;
+    // the pair's partials (contiguous: [chunk][head][128 sums, max, sum]; at most 9 chunks x 8 heads: 38 KB) into the
+    // tile area in one batch of loads, then the merge in chunk order from shared memory
+    const float* gbase = p.partials + size_t(pair) * p.max_chunks * p.G * S8_PART;
+    float* sbase = reinterpret_cast<float*>(smem);
+    stage_from_global<S8_THREADS>(reinterpret_cast<float4*>(sbase), reinterpret_cast<const float4*>(gbase), nch * p.G * (S8_PART / 4), tid);
+    __syncthreads();
     for (int idx = tid; idx < p.G * HD; idx += S8_THREADS) {
         const int hh = idx >> 7, d = idx & 127;
-        // all chunks' values first (independent loads, at most 16 chunks), then the merge in chunk order
-        float mc[16], lc[16], ac[16];
-#pragma unroll
-        for (int cc = 0; cc < 16; cc++) {
-            const float* q2 = base + (size_t(cc < nch ? cc : 0) * p.G + hh) * S8_PART;
-            mc[cc] = cc < nch ? __ldcg(q2 + HD) : NEG_BIG;
-            lc[cc] = cc < nch ? __ldcg(q2 + HD + 1) : 0.0f;
-            ac[cc] = cc < nch ? __ldcg(q2 + d) : 0.0f;
-        }
         float M = NEG_BIG;
-#pragma unroll
-        for (int cc = 0; cc < 16; cc++) M = fmaxf(M, mc[cc]);
+        for (int cc = 0; cc < nch; cc++) M = fmaxf(M, sbase[(cc * p.G + hh) * S8_PART + HD]);
         float L = 0.0f, num = 0.0f;
-#pragma unroll
-        for (int cc = 0; cc < 16; cc++) {
-            const float f = __expf(mc[cc] - M);
-            L += lc[cc] * f;
-            num += ac[cc] * f;
+        for (int cc = 0; cc < nch; cc++) {
+            const float* q2 = sbase + (cc * p.G + hh) * S8_PART;
+            const float f = __expf(q2[HD] - M);
+            L += q2[HD + 1] * f;
+            num += q2[d] * f;
         }
         Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
     }
@@ -283,7 +278,9 @@ __global__ void __launch_bounds__(S8_THREADS) sparse8_decode_kernel(const Sparse
 
 template <int DT, int SB>
 static EmblaStatus launch_sparse8(EmblaAttn* ctx, const Sparse8Params& p, int batch, cudaStream_t s) {
-    constexpr size_t smem = 1024 + 2 * CODE_BYTES + 2 * BLK * 4 + 8 * HD * 2;
+    // tiles, scales and queries; the last CTA of a pair stages up to 9 chunks x 8 heads x 528 bytes of partials over them
+    constexpr size_t smem = 1024 + 2 * CODE_BYTES + 2 * BLK * 4 + 8 * HD * 2 + 4096;
+    static_assert(9 * 8 * S8_PART * 4 <= 2 * CODE_BYTES + 2 * BLK * 4 + 8 * HD * 2 + 4096, "partials do not fit the tile area");
     dim3 grid(p.max_chunks, p.n_kv_heads, batch);
     EMBLA_CUDA_TRY(launch_kernel(ctx->pdl, sparse8_decode_kernel<DT, SB>, grid, dim3(S8_THREADS), smem, s, p));
     EMBLA_CUDA_TRY(cudaGetLastError());

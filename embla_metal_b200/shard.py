@@ -1,10 +1,23 @@
-"""Partition of a batch of independent sequences over ranks, and the max-over-ranks time reduction.
+"""How the attention path spreads over the GPUs of one box.
 
-Batched decode shards by sequence with no data-path collective; the only communication is the
-timing plumbing (a barrier and a MAX all-reduce), which works on any torch.distributed backend
-(nccl on GPUs, gloo in the CPU tests).
+* Batched decode shards by sequence: sequences are independent, every GPU holds the KV state of its own,
+  and nothing crosses GPUs on the data path (`shard_sequences`).
+* A long prefill chunk of a full layer shards by kv head: a GPU holds the cache pages of its kv heads
+  only and computes their query heads (`prefill_partition`); with more GPUs than kv heads the chunk's
+  tokens are cut as well. The per-head outputs are combined with one all-gather over NVLink (NCCL;
+  gloo in the CPU tests) and placed token-major, `o[T][n_q_heads * 128]`, which is what the
+  o-projection after attention reads (the reference's single GPU writes that layout directly,
+  Sources/EmblaMetal/Prefill.swift:343-344, 378-407). `HeadShardedPrefill` is that path as one object.
+
+The only other communication is the timing plumbing (`max_over_ranks`). Peers' data reaches a GPU
+through the collective into its own memory; no kernel of this library reads another GPU's memory.
 """
+from collections import namedtuple
+
 import torch
+
+PrefillShard = namedtuple("PrefillShard", "kv_shards tok_shards kv_part tok_part kv_head0 n_kv_heads q_head0 n_q_heads "
+                                          "token0 n_tokens")
 
 
 def shard_sequences(total, world, rank):
@@ -15,6 +28,86 @@ def shard_sequences(total, world, rank):
     count = base + (1 if rank < extra else 0)
     first = rank * base + min(rank, extra)
     return first, count
+
+
+def prefill_partition(n_q_heads, n_kv_heads, n_tokens, world, rank):
+    """Which kv heads, query heads and tokens of a prefill chunk `rank` of `world` computes.
+
+    Ranks split the kv heads first (rank // tok_shards picks the group of kv heads); once there are more
+    ranks than kv heads, the ranks of one kv head split the chunk's tokens into contiguous runs
+    (rank % tok_shards). With 4 kv heads: 2 GPUs take 2 kv heads each, 4 take one each, 8 take one kv
+    head and one half of the chunk each (the kv head's pages are then held by both)."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} of {world}")
+    kv_shards = min(world, n_kv_heads)
+    if n_kv_heads % kv_shards or world % kv_shards:
+        raise ValueError(f"{world} ranks do not divide {n_kv_heads} kv heads evenly")
+    tok_shards = world // kv_shards
+    if n_tokens % tok_shards:
+        raise ValueError(f"{n_tokens} tokens do not divide over {tok_shards} ranks a kv head")
+    g = n_q_heads // n_kv_heads
+    kv_part, tok_part = rank // tok_shards, rank % tok_shards
+    hkv = n_kv_heads // kv_shards
+    t = n_tokens // tok_shards
+    return PrefillShard(kv_shards, tok_shards, kv_part, tok_part, kv_part * hkv, hkv, kv_part * hkv * g, hkv * g,
+                        tok_part * t, t)
+
+
+def place_heads(gathered, o_full, kv_shards, tok_shards):
+    """gathered [world][T_l][hq_l * 128] as an all-gather leaves it (rank-major) -> o_full [T][Hq * 128], token-major:
+    rank kv_part * tok_shards + tok_part holds tokens tok_part * T_l .. and heads kv_part * hq_l .. One strided copy."""
+    world, t_l, w_l = gathered.shape
+    if world != kv_shards * tok_shards or tuple(o_full.shape) != (tok_shards * t_l, kv_shards * w_l):
+        raise ValueError(f"gathered {tuple(gathered.shape)} does not tile o {tuple(o_full.shape)}")
+    o_full.view(tok_shards, t_l, kv_shards, w_l).copy_(gathered.view(kv_shards, tok_shards, t_l, w_l).permute(1, 2, 0, 3))
+    return o_full
+
+
+def all_gather_rows(out, local, group=None):
+    """out [world, ...] <- every rank's `local`; one collective (NCCL: ncclAllGather; gloo for the CPU tests)."""
+    import torch.distributed as dist
+    if dist.get_backend(group) == "gloo":   # gloo has no flat all-gather into one tensor
+        dist.all_gather(list(out.unbind(0)), local, group=group)
+    else:
+        dist.all_gather_into_tensor(out, local, group=group)
+
+
+class HeadShardedPrefill:
+    """The full layers' prefill chunk on `world` GPUs: this rank's kv heads and tokens through
+    embla_attn_full_prefill, an all-gather of the per-head outputs on the same stream, the placement into
+    token-major rows. The caller owns the pool (its kv heads only: `shard.n_kv_heads`) and the queries of its
+    query heads and tokens."""
+
+    def __init__(self, n_q_heads, n_kv_heads, act_dtype, n_tokens, max_context, world=1, rank=0, group=None):
+        from . import attn
+        self.shard = prefill_partition(n_q_heads, n_kv_heads, n_tokens, world, rank)
+        self.world, self.group = world, group
+        self.ctx = attn.Attention(self.shard.n_q_heads, self.shard.n_kv_heads, act_dtype, 1, max_context)
+        dt = self.ctx.torch_dtype
+        self.o_local = torch.zeros(1, self.shard.n_tokens, self.shard.n_q_heads * 128, dtype=dt, device="cuda")
+        self.gathered = torch.zeros(world, self.shard.n_tokens, self.shard.n_q_heads * 128, dtype=dt, device="cuda")
+        self.o_full = torch.zeros(n_tokens, n_q_heads * 128, dtype=dt, device="cuda")
+
+    def attend(self, pool, block_table, layer, pos0, q_local, gains=None):
+        """The local kernel only: o_local [1][T_l][hq_l * 128]. pos0 = the position of THIS rank's first token."""
+        from . import attn
+        attn.full_prefill(self.ctx, pool, block_table, layer, pos0, q_local, self.o_local, gains=gains)
+        return self.o_local
+
+    def combine(self):
+        """All-gather of the per-head outputs and their placement: o_full [T][Hq * 128]."""
+        if self.world == 1:
+            self.o_full.copy_(self.o_local[0])
+            return self.o_full
+        all_gather_rows(self.gathered, self.o_local[0], self.group)
+        return place_heads(self.gathered, self.o_full, self.shard.kv_shards, self.shard.tok_shards)
+
+    def run(self, pool, block_table, layer, pos0, q_local, gains=None):
+        self.attend(pool, block_table, layer, pos0, q_local, gains)
+        return self.combine()
+
+    def close(self):
+        self.ctx.close()
 
 
 def max_over_ranks(value, device="cpu", group=None):

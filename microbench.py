@@ -1,8 +1,8 @@
 """Single-kernel timing cases on synthetic data (CUDA events; also the commands profiled under ncu).
 
-    python -m embla_metal_b200.microbench full_decode --batch 8 [--scores]
-    python -m embla_metal_b200.microbench sparse --batch 8        # score, select, gather-attend, sliding attend
-    python -m embla_metal_b200.microbench prefill --tokens 2048 --cached 30720
+    python microbench.py full_decode --batch 8 [--scores]
+    python microbench.py sparse --batch 8        # score, select, gather-attend, sliding attend
+    python microbench.py prefill --tokens 2048 --cached 30720
 
 Each case prints one line per kernel with its time per launch and the bandwidth or FLOP rate that follows
 from the algorithmic bytes / FLOPs of the launch.
@@ -11,7 +11,11 @@ import argparse
 
 import torch
 
-from . import attn, stack as stk
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from embla_metal_b200 import attn, stack as stk  # noqa: E402
 
 HQ, HKV, CTX = 16, 4, 32768
 
