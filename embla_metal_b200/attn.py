@@ -156,13 +156,14 @@ class Attention:
         self._trace_cap = max_launches
 
     def trace_end(self):
-        """[(entry, first_enter_ns, first_ready_ns, last_loop_end_ns, last_exit_ns)] of the launches since trace_begin."""
+        """[(entry, first_enter_ns, first_ready_ns, last_loop_end_ns, last_exit_ns, 4 phase marks)] of the launches since
+        trace_begin."""
         cap = self._trace_cap
-        stamps = (C.c_uint64 * (4 * cap))()
+        stamps = (C.c_uint64 * (8 * cap))()
         entries = (C.c_int32 * cap)()
         n = C.c_int32()
         _check(lib().embla_attn_trace_end(self.handle, _stream(), stamps, entries, cap, C.byref(n)))
-        return [(entries[i], *[stamps[4 * i + k] for k in range(4)]) for i in range(n.value)]
+        return [(entries[i], *[stamps[8 * i + k] for k in range(8)]) for i in range(n.value)]
 
     @staticmethod
     def view(block_table, seq_lens, layer, max_seq_len=0):

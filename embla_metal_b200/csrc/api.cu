@@ -128,12 +128,12 @@ EmblaStatus embla_attn_trace_begin(EmblaAttn* ctx, int32_t max_launches, void* s
         ctx->trace_dev = nullptr;
         ctx->trace_entry = nullptr;
         ctx->trace_cap = 0;
-        EMBLA_CUDA_TRY(cudaMalloc(&ctx->trace_dev, size_t(max_launches) * 4 * sizeof(unsigned long long)));
+        EMBLA_CUDA_TRY(cudaMalloc(&ctx->trace_dev, size_t(max_launches) * TRACE_SLOTS * sizeof(unsigned long long)));
         ctx->trace_entry = new (std::nothrow) int[max_launches];
         if (!ctx->trace_entry) EMBLA_FAIL(EMBLA_OOM, "embla_attn_trace_begin: host allocation failed");
         ctx->trace_cap = max_launches;
     }
-    EMBLA_CUDA_TRY(cudaMemsetAsync(ctx->trace_dev, 0xff, size_t(ctx->trace_cap) * 4 * sizeof(unsigned long long), s));
+    EMBLA_CUDA_TRY(cudaMemsetAsync(ctx->trace_dev, 0xff, size_t(ctx->trace_cap) * TRACE_SLOTS * sizeof(unsigned long long), s));
     ctx->trace_next = 0;
     ctx->trace_on = 1;
     return EMBLA_OK;
@@ -146,14 +146,14 @@ EmblaStatus embla_attn_trace_end(EmblaAttn* ctx, void* stream, uint64_t* stamps,
     *n_out = n;
     if (n == 0) return EMBLA_OK;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    EMBLA_CUDA_TRY(cudaMemcpyAsync(stamps, ctx->trace_dev, size_t(n) * 4 * sizeof(uint64_t), cudaMemcpyDeviceToHost, s));
+    EMBLA_CUDA_TRY(cudaMemcpyAsync(stamps, ctx->trace_dev, size_t(n) * TRACE_SLOTS * sizeof(uint64_t), cudaMemcpyDeviceToHost, s));
     EMBLA_CUDA_TRY(cudaStreamSynchronize(s));
     for (int i = 0; i < n; i++) {
         entries[i] = ctx->trace_entry[i];
-        // slots 2 and 3 are kept as complements on the device; a slot no CTA stamped reads 0
-        for (int k = 0; k < 4; k++) {
-            uint64_t& v = stamps[4 * i + k];
-            if (k >= 2) v = ~v;
+        // the "last CTA" slots (2, 3, 6, 7) are kept as complements on the device; a slot no CTA stamped reads 0
+        for (int k = 0; k < TRACE_SLOTS; k++) {
+            uint64_t& v = stamps[TRACE_SLOTS * i + k];
+            if ((k & 2) != 0) v = ~v;
             else if (v == ~uint64_t(0)) v = 0;
         }
     }

@@ -107,7 +107,7 @@ static EmblaStatus ring_maps(EmblaAttn* ctx, const Attn16Params& p, int batch, c
 template <int DT, int MODE, bool TMA, bool CL>
 static EmblaStatus launch_attn16_kernel(EmblaAttn* ctx, const Attn16Params& p, const CUtensorMap& mk, const CUtensorMap& mv,
                                         dim3 grid, cudaStream_t s) {
-    constexpr size_t smem = 1024 + A16_STAGES * A16_STAGE + 8 * HD * 2;
+    constexpr size_t smem = 1024 + A16_STAGES * A16_STAGE + 8 * HD * 2 + (CL ? A16_INBOX_BYTES : 0);
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
         EMBLA_CUDA_TRY(cudaFuncSetAttribute(attn16_decode_kernel<DT, MODE, TMA, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));

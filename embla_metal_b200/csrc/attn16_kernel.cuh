@@ -23,6 +23,10 @@ constexpr int A16_STAGES = 3;
 constexpr int A16_SIDE = A16_ROWS * HD * 2;           // bytes of one side (K or V) of a tile: 16 KiB
 constexpr int A16_STAGE = 2 * A16_SIDE;
 constexpr int A16_PART = HD + 4;                      // floats per (range, head): 128 sums, max, sum
+// Clusters: a head's partials are sent to the CTA that finishes it (head h: CTA h % ranges), into an inbox of
+// [sender][head of this owner] rows behind the stages and queries; ranges x ceil(heads / ranges) <= 15 rows.
+constexpr int A16_INBOX_ROWS = 15;
+constexpr int A16_INBOX_BYTES = A16_INBOX_ROWS * A16_PART * 4;
 enum { A16_SPARSE = 0, A16_SLIDING = 1 };
 
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(A16_THREADS) : "memory"); }
@@ -72,11 +76,11 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
     // Ring tiles of an "early" launch (the kernel ahead of it in the stream does not write this ring) are requested before
     // the wait for that kernel; seq_lens is an input of the whole step.
     const bool early = TMA && p.ctl.early != 0;
+    const int S = p.seq_lens[b];   // (read ahead of the wait in any case: nothing on the GPU writes the sequence lengths)
     if (!early) {
         pdl_wait();
         pdl_launch_dependents();
     }
-    const int S = p.seq_lens[b];
     const bool selecting = MODE == A16_SPARSE && S > EMBLA_TOPK + EMBLA_RECENT;
     const int count = MODE == A16_SLIDING ? min(S, p.window) : (selecting ? EMBLA_TOPK + EMBLA_RECENT : S);
     const int pos = S - 1;
@@ -175,26 +179,69 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             cp_async16(Vt + dst, base_v + roff[it], valid);
         }
     };
-    if (!TMA) {
-        resolve_tile(0);
+    // The queries' loads go out first: their latency then overlaps the address chains below instead of following them.
+    constexpr int QPW = 8 / (A16_THREADS / 32);   // heads a warp prepares
+    float xq[QPW][4];
 #pragma unroll
-        for (int t = 0; t < A16_STAGES - 1; t++) {
-            if (t < ntile) issue_tile(t);
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            resolve_tile(t + 1);
+    for (int k = 0; k < QPW; k++) {
+        const int hh = warp + k * (A16_THREADS / 32);
+        const size_t off = size_t(b) * p.q_stride + size_t(kvh * p.G + (hh < p.G ? hh : 0)) * HD;
+#pragma unroll
+        for (int i = 0; i < 4; i++) xq[k][i] = hh < p.G ? Act<DT>::load(p.q, off + lane + 32 * i) : 0.0f;
+    }
+    if (!TMA) {
+        // The first tiles' rows are resolved together: all their index loads in flight at once, then all their block-table
+        // loads, then the copies (resolved tile by tile, each chain of two dependent loads would follow the one before).
+        if (MODE == A16_SPARSE) {
+            constexpr int PRE = A16_STAGES;   // tiles 0 .. PRE - 2 are issued here, tile PRE - 1 stays resolved for the loop
+            const int ch = tid & 15;
+            int rows[PRE][8];
+            uint32_t valid[PRE];
+#pragma unroll
+            for (int t = 0; t < PRE; t++) {
+                valid[t] = 0;
+#pragma unroll
+                for (int it = 0; it < 8; it++) {
+                    const int j = (tile0 + t) * A16_ROWS + it * 8 + (tid >> 4);
+                    const bool ok = t < ntile && j < count;
+                    valid[t] |= uint32_t(ok) << it;
+                    rows[t][it] = ok ? (selecting ? int(p.idx[(size_t(b) * p.n_kv_heads + kvh) * (EMBLA_TOPK + EMBLA_RECENT) + j]) : j) : 0;
+                }
+            }
+            int blocks[PRE][8];
+#pragma unroll
+            for (int t = 0; t < PRE; t++)
+#pragma unroll
+                for (int it = 0; it < 8; it++) blocks[t][it] = p.block_table[size_t(b) * p.table_stride + (rows[t][it] >> 7)];
+#pragma unroll
+            for (int t = 0; t < PRE; t++) {
+                rvalid = valid[t];
+#pragma unroll
+                for (int it = 0; it < 8; it++)
+                    roff[it] = ((size_t(blocks[t][it]) * p.n_layers + p.layer) * p.n_kv_heads + kvh) * p.page_bytes +
+                               (rows[t][it] & 127) * (HD * 2) + ch * 16;
+                if (t < PRE - 1) {
+                    if (t < ntile) issue_tile(t);
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                }
+            }
+        } else {
+            resolve_tile(0);
+#pragma unroll
+            for (int t = 0; t < A16_STAGES - 1; t++) {
+                if (t < ntile) issue_tile(t);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                resolve_tile(t + 1);
+            }
         }
     }
     // ---- the kv head's queries (norm, RoPE for sliding layers) while the rows arrive
-    for (int hh = warp; hh < 8; hh += A16_THREADS / 32) {
-        float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (hh < p.G) {
-            const size_t off = size_t(b) * p.q_stride + size_t(kvh * p.G + hh) * HD;
 #pragma unroll
-            for (int i = 0; i < 4; i++) x[i] = Act<DT>::load(p.q, off + lane + 32 * i);
-            if (!p.prenormed) norm_rope_round<DT>(x, p.g1, p.g2, p.ng, MODE == A16_SLIDING ? pos : -1, p.rope_freq, lane);
-        }
+    for (int k = 0; k < QPW; k++) {
+        const int hh = warp + k * (A16_THREADS / 32);
+        if (hh < p.G && !p.prenormed) norm_rope_round<DT>(xq[k], p.g1, p.g2, p.ng, MODE == A16_SLIDING ? pos : -1, p.rope_freq, lane);
 #pragma unroll
-        for (int i = 0; i < 4; i++) Act<DT>::store(&qs[hh][0], lane + 32 * i, x[i]);
+        for (int i = 0; i < 4; i++) Act<DT>::store(&qs[hh][0], lane + 32 * i, xq[k][i]);
     }
     // Sliding layers, fused ring write (attention.metal:47-62): the current token's key (normed, rotated and rounded as
     // attn_sliding does) and value come from the qkv row, not from the ring. The warp that owns the token's row of its
@@ -232,6 +279,8 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
         qb0[t] = *reinterpret_cast<const uint32_t*>(&qs[g][d0]);
         qb1[t] = *reinterpret_cast<const uint32_t*>(&qs[g][d0 + 2]);
     }
+    trace_first(p.ctl.trace, 4);   // queries ready
+    trace_last(p.ctl.trace, 6);
     const float scale = rsqrtf(float(HD));
     float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;     // running max / sum of heads 2c, 2c + 1 over this warp's rows
     float OT[8][4];
@@ -254,6 +303,7 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             asm volatile("cp.async.wait_group %0;" ::"n"(A16_STAGES - 2) : "memory");
             cons_sync();
         }
+        if (t == 0) trace_last(p.ctl.trace, 7);   // the first tile has arrived
         // the 16 rows of this warp: lane holds rows r0 and r0 + 8
         const int R0 = warp * 16, r0 = R0 + rg;
         bool v0, v1;
@@ -408,9 +458,11 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
     }
     cons_sync();
     const int pair = b * p.n_kv_heads + kvh;
-    // this CTA's merged partial: to the global scratch, or (clusters) kept in shared memory behind the warps' partials
-    float* part = CL ? reinterpret_cast<float*>(smem + 4 * 8 * HD * 4 + 1024)
-                     : p.partials + (size_t(pair) * p.max_chunks + chunk) * p.G * A16_PART;
+    // This CTA's merged partial goes to the global scratch or, with clusters, head by head into the inbox of the CTA that
+    // finishes that head (head h: CTA h % nch), written straight into that CTA's shared memory.
+    float* part = p.partials + (size_t(pair) * p.max_chunks + chunk) * p.G * A16_PART;
+    float* inbox = reinterpret_cast<float*>(smem + A16_STAGES * A16_STAGE + 8 * HD * 2);
+    const int slots = CL ? (p.G + nch - 1) / nch : 0;   // heads an owner finishes
     for (int idx = tid; idx < p.G * HD; idx += A16_THREADS) {
         const int hh = idx >> 7, d = idx & 127;
         float M = NEG_BIG;
@@ -425,6 +477,13 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
         }
         if (nch == 1) {
             Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
+        } else if (CL) {
+            const uint32_t row = cluster_map(smem_u32(inbox + (chunk * slots + hh / nch) * A16_PART), uint32_t(hh % nch));
+            cluster_st_f32(row + uint32_t(d) * 4u, num);
+            if (d == 0) {
+                cluster_st_f32(row + HD * 4, M);
+                cluster_st_f32(row + (HD + 1) * 4, L);
+            }
         } else {
             part[hh * A16_PART + d] = num;
             if (d == 0) {
@@ -434,21 +493,20 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
         }
     }
     if (CL && nch > 1) {
-        // Every range's partial is in its CTA's shared memory: one cluster barrier, then CTA `chunk` merges heads
-        // chunk, chunk + nch, ... in range order, reading the other CTAs' rows through the cluster's window (all loads in
-        // flight together); a second barrier keeps every CTA's shared memory alive until the others have read it.
+        // One cluster barrier: every range's rows have arrived in their owners' inboxes; CTA `chunk` merges heads
+        // chunk, chunk + nch, ... in range order from its own shared memory. Nobody touches another CTA's memory after the
+        // barrier, so a CTA may leave as soon as it is done.
         cluster_arrive();
         cluster_wait();
-        const uint32_t mine = smem_u32(part);
-        for (int hh = chunk; hh < p.G; hh += nch) {
+        for (int slot = 0, hh = chunk; hh < p.G; slot++, hh += nch) {
             const int d = tid;
             float mc[8], lc[8], ac[8];
 #pragma unroll
             for (int r = 0; r < 8; r++) {
-                const uint32_t row = cluster_map(mine, uint32_t(r < nch ? r : 0)) + uint32_t(hh * A16_PART) * 4u;
-                mc[r] = r < nch ? cluster_ld_f32(row + HD * 4) : NEG_BIG;
-                lc[r] = r < nch ? cluster_ld_f32(row + (HD + 1) * 4) : 0.0f;
-                ac[r] = r < nch ? cluster_ld_f32(row + uint32_t(d) * 4u) : 0.0f;
+                const float* row = inbox + ((r < nch ? r : 0) * slots + slot) * A16_PART;
+                mc[r] = r < nch ? row[HD] : NEG_BIG;
+                lc[r] = r < nch ? row[HD + 1] : 0.0f;
+                ac[r] = r < nch ? row[d] : 0.0f;
             }
             float M = NEG_BIG;
 #pragma unroll
@@ -462,8 +520,6 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             }
             Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
         }
-        cluster_arrive();
-        cluster_wait();
         trace_last(p.ctl.trace, 3);
         return;
     }

@@ -28,10 +28,13 @@ constexpr int ERR_WAIT_FULL = 1, ERR_WAIT_EMPTY = 2, ERR_WAIT_DRAIN = 3;
 constexpr uint32_t WAIT_LIMIT = 1u << 20;
 constexpr long long WAIT_CYCLES = 1ll << 30;
 
+// Device timestamps a launch records when the profiler is on (trace_first / trace_last below).
+constexpr int TRACE_SLOTS = 8;
+
 // What every launch takes from its context besides its operands.
 struct KernelCtl {
     int* err;                    // device error word
-    unsigned long long* trace;   // 4 device timestamps of this launch (trace_* below), or nullptr
+    unsigned long long* trace;   // TRACE_SLOTS device timestamps of this launch (trace_* below), or nullptr
     long long wait_cycles;       // bound of every device-side wait
     int stall_at;                // diagnostic (embla_attn_inject_stall): the producer stops issuing at this item of
                                  // its range, so that the consumers' bounded wait runs out; -1: never
@@ -109,7 +112,7 @@ inline KernelCtl kernel_ctl(EmblaAttn* ctx) {
     c.trace = nullptr;
     if (ctx->trace_on && ctx->trace_next < ctx->trace_cap) {
         ctx->trace_entry[ctx->trace_next] = ctx->trace_tag;
-        c.trace = ctx->trace_dev + 4 * size_t(ctx->trace_next++);
+        c.trace = ctx->trace_dev + TRACE_SLOTS * size_t(ctx->trace_next++);
     }
     c.wait_cycles = ctx->wait_cycles;
     c.stall_at = ctx->stall_at;
@@ -209,6 +212,9 @@ __device__ __forceinline__ float cluster_ld_f32(uint32_t addr) {
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
     return v;
 }
+__device__ __forceinline__ void cluster_st_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 
 // Partial sums that other CTAs left in global memory -> shared memory, every load of a batch in flight together (the
 // last CTA of a split reads a few tens of KB once; read one dependent load at a time, that costs several microseconds).
@@ -232,8 +238,8 @@ __device__ __forceinline__ void stage_from_global(float4* dst, const float4* src
 
 // ---- device-timestamp profiler: per launch, when the first CTA entered (0), when the first CTA was past its
 // dependency wait (1), when the last CTA left its main loop (2) and when the last CTA finished (3), in nanoseconds of
-// the GPU's global timer. Slots 2 and 3 hold the complement, so that one atomicMin serves all four; the host
-// presets every slot to all ones. Thread 0 of every CTA stamps; a launch without a slot (the usual case) pays one
+// the GPU's global timer; slots 4-5 (first CTA to get there) and 6-7 (last CTA) are a kernel's own phase marks. The
+// "last" slots hold the complement, so that one atomicMin serves all; the host presets every slot to all ones. Thread 0 of every CTA stamps; a launch without a slot (the usual case) pays one
 // predictable branch.
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;

@@ -16,6 +16,8 @@
 //  * SCORES: each consumer thread also takes one key of the page and computes the kv head's query
 //    heads' dots as one fp32 fmaf chain over d = 0..127 (the summation order the CPU oracle fixes),
 //    so the selection that follows is reproducible bit for bit.
+#include <cstdlib>
+
 #include "kv_row.cuh"
 
 namespace embla {
@@ -74,6 +76,10 @@ __device__ __forceinline__ float f32_from_biased_byte(uint32_t x, int k) {
 }
 
 constexpr int QF_LD = HD + 4;   // fp32 query rows padded so that two heads never share a bank
+// where the cluster inbox starts in the (1024-byte aligned) dynamic shared memory: behind stages, queries and barriers
+__host__ __device__ constexpr size_t fd_inbox_offset(int stages, bool scores) {
+    return ((size_t(stages) * FD_STAGE_BYTES + 8 * HD * 2 + 2 * size_t(stages) * 8 + (scores ? 8 * QF_LD * 4 : 0)) + 15) / 16 * 16;
+}
 
 // acc = fma(q.lo, k.lo, acc); acc = fma(q.hi, k.hi, acc) on packed fp16 pairs: products exact, each step rounded
 // once to fp32 (the mixed-precision fma of sm_100).
@@ -88,7 +94,10 @@ __device__ __forceinline__ void fma_pair_f16(float& acc, uint32_t k, uint32_t q)
 // head count up to 8 (the count read at run time).
 // NCONS consumer warps share the keys of every page for the attention; with scores, 4 more warps (one key a thread)
 // compute the key scores from the same stage; the last warp is the producer.
-template <int DT, int SB, int NCONS, int STAGES, int SG>
+// CL: the key ranges of a pair are the CTAs of one thread-block cluster (at most 4), launched as such; every range sends
+// its partial rows, head by head, into the shared memory of the CTA that finishes that head (head h: CTA h % ranges), so
+// the combine needs one cluster barrier and no global scratch.
+template <int DT, int SB, int NCONS, int STAGES, int SG, bool CL>
 __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
     full_decode_kernel(const __grid_constant__ CUtensorMap tmap, const FullDecodeParams p) {
     constexpr bool SCORES = SG != 0;
@@ -113,11 +122,11 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
     // Launched with the dependent-launch attribute, the kernel ahead of this one in the stream may still be running
     // here. An "early" launch (the step driver knows that kernel writes none of this layer's pages) starts its first
     // pages before it waits for that kernel; seq_lens and the block table are inputs of the whole step.
+    const int S = p.seq_lens[b];   // (an input of the whole step: read ahead of the wait, its latency hidden behind it)
     if (!p.ctl.early) {
         pdl_wait();
         pdl_launch_dependents();
     }
-    const int S = p.seq_lens[b];
     const int npages = (S + BLK - 1) / BLK;
     const int pps = (npages + p.nsplit - 1) / p.nsplit;
     const int pg0 = split * pps;
@@ -466,6 +475,9 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
     const int pair = b * p.n_kv_heads + kvh;
     const float sink = sqrtf(float(HD));
     float* part = p.partials + (size_t(pair) * p.nsplit + split) * p.G * FD_PART;
+    // (clusters) rows [sender][head of this owner] that the other ranges write into this CTA's shared memory
+    float* inbox = reinterpret_cast<float*>(smem + fd_inbox_offset(STAGES, SCORES));
+    const int slots = CL ? (p.G + p.nsplit - 1) / p.nsplit : 0;   // heads an owner finishes
     for (int idx = tid; idx < p.G * HD; idx += THREADS) {
         const int hh = idx >> 7, d = idx & 127;
         float num = 0.0f, den = 0.0f;
@@ -476,10 +488,34 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
         }
         if (p.nsplit == 1) {
             Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / (sink + den));
+        } else if (CL) {
+            const uint32_t row = cluster_map(smem_u32(inbox + (split * slots + hh / p.nsplit) * FD_PART), uint32_t(hh % p.nsplit));
+            cluster_st_f32(row + uint32_t(d) * 4u, num);
+            if (d == 0) cluster_st_f32(row + HD * 4, den);
         } else {
             part[hh * FD_PART + d] = num;
             if (d == 0) part[hh * FD_PART + HD] = den;
         }
+    }
+    if (CL && p.nsplit > 1) {
+        // one cluster barrier: every range's rows are in their owners' inboxes; CTA `split` adds the rows of heads
+        // split, split + nsplit, ... in range order from its own shared memory and is done
+        cluster_arrive();
+        cluster_wait();
+        for (int idx = tid; idx < slots * HD; idx += THREADS) {
+            const int slot = idx >> 7, d = idx & 127, hh = split + slot * p.nsplit;
+            if (hh < p.G) {
+                float num = 0.0f, den = sink;
+                for (int r = 0; r < p.nsplit; r++) {
+                    const float* row = inbox + (r * slots + slot) * FD_PART;
+                    den += row[HD];
+                    num += row[d];
+                }
+                Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / den);
+            }
+        }
+        trace_last(p.ctl.trace, 3);
+        return;
     }
     if (p.nsplit == 1) {
         trace_last(p.ctl.trace, 3);
@@ -536,6 +572,9 @@ template <int STAGES, bool SCORES>
 constexpr size_t fd_smem_bytes() {
     return 1024 + size_t(STAGES) * FD_STAGE_BYTES + 8 * HD * 2 + 2 * STAGES * 8 + (SCORES ? 8 * QF_LD * 4 : 0);
 }
+// Cluster launches (at most 4 ranges) add the inbox: ranges x ceil(heads / ranges) rows of FD_PART floats, at most 6 rows
+// for up to 4 query heads a kv head, 9 for 8.
+constexpr int fd_inbox_rows(int G) { return G <= 4 ? 6 : 9; }
 
 // Key ranges per (sequence, kv head): fill `slots` resident CTAs in whole waves, with ranges long
 // enough to amortise a CTA's start-up (the reference's chunks8, Engine.swift:737-740, for 148 SMs).
@@ -556,28 +595,58 @@ int choose_splits(int pairs, int pages, int slots, int max_slots) {
     return best;
 }
 
+// The split of the attention-only (no scores) launch: up to 4 ranges a pair may run as one thread-block cluster that
+// combines through its shared memory, which saves the round trip through global scratch (worth about a page of
+// streaming); larger clusters leave SMs of a GPC idle, so more ranges than that combine through the scratch. The split is a
+// function of the shape only: every entry point that runs this kernel cuts a pair the same way and so adds in the same order.
+int choose_full_decode_split(int pairs, int pages, int slots, int max_slots, bool* cluster) {
+    const int any = choose_splits(pairs, pages, slots, max_slots);
+    const int few = choose_splits(pairs, pages, slots, 4 * pairs);
+    auto cost = [&](int ns) {
+        const long waves = (long(pairs) * ns + slots - 1) / slots;
+        return double(waves) * ((pages + ns - 1) / ns + 3.0);
+    };
+    static const bool use_clusters = []() { const char* e = getenv("EMBLA_NO_CLUSTER"); return !(e && e[0] == '1'); }();
+    if (use_clusters && few > 1 && cost(few) <= cost(any) + 1.0) {
+        *cluster = true;
+        return few;
+    }
+    *cluster = false;
+    return any;
+}
+
 }  // namespace embla
 
 using namespace embla;
 
-template <int DT, int SB, int SG>
-static EmblaStatus launch_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const FullDecodeParams& p, int batch,
-                                      cudaStream_t s) {
+template <int DT, int SB, int SG, bool CL>
+static EmblaStatus launch_full_decode_cl(EmblaAttn* ctx, const EmblaKVPool* pool, const FullDecodeParams& p, int batch,
+                                         cudaStream_t s) {
     constexpr int STAGES = 3;
     constexpr bool SCORES = SG != 0;
     constexpr int NCONS = SCORES ? 4 : 8;
     constexpr int FD_THREADS = (NCONS + (SCORES ? 4 : 0) + 1) * 32;
-    constexpr size_t smem = fd_smem_bytes<STAGES, SCORES>();
-    auto kern = full_decode_kernel<DT, SB, NCONS, STAGES, SG>;
+    const size_t smem = CL ? 1024 + fd_inbox_offset(STAGES, SCORES) + size_t(fd_inbox_rows(p.G)) * FD_PART * 4 : fd_smem_bytes<STAGES, SCORES>();
+    auto kern = full_decode_kernel<DT, SB, NCONS, STAGES, SG, CL>;
     static bool configured[64] = {};   // per instantiation and device
     if (!configured[ctx->device & 63]) {
-        EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            int(CL ? 1024 + fd_inbox_offset(STAGES, SCORES) + 9 * FD_PART * 4 : fd_smem_bytes<STAGES, SCORES>())));
         configured[ctx->device & 63] = true;
     }
     dim3 grid(p.nsplit, p.n_kv_heads, batch);
-    EMBLA_CUDA_TRY(launch_kernel(ctx->pdl, kern, grid, dim3(FD_THREADS), smem, s, pool->tmap_codes, p));
+    EMBLA_CUDA_TRY(launch_kernel_cluster(ctx->pdl, CL ? p.nsplit : 1, kern, grid, dim3(FD_THREADS), smem, s, pool->tmap_codes, p));
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;
+}
+
+template <int DT, int SB, int SG>
+static EmblaStatus launch_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const FullDecodeParams& p, int batch,
+                                      bool cluster, cudaStream_t s) {
+    // (the scoring variant keeps the combine through global scratch: with its fp32 queries the inbox would not leave room
+    // for two CTAs an SM)
+    if (SG == 0 && cluster) return launch_full_decode_cl<DT, SB, SG, SG == 0>(ctx, pool, p, batch, s);
+    return launch_full_decode_cl<DT, SB, SG, false>(ctx, pool, p, batch, s);
 }
 
 static EmblaStatus full_decode_impl(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view, const EmblaQuery* q,
@@ -631,11 +700,13 @@ static EmblaStatus full_decode_impl(EmblaAttn* ctx, const EmblaKVPool* pool, con
     p.norm_k = norm_k;
     const int pairs = view->batch * pool->n_kv_heads;
     const int pages = (max_len + BLK - 1) / BLK;
-    p.nsplit = choose_splits(pairs, pages, 2 * ctx->sm_count, ctx->partial_slots);
+    bool cluster = false;
+    if (scores_dev) p.nsplit = choose_splits(pairs, pages, 2 * ctx->sm_count, ctx->partial_slots);
+    else p.nsplit = choose_full_decode_split(pairs, pages, 2 * ctx->sm_count, ctx->partial_slots, &cluster);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
     const bool s4 = pool->scale_bytes == 4;
-#define EMBLA_FD(DT, SB, SC) launch_full_decode<DT, SB, SC>(ctx, pool, p, view->batch, s)
+#define EMBLA_FD(DT, SB, SC) launch_full_decode<DT, SB, SC>(ctx, pool, p, view->batch, cluster, s)
 #define EMBLA_FD_SG(SG) \
     (bf ? (s4 ? EMBLA_FD(EMBLA_BF16, 4, SG) : EMBLA_FD(EMBLA_BF16, 2, SG)) : (s4 ? EMBLA_FD(EMBLA_F16, 4, SG) : EMBLA_FD(EMBLA_F16, 2, SG)))
     if (scores_dev) {   // the head count compiled in for the usual groupings
@@ -698,7 +769,7 @@ static NoAllocDevice g_noalloc[64];
 template <int DT, int SB>
 static EmblaStatus noalloc_setup_kernel() {
     constexpr size_t smem = fd_smem_bytes<3, false>();
-    EMBLA_CUDA_TRY(cudaFuncSetAttribute(full_decode_kernel<DT, SB, 8, 3, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    EMBLA_CUDA_TRY(cudaFuncSetAttribute(full_decode_kernel<DT, SB, 8, 3, 0, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         int(smem)));
     return EMBLA_OK;
 }
@@ -782,16 +853,17 @@ extern "C" EmblaStatus embla_attn_full_decode_noalloc(const EmblaKVPool* pool, c
     p.ng = q->ng;
     const int pairs = view->batch * Hkv;
     const int pages = (view->max_seq_len + BLK - 1) / BLK;
-    p.nsplit = choose_splits(pairs, pages, 2 * d.sm_count, NOALLOC_MAX_SLOTS);
+    bool cluster_unused = false;   // (this entry point always combines through its fixed scratch)
+    p.nsplit = choose_full_decode_split(pairs, pages, 2 * d.sm_count, NOALLOC_MAX_SLOTS, &cluster_unused);
     constexpr size_t smem = fd_smem_bytes<3, false>();
     dim3 grid(p.nsplit, Hkv, view->batch);
     const bool s4 = pool->scale_bytes == 4;
     if (act_dtype == EMBLA_BF16) {
-        if (s4) full_decode_kernel<EMBLA_BF16, 4, 8, 3, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
-        else full_decode_kernel<EMBLA_BF16, 2, 8, 3, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
+        if (s4) full_decode_kernel<EMBLA_BF16, 4, 8, 3, 0, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
+        else full_decode_kernel<EMBLA_BF16, 2, 8, 3, 0, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
     } else {
-        if (s4) full_decode_kernel<EMBLA_F16, 4, 8, 3, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
-        else full_decode_kernel<EMBLA_F16, 2, 8, 3, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
+        if (s4) full_decode_kernel<EMBLA_F16, 4, 8, 3, 0, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
+        else full_decode_kernel<EMBLA_F16, 2, 8, 3, 0, false><<<grid, 9 * 32, smem, s>>>(pool->tmap_codes, p);
     }
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;

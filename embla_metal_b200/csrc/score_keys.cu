@@ -74,11 +74,11 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
     trace_first(p.ctl.trace, 0);
     // An "early" launch (the kernel ahead of it in the stream writes none of this layer's pages) starts its first pages
     // before it waits for that kernel; seq_lens and the block table are inputs of the whole step.
+    const int S = p.seq_lens[b];   // (an input of the whole step: read ahead of the wait, its latency hidden behind it)
     if (!p.ctl.early) {
         pdl_wait();
         pdl_launch_dependents();
     }
-    const int S = p.seq_lens[b];
     const int npages = (S + BLK - 1) / BLK;
     const int pps = (npages + p.nsplit - 1) / p.nsplit;
     const int pg0 = split * pps;

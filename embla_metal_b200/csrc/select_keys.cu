@@ -66,10 +66,10 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
     const int kvh = blockIdx.x / CL, b = blockIdx.y;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     trace_first(p.ctl.trace, 0);
+    const int S = p.seq_lens[b];   // (read ahead of the wait: nothing on the GPU writes the sequence lengths)
     pdl_wait();
     pdl_launch_dependents();
     trace_first(p.ctl.trace, 1);
-    const int S = p.seq_lens[b];
     // the reference does not select yet at or below 1152 keys (Engine.swift:796); uniform over the cluster, and
     // every CTA keeps taking the barriers
     const bool active = S > EMBLA_TOPK + EMBLA_RECENT;
@@ -114,6 +114,8 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
         for (int i = t; i < 2 * SEL_BINS; i += SEL_T) (&hist[0][0])[i] = 0;
     }
     __syncthreads();
+    trace_first(p.ctl.trace, 4);   // the scores are in registers
+    trace_last(p.ctl.trace, 6);
 
     uint32_t prefix = 0, mask = 0, k = EMBLA_TOPK;
 #pragma unroll
@@ -180,6 +182,7 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
             mask |= uint32_t(nb - 1) << shift;
             k -= sel[1];
         }
+        if (pass == 0) trace_last(p.ctl.trace, 7);   // the first digit is known
     }
     trace_last(p.ctl.trace, 2);
     // prefix is the TOPK-th largest pattern; every key above it, then the first k equal to it, in key order.

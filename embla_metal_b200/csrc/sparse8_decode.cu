@@ -45,10 +45,10 @@ __global__ void __launch_bounds__(S8_THREADS) sparse8_decode_kernel(const Sparse
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     trace_first(p.ctl.trace, 0);
+    const int S = p.seq_lens[b];   // (read ahead of the wait: nothing on the GPU writes the sequence lengths)
     pdl_wait();
     pdl_launch_dependents();
     trace_first(p.ctl.trace, 1);
-    const int S = p.seq_lens[b];
     const bool selecting = S > EMBLA_TOPK + EMBLA_RECENT;
     const int count = selecting ? EMBLA_TOPK + EMBLA_RECENT : S;
     const int nch = (count + BLK - 1) / BLK;

@@ -149,6 +149,7 @@ static EmblaStatus probe_mark(EmblaStack* st, int entry, cudaStream_t s) {
     do {                                                                                              \
         if (EmblaStatus s_ = probe_mark(st, entry, s)) return s_;                                     \
         ctx->trace_tag = entry;                                                                       \
+        ctx->pdl = use_pdl && last_write != -2; /* the step's first launch follows work that is not ours: plain order */ \
         ctx->early = st->early_ok && last_write != -2 && (reads) != TOUCH_NONE && last_write != (reads); \
         if (EmblaStatus s_ = (call)) return s_;                                                       \
         last_write = (writes);                                                                        \

@@ -121,11 +121,14 @@ EmblaStatus embla_attn_inject_stall(EmblaAttn* ctx, int32_t item);
 
 /* Device-timestamp profiler, the counterpart of the reference's per-part Profiler (StepEncoder.swift:7-65)
  * that does not serialise the launches it measures: between trace_begin and trace_end every launch
- * of this context (at most max_launches of them) records four times of the GPU's global nanosecond
- * timer - the first CTA entering, the first CTA past its wait for the preceding kernel, the last CTA
- * leaving its main loop, the last CTA finishing. trace_begin allocates on first use or growth (it then
- * synchronises the stream); trace_end synchronises the stream and writes stamps[launch][4] and the
- * entry point of each launch (EMBLA_ENTRY_* inside embla_stack_decode_step, else -1). */
+ * of this context (at most max_launches of them) records times of the GPU's global nanosecond timer:
+ * [0] the first CTA entering, [1] the first CTA past its wait for the preceding kernel, [2] the last CTA
+ * leaving its main loop, [3] the last CTA finishing, [4..7] a kernel's own phase marks (4, 5: first CTA
+ * to get there; 6, 7: last; 0 where a kernel has none). trace_begin allocates on first use or growth
+ * (it then synchronises the stream); trace_end synchronises the stream and writes
+ * stamps[launch][EMBLA_TRACE_SLOTS] and the entry point of each launch (EMBLA_ENTRY_* inside
+ * embla_stack_decode_step, else -1). */
+enum { EMBLA_TRACE_SLOTS = 8 };
 EmblaStatus embla_attn_trace_begin(EmblaAttn* ctx, int32_t max_launches, void* stream);
 EmblaStatus embla_attn_trace_end(EmblaAttn* ctx, void* stream, uint64_t* stamps, int32_t* entries, int32_t cap,
                                  int32_t* n_launches);
