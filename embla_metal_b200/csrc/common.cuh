@@ -215,6 +215,13 @@ __device__ __forceinline__ float cluster_ld_f32(uint32_t addr) {
 __device__ __forceinline__ void cluster_st_f32(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+__device__ __forceinline__ void cluster_st_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+// adds into another CTA's shared memory without waiting for an answer
+__device__ __forceinline__ void cluster_red_add_u32(uint32_t addr, uint32_t v) {
+    asm volatile("red.shared::cluster.add.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 
 // Partial sums that other CTAs left in global memory -> shared memory, every load of a batch in flight together (the
 // last CTA of a split reads a few tens of KB once; read one dependent load at a time, that costs several microseconds).

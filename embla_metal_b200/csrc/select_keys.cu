@@ -7,8 +7,9 @@
 // largest pattern, then a compaction in key order takes every key above it and the first equal ones.
 // A cluster of 1, 2, 4 or 8 CTAs of 1024 threads per (sequence, kv head) - more CTAs the fewer pairs
 // there are, so that small batches still fill the SMs; the patterns stay in registers after the one
-// read of the scores; histograms and offsets cross the cluster through distributed shared memory,
-// barriers are hardware cluster barriers (no spinning). The output order is the reference's:
+// read of the scores; histograms are read across the cluster through distributed shared memory, the
+// warps' counts for the ordered writes are written into every CTA of the cluster; barriers are
+// hardware cluster barriers (no spinning). The output order is the reference's:
 // [greater, ascending index][equal, ascending index][n .. n + 127].
 #include <cooperative_groups.h>
 
@@ -52,17 +53,13 @@ template <int ITEMS, bool BULK, bool SINGLE>
 __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    __shared__ uint32_t hist[2][SEL_BINS];         // this CTA's digit counts, double-buffered across passes
+    __shared__ __align__(16) uint32_t hist[2][SEL_BINS];   // this CTA's digit counts, double-buffered across passes
     __shared__ uint32_t wsum[SEL_WARPS];
-    __shared__ uint32_t sel[2];                    // digit, count above it
-    __shared__ uint32_t wcnt[2][SEL_WARPS];        // this CTA's per-warp counts of greater / equal keys
+    __shared__ uint32_t sel[2];                            // digit, count above it
+    __shared__ uint32_t wall[2][8][SEL_WARPS];             // per-warp counts of greater / equal keys of every CTA of the cluster
     __shared__ uint32_t base[2][SEL_WARPS + 1];
 
     const int CL = SINGLE ? 1 : int(cluster.num_blocks()), rank = SINGLE ? 0 : int(cluster.block_rank());
-    auto csync = [&]() {
-        if (SINGLE) __syncthreads();
-        else cluster.sync();
-    };
     const int kvh = blockIdx.x / CL, b = blockIdx.y;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     trace_first(p.ctl.trace, 0);
@@ -70,13 +67,13 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
     pdl_wait();
     pdl_launch_dependents();
     trace_first(p.ctl.trace, 1);
-    // the reference does not select yet at or below 1152 keys (Engine.swift:796); uniform over the cluster, and
-    // every CTA keeps taking the barriers
-    const bool active = S > EMBLA_TOPK + EMBLA_RECENT;
-    const int n = active ? S - EMBLA_RECENT : 0;
+    // the reference does not select yet at or below 1152 keys (Engine.swift:796); the whole cluster of a pair leaves
+    if (S <= EMBLA_TOPK + EMBLA_RECENT) return;
+    const int n = S - EMBLA_RECENT;
     const float* sc = p.scores + (size_t(b) * p.n_kv_heads + kvh) * p.scores_stride;
     uint32_t* out = p.idx + (size_t(b) * p.n_kv_heads + kvh) * (EMBLA_TOPK + EMBLA_RECENT);
 
+    for (int i = t; i < 2 * SEL_BINS; i += SEL_T) (&hist[0][0])[i] = 0;
     const int w0 = (rank * SEL_WARPS + warp) * 32 * ITEMS;
     const int lim = n - w0 - lane;                 // key of round i exists while 32 i < lim
     uint32_t v[ITEMS];
@@ -98,7 +95,6 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
                     bulk_load_1d(staged_raw + off, reinterpret_cast<const uint8_t*>(sc + cta0) + off, min(16384u, bytes - off), &bar);
             }
         }
-        for (int i = t; i < 2 * SEL_BINS; i += SEL_T) (&hist[0][0])[i] = 0;
         __syncthreads();
         if (bytes && !mbar_wait_bounded(p.ctl.wait_cycles, &bar, 0) && lane == 0) atomicExch(p.ctl.err, ERR_WAIT_FULL);
 #pragma unroll
@@ -111,11 +107,9 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
         for (int i = 0; i < ITEMS; i++) raw[i] = __ldg(src + (32 * i < lim ? 32 * i : 0));
 #pragma unroll
         for (int i = 0; i < ITEMS; i++) v[i] = 32 * i < lim ? order_bits(raw[i]) : 0u;
-        for (int i = t; i < 2 * SEL_BINS; i += SEL_T) (&hist[0][0])[i] = 0;
+        __syncthreads();
     }
-    __syncthreads();
-    trace_first(p.ctl.trace, 4);   // the scores are in registers
-    trace_last(p.ctl.trace, 6);
+    const uint32_t wall_here = smem_u32(&wall[0][0][0]);
 
     uint32_t prefix = 0, mask = 0, k = EMBLA_TOPK;
 #pragma unroll
@@ -139,50 +133,60 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
             }
             if (in) atomicAdd(&h[digit], 1u);
         }
-        csync();
+        if (pass == 1) trace_first(p.ctl.trace, 4);
+        if (SINGLE) {
+            __syncthreads();
+        } else {
+            cluster_arrive();
+            cluster_wait();
+        }
+        if (pass == 1) trace_first(p.ctl.trace, 5);
         // counts above each digit, from the top, over the cluster: the digit whose bucket holds the k-th largest.
-        // Thread t takes digits nb - 1 - 2t and nb - 2 - 2t.
-        uint32_t c0 = 0, c1 = 0;
-        if (2 * t < nb) {
+        // Thread t < nb / 4 takes digits nb - 1 - 4t .. nb - 4 - 4t, read as ONE 16-byte load a CTA, four CTAs' loads in
+        // flight together (loads from another CTA's shared memory are bound by their number and their latency: read as
+        // two 4-byte loads a digit pair they took 2.8 of a pass's 3.2 microseconds; adding the counts into every CTA's
+        // array with remote atomics instead took longer still).
+        uint32_t c[4] = {0, 0, 0, 0};   // c[j]: digit nb - 1 - 4t - j
+        if (4 * t < nb) {
+            const int word = nb - 4 - 4 * t;
             if (SINGLE) {
-                c0 = h[nb - 1 - 2 * t];
-                c1 = h[nb - 2 - 2 * t];
+                const uint4 q4 = *reinterpret_cast<const uint4*>(&h[word]);
+                c[0] = q4.w, c[1] = q4.z, c[2] = q4.y, c[3] = q4.x;
             } else {
-                for (int r = 0; r < CL; r++) {
-                    const uint32_t* hr = cluster.map_shared_rank(h, r);
-                    c0 += hr[nb - 1 - 2 * t];
-                    c1 += hr[nb - 2 - 2 * t];
+                for (int r0 = 0; r0 < CL; r0 += 4) {
+                    uint4 q4[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        q4[j] = r0 + j < CL ? *reinterpret_cast<const uint4*>(cluster.map_shared_rank(h, r0 + j) + word) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) c[0] += q4[j].w, c[1] += q4[j].z, c[2] += q4[j].y, c[3] += q4[j].x;
                 }
             }
         }
-        const uint32_t s = c0 + c1, incl = warp_incl_scan(s, lane);
-        if (lane == 31) wsum[warp] = incl;
         if (pass == 1) {   // the other buffer (read by the cluster before this pass's barrier) is refilled in pass 2
             hist[0][2 * t] = 0;
             hist[0][2 * t + 1] = 0;
         }
+        if (pass == 1) trace_last(p.ctl.trace, 6);
+        const uint32_t s = c[0] + c[1] + c[2] + c[3], incl = warp_incl_scan(s, lane);
+        if (lane == 31) wsum[warp] = incl;
         __syncthreads();
         const uint32_t ws = warp_incl_scan(wsum[lane], lane);
         const uint32_t wbase = __shfl_sync(0xffffffffu, ws, (warp + 31) & 31);
         uint32_t above = (warp ? wbase : 0u) + incl - s;
-        if (active) {
-            if (above < k && above + c0 >= k) {
-                sel[0] = uint32_t(nb - 1 - 2 * t);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            if (above < k && above + c[j] >= k) {
+                sel[0] = uint32_t(nb - 1 - 4 * t - j);
                 sel[1] = above;
             }
-            above += c0;
-            if (above < k && above + c1 >= k) {
-                sel[0] = uint32_t(nb - 2 - 2 * t);
-                sel[1] = above;
-            }
+            above += c[j];
         }
         __syncthreads();
-        if (active) {
-            prefix |= sel[0] << shift;
-            mask |= uint32_t(nb - 1) << shift;
-            k -= sel[1];
-        }
-        if (pass == 0) trace_last(p.ctl.trace, 7);   // the first digit is known
+        prefix |= sel[0] << shift;
+        mask |= uint32_t(nb - 1) << shift;
+        k -= sel[1];
+        if (pass == 1) trace_last(p.ctl.trace, 7);
     }
     trace_last(p.ctl.trace, 2);
     // prefix is the TOPK-th largest pattern; every key above it, then the first k equal to it, in key order.
@@ -200,27 +204,38 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
     }
     const uint32_t cg_incl = warp_incl_scan(uint32_t(__popc(mybg)), lane);
     const uint32_t ce_incl = warp_incl_scan(uint32_t(__popc(mybe)), lane);
-    if (lane == 31) {
-        wcnt[0][warp] = cg_incl;
-        wcnt[1][warp] = ce_incl;
+    // every warp's counts go to every CTA of the cluster (pushed again), so that the offsets below are local arithmetic
+    if (SINGLE) {
+        if (lane == 31) {
+            wall[0][0][warp] = cg_incl;
+            wall[1][0][warp] = ce_incl;
+        }
+        __syncthreads();
+    } else {
+        const uint32_t gcount = __shfl_sync(0xffffffffu, cg_incl, 31), ecount = __shfl_sync(0xffffffffu, ce_incl, 31);
+        if (lane < CL) {   // lane r writes this warp's two counts into CTA r
+            cluster_st_u32(cluster_map(wall_here + uint32_t((0 * 8 + rank) * SEL_WARPS + warp) * 4u, uint32_t(lane)), gcount);
+            cluster_st_u32(cluster_map(wall_here + uint32_t((1 * 8 + rank) * SEL_WARPS + warp) * 4u, uint32_t(lane)), ecount);
+        }
+        cluster_arrive();
+        cluster_wait();
     }
-    csync();
     // offsets of this CTA's warps: everything counted by lower ranks, then this CTA's lower warps
     if (warp < 2) {
         uint32_t before = 0, all = 0;
         for (int r = 0; r < CL; r++) {
-            uint32_t sum = SINGLE ? wcnt[warp][lane] : cluster.map_shared_rank(&wcnt[warp][0], r)[lane];
+            uint32_t sum = wall[warp][r][lane];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
             if (r < rank) before += sum;
             all += sum;
         }
-        const uint32_t mine = wcnt[warp][lane];
+        const uint32_t mine = wall[warp][rank][lane];
         base[warp][lane] = before + warp_incl_scan(mine, lane) - mine;
         if (lane == 0) base[warp][SEL_WARPS] = all;
     }
     __syncthreads();
-    if (active) {
+    {
         // lane i writes round i's keys: bit l of its ballot is key w0 + 32 i + l
         const uint32_t ngt = base[0][SEL_WARPS];
         uint32_t gpos = base[0][warp] + cg_incl - uint32_t(__popc(mybg));
@@ -239,7 +254,8 @@ __global__ void __launch_bounds__(SEL_T) select_keys_kernel(const SelectParams p
         if (rank == 0)
             for (int j = t; j < EMBLA_RECENT; j += SEL_T) out[EMBLA_TOPK + j] = uint32_t(n + j);
     }
-    if (!SINGLE) cluster.sync();   // no CTA leaves while another may still read its shared memory
+    // (the last loads from another CTA's shared memory, the third pass's, were complete before the barrier above, and every
+    // push into it too: a CTA may leave at once)
     trace_last(p.ctl.trace, 3);
 }
 
