@@ -1,4 +1,5 @@
 // Context, KV pool and block copies of the embla CUDA attention library.
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -62,6 +63,10 @@ EmblaStatus embla_attn_create(const EmblaAttnConfig* cfg, EmblaAttn** out) {
     ctx->early = 0;
     ctx->wait_cycles = WAIT_CYCLES;
     ctx->stall_at = -1;
+    {
+        const char* e = getenv("EMBLA_L2_PAGES");
+        ctx->l2_pages = e ? atoi(e) : 8;
+    }
     ctx->trace_dev = nullptr;
     ctx->trace_entry = nullptr;
     ctx->trace_cap = ctx->trace_next = ctx->trace_on = 0;

@@ -40,6 +40,11 @@ struct KernelCtl {
                                  // its range, so that the consumers' bounded wait runs out; -1: never
     int early;                   // the launch may fetch its cache rows before the kernel ahead of it in the stream
                                  // has finished (that kernel writes none of them; set by the step driver)
+    int l2_pages;                // early launches of the key-scoring pass: pages a CTA asks the L2 to fetch beyond its
+                                 // shared-memory stages while it waits for the kernel ahead of it (the HBM idles during that
+                                 // kernel's tail). Measured at 8 sequences: 8 pages take 1.5 of the pass's 44.5 microseconds;
+                                 // the same request in the full-layer kernel, and requests for a later kernel's pages issued
+                                 // from the selection, slowed their kernels down and sped nothing up.
 };
 
 // ---- host-side error plumbing -------------------------------------------------------------------
@@ -87,6 +92,7 @@ struct EmblaAttn {
     int early;                     // the next launch may read its cache ahead of the kernel before it (set by the step driver per launch)
     long long wait_cycles;         // bound of the device-side waits of this context's launches
     int stall_at;                  // diagnostic stall of the next launches' producers (-1: off)
+    int l2_pages;                  // pages an early key-scoring CTA asks the L2 for (EMBLA_L2_PAGES in the environment, default 8)
     // device-timestamp profiler (embla_attn_trace_*): 4 timestamps a launch, the entry point of each launch
     unsigned long long* trace_dev;
     int* trace_entry;              // host
@@ -117,6 +123,7 @@ inline KernelCtl kernel_ctl(EmblaAttn* ctx) {
     c.wait_cycles = ctx->wait_cycles;
     c.stall_at = ctx->stall_at;
     c.early = ctx->pdl ? ctx->early : 0;
+    c.l2_pages = ctx->l2_pages;
     return c;
 }
 }  // namespace embla
@@ -282,6 +289,10 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
         : "memory");
+}
+// Asks the L2 to fetch `bytes` (a multiple of 16) at `src` (16-byte aligned) from memory; nothing waits for it.
+__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(src)), "r"(bytes) : "memory");
 }
 // 1-D bulk copy global -> shared (both 16-byte aligned, bytes a multiple of 16).
 __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {

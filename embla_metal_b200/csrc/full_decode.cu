@@ -98,7 +98,7 @@ __device__ __forceinline__ void fma_pair_f16(float& acc, uint32_t k, uint32_t q)
 // its partial rows, head by head, into the shared memory of the CTA that finishes that head (head h: CTA h % ranges), so
 // the combine needs one cluster barrier and no global scratch.
 template <int DT, int SB, int NCONS, int STAGES, int SG, bool CL>
-__global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
+__global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32, 2)   // two CTAs an SM: at most 112 registers a thread
     full_decode_kernel(const __grid_constant__ CUtensorMap tmap, const FullDecodeParams p) {
     constexpr bool SCORES = SG != 0;
     constexpr int GT = SG == 9 ? 8 : SG;
@@ -138,14 +138,15 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
 
     // ---- producer: one lane keeps the ring of stages full
     const uint32_t tx = 2 * CODE_BYTES + 2 * BLK * SB;
-    auto issue = [&](int i) {
+    // `block`: the page's physical block if the caller has it already, else -1 (read from the table here)
+    auto issue = [&](int i, int block) {
         const int st = i % STAGES, use = i / STAGES;
         if (i == p.ctl.stall_at) return false;   // diagnostic stall: the consumers' wait for this page runs out
         if (use > 0 && !mbar_wait_bounded(p.ctl.wait_cycles, &empty[st], (use - 1) & 1)) {
             atomicExch(p.ctl.err, ERR_WAIT_EMPTY);
             return false;
         }
-        const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
+        if (block < 0) block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
         const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
         uint8_t* dst = stages + st * FD_STAGE_BYTES;
         mbar_expect_tx(&full[st], tx);
@@ -156,16 +157,30 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
     };
     int next = 0;
     bool issuing = true;
-    if (tid == NWORK * 32) {   // the producer lane sets the barriers up itself, so that it can start before anyone else
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], NWORK);
+    if (warp == NWORK) {
+        // The producer warp starts before anyone else: lane i looks up the block of the range's page i (the lookups in flight
+        // together), lane 0 sets the barriers up and requests the first pages into the stages (which start empty: no wait).
+        const int ahead = min(n, STAGES);
+        const int myblock = lane < ahead ? p.block_table[size_t(b) * p.table_stride + pg0 + lane] : 0;
+        if (lane == 0) {
+            for (int s = 0; s < STAGES; s++) {
+                mbar_init(&full[s], 1);
+                mbar_init(&empty[s], NWORK);
+            }
+            mbar_init(&patched, 1);
+            s_failed = 0;
+            s_issued = 0;
+            fence_barrier_init();
         }
-        mbar_init(&patched, 1);
-        s_failed = 0;
-        s_issued = 0;
-        fence_barrier_init();
-        for (; next < min(n, STAGES) && issuing; next++) issuing = issue(next);   // the stages start empty: no wait
+        __syncwarp();
+#pragma unroll
+        for (int s = 0; s < STAGES; s++) {
+            const int blk = __shfl_sync(0xffffffffu, myblock, s);
+            if (lane == 0 && s < n && issuing) {
+                issuing = issue(s, blk);
+                next = s + 1;
+            }
+        }
     }
     if (p.ctl.early) {
         pdl_wait();
@@ -238,7 +253,7 @@ __global__ void __launch_bounds__((NCONS + (SG != 0 ? 4 : 0) + 1) * 32)
             }
         }
         if (lane == 0)
-            for (; next < n && issuing; next++) issuing = issue(next);
+            for (; next < n && issuing; next++) issuing = issue(next, -1);
         if (appends) {
             __syncwarp();
             const int il = n - 1;

@@ -97,14 +97,15 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
     __shared__ uint64_t patched;
     __shared__ int s_failed, s_issued;
 
-    auto issue = [&](int i) {
+    // `block`: the page's physical block if the caller has it already, else -1 (read from the table here)
+    auto issue = [&](int i, int block) {
         const int st = i % STAGES, use = i / STAGES;
         if (i == p.ctl.stall_at) return false;   // diagnostic stall: the consumers' wait for this page runs out
         if (use > 0 && !mbar_wait_bounded(p.ctl.wait_cycles, &empty[st], (use - 1) & 1)) {
             atomicExch(p.ctl.err, ERR_WAIT_EMPTY);
             return false;
         }
-        const int block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
+        if (block < 0) block = p.block_table[size_t(b) * p.table_stride + pg0 + i];
         const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
         uint8_t* dst = stages + st * SK_STAGE;
         mbar_expect_tx(&full[st], SK_STAGE);
@@ -115,16 +116,36 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
     };
     int next = 0;
     bool issuing = true;
-    if (tid == SK_CONSUMERS * 32) {   // the producer lane sets the barriers up itself, so that it can start before anyone else
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], SK_CONSUMERS);
+    if (warp == SK_CONSUMERS) {
+        // The producer warp starts before anyone else: lane i looks up the block of the range's page i (all lookups in
+        // flight together), lane 0 sets the barriers up and requests the first pages into the stages (which start empty: no
+        // wait), and in an early launch the lanes after those ask the L2 for the K sides of their pages: the HBM has little
+        // else to do until the kernel ahead has finished.
+        const int ahead = min(n, STAGES + (p.ctl.early ? min(p.ctl.l2_pages, 32 - STAGES) : 0));
+        const int myblock = lane < ahead ? p.block_table[size_t(b) * p.table_stride + pg0 + lane] : 0;
+        if (lane == 0) {
+            for (int s = 0; s < STAGES; s++) {
+                mbar_init(&full[s], 1);
+                mbar_init(&empty[s], SK_CONSUMERS);
+            }
+            mbar_init(&patched, 1);
+            s_failed = 0;
+            s_issued = 0;
+            fence_barrier_init();
         }
-        mbar_init(&patched, 1);
-        s_failed = 0;
-        s_issued = 0;
-        fence_barrier_init();
-        for (; next < min(n, STAGES) && issuing; next++) issuing = issue(next);   // the stages start empty: no wait
+        __syncwarp();
+#pragma unroll
+        for (int s = 0; s < STAGES; s++) {
+            const int blk = __shfl_sync(0xffffffffu, myblock, s);
+            if (lane == 0 && s < n && issuing) {
+                issuing = issue(s, blk);
+                next = s + 1;
+            }
+        }
+        if (lane >= STAGES && lane < ahead) {
+            const size_t page = (size_t(myblock) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
+            l2_prefetch(p.pool + page * p.page_bytes, SK_STAGE);
+        }
     }
     if (p.ctl.early) {
         pdl_wait();
@@ -153,7 +174,7 @@ __global__ void __launch_bounds__(SK_THREADS) score_keys16_kernel(const __grid_c
             }
         }
         if (lane == 0)
-            for (; next < n && issuing; next++) issuing = issue(next);
+            for (; next < n && issuing; next++) issuing = issue(next, -1);
         if (appends) {
             __syncwarp();
             const int il = n - 1;
