@@ -249,9 +249,10 @@ class Ring:
         self.desc = RingDesc(self.k.data_ptr(), self.v.data_ptr(), self.k.stride(0), ring, window)
 
 
-def full_prefill(ctx, pool, block_table, layer, pos0, q, o, gains=None):
+def full_prefill(ctx, pool, block_table, layer, pos0, q, o, gains=None, qk8=False):
     """Causal ReLU² attention of a prefill chunk. q [batch, n_tokens, >= n_q_heads*128], o likewise
-    (token-major); pos0 int32 [batch]. The chunk's keys/values must already be appended."""
+    (token-major); pos0 int32 [batch]. The chunk's keys/values must already be appended. qk8: the int8 Q Kᵀ
+    build (embla_attn_full_prefill_qk8)."""
     view = Attention.view(block_table, None, layer)
     if gains is None:
         qd = Query(q.data_ptr(), q.stride(0), 1, 0, None, None)
@@ -260,9 +261,9 @@ def full_prefill(ctx, pool, block_table, layer, pos0, q, o, gains=None):
     if not getattr(ctx, "_prefill_reserved", False):   # set-up, once per context: the split-KV scratch
         _check(lib().embla_attn_reserve_prefill(ctx.handle, _stream()))
         ctx._prefill_reserved = True
-    _check(lib().embla_attn_full_prefill(ctx.handle, pool.handle, C.byref(view), _ptr(pos0), q.shape[1], C.byref(qd),
-                                         C.c_int64(q.stride(1)), _ptr(o), C.c_int64(o.stride(1)), C.c_int64(o.stride(0)),
-                                         _stream()))
+    fn = lib().embla_attn_full_prefill_qk8 if qk8 else lib().embla_attn_full_prefill
+    _check(fn(ctx.handle, pool.handle, C.byref(view), _ptr(pos0), q.shape[1], C.byref(qd),
+              C.c_int64(q.stride(1)), _ptr(o), C.c_int64(o.stride(1)), C.c_int64(o.stride(0)), _stream()))
 
 
 def sliding_prefill(ctx, ring, pos0, q, o, qgain=None):

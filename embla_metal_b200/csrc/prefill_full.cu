@@ -21,6 +21,7 @@
 // TMEM (512 columns): per tile S 128 (P aliases its first 64) and O 128. q is converted to fp16 once (bf16 values are exact
 // in fp16 inside its normal range); int8 codes and their products are exact; accumulation is fp32.
 // Every wait is bounded; a wait that runs out sets the context's error word and the CTA winds down.
+#include "kv_row.cuh"
 #include "tc05.cuh"
 
 namespace embla {
@@ -36,8 +37,13 @@ constexpr int PF_KVBUFS = 3;
 // reference keeps P in fp32, attn_nax.metal:11), and fp16's gradual underflow keeps the small weights to 2^-24 of the
 // scaled unit. The sink of the denominator takes the same factor, so O / (sink + sum p) is unchanged.
 constexpr float PF_QSCALE = 0.125f, PF_PSCALE = PF_QSCALE * PF_QSCALE;
+// QK8: the integer dots are bounded by 127 x 127 x 128 whatever the queries' size, so the ReLU² warps scale them by the
+// key's factor and this constant only, u = S x kscale / sqrt(D) x 2^-8 (u^2 stays inside fp16 for key scales up to 0.25);
+// the row's own factor rho = qscale x PF_QSCALE x 2^8 multiplies every weight of the row by rho^2, so it only moves the
+// sink: O / (sink + sum p) = sum u^2 v / (sink / rho^2 + sum u^2).
+constexpr float PF_QK8_C0 = 1.0f / 256.0f;
 // alignment slack, 2 Q tiles, 3 converted sides, 3 raw int8 sides, 2 pages' scales, barriers
-constexpr size_t PF_SMEM = 1024 + 2 * PF_TILE16 + PF_KVBUFS * PF_TILE16 + PF_KVBUFS * CODE_BYTES + 2 * 1024 + 256;
+constexpr size_t PF_SMEM = 1024 + 2 * PF_TILE16 + PF_KVBUFS * PF_TILE16 + PF_KVBUFS * CODE_BYTES + 2 * 1024 + 256 + 2 * 1024;
 
 struct PrefillParams {
     const uint8_t* pool;
@@ -92,7 +98,12 @@ __device__ __forceinline__ void convert_side(const uint8_t* raw, uint8_t* dst, i
     }
 }
 
-template <int DT, int SB>
+// QK8: the reference's int8 Q Kᵀ variant (attn_nax.metal:14-22, 124-204 with q_prep_b's QK8 branch, prefill.metal:421-422;
+// switched on by EMBLA_ATT8, Prefill.swift:142-144): every query row is quantised like a cache row (write_row8: rounded to
+// the activation dtype, codes rint(x 127 / max|x|), scale max|x| / 127), S = Q8 K8ᵀ runs as tcgen05.mma kind::i8 on the
+// cache's codes as they are (int32 in TMEM, exact), and the ReLU² warps scale it: s = S x qscale(row) x kscale(key) / √D.
+// P V stays fp16 as in the other variant. Twice the tensor rate for Q Kᵀ, and no conversion of the K side at all.
+template <int DT, int SB, bool QK8>
 __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __grid_constant__ CUtensorMap tmap,
                                                                      const PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -102,6 +113,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     uint8_t* raw = kvb + PF_KVBUFS * PF_TILE16;                       // [3][16 KiB] int8 sides as loaded
     uint8_t* scl = raw + PF_KVBUFS * CODE_BYTES;                      // [2 pages][K scales | V scales], 1 KiB each
     uint64_t* bars = reinterpret_cast<uint64_t*>(scl + 2 * 1024);
+    float* qsc = reinterpret_cast<float*>(scl + 2 * 1024 + 256);     // QK8: [2 tiles][128] 1 / rho^2 of the int8 query rows
+    float* kfac = qsc + 2 * BLK;                                      // QK8: [2 pages][128] kscale / sqrt(D) x 2^-8 of the page's keys
     uint64_t* raw_full = bars;            // [3]
     uint64_t* raw_empty = bars + 3;       // [3]
     uint64_t* kv_ready = bars + 6;        // [3]
@@ -109,6 +122,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     uint64_t* s_full = bars + 12;         // [2 tiles]
     uint64_t* p_ready = bars + 14;        // [2 tiles]
     uint64_t* o_done = bars + 16;
+    uint64_t* kf_ready = bars + 17;       // [2 pages] QK8: the page's key factors are set out (converters -> ReLU² warps)
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
 
@@ -143,6 +157,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             mbar_init(&p_ready[i], 4);
         }
         mbar_init(o_done, 1);
+        mbar_init(&kf_ready[0], PF_CONV_WARPS);
+        mbar_init(&kf_ready[1], PF_CONV_WARPS);
         s_abort = 0;
         fence_barrier_init();
     }
@@ -151,7 +167,51 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     // ---- Q tiles: [128 tokens][128 dims] of head h as fp16 in the K-major swizzled layout
     for (int x = 0; x < 2; x++) {
         uint8_t* Qx = Qs + x * PF_TILE16;
-        if (p.prenormed) {
+        if (QK8) {
+            // one warp a row, four rows a trip with their loads in flight together: head norm (unless the rows come normed),
+            // then the row as int8 codes, K-major [128 rows][128 B] under the 128-byte swizzle, and its scale
+            for (int r4 = warp * 4; r4 < BLK; r4 += 4 * (PF_THREADS / 32)) {
+                float xq[4][4];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const int r = r4 + k;
+                    const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + r) * p.q_token_stride + size_t(h) * HD;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) xq[k][i] = r < rows[x] ? Act<DT>::load(p.q, off + lane + 32 * i) : 0.0f;
+                }
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const int r = r4 + k;
+                    if (r < rows[x] && !p.prenormed) {
+                        float ss = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 4; i++) ss = __fadd_rn(ss, __fmul_rn(xq[k][i], xq[k][i]));
+                        float tot = 0.0f;
+                        for (int l = 0; l < 32; l++) tot = __fadd_rn(tot, __shfl_sync(0xffffffffu, ss, l));
+                        const float rr = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, float(HD)), EPS32)));
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int d = lane + 32 * i;
+                            float gn = __fmul_rn(rr, __fadd_rn(1.0f, Act<DT>::load(p.g1, d)));
+                            gn = __fmul_rn(gn, __fadd_rn(1.0f, Act<DT>::load(p.g2, d)));
+                            xq[k][i] = __fmul_rn(xq[k][i], gn);
+                        }
+                    }
+                    int code[4];
+                    float qscale;
+                    kv_row_quantise<DT>(xq[k], code, qscale);   // (rows past the chunk: zeros, scale 0)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int d = lane + 32 * i;
+                        Qx[r * 128 + (((d >> 4) ^ (r & 7)) << 4) + (d & 15)] = uint8_t(int8_t(code[i]));
+                    }
+                    if (lane == 0) {
+                        const float rho = qscale * PF_QSCALE / PF_QK8_C0;
+                        qsc[x * BLK + r] = 1.0f / (rho * rho);   // (a zero row: infinity, and its output 0 / infinity = 0)
+                    }
+                }
+            }
+        } else if (p.prenormed) {
             for (int i = tid; i < BLK * 16; i += PF_THREADS) {
                 const int r = i >> 4, c8 = i & 15;
                 uint4 v = make_uint4(0, 0, 0, 0);
@@ -251,10 +311,18 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             // i = page index inside this CTA's range (buffers and barrier phases count from 0), jb + i = the page
             auto issue_s = [&](int x, int i) {
                 const uint32_t ka = smem_u32(kvb + ((2 * i) % 3) * PF_TILE16);
+                if (QK8) {
+                    // int8 operands: one [128 rows][128 B] tile holds all 128 dims, 32 of them (32 bytes) an instruction
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) {
-                    const uint32_t koff = (ks >> 2) * (BLK * 128) + (ks & 3) * 32;
-                    umma_ss(tmem + 128 * x, umma_desc(qa + x * PF_TILE16 + koff, 16, 1024), umma_desc(ka + koff, 16, 1024), PF_IDESC_QK, ks > 0);
+                    for (int ks = 0; ks < 4; ks++)
+                        umma_ss_i8(tmem + 128 * x, umma_desc(qa + x * PF_TILE16 + ks * 32, 16, 1024), umma_desc(ka + ks * 32, 16, 1024),
+                                   PF_IDESC_QK8, ks > 0);
+                } else {
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++) {
+                        const uint32_t koff = (ks >> 2) * (BLK * 128) + (ks & 3) * 32;
+                        umma_ss(tmem + 128 * x, umma_desc(qa + x * PF_TILE16 + koff, 16, 1024), umma_desc(ka + koff, 16, 1024), PF_IDESC_QK, ks > 0);
+                    }
                 }
                 tc_commit(&s_full[x]);
             };
@@ -307,11 +375,27 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             ok = mbar_wait_bounded(p.ctl.wait_cycles, &raw_full[slot], (c / 3) & 1);
             if (ok && c >= 3) ok = mbar_wait_bounded(p.ctl.wait_cycles, &kv_free[slot], ((c / 3) - 1) & 1);
             if (!ok) break;
-            convert_side<SB>(raw + slot * CODE_BYTES, kvb + slot * PF_TILE16, ctid, scl + ((c >> 1) & 1) * 1024 + side * BLK * SB,
-                             side == 0 ? rsqrtf(float(HD)) : 1.0f);
+            if (QK8 && side == 0) {
+                // the K side goes to the tensor cores as it is: the codes, already K-major under the 128-byte swizzle, are
+                // copied into the operand buffer (so that buffers and barriers turn over as in the other variant), and the
+                // keys' factors kscale / sqrt(D) are set out for the ReLU² warps
+                const uint4* src = reinterpret_cast<const uint4*>(raw + slot * CODE_BYTES);
+                uint4* dst = reinterpret_cast<uint4*>(kvb + slot * PF_TILE16);
+#pragma unroll
+                for (int it = 0; it < CODE_BYTES / 16 / (PF_CONV_WARPS * 32); it++) dst[it * (PF_CONV_WARPS * 32) + ctid] = src[it * (PF_CONV_WARPS * 32) + ctid];
+                const uint8_t* ksc = scl + ((c >> 1) & 1) * 1024;
+                if (ctid < BLK)
+                    kfac[((c >> 1) & 1) * BLK + ctid] =
+                        (SB == 4 ? reinterpret_cast<const float*>(ksc)[ctid] : __half2float(reinterpret_cast<const __half*>(ksc)[ctid])) *
+                        (rsqrtf(float(HD)) * PF_QK8_C0);
+            } else {
+                convert_side<SB>(raw + slot * CODE_BYTES, kvb + slot * PF_TILE16, ctid, scl + ((c >> 1) & 1) * 1024 + side * BLK * SB,
+                                 side == 0 ? rsqrtf(float(HD)) : 1.0f);
+            }
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
+                if (QK8 && side == 0) mbar_arrive(&kf_ready[(c >> 1) & 1]);
                 mbar_arrive(&kv_ready[slot]);
                 mbar_arrive(&raw_empty[slot]);
             }
@@ -331,17 +415,32 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         bool ok = true;
         for (int i = 0; i < nx; i++) {
             const int j = jb + i;
-            ok = __all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &s_full[x], i & 1));
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &s_full[x], i & 1) &&
+                                             (!QK8 || mbar_wait_bounded(p.ctl.wait_cycles, &kf_ready[i & 1], (i >> 1) & 1)));
             if (!ok) break;   // (warp-uniform: the TMEM loads below are warp-collective)
             tc_fence_after();
             const bool diag = j * BLK + BLK - 1 > p0 + t0[x];   // some (row, key) of this page is masked
             // chunk cc + 1 of the row is on its way from TMEM while chunk cc is squared and packed
             uint32_t sbuf[2][32];
             tmem_ld32(tS + lane_sel, sbuf[0]);
+            const float4* kf4 = reinterpret_cast<const float4*>(kfac + (i & 1) * BLK);
 #pragma unroll
             for (int cc = 0; cc < 4; cc++) {
                 uint32_t(&s)[32] = sbuf[cc & 1];
                 if (cc < 3) tmem_ld32_async(tS + 32 * (cc + 1) + lane_sel, sbuf[(cc + 1) & 1]);
+                if (QK8) {
+                    // int32 dots -> u = S x the key's factor (one broadcast load a 4 keys). |S| < 2^22, so S + 1.5 x 2^23 as
+                    // float bits is that float exactly: an integer add and a float subtract instead of a conversion (which
+                    // runs at a quarter of their rate).
+#pragma unroll
+                    for (int e4 = 0; e4 < 8; e4++) {
+                        const float4 kf = kf4[8 * cc + e4];
+                        s[4 * e4 + 0] = __float_as_uint((__uint_as_float(s[4 * e4 + 0] + 0x4B400000u) - 12582912.0f) * kf.x);
+                        s[4 * e4 + 1] = __float_as_uint((__uint_as_float(s[4 * e4 + 1] + 0x4B400000u) - 12582912.0f) * kf.y);
+                        s[4 * e4 + 2] = __float_as_uint((__uint_as_float(s[4 * e4 + 2] + 0x4B400000u) - 12582912.0f) * kf.z);
+                        s[4 * e4 + 3] = __float_as_uint((__uint_as_float(s[4 * e4 + 3] + 0x4B400000u) - 12582912.0f) * kf.w);
+                    }
+                }
                 uint32_t pk[16];
                 if (diag) {
 #pragma unroll
@@ -399,7 +498,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             pcol[size_t(HD) * BLK] = rowsum;
         } else if (nx > 0) {
             tc_fence_after();
-            const float inv = 1.0f / (sqrtf(float(HD)) * PF_PSCALE + rowsum);
+            const float inv = 1.0f / (sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + r] : 1.0f) + rowsum);
             uint16_t* orow = static_cast<uint16_t*>(p.o) + size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
 #pragma unroll 1
             for (int cc = 0; cc < 4; cc++) {
@@ -455,7 +554,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         if (c < HD) tile[(lane + 32 * i) * (HD + 1) + c] = acc[i];
-                        else den[lane + 32 * i] = sqrtf(float(HD)) * PF_PSCALE + acc[i];
+                        else den[lane + 32 * i] = sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + lane + 32 * i] : 1.0f) + acc[i];
                     }
                 }
                 __syncthreads();
@@ -497,9 +596,9 @@ extern "C" EmblaStatus embla_attn_reserve_prefill(EmblaAttn* ctx, void* stream) 
     return EMBLA_OK;
 }
 
-template <int DT, int SB>
+template <int DT, int SB, bool QK8>
 static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, PrefillParams& p, int batch, int max_pages, cudaStream_t s) {
-    auto kern = full_prefill_kernel<DT, SB>;
+    auto kern = full_prefill_kernel<DT, SB, QK8>;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
         EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PF_SMEM)));
@@ -540,10 +639,10 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     return EMBLA_OK;
 }
 
-extern "C" EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
-                                               const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
-                                               int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
-                                               int64_t o_seq_stride, void* stream) {
+static EmblaStatus full_prefill_impl(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                     const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
+                                     int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
+                                     int64_t o_seq_stride, bool qk8, void* stream) {
     if (!ctx || !pool || !view || !pos0_dev || !q || !q->q_dev || !o_dev)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_prefill: null argument");
     if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_prefill: the pool is not int8");
@@ -582,6 +681,22 @@ extern "C" EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16, s4 = pool->scale_bytes == 4;
     // pages a tile may see, from the caller's bound on pos0 + n_tokens (sizes the page split only)
     const int max_pages = ((view->max_seq_len > 0 ? view->max_seq_len : ctx->cfg.max_context) + BLK - 1) / BLK;
-    if (bf) return s4 ? launch_prefill<EMBLA_BF16, 4>(ctx, pool, p, view->batch, max_pages, s) : launch_prefill<EMBLA_BF16, 2>(ctx, pool, p, view->batch, max_pages, s);
-    return s4 ? launch_prefill<EMBLA_F16, 4>(ctx, pool, p, view->batch, max_pages, s) : launch_prefill<EMBLA_F16, 2>(ctx, pool, p, view->batch, max_pages, s);
+#define EMBLA_PF(DT, SB) (qk8 ? launch_prefill<DT, SB, true>(ctx, pool, p, view->batch, max_pages, s) : launch_prefill<DT, SB, false>(ctx, pool, p, view->batch, max_pages, s))
+    if (bf) return s4 ? EMBLA_PF(EMBLA_BF16, 4) : EMBLA_PF(EMBLA_BF16, 2);
+    return s4 ? EMBLA_PF(EMBLA_F16, 4) : EMBLA_PF(EMBLA_F16, 2);
+#undef EMBLA_PF
+}
+
+extern "C" EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                               const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
+                                               int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
+                                               int64_t o_seq_stride, void* stream) {
+    return full_prefill_impl(ctx, pool, view, pos0_dev, n_tokens, q, q_token_stride, o_dev, o_token_stride, o_seq_stride, false, stream);
+}
+
+extern "C" EmblaStatus embla_attn_full_prefill_qk8(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                                   const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
+                                                   int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
+                                                   int64_t o_seq_stride, void* stream) {
+    return full_prefill_impl(ctx, pool, view, pos0_dev, n_tokens, q, q_token_stride, o_dev, o_token_stride, o_seq_stride, true, stream);
 }

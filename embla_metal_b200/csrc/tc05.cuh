@@ -29,6 +29,14 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
         "r"(accumulate)
         : "memory");
 }
+// D[tmem] (+)= A[smem] * B[smem], int8 operands, int32 accumulators
+__device__ __forceinline__ void umma_ss_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc),
+        "r"(accumulate)
+        : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -83,5 +91,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo, 
 // kind::f16, A and B fp16, D fp32, M = 128, N = 128; B K-major (Q Kᵀ) or MN-major (P V)
 constexpr uint32_t PF_IDESC_QK = (1u << 4) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t PF_IDESC_PV = PF_IDESC_QK | (1u << 16);
+// kind::i8, A and B signed 8-bit (format 1) K-major, D int32 (format 2), M = 128, N = 128
+constexpr uint32_t PF_IDESC_QK8 = (2u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 
 }  // namespace embla

@@ -299,6 +299,16 @@ EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, con
                                     const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
                                     int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
                                     int64_t o_seq_stride, void* stream);
+/* The reference's int8 Q Kᵀ build of the same kernel (QK8: attn_nax.metal:14-22, 62, 124-204, with q_prep_b's QK8
+ * branch, prefill.metal:421-422; switched on by EMBLA_ATT8, Prefill.swift:142-144; measurement-only there): every
+ * query row is quantised like a cache row (rounded to the activation dtype, codes rint(x 127 / max|x|), scale
+ * max|x| / 127), Q Kᵀ runs in int8 on the cache's codes as they are (tcgen05.mma kind::i8, int32 accumulators: the dots
+ * are exact), and a score is dot x query scale x key scale / sqrt(128). P V as in embla_attn_full_prefill. Same
+ * operands; the result differs from embla_attn_full_prefill's by the quantisation of the queries. */
+EmblaStatus embla_attn_full_prefill_qk8(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                        const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
+                                        int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
+                                        int64_t o_seq_stride, void* stream);
 /* Part of Engine.init's scratch set-up (`apart`, Engine.swift:242-258) that only prefill needs: about 39 MB of
  * partial sums, with which embla_attn_full_prefill cuts the pages of a (256 tokens, head) unit over several CTAs
  * when a chunk has fewer units than the GPU has SMs (short chunks, head-sharded prefill). Allocates once per

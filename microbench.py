@@ -75,7 +75,7 @@ def sparse(batch):
     st.ctx.check()
 
 
-def prefill(tokens, cached):
+def prefill(tokens, cached, qk8=False):
     S = cached + tokens
     npg = (S + 127) // 128
     ctx = attn.Attention(HQ, HKV, attn.BF16, 1, npg * 128)
@@ -87,11 +87,11 @@ def prefill(tokens, cached):
     q = torch.randn(1, tokens, HQ * 128, device="cuda", dtype=torch.bfloat16)
     o = torch.zeros_like(q)
     pos0 = torch.tensor([cached], dtype=torch.int32, device="cuda")
-    ts = _events(lambda: attn.full_prefill(ctx, pool, tbl, 0, pos0, q, o))
+    ts = _events(lambda: attn.full_prefill(ctx, pool, tbl, 0, pos0, q, o, qk8=qk8))
     ctx.check()
     flop = 4 * HQ * 128 * sum(cached + i + 1 for i in range(tokens))
     med = ts[len(ts) // 2]
-    print(f"full_prefill {tokens} tokens after {cached}: {med:.4f} ms, {flop / med / 1e9:.0f} TFLOP/s "
+    print(f"full_prefill{' (int8 Q K^T)' if qk8 else ''} {tokens} tokens after {cached}: {med:.4f} ms, {flop / med / 1e9:.0f} TFLOP/s "
           f"(min-time {flop / ts[0] / 1e9:.0f}), {tokens / med * 1e3:.0f} tok/s")
 
 
@@ -121,6 +121,7 @@ def main():
     ap.add_argument("--raw", action="store_true", help="sliding_prefill: queries arrive raw (fused head norm + RoPE)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--scores", action="store_true")
+    ap.add_argument("--qk8", action="store_true", help="prefill: the int8 Q K^T build")
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--cached", type=int, default=30720)
     a = ap.parse_args()
@@ -131,7 +132,7 @@ def main():
     elif a.case == "sliding_prefill":
         sliding_prefill(a.tokens, a.cached if a.cached != 30720 else 2048, a.window, a.raw)
     else:
-        prefill(a.tokens, a.cached)
+        prefill(a.tokens, a.cached, a.qk8)
 
 
 if __name__ == "__main__":

@@ -367,10 +367,11 @@ void orc_sliding_attend(const uint16_t* q, int ld_tok, int T, int dtype, int pre
 // sees keys c <= p0 + r; out[r][h·128 + d] token-major. Rows r0, r0 + rstep, ... are computed
 // (the others are left untouched), so a full-size chunk can be checked on a subset. `o_f32` (optional) receives
 // the unrounded fp32 results.
-void orc_full_prefill(const uint16_t* q, int ld_tok, int Tq, int dtype, int prenormed,
-                      const uint16_t* g1, const uint16_t* g2,
-                      int kv_kind, const void* kc, const float* ks, const void* vc, const float* vs,
-                      int Hq, int Hkv, int p0, int ldS, uint16_t* o, int r0, int rstep, int nthreads, float* o_f32) {
+static void full_prefill_impl(const uint16_t* q, int ld_tok, int Tq, int dtype, int prenormed,
+                              const uint16_t* g1, const uint16_t* g2,
+                              int kv_kind, const void* kc, const float* ks, const void* vc, const float* vs,
+                              int Hq, int Hkv, int p0, int ldS, uint16_t* o, int r0, int rstep, int nthreads, float* o_f32,
+                              bool qk8) {
     const int G = Hq / Hkv;
     const float scale = 1.0f / std::sqrt(float(HD));
     std::vector<int> rows;
@@ -378,14 +379,38 @@ void orc_full_prefill(const uint16_t* q, int ld_tok, int Tq, int dtype, int pren
     parallel_for(int(rows.size()) * Hq, nthreads, [&](int item) {
         const int r = rows[item / Hq], h = item % Hq, kvh = h / G, S = p0 + r + 1;
         float qn[HD], kr[HD], vr[HD], acc[HD];
-        prep_q(q + size_t(r) * ld_tok + size_t(h) * HD, dtype, prenormed, g1, g2, 2, -1, qn);
+        int8_t q8[HD];
+        float qscale = 0.0f;
+        if (qk8) {
+            // q_prep_b's QK8 branch (prefill.metal:421-422): the head-normed row (not yet rounded) through write_row8
+            // (common.metal:74-84): rounded to the activation dtype, a = max |x|, codes rint(x 127 / a), scale a / 127
+            const uint16_t* qr = q + size_t(r) * ld_tok + size_t(h) * HD;
+            for (int d = 0; d < HD; d++) qn[d] = load_act(qr[d], dtype);
+            if (!prenormed) head_norm(qn, g1, g2, 2, dtype);
+            float a = 0.0f;
+            for (int d = 0; d < HD; d++) { qn[d] = round_act(qn[d], dtype); a = std::max(a, std::fabs(qn[d])); }
+            const float inv = a > 0.0f ? 127.0f / a : 0.0f;
+            for (int d = 0; d < HD; d++) q8[d] = int8_t(int(std::rint(qn[d] * inv)));
+            qscale = a / 127.0f;
+        } else {
+            prep_q(q + size_t(r) * ld_tok + size_t(h) * HD, dtype, prenormed, g1, g2, 2, -1, qn);
+        }
         for (int d = 0; d < HD; d++) acc[d] = 0.0f;
         float psum = 0.0f;
         for (int j = 0; j < S; j++) {
             const size_t row = size_t(kvh) * ldS + j;
-            load_row(kc, kv_kind, dtype, row, kr);
-            float t = canon_dot(qn, kr);
-            if (kv_kind == 0) t *= ks[row];
+            float t;
+            if (qk8) {
+                // int8 x int8 -> int32 (attn_nax.metal:188-204), then x the row's query scale, x the key's scale
+                const int8_t* k8 = static_cast<const int8_t*>(kc) + row * HD;
+                int si = 0;
+                for (int d = 0; d < HD; d++) si += int(q8[d]) * int(k8[d]);
+                t = float(si) * qscale * ks[row];
+            } else {
+                load_row(kc, kv_kind, dtype, row, kr);
+                t = canon_dot(qn, kr);
+                if (kv_kind == 0) t *= ks[row];
+            }
             const float a = std::max(t * scale, 0.0f), w = a * a;
             if (w != 0.0f) {
                 psum += w;
@@ -400,6 +425,23 @@ void orc_full_prefill(const uint16_t* q, int ld_tok, int Tq, int dtype, int pren
         // the same quotient before it is rounded to the storage dtype, for tolerance checks on 16-bit outputs
         if (o_f32) for (int d = 0; d < HD; d++) o_f32[(size_t(r) * Hq + h) * HD + d] = acc[d] / den;
     });
+}
+
+void orc_full_prefill(const uint16_t* q, int ld_tok, int Tq, int dtype, int prenormed,
+                      const uint16_t* g1, const uint16_t* g2,
+                      int kv_kind, const void* kc, const float* ks, const void* vc, const float* vs,
+                      int Hq, int Hkv, int p0, int ldS, uint16_t* o, int r0, int rstep, int nthreads, float* o_f32) {
+    full_prefill_impl(q, ld_tok, Tq, dtype, prenormed, g1, g2, kv_kind, kc, ks, vc, vs, Hq, Hkv, p0, ldS, o, r0, rstep, nthreads, o_f32,
+                      false);
+}
+
+// The reference's measurement-only QK8 build of the same kernel (attn_nax.metal:14-22, 62, 124-204; EMBLA_ATT8,
+// Prefill.swift:142-144): Q Kᵀ in int8 with the query rows quantised by q_prep_b; int8 cache only.
+void orc_full_prefill_qk8(const uint16_t* q, int ld_tok, int Tq, int dtype, int prenormed,
+                          const uint16_t* g1, const uint16_t* g2,
+                          const void* kc, const float* ks, const void* vc, const float* vs,
+                          int Hq, int Hkv, int p0, int ldS, uint16_t* o, int r0, int rstep, int nthreads, float* o_f32) {
+    full_prefill_impl(q, ld_tok, Tq, dtype, prenormed, g1, g2, 0, kc, ks, vc, vs, Hq, Hkv, p0, ldS, o, r0, rstep, nthreads, o_f32, true);
 }
 
 // ---- batched drivers for the timed CPU baseline ------------------------------------------------

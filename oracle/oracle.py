@@ -158,9 +158,10 @@ def sliding_attend(q_bits, dtype, ring_k, ring_v, p0, W, qgain=None, nthreads=1)
     return o
 
 
-def full_prefill(q_bits, dtype, k, ks, v, vs, p0, kv_kind=0, gains=None, r0=0, rstep=1, nthreads=1, want_f32=False):
+def full_prefill(q_bits, dtype, k, ks, v, vs, p0, kv_kind=0, gains=None, r0=0, rstep=1, nthreads=1, want_f32=False, qk8=False):
     """q [Tq, Hq, 128]; caches [Hkv, ldS, 128] holding p0 + Tq keys. Returns o [Tq, Hq, 128]
-    (rows outside r0::rstep are zero); with want_f32 also the unrounded fp32 results."""
+    (rows outside r0::rstep are zero); with want_f32 also the unrounded fp32 results. qk8: the reference's int8 Q Kᵀ
+    build (query rows quantised like cache rows, integer dots; int8 cache only)."""
     q = _c(q_bits, np.uint16)
     Tq, Hq = q.shape[0], q.shape[1]
     Hkv, ldS = k.shape[0], k.shape[1]
@@ -170,8 +171,13 @@ def full_prefill(q_bits, dtype, k, ks, v, vs, p0, kv_kind=0, gains=None, r0=0, r
         g1, g2 = _c(gains[0], np.uint16), _c(gains[1], np.uint16)
     o = np.zeros((Tq, Hq, HD), np.uint16)
     o32 = np.zeros((Tq, Hq, HD), np.float32) if want_f32 else None
-    lib().orc_full_prefill(_p(q), Hq * HD, Tq, dtype, int(gains is None), _p(g1), _p(g2), kv_kind, _p(k), _p(ks), _p(v),
-                           _p(vs), Hq, Hkv, p0, ldS, _p(o), r0, rstep, nthreads, _p(o32))
+    if qk8:
+        assert kv_kind == 0
+        lib().orc_full_prefill_qk8(_p(q), Hq * HD, Tq, dtype, int(gains is None), _p(g1), _p(g2), _p(k), _p(ks), _p(v),
+                                   _p(vs), Hq, Hkv, p0, ldS, _p(o), r0, rstep, nthreads, _p(o32))
+    else:
+        lib().orc_full_prefill(_p(q), Hq * HD, Tq, dtype, int(gains is None), _p(g1), _p(g2), kv_kind, _p(k), _p(ks), _p(v),
+                               _p(vs), Hq, Hkv, p0, ldS, _p(o), r0, rstep, nthreads, _p(o32))
     return (o, o32) if want_f32 else o
 
 

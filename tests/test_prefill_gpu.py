@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "attention_golden.npz")
 
 
-def _prefill(q_bits, k, ks, v, vs, p0, dtype, scale_f16, gains=None, rows=None, nthreads=8):
+def _prefill(q_bits, k, ks, v, vs, p0, dtype, scale_f16, gains=None, rows=None, nthreads=8, qk8=False):
     """Runs the CUDA kernel on dense caches [Hkv, p0 + T, 128]; returns (got, want) on `rows`: the kernel's stored
     outputs and the oracle's fp32 accumulation (before rounding to the storage dtype)."""
     import torch
@@ -29,30 +29,41 @@ def _prefill(q_bits, k, ks, v, vs, p0, dtype, scale_f16, gains=None, rows=None, 
     qt = util.act_tensor(q_bits.reshape(1, T, Hq * 128), dtype)
     ot = torch.zeros_like(qt)
     gt = None if gains is None else tuple(util.act_tensor(x, dtype) for x in gains)
-    attn.full_prefill(ctx, pool, tbl, 1, torch.tensor([p0], dtype=torch.int32, device="cuda"), qt, ot, gains=gt)
+    attn.full_prefill(ctx, pool, tbl, 1, torch.tensor([p0], dtype=torch.int32, device="cuda"), qt, ot, gains=gt, qk8=qk8)
     ctx.check()
     got = orc.from_bits(util.act_bits(ot), dtype).reshape(T, Hq, 128)
     ot2 = torch.zeros_like(qt)
-    attn.full_prefill(ctx, pool, tbl, 1, torch.tensor([p0], dtype=torch.int32, device="cuda"), qt, ot2, gains=gt)
+    attn.full_prefill(ctx, pool, tbl, 1, torch.tensor([p0], dtype=torch.int32, device="cuda"), qt, ot2, gains=gt, qk8=qk8)
     torch.cuda.synchronize()
     assert torch.equal(ot.view(torch.int16), ot2.view(torch.int16)), "two runs differ"
     r0, rstep = (0, 1) if rows is None else rows
-    _, want = orc.full_prefill(q_bits, dtype, k, ks, v, vs, p0, gains=gains, r0=r0, rstep=rstep, nthreads=nthreads, want_f32=True)
+    _, want = orc.full_prefill(q_bits, dtype, k, ks, v, vs, p0, gains=gains, r0=r0, rstep=rstep, nthreads=nthreads, want_f32=True,
+                               qk8=qk8)
     pool.close()
     ctx.close()
     return got[r0::rstep], want[r0::rstep]
 
 
-def _case(T, p0, Hq, Hkv, dtype, scale_f16, seed, gains=False, rows=None):
+def _case(T, p0, Hq, Hkv, dtype, scale_f16, seed, gains=False, rows=None, qk8=False):
     rng = np.random.default_rng(seed)
     q = orc.to_bits(rng.standard_normal((T, Hq, 128)), dtype)
     k, ks, v, vs = util.int8_cache(rng, Hkv, p0 + T, scale_f16)
     g = None
     if gains:
         g = (orc.to_bits(rng.standard_normal(128) * 0.1, dtype), orc.to_bits(rng.standard_normal(128) * 0.1, dtype))
-    got, want = _prefill(q, k, ks, v, vs, p0, dtype, scale_f16, gains=g, rows=rows)
+    got, want = _prefill(q, k, ks, v, vs, p0, dtype, scale_f16, gains=g, rows=rows, qk8=qk8)
     ok, msg = util.close_stored(got, want, util.BF16_STEP if dtype == orc.BF16 else 2.0 ** -10)
     assert ok, f"T={T} p0={p0}: {msg}"
+    if qk8:
+        # how far the int8 queries move the result from the fp32-accumulated attention of the unquantised queries
+        # (the reference keeps this build for measurement only): reported, and bounded loosely
+        r0, rstep = (0, 1) if rows is None else rows
+        _, exact = orc.full_prefill(q, dtype, k, ks, v, vs, p0, gains=g, r0=r0, rstep=rstep, nthreads=8, want_f32=True)
+        exact = exact[r0::rstep]
+        err = np.abs(got - exact)
+        rms = float(np.sqrt((err ** 2).mean() / (exact ** 2).mean()))
+        print(f"QK8 T={T} p0={p0}: against unquantised queries max-abs {err.max():.3e}, rel-rms {rms:.3e}")
+        assert rms < 3e-2
 
 
 @pytest.mark.parametrize("T,p0", [(128, 0), (1, 0), (5, 123), (128, 128), (129, 127), (300, 1000), (257, 2047)])
@@ -72,6 +83,22 @@ def test_prefill_reference_shape_gains_fp32_scales():
 
 def test_prefill_fp16_activations():
     _case(140, 77, 16, 4, orc.F16, True, seed=5)
+
+
+@pytest.mark.parametrize("T,p0", [(128, 0), (5, 123), (300, 1000), (257, 2047)])
+def test_prefill_qk8_shapes(T, p0):
+    """The int8 Q Kᵀ build against the restatement of the reference's QK8 arithmetic (integer dots are exact on both sides)."""
+    _case(T, p0, 16, 4, orc.BF16, True, seed=T * 11 + p0, qk8=True)
+
+
+def test_prefill_qk8_reference_shape_and_fp16():
+    _case(200, 333, 16, 2, orc.BF16, False, seed=4, gains=True, qk8=True)
+    _case(140, 77, 16, 4, orc.F16, True, seed=6, qk8=True)
+    _case(200, 12000, 16, 4, orc.BF16, True, seed=23, rows=(3, 5), qk8=True)      # pages split over CTAs
+
+
+def test_prefill_qk8_config3_size():
+    _case(2048, 30720, 16, 4, orc.BF16, True, seed=3, rows=(5, 37), qk8=True)
 
 
 def test_prefill_golden():

@@ -204,9 +204,11 @@ def test_dependent_launch_overlap_changes_nothing():
         "st.ctx.check()\n"
         "print(hashlib.sha256(st.o.view(torch.int16).cpu().numpy().tobytes()).hexdigest())\n" % root)
     digests = []
-    for no_pdl in ("0", "1"):
-        env = dict(os.environ, EMBLA_NO_PDL=no_pdl)
+    # with dependent-launch overlap and cache rows requested ahead of the wait (the default); with the overlap but every
+    # request after the wait; with neither
+    for no_pdl, no_early in (("0", "0"), ("0", "1"), ("1", "0")):
+        env = dict(os.environ, EMBLA_NO_PDL=no_pdl, EMBLA_NO_EARLY=no_early)
         out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
         assert out.returncode == 0, out.stderr[-800:]
         digests.append(out.stdout.strip().splitlines()[-1])
-    assert digests[0] == digests[1] and len(digests[0]) == 64
+    assert digests[0] == digests[1] == digests[2] and len(digests[0]) == 64

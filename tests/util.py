@@ -92,3 +92,38 @@ def act_bits(t):
     """torch 16-bit tensor -> uint16 numpy storage."""
     import torch
     return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def stack_oracle_rows(st, li, b, pos_b):
+    """What the CPU oracle gives for layer `li`, sequence `b` of a DecodeStack after a step at position `pos_b`, fed the
+    very pages and rings the step left behind and the step's query row (fp16 stacks, queries prenormed). Returns
+    [Hq, 128] floats; for a sparse layer past 1152 keys the oracle scores and selects the keys itself."""
+    import torch
+    from embla_metal_b200 import stack as stk
+    Hq, Hkv, S = st.Hq, st.Hkv, pos_b + 1
+    kind = st.kinds[li]
+    q = st.qkv[li, b, :Hq * 128].view(torch.int16).cpu().numpy().view(np.uint16).reshape(Hq, 128)
+    slot = sum(1 for k in st.kinds[:li] if k == kind)
+    n = (S + 127) // 128
+    if kind == stk.FULL:
+        pages = st.full_pool.raw()[st.table[b, :n].long(), slot].cpu().numpy()        # [n, Hkv, page_bytes]
+        k = pages[:, :, :16384].reshape(n, Hkv, 128, 128).transpose(1, 0, 2, 3).reshape(Hkv, n * 128, 128).view(np.int8)
+        v = pages[:, :, 16384:32768].reshape(n, Hkv, 128, 128).transpose(1, 0, 2, 3).reshape(Hkv, n * 128, 128).view(np.int8)
+        sc = np.ascontiguousarray(pages[:, :, 32768:]).view(np.float16).reshape(n, Hkv, 2, 128).astype(np.float32)
+        ks = sc[:, :, 0].transpose(1, 0, 2).reshape(Hkv, n * 128)
+        vs = sc[:, :, 1].transpose(1, 0, 2).reshape(Hkv, n * 128)
+        c = np.ascontiguousarray
+        return orc.from_bits(orc.full_decode(q, orc.F16, c(k[:, :S]), c(ks[:, :S]), c(v[:, :S]), c(vs[:, :S]), S)[0], orc.F16)
+    if kind == stk.SPARSE:
+        pages = st.sparse_pool.raw()[st.table[b, :n].long(), slot].cpu().numpy().view(np.uint16)   # [n, Hkv, 2 * 128 * 128]
+        k = np.ascontiguousarray(pages[:, :, :16384].reshape(n, Hkv, 128, 128).transpose(1, 0, 2, 3).reshape(Hkv, n * 128, 128)[:, :S])
+        v = np.ascontiguousarray(pages[:, :, 16384:].reshape(n, Hkv, 128, 128).transpose(1, 0, 2, 3).reshape(Hkv, n * 128, 128)[:, :S])
+        idx = orc.select_keys(orc.score_keys(q, orc.F16, k, S, nthreads=4), S) if S > 1152 else None
+        return orc.from_bits(orc.sparse_decode(q, orc.F16, k, None, v, None, S, idx=idx, kv_kind=1), orc.F16)
+    if kind == stk.SLIDING:
+        ring = st.rings[slot]
+        rk = ring.k[b].view(torch.int16).cpu().numpy().view(np.uint16)
+        rv = ring.v[b].view(torch.int16).cpu().numpy().view(np.uint16)
+        window = ring.desc.window
+        return orc.from_bits(orc.sliding_attend(q[None], orc.F16, rk, rv, pos_b, window), orc.F16)[0]
+    raise ValueError(f"layer kind {kind}")
