@@ -347,8 +347,10 @@ PREFILL_FLOP = 4 * HQ * 128 * sum(PREFILL_CACHED + i + 1 for i in range(PREFILL_
 def prefill_leg(rank, world, barrier, reps=10):
     """The 2048-token causal chunk appended to 30720 cached positions of the int8 cache, bf16 q, on the same GPUs, through
     embla_metal_b200.shard.HeadShardedPrefill: one GPU computes all heads; 2 or 4 GPUs shard by kv head, 8 GPUs by
-    (kv head, half of the chunk); the per-head outputs are combined with an NCCL all-gather and placed token-major
-    inside the timed region. The attention kernel and the combine are also timed on their own."""
+    (kv head, half of the chunk). Two ways to the token-major output on every GPU, both timed with the combine inside
+    the timed region: the kernel's epilogue stores its rows into every GPU's output over NVLink and one barrier follows
+    (fused), or an NCCL all-gather of the per-head outputs and a strided placement. The line's `ms` is the faster one that
+    gave the all-gather path's bits; the attention kernel and the all-gather combine are also timed on their own."""
     import torch
     import torch.distributed as dist
     from embla_metal_b200 import attn, shard
@@ -383,10 +385,29 @@ def prefill_leg(rank, world, barrier, reps=10):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    ms = timed_ms(lambda: hsp.run(pool, tbl, 0, p0, q))
+    gather_ms = timed_ms(lambda: hsp.run(pool, tbl, 0, p0, q))
     hsp.ctx.check()
     kernel_ms = timed_ms(lambda: hsp.attend(pool, tbl, 0, p0, q))
     combine_ms = timed_ms(hsp.combine) if world > 1 else 0.0
+    ms, mode, fused_ms, fused_same = gather_ms, "allgather", None, None
+    if world > 1:
+        # the same chunk with the all-gather inside the kernel: its epilogue stores the rows into every GPU's output over
+        # NVLink (symmetric memory), then one barrier across the GPUs; checked against the all-gather path's output
+        try:
+            fz = shard.HeadShardedPrefill(HQ, HKV, attn.BF16, PREFILL_T, PREFILL_CACHED + PREFILL_T, world, rank, fused=True)
+            fused_ms = timed_ms(lambda: fz.run(pool, tbl, 0, p0, q))
+            fz.ctx.check()
+            hsp.run(pool, tbl, 0, p0, q)
+            fz.run(pool, tbl, 0, p0, q)
+            barrier()
+            same = torch.tensor([int(torch.equal(fz.o_full.view(torch.int16), hsp.o_full.view(torch.int16)))], device="cuda")
+            dist.all_reduce(same, op=dist.ReduceOp.MIN)
+            fused_same = bool(same.item())
+            fz.close()
+            if fused_same and fused_ms < ms:
+                ms, mode = fused_ms, "fused"
+        except Exception as e:   # symmetric memory is not available everywhere: the all-gather path stands
+            fused_ms, fused_same = None, f"unavailable: {type(e).__name__}: {e}"[:200]
     pool.close()
     hsp.close()
     peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
@@ -395,6 +416,7 @@ def prefill_leg(rank, world, barrier, reps=10):
     sliding = sliding_prefill_case(rank, reps) if world == 1 else None
     return {"sliding_config_1b": sliding, "metric": "prefill attn tok/s", "workload": "config 3: 2048-token causal chunk after 30720 cached positions, int8 KV, bf16 q",
             "value": PREFILL_T / (ms * 1e-3), "unit": "tok/s", "ms": ms, "tflops": tflops, "n_gpus": world,
+            "mode": mode, "allgather_path_ms": gather_ms, "fused_path_ms": fused_ms, "fused_equals_allgather": fused_same,
             "kernel_ms": kernel_ms, "allgather_and_placement_ms": combine_ms,
             "sharding": ("none" if world == 1 else f"{sh.kv_shards} kv-head shards x {sh.tok_shards} chunk halves, NCCL all-gather of per-head outputs, token-major placement"),
             "allgather_bytes": 0 if world == 1 else PREFILL_T * HQ * 128 * 2,

@@ -266,6 +266,24 @@ def full_prefill(ctx, pool, block_table, layer, pos0, q, o, gains=None, qk8=Fals
               C.c_int64(q.stride(1)), _ptr(o), C.c_int64(o.stride(1)), C.c_int64(o.stride(0)), _stream()))
 
 
+def full_prefill_scatter(ctx, pool, block_table, layer, pos0, q, o, peer_ptrs, o_token_stride, gains=None):
+    """embla_attn_full_prefill that also stores its rows to `peer_ptrs` (device addresses in other GPUs' memory: where this
+    rank's slab starts inside each GPU's token-major output, rows `o_token_stride` elements apart). o [1, n_tokens, ...]
+    is this GPU's own place of the slab, a view with the same row stride."""
+    view = Attention.view(block_table, None, layer)
+    if gains is None:
+        qd = Query(q.data_ptr(), q.stride(0), 1, 0, None, None)
+    else:
+        qd = Query(q.data_ptr(), q.stride(0), 0, 2, gains[0].data_ptr(), gains[1].data_ptr())
+    if not getattr(ctx, "_prefill_reserved", False):
+        _check(lib().embla_attn_reserve_prefill(ctx.handle, _stream()))
+        ctx._prefill_reserved = True
+    arr = (C.c_void_p * max(1, len(peer_ptrs)))(*[C.c_void_p(p) for p in peer_ptrs])
+    _check(lib().embla_attn_full_prefill_scatter(ctx.handle, pool.handle, C.byref(view), _ptr(pos0), q.shape[1], C.byref(qd),
+                                                 C.c_int64(q.stride(1)), _ptr(o), arr, len(peer_ptrs), C.c_int64(o_token_stride),
+                                                 C.c_int64(o.stride(0)), _stream()))
+
+
 def sliding_prefill(ctx, ring, pos0, q, o, qgain=None):
     """Softmax attention of a prefill chunk over each token's window; q, o [batch, n_tokens, >= n_q_heads*128].
     The chunk's keys/values must already be in the ring (Attention.sliding_write)."""

@@ -50,7 +50,9 @@ def build(force=False, verbose=False):
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.run(["nvcc", "-arch=sm_100a", "-shared", "-o", LIB, *objs, "-cudart", "static"], check=True)
+    # linked beside the library and renamed over it, so that a reader never finds a half-written file
+    subprocess.run(["nvcc", "-arch=sm_100a", "-shared", "-o", LIB + ".part", *objs, "-cudart", "static"], check=True)
+    os.replace(LIB + ".part", LIB)
     return LIB
 
 

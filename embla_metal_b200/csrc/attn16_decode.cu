@@ -177,6 +177,7 @@ extern "C" EmblaStatus embla_attn_sparse_decode(EmblaAttn* ctx, const EmblaKVPoo
                                                 const EmblaQuery* q, const uint32_t* idx_dev, void* o_dev,
                                                 int64_t o_stride, void* stream) {
     if (!ctx || !pool || !view || !o_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sparse_decode: null argument");
+    EMBLA_CHECK_DEVICE("embla_attn_sparse_decode", ctx, pool);
     if (EmblaStatus st = check_query("embla_attn_sparse_decode", q)) return st;
     if (pool->kv_dtype != EMBLA_KV_16BIT)
         EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_sparse_decode: the pool is not 16-bit");
@@ -214,6 +215,7 @@ extern "C" EmblaStatus embla_sliding_write(EmblaAttn* ctx, const EmblaRing* ring
                                            int64_t seq_stride, int32_t prenormed, const void* kgain_dev, void* stream) {
     if (!ctx || !ring || !ring->k_dev || !ring->v_dev || !pos0_dev || !k_dev || !v_dev)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_sliding_write: null argument");
+    EMBLA_CHECK_DEVICE("embla_sliding_write", ctx, static_cast<const EmblaKVPool*>(nullptr));
     if (batch <= 0 || n_tokens <= 0 || ring->ring <= 0 || (!prenormed && !kgain_dev))
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_sliding_write: batch %d, n_tokens %d, ring %d", batch, n_tokens, ring->ring);
     SlidingWriteParams p;
@@ -267,6 +269,7 @@ static EmblaStatus sliding_decode_impl(EmblaAttn* ctx, const EmblaRing* ring, co
                                        void* stream) {
     if (!ctx || !ring || !ring->k_dev || !ring->v_dev || !seq_lens_dev || !o_dev)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sliding_decode: null argument");
+    EMBLA_CHECK_DEVICE("embla_attn_sliding_decode", ctx, static_cast<const EmblaKVPool*>(nullptr));
     if (EmblaStatus st = check_query("embla_attn_sliding_decode", q)) return st;
     // sliding layers norm q with ONE gain vector whatever ng says (attention.metal:47-48): it must be there
     if (!q->prenormed && !q->g1_dev)

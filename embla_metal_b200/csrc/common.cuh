@@ -63,6 +63,18 @@ void set_error(const char* fmt, ...);
         }                                                                                            \
     } while (0)
 
+// The context's scratch and a pool's pages live on one device: a call made with another device current would launch
+// there, with addresses that mean nothing on it.
+#define EMBLA_CHECK_DEVICE(fn, ctx_, pool_)                                                                      \
+    do {                                                                                                         \
+        int dev_ = -1;                                                                                           \
+        EMBLA_CUDA_TRY(cudaGetDevice(&dev_));                                                                    \
+        if (dev_ != (ctx_)->device)                                                                              \
+            EMBLA_FAIL(EMBLA_BAD_ARG, "%s: the context lives on device %d, the current device is %d", fn, (ctx_)->device, dev_); \
+        if ((pool_) != nullptr && (pool_)->device != dev_)                                                       \
+            EMBLA_FAIL(EMBLA_BAD_ARG, "%s: the pool lives on device %d, the current device is %d", fn, (pool_)->device, dev_);   \
+    } while (0)
+
 }  // namespace embla
 
 // ---- handles --------------------------------------------------------------------------------------

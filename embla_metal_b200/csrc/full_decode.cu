@@ -668,6 +668,7 @@ static EmblaStatus full_decode_impl(EmblaAttn* ctx, const EmblaKVPool* pool, con
                                     void* o_dev, int64_t o_stride, float* scores_dev, int64_t scores_stride, const void* k_new,
                                     const void* v_new, int64_t kv_stride, int32_t norm_k, void* stream) {
     if (!ctx || !pool || !view || !q || !o_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode: null argument");
+    EMBLA_CHECK_DEVICE("embla_attn_full_decode", ctx, pool);
     if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_decode: the pool is not int8");
     if (pool->n_kv_heads != ctx->cfg.n_kv_heads)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode: pool has %d kv heads, context %d", pool->n_kv_heads,

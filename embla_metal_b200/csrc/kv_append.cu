@@ -68,6 +68,7 @@ extern "C" EmblaStatus embla_kv_append(EmblaAttn* ctx, EmblaKVPool* pool, const 
                                        const void* k_dev, const void* v_dev, int64_t token_stride, int64_t seq_stride,
                                        int32_t norm_k, void* stream) {
     if (!ctx || !pool || !view || !pos0_dev || !k_dev || !v_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_append: null argument");
+    EMBLA_CHECK_DEVICE("embla_kv_append", ctx, pool);
     if (view->layer < 0 || view->layer >= pool->n_layers)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_kv_append: layer %d outside the pool's %d", view->layer, pool->n_layers);
     if (view->batch <= 0 || n_tokens <= 0 || !view->block_table_dev)

@@ -32,6 +32,7 @@ constexpr int PF_MMA = PF_PRODUCER + 1;
 constexpr int PF_THREADS = (PF_MMA + 1) * 32;
 constexpr int PF_TILE16 = BLK * HD * 2;            // 32 KiB: 128 rows x 128 dims fp16
 constexpr int PF_KVBUFS = 3;
+constexpr int PF_MAX_PEERS = 8;
 // The queries enter the tensor cores scaled by 2^-3 (exact), so the weights p = relu(s)^2, which the kernel keeps as
 // fp16 (P in TMEM, packed row sums), come out scaled by 2^-6: a score of 2047 still squares inside fp16's range (the
 // reference keeps P in fp32, attn_nax.metal:11), and fp16's gradual underflow keeps the small weights to 2^-24 of the
@@ -53,6 +54,10 @@ struct PrefillParams {
     const void* g1;
     const void* g2;
     void* o;
+    // scatter mode (head-sharded prefill on several GPUs): the output rows also go, with plain stores, to these addresses in
+    // other GPUs' memory (each where this rank's slab starts inside that GPU's token-major output, same strides)
+    void* o_peer[PF_MAX_PEERS];
+    int n_peers;
     KernelCtl ctl;
     float* partials;      // split-KV: [unit][split][tile][128 + 1 columns][128 rows] fp32 (unnormalised O, then the row sums)
     int* counters;        // [unit] arrivals
@@ -499,7 +504,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         } else if (nx > 0) {
             tc_fence_after();
             const float inv = 1.0f / (sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + r] : 1.0f) + rowsum);
-            uint16_t* orow = static_cast<uint16_t*>(p.o) + size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
+            const size_t ooff = size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
+            uint16_t* orow = static_cast<uint16_t*>(p.o) + ooff;
 #pragma unroll 1
             for (int cc = 0; cc < 4; cc++) {
                 uint32_t acc[32];
@@ -517,8 +523,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                     }
 #pragma unroll
                     for (int v4 = 0; v4 < 4; v4++)
-                        *reinterpret_cast<uint4*>(orow + 32 * cc + 8 * v4) =
-                            make_uint4(outw[4 * v4], outw[4 * v4 + 1], outw[4 * v4 + 2], outw[4 * v4 + 3]);
+                    {
+                        const uint4 val = make_uint4(outw[4 * v4], outw[4 * v4 + 1], outw[4 * v4 + 2], outw[4 * v4 + 3]);
+                        *reinterpret_cast<uint4*>(orow + 32 * cc + 8 * v4) = val;
+                        for (int pr = 0; pr < p.n_peers; pr++)   // the same 16 bytes into every peer's copy (NVLink stores)
+                            *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o_peer[pr]) + ooff + 32 * cc + 8 * v4) = val;
+                    }
                 }
             }
         }
@@ -562,7 +572,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                     const float inv = 1.0f / den[r];
                     const size_t off = size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
 #pragma unroll
-                    for (int i = 0; i < 4; i++) Act<DT>::store(p.o, off + lane + 32 * i, tile[r * (HD + 1) + lane + 32 * i] * inv);
+                    for (int i = 0; i < 4; i++) {
+                        const float val = tile[r * (HD + 1) + lane + 32 * i] * inv;
+                        Act<DT>::store(p.o, off + lane + 32 * i, val);
+                        for (int pr = 0; pr < p.n_peers; pr++) Act<DT>::store(p.o_peer[pr], off + lane + 32 * i, val);
+                    }
                 }
                 __syncthreads();
             }
@@ -642,9 +656,10 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
 static EmblaStatus full_prefill_impl(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
                                      const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
                                      int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
-                                     int64_t o_seq_stride, bool qk8, void* stream) {
+                                     int64_t o_seq_stride, bool qk8, void* stream, void* const* o_peers = nullptr, int n_peers = 0) {
     if (!ctx || !pool || !view || !pos0_dev || !q || !q->q_dev || !o_dev)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_prefill: null argument");
+    EMBLA_CHECK_DEVICE("embla_attn_full_prefill", ctx, pool);
     if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_prefill: the pool is not int8");
     if (pool->n_kv_heads != ctx->cfg.n_kv_heads || view->layer < 0 || view->layer >= pool->n_layers)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_prefill: pool/layer mismatch");
@@ -662,6 +677,8 @@ static EmblaStatus full_prefill_impl(EmblaAttn* ctx, const EmblaKVPool* pool, co
     p.g1 = q->g1_dev;
     p.g2 = q->g2_dev;
     p.o = o_dev;
+    p.n_peers = n_peers;
+    for (int i = 0; i < PF_MAX_PEERS; i++) p.o_peer[i] = i < n_peers ? o_peers[i] : nullptr;
     p.ctl = kernel_ctl(ctx);
     p.q_token_stride = q_token_stride;
     p.q_seq_stride = q->q_stride;
@@ -692,6 +709,19 @@ extern "C" EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool
                                                int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
                                                int64_t o_seq_stride, void* stream) {
     return full_prefill_impl(ctx, pool, view, pos0_dev, n_tokens, q, q_token_stride, o_dev, o_token_stride, o_seq_stride, false, stream);
+}
+
+extern "C" EmblaStatus embla_attn_full_prefill_scatter(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                                       const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
+                                                       int64_t q_token_stride, void* o_dev, void* const* o_peers_dev, int32_t n_peers,
+                                                       int64_t o_token_stride, int64_t o_seq_stride, void* stream) {
+    if (n_peers < 0 || n_peers > PF_MAX_PEERS || (n_peers > 0 && !o_peers_dev))
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_prefill_scatter: %d peers (0..%d)", n_peers, PF_MAX_PEERS);
+    for (int i = 0; i < n_peers; i++)
+        if (!o_peers_dev[i] || reinterpret_cast<uintptr_t>(o_peers_dev[i]) % 16)
+            EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_prefill_scatter: peer %d's address is null or not 16-byte aligned", i);
+    return full_prefill_impl(ctx, pool, view, pos0_dev, n_tokens, q, q_token_stride, o_dev, o_token_stride, o_seq_stride, false, stream,
+                             o_peers_dev, n_peers);
 }
 
 extern "C" EmblaStatus embla_attn_full_prefill_qk8(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,

@@ -269,6 +269,7 @@ static EmblaStatus score_keys_impl(EmblaAttn* ctx, const EmblaKVPool* pool, cons
                                    int64_t q_stride, float* scores_dev, int64_t scores_stride, const void* k_new,
                                    const void* v_new, int64_t kv_stride, int32_t norm_k, void* stream) {
     if (!ctx || !pool || !view || !q_dev || !scores_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_score_keys: null argument");
+    EMBLA_CHECK_DEVICE("embla_score_keys", ctx, pool);
     if (pool->kv_dtype != EMBLA_KV_16BIT) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_score_keys: the pool is not 16-bit");
     if (pool->n_kv_heads != ctx->cfg.n_kv_heads || view->layer < 0 || view->layer >= pool->n_layers)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_score_keys: pool/layer mismatch");

@@ -310,6 +310,7 @@ extern "C" EmblaStatus embla_select_keys(EmblaAttn* ctx, const float* scores_dev
                                          const int32_t* seq_lens_dev, int32_t batch, int32_t max_seq_len,
                                          uint32_t* idx_dev, void* stream) {
     if (!ctx || !scores_dev || !seq_lens_dev || !idx_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_select_keys: null argument");
+    EMBLA_CHECK_DEVICE("embla_select_keys", ctx, static_cast<const EmblaKVPool*>(nullptr));
     if (batch <= 0) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_select_keys: batch %d", batch);
     const int max_len = max_seq_len > 0 ? max_seq_len : ctx->cfg.max_context;
     if (scores_stride < max_len) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_select_keys: scores_stride %lld under max_seq_len %d",

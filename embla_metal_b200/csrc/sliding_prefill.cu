@@ -236,6 +236,7 @@ extern "C" EmblaStatus embla_attn_sliding_prefill(EmblaAttn* ctx, const EmblaRin
                                                   int64_t o_token_stride, int64_t o_seq_stride, void* stream) {
     if (!ctx || !ring || !ring->k_dev || !ring->v_dev || !pos0_dev || !q || !q->q_dev || !o_dev)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sliding_prefill: null argument");
+    EMBLA_CHECK_DEVICE("embla_attn_sliding_prefill", ctx, static_cast<const EmblaKVPool*>(nullptr));
     if (batch <= 0 || n_tokens <= 0 || ring->window <= 0 || ring->window + n_tokens > ring->ring)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sliding_prefill: the ring (%d slots) must hold the window (%d) and the chunk (%d tokens)",
                    ring->ring, ring->window, n_tokens);

@@ -3,35 +3,58 @@
 // attn_sliding8_b (Sources/EmblaMetal/Kernels/prefill.metal:129-180, 439-548) for whole chunks; short chunks
 // and odd rings take the mma.sync kernel of sliding_prefill.cu.
 //
-//   S = Q Kᵀ   tcgen05.mma kind::f16, M = 128 query rows, N = 128 keys (one 128-slot block of the ring), K = 128 dims
+//   S = Q Kᵀ   tcgen05.mma kind::f16, M = 128 query rows, N = up to 128 keys (one 128-slot block of the ring), K = 128 dims
 //   O += P V   A = P read from TMEM, B = V from shared memory (MN-major)
 // A query tile is 128 / G consecutive tokens x the G query heads of one kv head (row = token * G + head), so all its
 // rows share one run of ring blocks: the union of their windows, window + 128 / G - 1 positions. One CTA owns two
 // consecutive tiles, which share every block fetched. The keys and values are 16-bit already: the TMA producer puts
 // each block straight into the UMMA operand layout ([dims 0-63 | 64-127][128 keys][128 B], 128-byte swizzle), K as the
-// K-major operand of Q Kᵀ and V as the MN-major operand of P V; no conversion warps.
+// K-major operand of Q Kᵀ and V as the MN-major operand of P V; no conversion warps. Of a block at the edge of a tile's
+// windows only the 16-key groups some row can see are multiplied (N of Q Kᵀ and the k-steps of P V shrink to them).
 //
-// The softmax takes two passes over the blocks instead of rescaling O in TMEM: pass A runs only S = Q Kᵀ and the
-// softmax warps keep each row's maximum over its window; pass B runs S again, p = exp(s - max) (masked to the row's own
-// window), P in the activation dtype over the consumed S columns (bfloat16: P = hi + lo, two products, so that its
-// rounding stays below 2^-16), O += P V; at the end O / Σp. A window is at most ten blocks, so
-// the second Q Kᵀ costs half as much again as one pass and keeps the tensor pipe's work free of read-modify-write on O.
-//   warps 0-7   two warpgroups, one per tile, one query row a thread
-//   warp 8      TMA producer (3 buffers of 32 KiB: K blocks in pass A, K and V blocks in pass B)
-//   warp 9      MMA issuer; in pass B per block S0, P V1 (block before), S1, P V0, as the full-layer kernel
-// Every wait is bounded; a wait that runs out sets the context's error word and the CTA winds down.
+// One pass over the blocks with a running row maximum that is allowed to go stale: p = exp2(s - m) where m is the
+// maximum the row had when it was last adopted; m moves (and the row of O in TMEM and the row sum are rescaled by
+// exp2(m_old - m_new)) only when a block's maximum exceeds it by more than 2^8, so p stays below 2^8, O and the sum
+// share one m at all times, and O / Σp does not depend on it. After the first block or two a rescale is rare.
+//   warps 0-7   two warpgroups, one per tile, one query row a thread: the row's 128 scores of a block are read into
+//               registers at once (so P can go anywhere over S), maximum, weights, P; about four instructions a score
+//   warp 8      TMA producer (4 buffers of 32 KiB: K block, V block, K block, ...)
+//   warp 9      MMA issuer: per block P V of tile 0, S of tile 0 for the next block, P V of tile 1, S of tile 1 (next)
+// A tile's next S is issued right behind its P V (the tensor pipe runs them in order), so the row's softmax of the next
+// block overlaps the other tile's products. Every wait is bounded; a wait that runs out sets the context's error word
+// and the CTA winds down.
 #include "attn16_common.cuh"
 #include "sliding_prefill_tc.cuh"
 #include "tc05.cuh"
 
 namespace embla {
 
-constexpr int ST_PRODUCER = 8, ST_MMA = 9;
+constexpr int ST_SOFTMAX_WARPS = 8, ST_PRODUCER = 8, ST_MMA = 9;
 constexpr int ST_THREADS = (ST_MMA + 1) * 32;
 constexpr int ST_TILE = BLK * HD * 2;     // 32 KiB
-constexpr int ST_BUFS = 3;
+constexpr int ST_BUFS = 4;
 constexpr size_t ST_SMEM = 1024 + 2 * ST_TILE + ST_BUFS * ST_TILE + 256;
+constexpr float ST_STALE = 8.0f;          // how far (in powers of two) a block's maximum may exceed the adopted one
 
+// max of three (one instruction on this architecture)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// The 16-key groups [n0, n1) of block j that hold a key of [klo, khi] (the union of a tile's windows); false if none.
+__device__ __forceinline__ bool block_cols(int j, int jlo, int jhi, int klo, int khi, int& n0, int& n1) {
+    if (j < jlo || j > jhi) return false;
+    n0 = max(klo - j * BLK, 0) & ~15;
+    n1 = (min(khi - j * BLK, BLK - 1) + 16) & ~15;
+    return true;
+}
 
 template <int DT>
 __global__ void __launch_bounds__(ST_THREADS, 1)
@@ -39,14 +62,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* Qs = smem;                                  // [2 tiles][32 KiB]
-    uint8_t* kvb = smem + 2 * ST_TILE;                   // [3][32 KiB] K or V blocks
+    uint8_t* kvb = smem + 2 * ST_TILE;                   // [4][32 KiB] K or V blocks
     uint64_t* bars = reinterpret_cast<uint64_t*>(kvb + ST_BUFS * ST_TILE);
-    uint64_t* kv_ready = bars;          // [3]
-    uint64_t* kv_free = bars + 3;       // [3]
-    uint64_t* s_full = bars + 6;        // [2 tiles]
-    uint64_t* p_ready = bars + 8;       // [2 tiles]: the tile's warps are done with S (pass A) / have stored P (pass B)
-    uint64_t* o_done = bars + 10;
-    uint64_t* v_clean = bars + 11;      // the last V block holds no rows past the chunk any more
+    uint64_t* kv_ready = bars;          // [4]
+    uint64_t* kv_free = bars + 4;       // [4]
+    uint64_t* s_full = bars + 8;        // [2 tiles]
+    uint64_t* p_ready = bars + 10;      // [2 tiles]: the tile's 4 warps have stored P
+    uint64_t* o_done = bars + 14;
+    uint64_t* v_clean = bars + 15;      // the last V block holds no rows past the chunk any more
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
 
@@ -54,13 +77,15 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
     const int kvh = blockIdx.y, b = blockIdx.z;
     const int tpt = BLK / p.G;                            // tokens of a tile
     const int p0 = p.pos0[b];
-    int t0[2], ntok[2], jlo[2], jhi[2];
+    int t0[2], ntok[2], jlo[2], jhi[2], klo[2], khi[2];
 #pragma unroll
     for (int x = 0; x < 2; x++) {
         t0[x] = (2 * blockIdx.x + x) * tpt;
         ntok[x] = max(0, min(tpt, p.n_tokens - t0[x]));
         const int pa = p0 + t0[x], pz = pa + ntok[x] - 1;
-        jlo[x] = max(0, pa - p.window + 1) >> 7;          // blocks of 128 positions the tile's windows touch
+        klo[x] = max(0, pa - p.window + 1);               // the keys some row of the tile sees
+        khi[x] = pz;
+        jlo[x] = klo[x] >> 7;                             // blocks of 128 positions they lie in
         jhi[x] = ntok[x] > 0 ? pz >> 7 : -1;
     }
     const int jb = ntok[1] > 0 ? min(jlo[0], jlo[1]) : jlo[0];
@@ -72,7 +97,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
     const int chunk_end = p0 + p.n_tokens - 1;
     const bool clean_v = je == (chunk_end >> 7) && (chunk_end & (BLK - 1)) != BLK - 1;
 
-    if (tid == 0) {
+    // The producer sets the barriers up and requests the first blocks while the other warps stage Q.
+    if (warp == ST_PRODUCER && lane == 0) {
         for (int i = 0; i < ST_BUFS; i++) {
             mbar_init(&kv_ready[i], 1);
             mbar_init(&kv_free[i], 1);
@@ -86,77 +112,83 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
         s_abort = 0;
         fence_barrier_init();
     }
+    auto request = [&](int c) {                            // load c: K of block jb + c / 2 (even c) or its V (odd c)
+        const int j = jb + (c >> 1), slot = c % ST_BUFS;
+        const int y = kvh * p.ring + (j * BLK) % p.ring;
+        uint8_t* dst = kvb + slot * ST_TILE;
+        const CUtensorMap* map = (c & 1) ? &map_v : &map_k;
+        mbar_expect_tx(&kv_ready[slot], ST_TILE);
+        tma_load_3d(dst, map, 0, y, b, &kv_ready[slot]);
+        tma_load_3d(dst + BLK * 128, map, 128, y, b, &kv_ready[slot]);
+    };
+    if (warp == ST_PRODUCER && lane == 0)
+        for (int c = 0; c < min(ST_BUFS, 2 * nblk); c++) request(c);
     if (warp == ST_MMA) tmem_alloc(&s_tmem, 512);
 
     // ---- Q tiles: row r = token r / G, head r % G, as fp16 in the K-major swizzled layout (norm + RoPE at the token's
     // position when the queries arrive raw, as attn_sliding_b does)
-    for (int x = 0; x < 2; x++) {
-        uint8_t* Qx = Qs + x * ST_TILE;
-        if (p.prenormed) {
-            // rows as they are: 16 bytes a thread and trip, many loads in flight
+    if (warp < ST_SOFTMAX_WARPS) {
+        for (int x = 0; x < 2; x++) {
+            uint8_t* Qx = Qs + x * ST_TILE;
+            if (p.prenormed) {
+                // rows as they are: 16 bytes a thread and trip, many loads in flight
 #pragma unroll 4
-            for (int i = tid; i < BLK * 16; i += ST_THREADS) {
-                const int r = i >> 4, c8 = i & 15, t = r / p.G, hh = r % p.G;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (t < ntok[x]) {
-                    const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + t) * p.q_token_stride + size_t(kvh * p.G + hh) * HD + c8 * 8;
-                    v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
+                for (int i = tid; i < BLK * 16; i += ST_SOFTMAX_WARPS * 32) {
+                    const int r = i >> 4, c8 = i & 15, t = r / p.G, hh = r % p.G;
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (t < ntok[x]) {
+                        const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + t) * p.q_token_stride + size_t(kvh * p.G + hh) * HD + c8 * 8;
+                        v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
+                    }
+                    *reinterpret_cast<uint4*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v;
                 }
-                *reinterpret_cast<uint4*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v;
+                continue;
             }
-            continue;
-        }
-        // raw queries: four rows a warp and trip, their loads in flight together before the norms
-        for (int r4 = warp * 4; r4 < BLK; r4 += 4 * (ST_THREADS / 32)) {
-            float xq[4][4];
+            // raw queries: four rows a warp and trip, their loads in flight together before the norms
+            for (int r4 = warp * 4; r4 < BLK; r4 += 4 * ST_SOFTMAX_WARPS) {
+                float xq[4][4];
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const int r = r4 + k, t = r / p.G, hh = r % p.G;
-                const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + t) * p.q_token_stride + size_t(kvh * p.G + hh) * HD;
+                for (int k = 0; k < 4; k++) {
+                    const int r = r4 + k, t = r / p.G, hh = r % p.G;
+                    const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + t) * p.q_token_stride + size_t(kvh * p.G + hh) * HD;
 #pragma unroll
-                for (int i = 0; i < 4; i++) xq[k][i] = t < ntok[x] ? Act<DT>::load(p.q, off + lane + 32 * i) : 0.0f;
-            }
+                    for (int i = 0; i < 4; i++) xq[k][i] = t < ntok[x] ? Act<DT>::load(p.q, off + lane + 32 * i) : 0.0f;
+                }
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const int r = r4 + k, t = r / p.G;
-                if (t < ntok[x]) norm_rope_round<DT>(xq[k], p.g1, p.g1, 1, p0 + t0[x] + t, p.rope_freq, lane);
+                for (int k = 0; k < 4; k++) {
+                    const int r = r4 + k, t = r / p.G;
+                    if (t < ntok[x]) norm_rope_round<DT>(xq[k], p.g1, p.g1, 1, p0 + t0[x] + t, p.rope_freq, lane);
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int d = lane + 32 * i, c8 = d >> 3;
-                    Act<DT>::store(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4) + (d & 7) * 2, 0, xq[k][i]);
+                    for (int i = 0; i < 4; i++) {
+                        const int d = lane + 32 * i, c8 = d >> 3;
+                        Act<DT>::store(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4) + (d & 7) * 2, 0, xq[k][i]);
+                    }
                 }
             }
         }
+        fence_proxy_async();  // Q was written by ordinary stores; the tensor pipe reads it through the async proxy
     }
-    fence_proxy_async();      // Q was written by ordinary stores; the tensor pipe reads it through the async proxy
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = s_tmem;
-    // TMEM columns: S/P of tile 0 at 0, of tile 1 at 128 (P overwrites the first 64 columns of its S); O at 256, 384
+    // TMEM columns: S of tile 0 at 0, of tile 1 at 128; O at 256, 384. P of keys 64 h + 16 k .. + 15 goes over S: 8 columns
+    // at 64 h + 8 k (bfloat16: its low part 32 columns further on).
 
-    // Loads, in order: pass A the K block of every j; pass B the K block then the V block of every j. Load c uses buffer c % 3.
     if (warp == ST_PRODUCER) {
         if (lane == 0) {
-            for (int c = 0; c < 3 * nblk; c++) {
-                const int j = jb + (c < nblk ? c : (c - nblk) >> 1);
-                const bool is_v = c >= nblk && ((c - nblk) & 1);
-                const int slot = c % ST_BUFS;
-                if (c >= ST_BUFS && !mbar_wait_bounded(p.ctl.wait_cycles, &kv_free[slot], ((c / ST_BUFS) - 1) & 1)) {
+            for (int c = ST_BUFS; c < 2 * nblk; c++) {
+                if (!mbar_wait_bounded(p.ctl.wait_cycles, &kv_free[c % ST_BUFS], ((c / ST_BUFS) - 1) & 1)) {
                     atomicCAS(p.ctl.err, 0, 1000 + c);
                     break;
                 }
                 if (*reinterpret_cast<volatile int*>(&s_abort)) break;
-                const int y = kvh * p.ring + (j * BLK) % p.ring;
-                uint8_t* dst = kvb + slot * ST_TILE;
-                mbar_expect_tx(&kv_ready[slot], ST_TILE);
-                tma_load_3d(dst, is_v ? &map_v : &map_k, 0, y, b, &kv_ready[slot]);
-                tma_load_3d(dst + BLK * 128, is_v ? &map_v : &map_k, 128, y, b, &kv_ready[slot]);
+                request(c);
             }
         }
         if (clean_v) {
             __syncwarp();
-            const int cl = 3 * nblk - 1;                   // the last load: V of block je
+            const int cl = 2 * nblk - 1;                   // the last load: V of block je
             uint8_t* vb = kvb + (cl % ST_BUFS) * ST_TILE;
             if (mbar_wait_bounded(p.ctl.wait_cycles, &kv_ready[cl % ST_BUFS], (cl / ST_BUFS) & 1)) {
                 const int first = (chunk_end & (BLK - 1)) + 1;
@@ -175,111 +207,77 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
         if (lane == 0) {
             const uint32_t qa = smem_u32(Qs);
             bool ok = true;
-            int c = 0;                 // loads consumed so far
-            int site = 0;              // where a wait gave up: 100 pass + 10 step + ..., reported in the error word
+            int site = 0;              // where a wait gave up, reported in the error word
             int us[2] = {0, 0};        // S products issued per tile (the phase counters of s_full / p_ready)
             auto wait_load = [&](int cc) {
                 if (!mbar_wait_bounded(p.ctl.wait_cycles, &kv_ready[cc % ST_BUFS], (cc / ST_BUFS) & 1)) return false;
-                return !(clean_v && cc == 3 * nblk - 1) || mbar_wait_bounded(p.ctl.wait_cycles, v_clean, 0);
+                return !(clean_v && cc == 2 * nblk - 1) || mbar_wait_bounded(p.ctl.wait_cycles, v_clean, 0);
             };
             // bfloat16 operands: formats of A and B in the instruction descriptor (bits 7-9 and 10-12)
             constexpr uint32_t fmt = DT == EMBLA_BF16 ? (1u << 7) | (1u << 10) : 0u;
-            auto issue_s = [&](int x, int cc) {
-                const uint32_t ka = smem_u32(kvb + (cc % ST_BUFS) * ST_TILE);
+            auto issue_s = [&](int x, int cc, int n0, int n1) {       // keys n0 .. n1 - 1 of the block in buffer cc % 4
+                const uint32_t ka = smem_u32(kvb + (cc % ST_BUFS) * ST_TILE) + n0 * 128;
+                const uint32_t idesc = ((PF_IDESC_QK & ~(0x3Fu << 17)) | (uint32_t(n1 - n0) >> 3 << 17)) | fmt;
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
                     const uint32_t koff = (ks >> 2) * (BLK * 128) + (ks & 3) * 32;
-                    umma_ss(tmem + 128 * x, umma_desc(qa + x * ST_TILE + koff, 16, 1024), umma_desc(ka + koff, 16, 1024), PF_IDESC_QK | fmt, ks > 0);
+                    umma_ss(tmem + 128 * x + n0, umma_desc(qa + x * ST_TILE + koff, 16, 1024), umma_desc(ka + koff, 16, 1024), idesc, ks > 0);
                 }
                 tc_commit(&s_full[x]);
                 us[x]++;
             };
-            auto issue_pv = [&](int x, int cc, bool first) {
+            auto issue_pv = [&](int x, int cc, bool first, int n0, int n1) {
                 const uint32_t va = smem_u32(kvb + (cc % ST_BUFS) * ST_TILE);
-#pragma unroll
-                for (int ks = 0; ks < 8; ks++) {
+                for (int ks = n0 >> 4; ks < n1 >> 4; ks++) {
                     const uint64_t vd = umma_desc(va + ks * 2048, BLK * 128, 1024);
-                    if (DT == EMBLA_F16) {
-                        umma_ts(tmem + 256 + 128 * x, tmem + 128 * x + 8 * ks, vd, PF_IDESC_PV, (!first) | (ks > 0));
-                    } else {   // keys 64 h .. 64 h + 63: P hi at columns 64 h, P lo at 64 h + 32
-                        const uint32_t pa = tmem + 128 * x + 64 * (ks >> 2) + 8 * (ks & 3);
-                        umma_ts(tmem + 256 + 128 * x, pa, vd, PF_IDESC_PV | fmt, (!first) | (ks > 0));
-                        umma_ts(tmem + 256 + 128 * x, pa + 32, vd, PF_IDESC_PV | fmt, 1);
-                    }
+                    const uint32_t pa = tmem + 128 * x + 64 * (ks >> 2) + 8 * (ks & 3);
+                    umma_ts(tmem + 256 + 128 * x, pa, vd, PF_IDESC_PV | fmt, (!first) | (ks > (n0 >> 4)));
+                    if (DT == EMBLA_BF16) umma_ts(tmem + 256 + 128 * x, pa + 32, vd, PF_IDESC_PV | fmt, 1);
                 }
             };
-            // the tile's warps are done with the S product before its us[x]-th (they arrive once per product)
-            auto wait_tile = [&](int x) { return us[x] == 0 || mbar_wait_bounded(p.ctl.wait_cycles, &p_ready[x], (us[x] - 1) & 1); };
-            // ---- pass A: row maxima
-            for (int i = 0; i < nblk && ok; i++, c++) {
-                const int j = jb + i;
-                site = 100 + i;
-                ok = wait_load(c);
-                if (!ok) break;
+            int n0 = 0, n1 = 0;
+            // ---- the first block's S products
+            site = 100;
+            ok = wait_load(0);
+            if (ok) {
                 tc_fence_after();
 #pragma unroll
-                for (int x = 0; x < 2; x++) {
-                    if (j < jlo[x] || j > jhi[x]) continue;
-                    site = 200 + 20 * x + i;
-                    ok = ok && wait_tile(x);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_s(x, c);
-                }
-                tc_commit(&kv_free[c % ST_BUFS]);
+                for (int x = 0; x < 2; x++)
+                    if (block_cols(jb, jlo[x], jhi[x], klo[x], khi[x], n0, n1)) issue_s(x, 0, n0, n1);
+                tc_commit(&kv_free[0]);
             }
-            // ---- pass B: S again, P V. Per block: S0, P V1 of the block before, S1, P V0.
-            int pv1_load = -1;         // the V load of tile 1's pending P V
+            // ---- per block: P V of tile 0, S of tile 0 on the next block, P V of tile 1, S of tile 1 on the next block
             bool first_pv[2] = {true, true};
-            for (int i = 0; i <= nblk && ok; i++) {
-                const int j = jb + i;
-                const bool a0 = i < nblk && j >= jlo[0] && j <= jhi[0], a1 = i < nblk && j >= jlo[1] && j <= jhi[1];
-                const int ck = c, cv = c + 1;
-                if (i < nblk) {
-                    site = 300 + i;
-                    ok = wait_load(ck);
-                    if (!ok) break;
-                    tc_fence_after();
-                }
-                if (a0) {
-                    site = 400 + i;
-                    ok = wait_tile(0);      // pass A's last S of tile 0 has been read (first block), or P V0 before was issued
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_s(0, ck);
-                }
-                if (pv1_load >= 0) {
-                    site = 500 + i;
-                    ok = mbar_wait_bounded(p.ctl.wait_cycles, &p_ready[1], (us[1] - 1) & 1) && wait_load(pv1_load);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_pv(1, pv1_load, first_pv[1]);
-                    first_pv[1] = false;
-                    tc_commit(&kv_free[pv1_load % ST_BUFS]);   // V of the block before: both tiles' P V are issued
-                    pv1_load = -1;
-                } else if (i >= 1) {
-                    tc_commit(&kv_free[(c - 1) % ST_BUFS]);    // (tile 1 did not use that V)
-                }
-                if (a1) {
-                    if (first_pv[1]) {       // pass A's last S of tile 1 must have been read before this overwrites it
-                        site = 600 + i;
-                        ok = wait_tile(1);
+            for (int i = 0; i < nblk && ok; i++) {
+                const int j = jb + i, cv = 2 * i + 1, ck = 2 * i + 2;
+                const bool next = i + 1 < nblk;
+                bool k_here = false;
+                site = 200 + i;
+                ok = wait_load(cv);
+                if (!ok) break;
+#pragma unroll
+                for (int x = 0; x < 2; x++) {
+                    if (block_cols(j, jlo[x], jhi[x], klo[x], khi[x], n0, n1)) {
+                        site = 300 + 100 * x + i;
+                        ok = mbar_wait_bounded(p.ctl.wait_cycles, &p_ready[x], (us[x] - 1) & 1);
                         if (!ok) break;
                         tc_fence_after();
+                        issue_pv(x, cv, first_pv[x], n0, n1);
+                        first_pv[x] = false;
                     }
-                    issue_s(1, ck);
+                    if (x == 1) tc_commit(&kv_free[cv % ST_BUFS]);     // V of this block: both tiles' P V are issued
+                    if (next && block_cols(j + 1, jlo[x], jhi[x], klo[x], khi[x], n0, n1)) {
+                        if (!k_here) {
+                            site = 500 + i;
+                            ok = wait_load(ck);
+                            if (!ok) break;
+                            tc_fence_after();
+                            k_here = true;
+                        }
+                        issue_s(x, ck, n0, n1);
+                    }
                 }
-                if (i < nblk) tc_commit(&kv_free[ck % ST_BUFS]);   // K of this block
-                if (a0) {
-                    site = 700 + i;
-                    ok = mbar_wait_bounded(p.ctl.wait_cycles, &p_ready[0], (us[0] - 1) & 1) && wait_load(cv);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_pv(0, cv, first_pv[0]);
-                    first_pv[0] = false;
-                }
-                if (a1) pv1_load = cv;
-                if (i < nblk) c += 2;
+                if (next && ok) tc_commit(&kv_free[ck % ST_BUFS]);     // K of the next block: both tiles' S are issued
             }
             if (!ok) {
                 atomicCAS(p.ctl.err, 0, 2000 + site);
@@ -291,77 +289,94 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
         // ---- softmax warps: warpgroup x owns tile x, one query row a thread
         const int x = warp >> 2, r = tid & 127;
         const uint32_t lane_sel = uint32_t((warp & 3) * 32) << 16;
-        const uint32_t tS = tmem + 128 * x, tO = tmem + 256 + 128 * x;
+        const uint32_t tS = tmem + 128 * x + lane_sel, tO = tmem + 256 + 128 * x + lane_sel;
         const int tok = r / p.G;
         const bool row_ok = tok < ntok[x];
         const int pos_r = p0 + t0[x] + tok;                   // this row's position; it sees pos_r - window + 1 .. pos_r
         const int nx = ntok[x] > 0 ? jhi[x] - jlo[x] + 1 : 0;
         const float c2 = rsqrtf(float(HD)) * 1.4426950408889634f;   // scores to base-2 exponents
-        float mrow = NEG_BIG, rowsum = 0.0f;
+        float m2 = NEG_BIG, rowsum = 0.0f;                    // adopted maximum (base-2 exponent), sum of the weights
         bool ok = true;
         int u = 0;                                             // S products of this tile seen so far
-        for (int pass = 0; pass < 2 && ok; pass++) {
-            const float mc = mrow * c2;
-            for (int i = 0; i < nx && ok; i++, u++) {
-                const int j = jlo[x] + i;
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &s_full[x], u & 1));
-                if (!ok) break;   // (warp-uniform: the TMEM loads below are warp-collective)
-                tc_fence_after();
-                // weights of 32 keys from kb on: exp(s - max) masked to the row's window, summed in fp32, packed in pairs
-                auto weights = [&](const uint32_t (&sv)[32], int kb, uint32_t (&hi)[16], uint32_t (&lo)[16]) {
+        for (; u < nx && ok; u++) {
+            const int j = jlo[x] + u;
+            int n0 = 0, n1 = 0;
+            block_cols(j, jlo[x], jhi[x], klo[x], khi[x], n0, n1);
+            // visible keys of this row in the block: lo_r <= e <= hi_r
+            const int lo_r = row_ok ? pos_r - p.window + 1 - j * BLK : BLK, hi_r = pos_r - j * BLK;
+            // a chunk of 32 keys is taken if it holds a key of the tile's windows, and needs no masks if every row of a
+            // full tile sees all its keys (both the same for the whole tile)
+            bool act[4], inner[4];
 #pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        const int kp = kb + e;
-                        float w0 = exp2f(fmaf(__uint_as_float(sv[e]), c2, -mc)), w1 = exp2f(fmaf(__uint_as_float(sv[e + 1]), c2, -mc));
-                        if (!(row_ok && kp <= pos_r && kp > pos_r - p.window)) w0 = 0.0f;
-                        if (!(row_ok && kp + 1 <= pos_r && kp + 1 > pos_r - p.window)) w1 = 0.0f;
-                        rowsum += w0 + w1;
-                        hi[e >> 1] = pack_act2<DT>(w0, w1);
-                        if (DT == EMBLA_BF16) lo[e >> 1] = pack_act2<DT>(w0 - Act<EMBLA_BF16>::round(w0), w1 - Act<EMBLA_BF16>::round(w1));
-                    }
-                };
-                if (pass == 0) {
-#pragma unroll
-                    for (int cc = 0; cc < 4; cc++) {
-                        uint32_t s[32];
-                        tmem_ld32(tS + 32 * cc + lane_sel, s);
-                        const int kb = j * BLK + 32 * cc;
-#pragma unroll
-                        for (int e = 0; e < 32; e++) {
-                            const int kp = kb + e;
-                            if (kp <= pos_r && kp > pos_r - p.window) mrow = fmaxf(mrow, __uint_as_float(s[e]));
-                        }
-                    }
-                } else if (DT == EMBLA_F16) {
-#pragma unroll
-                    for (int cc = 0; cc < 4; cc++) {
-                        uint32_t s[32], pk[16], unused[16];
-                        tmem_ld32(tS + 32 * cc + lane_sel, s);
-                        weights(s, j * BLK + 32 * cc, pk, unused);
-                        // P goes over the S columns already consumed: chunk cc's 16 columns lie inside [0, 32 cc + 32)
-                        tmem_st16(tS + 16 * cc + lane_sel, pk);
-                    }
-                } else {
-                    // bfloat16: per 64 keys both S chunks are read before P hi (32 columns) and P lo (32 columns) overwrite them
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        uint32_t sa[32], ha[16], la[16];
-                        tmem_ld32(tS + 64 * h + lane_sel, sa);
-                        weights(sa, j * BLK + 64 * h, ha, la);
-                        uint32_t sb[32], hb[16], lb[16];
-                        tmem_ld32(tS + 64 * h + 32 + lane_sel, sb);
-                        tmem_st16(tS + 64 * h + lane_sel, ha);
-                        tmem_st16(tS + 64 * h + 32 + lane_sel, la);
-                        weights(sb, j * BLK + 64 * h + 32, hb, lb);
-                        tmem_st16(tS + 64 * h + 16 + lane_sel, hb);
-                        tmem_st16(tS + 64 * h + 48 + lane_sel, lb);
-                    }
-                }
-                if (pass == 1) tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&p_ready[x]);
+            for (int cc = 0; cc < 4; cc++) {
+                act[cc] = 32 * cc < n1 && 32 * cc + 32 > n0;
+                inner[cc] = ntok[x] == tpt && j * BLK + 32 * cc + 31 <= p0 + t0[x] && j * BLK + 32 * cc >= khi[x] - p.window + 1;
             }
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &s_full[x], u & 1));
+            if (!ok) break;   // (warp-uniform: the TMEM loads below are warp-collective)
+            tc_fence_after();
+            uint32_t s[4][32];
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++)
+                if (act[cc]) tmem_ld32_async(tS + 32 * cc, s[cc]);
+            float bm = NEG_BIG;
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) {
+                if (!act[cc]) continue;
+                tmem_ld_arrived(s[cc]);
+                if (inner[cc]) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) bm = max3(bm, __uint_as_float(s[cc][e]), __uint_as_float(s[cc][e + 1]));
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; e++)
+                        if (32 * cc + e >= lo_r && 32 * cc + e <= hi_r) bm = fmaxf(bm, __uint_as_float(s[cc][e]));
+                }
+            }
+            const float bm2 = bm * c2;
+            if (u == 0) {
+                m2 = bm2;                                      // nothing accumulated yet
+            } else if (__any_sync(0xffffffffu, bm2 > m2 + ST_STALE)) {
+                // (the tile's S of this block is complete, so its P V of the block before is: O is at rest)
+                const float mn = fmaxf(m2, bm2), f = ex2_approx(m2 - mn);
+                m2 = mn;
+                rowsum *= f;
+#pragma unroll 1
+                for (int cc = 0; cc < 4; cc++) {
+                    uint32_t acc[32];
+                    tmem_ld32(tO + 32 * cc, acc);
+#pragma unroll
+                    for (int e = 0; e < 32; e++) acc[e] = __float_as_uint(__uint_as_float(acc[e]) * f);
+                    tmem_st32(tO + 32 * cc, acc);
+                }
+            }
+            // weights of a chunk: exp2(s - m), masked to the row's window where the chunk needs it, summed in fp32, packed in pairs
+            const float nm2 = -m2;
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) {
+                if (!act[cc]) continue;
+                uint32_t hi[16], lo[16];
+                float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float w0 = ex2_approx(fmaf(__uint_as_float(s[cc][e]), c2, nm2)), w1 = ex2_approx(fmaf(__uint_as_float(s[cc][e + 1]), c2, nm2));
+                    if (!inner[cc]) {
+                        if (!(32 * cc + e >= lo_r && 32 * cc + e <= hi_r)) w0 = 0.0f;
+                        if (!(32 * cc + e + 1 >= lo_r && 32 * cc + e + 1 <= hi_r)) w1 = 0.0f;
+                    }
+                    sum0 += w0;
+                    sum1 += w1;
+                    hi[e >> 1] = pack_act2<DT>(w0, w1);
+                    if (DT == EMBLA_BF16) lo[e >> 1] = pack_act2<DT>(w0 - Act<EMBLA_BF16>::round(w0), w1 - Act<EMBLA_BF16>::round(w1));
+                }
+                rowsum += sum0 + sum1;
+                tmem_st16(tS + 64 * (cc >> 1) + 16 * (cc & 1), hi);
+                if (DT == EMBLA_BF16) tmem_st16(tS + 64 * (cc >> 1) + 16 * (cc & 1) + 32, lo);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready[x]);
         }
         if (ok) {
             ok = mbar_wait_bounded(p.ctl.wait_cycles, o_done, 0);
@@ -372,7 +387,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
             atomicCAS(p.ctl.err, 0, 3000 + 100 * x + u);
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
         } else if (ntok[x] > 0) {
-            // (the TMEM loads are warp-collective: every thread of the warpgroup takes them, rows past the chunk only skip the stores)
+            // (the TMEM loads are warp-collective: every thread of the warp takes them, rows past the chunk only skip the stores)
             tc_fence_after();
             const float inv = row_ok ? 1.0f / rowsum : 0.0f;
             uint16_t* orow = static_cast<uint16_t*>(p.o) + size_t(b) * p.o_seq_stride + size_t(t0[x] + tok) * p.o_token_stride +
@@ -380,7 +395,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
 #pragma unroll 1
             for (int cc = 0; cc < 4; cc++) {
                 uint32_t acc[32];
-                tmem_ld32(tO + 32 * cc + lane_sel, acc);
+                tmem_ld32(tO + 32 * cc, acc);
                 if (row_ok) {
                     uint32_t outw[16];
 #pragma unroll

@@ -296,6 +296,7 @@ extern "C" EmblaStatus embla_attn_sparse_decode_int8(EmblaAttn* ctx, const Embla
                                                      const EmblaQuery* q, const uint32_t* idx_dev, void* o_dev,
                                                      int64_t o_stride, void* stream) {
     if (!ctx || !pool || !view || !q || !q->q_dev || !o_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sparse_decode_int8: null argument");
+    EMBLA_CHECK_DEVICE("embla_attn_sparse_decode_int8", ctx, pool);
     if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_sparse_decode_int8: the pool is not int8");
     if (pool->n_kv_heads != ctx->cfg.n_kv_heads || view->layer < 0 || view->layer >= pool->n_layers)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_sparse_decode_int8: pool/layer mismatch");

@@ -4,13 +4,16 @@
   and nothing crosses GPUs on the data path (`shard_sequences`).
 * A long prefill chunk of a full layer shards by kv head: a GPU holds the cache pages of its kv heads
   only and computes their query heads (`prefill_partition`); with more GPUs than kv heads the chunk's
-  tokens are cut as well. The per-head outputs are combined with one all-gather over NVLink (NCCL;
-  gloo in the CPU tests) and placed token-major, `o[T][n_q_heads * 128]`, which is what the
+  tokens are cut as well. Every GPU ends up with the token-major `o[T][n_q_heads * 128]` that the
   o-projection after attention reads (the reference's single GPU writes that layout directly,
-  Sources/EmblaMetal/Prefill.swift:343-344, 378-407). `HeadShardedPrefill` is that path as one object.
+  Sources/EmblaMetal/Prefill.swift:343-344, 378-407). `HeadShardedPrefill` is that path as one object,
+  two ways: the kernel's epilogue stores every output row into all GPUs' outputs itself, over NVLink into
+  symmetric memory, followed by one barrier across the GPUs (`fused=True`: compute and all-gather are one
+  kernel); or the kernel writes a local slab, one NCCL all-gather (gloo in the CPU tests) collects the slabs
+  and a strided copy places them.
 
-The only other communication is the timing plumbing (`max_over_ranks`). Peers' data reaches a GPU
-through the collective into its own memory; no kernel of this library reads another GPU's memory.
+The only other communication is the timing plumbing (`max_over_ranks`). No kernel of this library READS
+another GPU's memory; the fused path writes into it with plain stores.
 """
 from collections import namedtuple
 
@@ -78,12 +81,29 @@ class HeadShardedPrefill:
     token-major rows. The caller owns the pool (its kv heads only: `shard.n_kv_heads`) and the queries of its
     query heads and tokens."""
 
-    def __init__(self, n_q_heads, n_kv_heads, act_dtype, n_tokens, max_context, world=1, rank=0, group=None):
+    def __init__(self, n_q_heads, n_kv_heads, act_dtype, n_tokens, max_context, world=1, rank=0, group=None, fused=False):
         from . import attn
         self.shard = prefill_partition(n_q_heads, n_kv_heads, n_tokens, world, rank)
-        self.world, self.group = world, group
+        self.world, self.rank, self.group = world, rank, group
         self.ctx = attn.Attention(self.shard.n_q_heads, self.shard.n_kv_heads, act_dtype, 1, max_context)
         dt = self.ctx.torch_dtype
+        self.fused = bool(fused) and world > 1
+        self.width = n_q_heads * 128
+        if self.fused:
+            # every rank's output lives in symmetric memory: the peers' copies are mapped into this process, and the
+            # kernel's epilogue stores this rank's rows into all of them
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm
+            self.o_full = symm.empty((n_tokens, self.width), dtype=dt, device=torch.device("cuda", torch.cuda.current_device()))
+            self.o_full.zero_()
+            self._symm = symm.rendezvous(self.o_full, group if group is not None else dist.group.WORLD)
+            slab = (self.shard.token0 * self.width + self.shard.q_head0 * 128) * self.o_full.element_size()
+            self.peer_ptrs = [int(self._symm.buffer_ptrs[r]) + slab for r in range(world) if r != rank]
+            # this GPU's own place of the slab, as [1, T_l, ...] rows of the full width
+            self.o_local = self.o_full[self.shard.token0:self.shard.token0 + self.shard.n_tokens,
+                                       self.shard.q_head0 * 128:(self.shard.q_head0 + self.shard.n_q_heads) * 128].unsqueeze(0)
+            self.gathered = None
+            return
         self.o_local = torch.zeros(1, self.shard.n_tokens, self.shard.n_q_heads * 128, dtype=dt, device="cuda")
         self.gathered = torch.zeros(world, self.shard.n_tokens, self.shard.n_q_heads * 128, dtype=dt, device="cuda")
         self.o_full = torch.zeros(n_tokens, n_q_heads * 128, dtype=dt, device="cuda")
@@ -91,11 +111,21 @@ class HeadShardedPrefill:
     def attend(self, pool, block_table, layer, pos0, q_local, gains=None):
         """The local kernel only: o_local [1][T_l][hq_l * 128]. pos0 = the position of THIS rank's first token."""
         from . import attn
-        attn.full_prefill(self.ctx, pool, block_table, layer, pos0, q_local, self.o_local, gains=gains)
+        if self.fused:
+            attn.full_prefill_scatter(self.ctx, pool, block_table, layer, pos0, q_local, self.o_local, self.peer_ptrs, self.width,
+                                      gains=gains)
+        else:
+            attn.full_prefill(self.ctx, pool, block_table, layer, pos0, q_local, self.o_local, gains=gains)
         return self.o_local
 
     def combine(self):
-        """All-gather of the per-head outputs and their placement: o_full [T][Hq * 128]."""
+        """All-gather of the per-head outputs and their placement: o_full [T][Hq * 128]. Fused: the rows are already in
+        every GPU's output once every rank's kernel has finished, which one barrier across the GPUs establishes (a caller
+        that reuses the output must also keep a peer from overwriting it while it is still read: another barrier, or two
+        outputs in turn)."""
+        if self.fused:
+            self._symm.barrier()
+            return self.o_full
         if self.world == 1:
             self.o_full.copy_(self.o_local[0])
             return self.o_full

@@ -299,6 +299,17 @@ EmblaStatus embla_attn_full_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, con
                                     const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
                                     int64_t q_token_stride, void* o_dev, int64_t o_token_stride,
                                     int64_t o_seq_stride, void* stream);
+/* No counterpart in the reference (it runs one GPU): embla_attn_full_prefill for a chunk sharded over several GPUs by kv
+ * head. Besides o_dev, every output row is stored, by the kernel's own epilogue and with plain stores over NVLink, to
+ * o_peers_dev[i] for i < n_peers (at most 8; a host array of device addresses): each the address, in another GPU's memory
+ * mapped into this process (CUDA IPC, symmetric memory, peer access), of the place of THIS rank's rows in that GPU's
+ * token-major output, addressed with the same strides as o_dev. The compute and the all-gather of the per-head outputs are
+ * then one kernel: when every rank's call has completed (a barrier across the GPUs after it, which is the caller's, as
+ * is not overwriting a peer's output that the peer still reads), every GPU holds the whole o[T][n_q_heads * 128]. */
+EmblaStatus embla_attn_full_prefill_scatter(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
+                                            const int32_t* pos0_dev, int32_t n_tokens, const EmblaQuery* q,
+                                            int64_t q_token_stride, void* o_dev, void* const* o_peers_dev, int32_t n_peers,
+                                            int64_t o_token_stride, int64_t o_seq_stride, void* stream);
 /* The reference's int8 Q Kᵀ build of the same kernel (QK8: attn_nax.metal:14-22, 62, 124-204, with q_prep_b's QK8
  * branch, prefill.metal:421-422; switched on by EMBLA_ATT8, Prefill.swift:142-144; measurement-only there): every
  * query row is quantised like a cache row (rounded to the activation dtype, codes rint(x 127 / max|x|), scale

@@ -9,7 +9,7 @@ from tests import util
 pytestmark = pytest.mark.gpu
 
 
-def _case(T, p0, W, RING, Hq, Hkv, dtype, seed, gains=False, rows=None, poison=False):
+def _case(T, p0, W, RING, Hq, Hkv, dtype, seed, gains=False, rows=None, poison=False, ramp=0.0):
     import torch
     from embla_metal_b200 import attn
     rng = np.random.default_rng(seed)
@@ -31,7 +31,8 @@ def _case(T, p0, W, RING, Hq, Hkv, dtype, seed, gains=False, rows=None, poison=F
     ring.k.copy_(util.act_tensor(rk[None], dtype))
     ring.v.copy_(util.act_tensor(rv[None], dtype))
     q = orc.to_bits(rng.standard_normal((T, Hq, 128)), dtype)
-    k = orc.to_bits(rng.standard_normal((T, Hkv, 128)), dtype)
+    # ramp: the keys grow along the chunk, so that a row's maximum keeps rising from block to block by large factors
+    k = orc.to_bits(rng.standard_normal((T, Hkv, 128)) * (1.0 + ramp * np.arange(T)[:, None, None] / T), dtype)
     v = orc.to_bits(rng.standard_normal((T, Hkv, 128)), dtype)
     orc.sliding_write(k, v, dtype, rk, rv, p0, kgain=kg)
     want = orc.from_bits(orc.sliding_attend(q, dtype, rk, rv, p0, W, qgain=qg, nthreads=8), dtype)
@@ -77,3 +78,11 @@ def test_sliding_prefill_tensor_core_path_edges():
     # bfloat16 (P = hi + lo): the reference's window and a long one, never-written slots after the chunk
     _case(333, 900, 1024, 4096, 16, 4, orc.BF16, seed=16, gains=True, poison=True)
     _case(2048, 2048, 1024, 4096, 16, 4, orc.BF16, seed=17)
+
+
+def test_sliding_prefill_rising_maxima():
+    """Scores whose maximum grows by many powers of two across the blocks of a window: the kernel's adopted row maximum has
+    to move, and O and the row sum with it, several times a row."""
+    _case(600, 1000, 512, 2048, 16, 4, orc.F16, seed=18, ramp=8.0)
+    _case(600, 1000, 512, 2048, 16, 4, orc.BF16, seed=19, ramp=8.0)
+    _case(300, 0, 1024, 4096, 8, 1, orc.F16, seed=20, ramp=5.0)

@@ -212,3 +212,34 @@ def test_dependent_launch_overlap_changes_nothing():
         assert out.returncode == 0, out.stderr[-800:]
         digests.append(out.stdout.strip().splitlines()[-1])
     assert digests[0] == digests[1] == digests[2] and len(digests[0]) == 64
+
+
+def test_step_replays_from_a_cuda_graph():
+    """A whole step (36 kinds of launches with their dependent-launch edges) captured into a CUDA graph on a side stream and
+    replayed with other query rows and other positions in the same device arrays gives the bits of the direct calls (the
+    second set of positions lies past the first, so that the rows a step appends never land inside what the other step
+    reads). Run in a child process, so that a refused capture cannot leave this process's stream in capture mode."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import sys, torch; sys.path.insert(0, %r)\n"
+        "from embla_metal_b200 import stack as stk\n"
+        "st = stk.DecodeStack(stk.cycle_kinds(8) + [stk.FULL, stk.SPARSE_SHARED], 4, 4096, window=256, ring=1024)\n"
+        "st.fill_random(4)\n"
+        "g = torch.Generator(device='cuda').manual_seed(2)\n"
+        "rows = [torch.randn(st.qkv.shape, device='cuda', generator=g).to(st.dtype) for _ in range(2)]\n"
+        "poss = [[3000, 1500, 1100, 200], [4095, 3000, 1152, 300]]\n"
+        "want = []\n"
+        "for r, ps in zip(rows, poss):\n"
+        "    st.set_positions(ps); st.max_seq_len = 4096; st.qkv.copy_(r); st.step(); st.ctx.check(); want.append(st.o.clone())\n"
+        "graph = torch.cuda.CUDAGraph()\n"
+        "with torch.cuda.graph(graph):\n"
+        "    st.step()\n"
+        "for r, ps, w in zip(rows, poss, want):\n"
+        "    st.set_positions(ps); st.qkv.copy_(r); st.o.zero_(); graph.replay(); torch.cuda.synchronize(); st.ctx.check()\n"
+        "    assert torch.equal(st.o.view(torch.int16), w.view(torch.int16)), 'replay differs'\n"
+        "print('graph ok')\n" % root)
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "graph ok" in out.stdout, (out.stdout + out.stderr)[-1200:]
