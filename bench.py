@@ -389,7 +389,7 @@ def prefill_leg(rank, world, barrier, reps=10):
     hsp.ctx.check()
     kernel_ms = timed_ms(lambda: hsp.attend(pool, tbl, 0, p0, q))
     combine_ms = timed_ms(hsp.combine) if world > 1 else 0.0
-    ms, mode, fused_ms, fused_same = gather_ms, "allgather", None, None
+    ms, mode, fused_ms, fused_same = gather_ms, ("allgather" if world > 1 else "one GPU"), None, None
     if world > 1:
         # the same chunk with the all-gather inside the kernel: its epilogue stores the rows into every GPU's output over
         # NVLink (symmetric memory), then one barrier across the GPUs; checked against the all-gather path's output

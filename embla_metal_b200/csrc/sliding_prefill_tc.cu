@@ -127,23 +127,34 @@ __global__ void __launch_bounds__(ST_THREADS, 1)
 
     // ---- Q tiles: row r = token r / G, head r % G, as fp16 in the K-major swizzled layout (norm + RoPE at the token's
     // position when the queries arrive raw, as attn_sliding_b does)
-    if (warp < ST_SOFTMAX_WARPS) {
+    if (warp < ST_SOFTMAX_WARPS && p.prenormed) {
+        // rows as they are: 16 bytes a thread and trip, all sixteen loads of a thread (both tiles) in flight before the stores
+        constexpr int TRIPS = BLK * 16 / (ST_SOFTMAX_WARPS * 32);
+        uint4 v[2][TRIPS];
+#pragma unroll
+        for (int x = 0; x < 2; x++) {
+#pragma unroll
+            for (int k = 0; k < TRIPS; k++) {
+                const int i = tid + k * (ST_SOFTMAX_WARPS * 32), r = i >> 4, c8 = i & 15, t = r / p.G, hh = r % p.G;
+                v[x][k] = make_uint4(0, 0, 0, 0);
+                if (t < ntok[x]) {
+                    const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + t) * p.q_token_stride + size_t(kvh * p.G + hh) * HD + c8 * 8;
+                    v[x][k] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
+                }
+            }
+        }
+#pragma unroll
+        for (int x = 0; x < 2; x++) {
+#pragma unroll
+            for (int k = 0; k < TRIPS; k++) {
+                const int i = tid + k * (ST_SOFTMAX_WARPS * 32), r = i >> 4, c8 = i & 15;
+                *reinterpret_cast<uint4*>(Qs + x * ST_TILE + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v[x][k];
+            }
+        }
+        fence_proxy_async();  // Q was written by ordinary stores; the tensor pipe reads it through the async proxy
+    } else if (warp < ST_SOFTMAX_WARPS) {
         for (int x = 0; x < 2; x++) {
             uint8_t* Qx = Qs + x * ST_TILE;
-            if (p.prenormed) {
-                // rows as they are: 16 bytes a thread and trip, many loads in flight
-#pragma unroll 4
-                for (int i = tid; i < BLK * 16; i += ST_SOFTMAX_WARPS * 32) {
-                    const int r = i >> 4, c8 = i & 15, t = r / p.G, hh = r % p.G;
-                    uint4 v = make_uint4(0, 0, 0, 0);
-                    if (t < ntok[x]) {
-                        const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + t) * p.q_token_stride + size_t(kvh * p.G + hh) * HD + c8 * 8;
-                        v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
-                    }
-                    *reinterpret_cast<uint4*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v;
-                }
-                continue;
-            }
             // raw queries: four rows a warp and trip, their loads in flight together before the norms
             for (int r4 = warp * 4; r4 < BLK; r4 += 4 * ST_SOFTMAX_WARPS) {
                 float xq[4][4];

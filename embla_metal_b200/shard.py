@@ -104,9 +104,12 @@ class HeadShardedPrefill:
                                        self.shard.q_head0 * 128:(self.shard.q_head0 + self.shard.n_q_heads) * 128].unsqueeze(0)
             self.gathered = None
             return
+        self.o_full = torch.zeros(n_tokens, n_q_heads * 128, dtype=dt, device="cuda")
+        if world == 1:                      # one GPU: the kernel writes the token-major output itself
+            self.o_local, self.gathered = self.o_full.unsqueeze(0), None
+            return
         self.o_local = torch.zeros(1, self.shard.n_tokens, self.shard.n_q_heads * 128, dtype=dt, device="cuda")
         self.gathered = torch.zeros(world, self.shard.n_tokens, self.shard.n_q_heads * 128, dtype=dt, device="cuda")
-        self.o_full = torch.zeros(n_tokens, n_q_heads * 128, dtype=dt, device="cuda")
 
     def attend(self, pool, block_table, layer, pos0, q_local, gains=None):
         """The local kernel only: o_local [1][T_l][hq_l * 128]. pos0 = the position of THIS rank's first token."""
@@ -127,7 +130,6 @@ class HeadShardedPrefill:
             self._symm.barrier()
             return self.o_full
         if self.world == 1:
-            self.o_full.copy_(self.o_local[0])
             return self.o_full
         all_gather_rows(self.gathered, self.o_local[0], self.group)
         return place_heads(self.gathered, self.o_full, self.shard.kv_shards, self.shard.tok_shards)
