@@ -252,3 +252,64 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
     }
     return EMBLA_OK;
 }
+
+// The attention branch of the reference's Prefill.encode loop (Sources/EmblaMetal/Prefill.swift:282-345) for a chunk of
+// tokens: per layer the chunk's keys and values into the layer's cache, then the chunk's attention over it.
+extern "C" EmblaStatus embla_stack_prefill_chunk(EmblaStack* st, const EmblaStackChunk* ck, void* stream) {
+    if (!st || !ck || !ck->qkv_dev || !ck->o_dev || !ck->pos0_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_prefill_chunk: null argument");
+    EmblaAttn* ctx = st->ctx;
+    const int Hq = ctx->cfg.n_q_heads, Hkv = ctx->cfg.n_kv_heads, B = ck->batch, T = ck->n_tokens;
+    const int n_layers = int(st->layers.size());
+    if (B <= 0 || B > ctx->cfg.max_batch || T <= 0) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_prefill_chunk: batch %d, n_tokens %d", B, T);
+    if (ck->kv_only_layers < 0 || ck->kv_only_layers > n_layers)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_prefill_chunk: %d K/V-only layers of %d", ck->kv_only_layers, n_layers);
+    for (const EmblaLayerDesc& L : st->layers)
+        if (L.kind == EMBLA_LAYER_SPARSE || L.kind == EMBLA_LAYER_SPARSE_SHARED)
+            EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_stack_prefill_chunk: the stack has sparse layers (the reference's prefill half has none: "
+                                          "their tokens go through embla_stack_decode_step)");
+    const size_t esz = 2;
+    const int max_len = ck->max_seq_len > 0 ? ck->max_seq_len : ctx->cfg.max_context;
+    for (int li = 0; li < n_layers; li++) {
+        const EmblaLayerDesc& L = st->layers[li];
+        const bool kv_only = li >= n_layers - ck->kv_only_layers;
+        const uint8_t* row = static_cast<const uint8_t*>(ck->qkv_dev) + size_t(li) * ck->qkv_layer_stride * esz;
+        const void* kp = row + size_t(Hq) * HD * esz;
+        const void* vp = row + size_t(Hq + Hkv) * HD * esz;
+        void* op = static_cast<uint8_t*>(ck->o_dev) + size_t(li) * ck->o_layer_stride * esz;
+        EmblaQuery q;
+        q.q_dev = row;
+        q.q_stride = ck->qkv_seq_stride;
+        q.prenormed = L.g1_dev ? 0 : 1;
+        q.g1_dev = L.g1_dev;
+        q.g2_dev = L.g2_dev;
+        if (L.kind == EMBLA_LAYER_SLIDING) {
+            const EmblaRing* ring = &st->rings[L.slot];
+            q.ng = L.g1_dev ? 1 : 0;
+            if (EmblaStatus e = embla_sliding_write(ctx, ring, ck->pos0_dev, B, T, kp, vp, ck->qkv_token_stride, ck->qkv_seq_stride,
+                                                    L.kgain_dev ? 0 : 1, L.kgain_dev, stream))
+                return e;
+            if (kv_only) continue;
+            if (EmblaStatus e = embla_attn_sliding_prefill(ctx, ring, ck->pos0_dev, B, T, &q, ck->qkv_token_stride, op, ck->o_token_stride,
+                                                           ck->o_seq_stride, stream))
+                return e;
+            continue;
+        }
+        if (!ck->full_table_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_prefill_chunk: no block table for the full layers");
+        q.ng = L.g1_dev ? (L.g2_dev ? 2 : 1) : 0;
+        EmblaKVView view;
+        view.batch = B;
+        view.layer = L.slot;
+        view.seq_lens_dev = nullptr;
+        view.max_seq_len = max_len;
+        view.block_table_dev = ck->full_table_dev;
+        view.table_stride = ck->full_table_stride;
+        if (EmblaStatus e = embla_kv_append(ctx, st->full_pool, &view, ck->pos0_dev, T, kp, vp, ck->qkv_token_stride, ck->qkv_seq_stride,
+                                            L.norm_k, stream))
+            return e;
+        if (kv_only) continue;
+        if (EmblaStatus e = embla_attn_full_prefill(ctx, st->full_pool, &view, ck->pos0_dev, T, &q, ck->qkv_token_stride, op,
+                                                    ck->o_token_stride, ck->o_seq_stride, stream))
+            return e;
+    }
+    return EMBLA_OK;
+}

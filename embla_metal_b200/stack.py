@@ -29,6 +29,14 @@ class StackStep(C.Structure):
                 ("batch", C.c_int32), ("max_seq_len", C.c_int32)]
 
 
+class StackChunk(C.Structure):
+    _fields_ = [("qkv_dev", C.c_void_p), ("qkv_token_stride", C.c_int64), ("qkv_seq_stride", C.c_int64),
+                ("qkv_layer_stride", C.c_int64), ("o_dev", C.c_void_p), ("o_token_stride", C.c_int64),
+                ("o_seq_stride", C.c_int64), ("o_layer_stride", C.c_int64), ("pos0_dev", C.c_void_p),
+                ("full_table_dev", C.c_void_p), ("full_table_stride", C.c_int32), ("batch", C.c_int32),
+                ("n_tokens", C.c_int32), ("max_seq_len", C.c_int32), ("kv_only_layers", C.c_int32)]
+
+
 def cycle_kinds(n_layers):
     """The benchmark's stack: layers cycling sparse, sliding, sliding, full."""
     return [(SPARSE, SLIDING, SLIDING, FULL)[i % 4] for i in range(n_layers)]
@@ -138,6 +146,19 @@ class DecodeStack:
         """One decode step from the device-resident qkv rows; results in self.o."""
         st = self._step_struct()
         attn._check(attn.lib().embla_stack_decode_step(self.handle, C.byref(st), attn._stream()))
+
+    def prefill_chunk(self, qkv, o, pos0, kv_only_layers=0, max_seq_len=0):
+        """A chunk of new tokens through every layer (sliding and full layers only): qkv [n_layers, batch, T, qkv_width],
+        o [n_layers, batch, T, o_width] on the device, pos0 int32 [batch] the position of each sequence's first new token.
+        The last `kv_only_layers` layers only store their keys and values."""
+        n, b, t, _ = qkv.shape
+        if (n, b) != (len(self.kinds), self.batch) or tuple(o.shape[:3]) != (n, b, t):
+            raise ValueError(f"qkv {tuple(qkv.shape)} / o {tuple(o.shape)} do not fit {len(self.kinds)} layers x {self.batch} sequences")
+        if qkv.stride(3) != 1 or o.stride(3) != 1:
+            raise ValueError("rows must be contiguous")
+        ck = StackChunk(qkv.data_ptr(), qkv.stride(2), qkv.stride(1), qkv.stride(0), o.data_ptr(), o.stride(2), o.stride(1),
+                        o.stride(0), pos0.data_ptr(), self.table.data_ptr(), self.table.stride(0), b, t, max_seq_len, kv_only_layers)
+        attn._check(attn.lib().embla_stack_prefill_chunk(self.handle, C.byref(ck), attn._stream()))
 
     def step_host(self):
         """One decode step from pinned host rows: qkv_host -> device, attention, o -> o_host."""

@@ -374,6 +374,30 @@ EmblaStatus embla_stack_create(EmblaAttn* ctx, const EmblaLayerDesc* layers, int
                                EmblaKVPool* sparse_pool, const EmblaRing* rings, int32_t n_rings, EmblaStack** out);
 void        embla_stack_destroy(EmblaStack* stack);
 EmblaStatus embla_stack_decode_step(EmblaStack* stack, const EmblaStackStep* step, void* stream);
+/* The attention branch of Prefill.encode's per-layer loop (Prefill.swift:282-345) as one call: for a chunk of
+ * n_tokens new tokens per sequence at positions pos0_dev[b] + t, every layer of the stack in order:
+ *   sliding: kv_sliding_b then attn_sliding(8)_b  -> embla_sliding_write + embla_attn_sliding_prefill
+ *   full:    kv_append_b then q_prep_b + relu2_prefill_nax -> embla_kv_append + embla_attn_full_prefill
+ * all enqueued on one stream. The last `kv_only_layers` layers of the stack only store their keys and values (the
+ * reference's layer 16, "its K/V only", Prefill.swift:286, 327); their rows of o_dev are left untouched. Sparse layers
+ * are refused with EMBLA_UNSUPPORTED: the reference's prefill half has none. With split-KV scratch reserved
+ * (embla_attn_reserve_prefill) the call neither allocates nor synchronises. */
+typedef struct {
+    const void*    qkv_dev;            /* [n_layers][batch][n_tokens][qkv_token_stride]: q, k, v of a token as in a decode step */
+    int64_t        qkv_token_stride;   /* elements between tokens (4096 in the reference) */
+    int64_t        qkv_seq_stride;     /* elements between sequences */
+    int64_t        qkv_layer_stride;   /* elements between layers */
+    void*          o_dev;              /* [n_layers][batch][n_tokens][o_token_stride] */
+    int64_t        o_token_stride, o_seq_stride, o_layer_stride;
+    const int32_t* pos0_dev;           /* [batch] position of each sequence's first new token */
+    const int32_t* full_table_dev;     /* block table into the int8 pool */
+    int32_t        full_table_stride;
+    int32_t        batch;
+    int32_t        n_tokens;           /* tokens of the chunk, the same for every sequence */
+    int32_t        max_seq_len;        /* host-side upper bound of pos0 + n_tokens; 0 = max_context */
+    int32_t        kv_only_layers;     /* trailing layers that only store K/V */
+} EmblaStackChunk;
+EmblaStatus embla_stack_prefill_chunk(EmblaStack* stack, const EmblaStackChunk* chunk, void* stream);
 /* Timing probe, the counterpart of the reference's per-part Profiler (StepEncoder.swift:7-65):
  * CUDA events are recorded on the stream around every launch of entry point `entry` (-1: off);
  * read_probe returns their summed time and count since the last read, after the caller has

@@ -243,3 +243,64 @@ def test_step_replays_from_a_cuda_graph():
         "print('graph ok')\n" % root)
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and "graph ok" in out.stdout, (out.stdout + out.stderr)[-1200:]
+
+
+def test_prefill_chunk_equals_token_by_token_steps():
+    """embla_stack_prefill_chunk (the attention branch of Prefill.encode: per layer the chunk's K/V into the cache, then the
+    chunk's attention) against the same tokens fed one at a time through embla_stack_decode_step on a twin stack: the
+    caches end bit-identical (int8 pages with their scales, rings) and every token's outputs agree within the attention
+    tolerance (the chunk runs the tcgen05 prefill kernels, the steps the decode kernels)."""
+    import torch
+    from embla_metal_b200 import stack as stk
+    from tests import util
+    kinds = [stk.SLIDING, stk.FULL, stk.SLIDING, stk.FULL]
+    B, T, ctxlen = 2, 150, 1024
+    pos0 = [300, 41]
+    twins = []
+    for _ in range(2):
+        st = stk.DecodeStack(kinds, B, ctxlen, window=256, ring=1024)
+        st.fill_random(11)
+        twins.append(st)
+    chunked, stepped = twins
+    g = torch.Generator(device="cuda").manual_seed(5)
+    qkv = torch.randn(len(kinds), B, T, chunked.qkv_width, device="cuda", generator=g).to(chunked.dtype)
+    o = torch.zeros(len(kinds), B, T, chunked.o_width, dtype=chunked.dtype, device="cuda")
+    chunked.prefill_chunk(qkv, o, torch.tensor(pos0, dtype=torch.int32, device="cuda"), max_seq_len=max(pos0) + T)
+    chunked.ctx.check()
+    want = torch.zeros_like(o)
+    for t in range(T):
+        stepped.set_positions([p + t for p in pos0])
+        stepped.qkv.copy_(qkv[:, :, t])
+        stepped.step()
+        want[:, :, t] = stepped.o
+    stepped.ctx.check()
+    torch.cuda.synchronize()
+    assert torch.equal(chunked.full_pool.raw(), stepped.full_pool.raw()), "int8 caches differ"
+    for a, b in zip(chunked.rings, stepped.rings):
+        assert torch.equal(a.k, b.k) and torch.equal(a.v, b.v), "rings differ"
+    for li in range(len(kinds)):
+        ok, msg = util.close(o[li].float().cpu().numpy(), want[li].float().cpu().numpy(), out_ulp=2.0 ** -10)   # one fp16 step
+        assert ok, f"layer {li} (kind {kinds[li]}): {msg}"
+    # the last layer as the reference's layer 16: its keys and values only
+    third = stk.DecodeStack(kinds, B, ctxlen, window=256, ring=1024)
+    third.fill_random(11)
+    o3 = torch.full_like(o, 3.0)
+    third.prefill_chunk(qkv, o3, torch.tensor(pos0, dtype=torch.int32, device="cuda"), kv_only_layers=1, max_seq_len=max(pos0) + T)
+    third.ctx.check()
+    torch.cuda.synchronize()
+    assert torch.equal(third.full_pool.raw(), chunked.full_pool.raw())
+    assert torch.equal(o3[:3], o[:3]) and bool((o3[3] == 3.0).all())
+    for st in (chunked, stepped, third):
+        st.close()
+
+
+def test_prefill_chunk_refuses_sparse_layers():
+    import torch
+    from embla_metal_b200 import attn, stack as stk
+    st = stk.DecodeStack(stk.cycle_kinds(4), 1, 512, window=128, ring=512)
+    qkv = torch.zeros(4, 1, 8, st.qkv_width, dtype=st.dtype, device="cuda")
+    o = torch.zeros(4, 1, 8, st.o_width, dtype=st.dtype, device="cuda")
+    with pytest.raises(attn.EmblaError) as e:
+        st.prefill_chunk(qkv, o, torch.zeros(1, dtype=torch.int32, device="cuda"))
+    assert e.value.status == attn.UNSUPPORTED
+    st.close()
