@@ -210,6 +210,33 @@ extern "C" EmblaStatus embla_attn_sparse_decode(EmblaAttn* ctx, const EmblaKVPoo
                                      static_cast<cudaStream_t>(stream));
 }
 
+// The full layers' ReLU² decode over a 16-bit pool (attn_full, attention.metal:148-220; the reference's EMBLA_KV8=0 build):
+// every key of the sequence through the gathered-rows path, split into ranges as the sparse layers' attend. Reached
+// through embla_attn_full_decode / embla_attn_full_step, which have checked their arguments.
+namespace embla {
+EmblaStatus attn16_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view, const EmblaQuery* q, void* o_dev,
+                               int64_t o_stride, int max_len, cudaStream_t stream) {
+    Attn16Params p = {};
+    p.pool = pool->base;
+    p.block_table = view->block_table_dev;
+    p.table_stride = view->table_stride;
+    p.idx = nullptr;
+    p.seq_lens = view->seq_lens_dev;
+    p.q = q->q_dev;
+    p.g1 = q->g1_dev;
+    p.g2 = q->g2_dev;
+    p.prenormed = q->prenormed;
+    p.ng = q->ng;
+    p.q_stride = q->q_stride;
+    p.o = o_dev;
+    p.o_stride = o_stride;
+    p.page_bytes = pool->page_bytes;
+    p.layer = view->layer;
+    p.n_layers = pool->n_layers;
+    return launch_attn16<A16_FULL>(ctx, p, view->batch, max_len, stream);
+}
+}  // namespace embla
+
 extern "C" EmblaStatus embla_sliding_write(EmblaAttn* ctx, const EmblaRing* ring, const int32_t* pos0_dev, int32_t batch,
                                            int32_t n_tokens, const void* k_dev, const void* v_dev, int64_t token_stride,
                                            int64_t seq_stride, int32_t prenormed, const void* kgain_dev, void* stream) {

@@ -27,7 +27,18 @@ constexpr int A16_PART = HD + 4;                      // floats per (range, head
 // [sender][head of this owner] rows behind the stages and queries; ranges x ceil(heads / ranges) <= 15 rows.
 constexpr int A16_INBOX_ROWS = 15;
 constexpr int A16_INBOX_BYTES = A16_INBOX_ROWS * A16_PART * 4;
-enum { A16_SPARSE = 0, A16_SLIDING = 1 };
+enum { A16_SPARSE = 0, A16_SLIDING = 1, A16_FULL = 2 };
+// A16_FULL: the full layers' ReLU² attention over a 16-bit cache (attn_full, attention.metal:148-220): every key of the
+// sequence, weight max(s / sqrt(D), 0)², o = sum w v / (sqrt(D) + sum w). It runs through the softmax machinery with the
+// running maximum pinned at zero (every rescale factor is exp(0) = 1, merges add) and the sink added where the softmax
+// kernels divide. fp16 P carries the weights times 2^-6, so that a weight up to 4e6 (|s| up to 2000) still fits.
+template <int DT, int MODE>
+__device__ __forceinline__ float a16_pscale() { return (MODE == A16_FULL && DT == EMBLA_F16) ? 0.015625f : 1.0f; }
+template <int DT, int MODE>
+__device__ __forceinline__ float a16_finish(float num, float L) {
+    if (MODE == A16_FULL) return num * (1.0f / a16_pscale<DT, MODE>()) / (sqrtf(float(HD)) + L);
+    return num / L;
+}
 
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" ::"n"(A16_THREADS) : "memory"); }
 
@@ -192,7 +203,7 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
     if (!TMA) {
         // The first tiles' rows are resolved together: all their index loads in flight at once, then all their block-table
         // loads, then the copies (resolved tile by tile, each chain of two dependent loads would follow the one before).
-        if (MODE == A16_SPARSE) {
+        if (MODE != A16_SLIDING) {
             constexpr int PRE = A16_STAGES;   // tiles 0 .. PRE - 2 are issued here, tile PRE - 1 stays resolved for the loop
             const int ch = tid & 15;
             int rows[PRE][8];
@@ -282,7 +293,8 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
     trace_first(p.ctl.trace, 4);   // queries ready
     trace_last(p.ctl.trace, 6);
     const float scale = rsqrtf(float(HD));
-    float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;     // running max / sum of heads 2c, 2c + 1 over this warp's rows
+    // running max / sum of heads 2c, 2c + 1 over this warp's rows (ReLU²: the maximum stays at zero)
+    float m0 = MODE == A16_FULL ? 0.0f : NEG_BIG, m1 = m0, l0 = 0.0f, l1 = 0.0f;
     float OT[8][4];
 #pragma unroll
     for (int i = 0; i < 8; i++) OT[i][0] = OT[i][1] = OT[i][2] = OT[i][3] = 0.0f;
@@ -350,33 +362,46 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             mma16<DT>(s, x0.x, x1.x, x0.y, x1.y, qb0[2 * m], qb1[2 * m]);
             mma16<DT>(s, x0.z, x1.z, x0.w, x1.w, qb0[2 * m + 1], qb1[2 * m + 1]);
         }
-        s[0] = v0 ? s[0] * scale : NEG_BIG;
-        s[1] = v0 ? s[1] * scale : NEG_BIG;
-        s[2] = v1 ? s[2] * scale : NEG_BIG;
-        s[3] = v1 ? s[3] * scale : NEG_BIG;
-        float tm0 = fmaxf(s[0], s[2]), tm1 = fmaxf(s[1], s[3]);
-#pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-            tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, o));
-            tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, o));
-        }
-        const float n0 = fmaxf(m0, tm0), n1 = fmaxf(m1, tm1);
-        const float f0 = __expf(m0 - n0), f1 = __expf(m1 - n1);
-        m0 = n0;
-        m1 = n1;
         float pw[4];
-        pw[0] = v0 ? __expf(s[0] - m0) : 0.0f;
-        pw[1] = v0 ? __expf(s[1] - m1) : 0.0f;
-        pw[2] = v1 ? __expf(s[2] - m0) : 0.0f;
-        pw[3] = v1 ? __expf(s[3] - m1) : 0.0f;
-        l0 = l0 * f0 + pw[0] + pw[2];
-        l1 = l1 * f1 + pw[1] + pw[3];
+        if (MODE == A16_FULL) {
+            // ReLU²: no maximum, nothing to rescale; the row sums take the weights themselves, P a power of two of them
+            const float a0 = fmaxf(s[0] * scale, 0.0f), a1 = fmaxf(s[1] * scale, 0.0f), a2 = fmaxf(s[2] * scale, 0.0f), a3 = fmaxf(s[3] * scale, 0.0f);
+            const float w0 = v0 ? a0 * a0 : 0.0f, w1 = v0 ? a1 * a1 : 0.0f, w2 = v1 ? a2 * a2 : 0.0f, w3 = v1 ? a3 * a3 : 0.0f;
+            l0 += w0 + w2;
+            l1 += w1 + w3;
+            constexpr float ps = (DT == EMBLA_F16) ? 0.015625f : 1.0f;
+            pw[0] = w0 * ps;
+            pw[1] = w1 * ps;
+            pw[2] = w2 * ps;
+            pw[3] = w3 * ps;
+        } else {
+            s[0] = v0 ? s[0] * scale : NEG_BIG;
+            s[1] = v0 ? s[1] * scale : NEG_BIG;
+            s[2] = v1 ? s[2] * scale : NEG_BIG;
+            s[3] = v1 ? s[3] * scale : NEG_BIG;
+            float tm0 = fmaxf(s[0], s[2]), tm1 = fmaxf(s[1], s[3]);
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            OT[i][0] *= f0;
-            OT[i][1] *= f1;
-            OT[i][2] *= f0;
-            OT[i][3] *= f1;
+            for (int o = 4; o < 32; o <<= 1) {
+                tm0 = fmaxf(tm0, __shfl_xor_sync(0xffffffffu, tm0, o));
+                tm1 = fmaxf(tm1, __shfl_xor_sync(0xffffffffu, tm1, o));
+            }
+            const float n0 = fmaxf(m0, tm0), n1 = fmaxf(m1, tm1);
+            const float f0 = __expf(m0 - n0), f1 = __expf(m1 - n1);
+            m0 = n0;
+            m1 = n1;
+            pw[0] = v0 ? __expf(s[0] - m0) : 0.0f;
+            pw[1] = v0 ? __expf(s[1] - m1) : 0.0f;
+            pw[2] = v1 ? __expf(s[2] - m0) : 0.0f;
+            pw[3] = v1 ? __expf(s[3] - m1) : 0.0f;
+            l0 = l0 * f0 + pw[0] + pw[2];
+            l1 = l1 * f1 + pw[1] + pw[3];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                OT[i][0] *= f0;
+                OT[i][1] *= f1;
+                OT[i][2] *= f0;
+                OT[i][3] *= f1;
+            }
         }
         const uint8_t* vA = Vt + (R0 + kA) * 128 + ((g ^ kA) << 4);
         const uint8_t* vB = Vt + (R0 + kB) * 128 + ((g ^ kB) << 4);
@@ -476,7 +501,7 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             num += red[w][hh][d] * f;
         }
         if (nch == 1) {
-            Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
+            Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, a16_finish<DT, MODE>(num, L));
         } else if (CL) {
             const uint32_t row = cluster_map(smem_u32(inbox + (chunk * slots + hh / nch) * A16_PART), uint32_t(hh % nch));
             cluster_st_f32(row + uint32_t(d) * 4u, num);
@@ -518,7 +543,7 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
                 L += lc[r] * f;
                 num += ac[r] * f;
             }
-            Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
+            Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, a16_finish<DT, MODE>(num, L));
         }
         trace_last(p.ctl.trace, 3);
         return;
@@ -557,7 +582,7 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             L += q2[HD + 1] * f;
             num += q2[d] * f;
         }
-        Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, num / L);
+        Act<DT>::store(p.o, size_t(b) * p.o_stride + size_t(kvh * p.G + hh) * HD + d, a16_finish<DT, MODE>(num, L));
     }
     trace_last(p.ctl.trace, 3);
 }

@@ -355,4 +355,8 @@ typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cu
                                            CUtensorMapFloatOOBfill);
 TensorMapEncodeTiledFn tensor_map_encoder();
 
+// full-layer (ReLU²) decode over a 16-bit pool (attn16_decode.cu), reached from embla_attn_full_decode
+EmblaStatus attn16_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view, const EmblaQuery* q, void* o_dev,
+                               int64_t o_stride, int max_len, cudaStream_t stream);
+
 }  // namespace embla

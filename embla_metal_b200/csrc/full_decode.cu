@@ -669,7 +669,6 @@ static EmblaStatus full_decode_impl(EmblaAttn* ctx, const EmblaKVPool* pool, con
                                     const void* v_new, int64_t kv_stride, int32_t norm_k, void* stream) {
     if (!ctx || !pool || !view || !q || !o_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode: null argument");
     EMBLA_CHECK_DEVICE("embla_attn_full_decode", ctx, pool);
-    if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_decode: the pool is not int8");
     if (pool->n_kv_heads != ctx->cfg.n_kv_heads)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode: pool has %d kv heads, context %d", pool->n_kv_heads,
                    ctx->cfg.n_kv_heads);
@@ -684,6 +683,22 @@ static EmblaStatus full_decode_impl(EmblaAttn* ctx, const EmblaKVPool* pool, con
     const int max_len = view->max_seq_len > 0 ? view->max_seq_len : ctx->cfg.max_context;
     if (max_len > ctx->cfg.max_context)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_full_decode: max_seq_len %d over the context's %d", max_len, ctx->cfg.max_context);
+
+    if (pool->kv_dtype == EMBLA_KV_16BIT) {
+        // The reference's build without the int8 cache (EMBLA_KV8=0: attn_full, attention.metal:148-220): the rows are stored
+        // in the activation dtype and the same entry point serves it, as separate launches: the key scores (SCORES: the
+        // scoring pass of the sparse layers, which needs the queries as they enter the dot products), then the ReLU²
+        // attention over every key. The token's row is appended with embla_kv_append beforehand.
+        if (k_new) {
+            EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_step: a 16-bit pool takes embla_kv_append, then embla_attn_full_decode");
+        }
+        if (scores_dev) {
+            if (!q->prenormed) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_decode: key scores over a 16-bit pool need prenormed queries");
+            if (EmblaStatus st = embla_score_keys(ctx, pool, view, q->q_dev, q->q_stride, scores_dev, scores_stride, stream)) return st;
+        }
+        return attn16_full_decode(ctx, pool, view, q, o_dev, o_stride, max_len, static_cast<cudaStream_t>(stream));
+    }
+    if (pool->kv_dtype != EMBLA_KV_INT8) EMBLA_FAIL(EMBLA_UNSUPPORTED, "embla_attn_full_decode: unknown pool dtype %d", pool->kv_dtype);
 
     FullDecodeParams p = {};
     p.pool = pool->base;

@@ -166,7 +166,10 @@ EmblaStatus embla_kv_append(EmblaAttn* ctx, EmblaKVPool* pool, const EmblaKVView
  * combine. o_dev is [batch][o_stride] elements, head h at h * 128. When `scores_dev` is not NULL
  * (the reference's SCORES variant, attention.metal:146, 296-306) the kernel also writes
  * scores[b][kv head][j] = max over the kv head's query heads of q·k_j·kscale_j for j < seq_len,
- * rows of `scores_stride` floats, bit-exact against the oracle's summation order. */
+ * rows of `scores_stride` floats, bit-exact against the oracle's summation order.
+ * A 16-bit pool is served too: the reference's build without the int8 cache (EMBLA_KV8=0, Engine.swift:163: attn_full,
+ * attention.metal:148-220), the rows in the activation dtype and no scales; the scores then come from a scoring pass of
+ * their own ahead of the attention (queries prenormed), and embla_attn_full_step is refused (embla_kv_append first). */
 EmblaStatus embla_attn_full_decode(EmblaAttn* ctx, const EmblaKVPool* pool, const EmblaKVView* view,
                                    const EmblaQuery* q, void* o_dev, int64_t o_stride,
                                    float* scores_dev, int64_t scores_stride, void* stream);

@@ -33,13 +33,17 @@ def _events(fn, reps=10, warm=3):
     return sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(reps))
 
 
-def full_decode(batch, scores):
+def full_decode(batch, scores, kv16=False):
     npg = CTX // 128
     ctx = attn.Attention(HQ, HKV, attn.F16, max_batch=batch, max_context=CTX)
-    pool = attn.KVPool(1, HKV, batch * npg, attn.KV_INT8, attn.SCALE_F16)
-    raw = pool.raw()
-    raw.view(-1).random_(0, 256)
-    raw[..., 32768:].view(torch.float16).fill_(0.01)
+    if kv16:   # the build without the int8 cache: rows in the activation dtype, 512 B a key
+        pool = attn.KVPool(1, HKV, batch * npg, attn.KV_16BIT)
+        pool.raw().view(torch.float16).normal_()
+    else:
+        pool = attn.KVPool(1, HKV, batch * npg, attn.KV_INT8, attn.SCALE_F16)
+        raw = pool.raw()
+        raw.view(-1).random_(0, 256)
+        raw[..., 32768:].view(torch.float16).fill_(0.01)
     table = torch.randperm(batch * npg, device="cuda", dtype=torch.int32).view(batch, npg).contiguous()
     lens = torch.full((batch,), CTX, dtype=torch.int32, device="cuda")
     q = torch.randn(batch, HQ * 128, device="cuda", dtype=torch.float16)
@@ -47,8 +51,8 @@ def full_decode(batch, scores):
     sc = torch.zeros(batch, HKV, CTX, device="cuda") if scores else None
     ts = _events(lambda: ctx.full_decode(pool, table, lens, 0, q, o, scores=sc, max_seq_len=CTX))
     ctx.check()
-    nbytes = batch * HKV * CTX * 260
-    print(f"full_decode batch {batch} scores {bool(scores)}: {1e3 * ts[len(ts) // 2]:.1f} us/launch, "
+    nbytes = batch * HKV * CTX * (512 if kv16 else 260)
+    print(f"full_decode{' (16-bit cache)' if kv16 else ''} batch {batch} scores {bool(scores)}: {1e3 * ts[len(ts) // 2]:.1f} us/launch, "
           f"{nbytes / ts[len(ts) // 2] / 1e6:.0f} GB/s (min {nbytes / ts[0] / 1e6:.0f})")
 
 
@@ -122,11 +126,12 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--scores", action="store_true")
     ap.add_argument("--qk8", action="store_true", help="prefill: the int8 Q K^T build")
+    ap.add_argument("--kv16", action="store_true", help="full_decode: a 16-bit cache instead of int8")
     ap.add_argument("--tokens", type=int, default=2048)
     ap.add_argument("--cached", type=int, default=30720)
     a = ap.parse_args()
     if a.case == "full_decode":
-        full_decode(a.batch, a.scores)
+        full_decode(a.batch, a.scores, a.kv16)
     elif a.case == "sparse":
         sparse(a.batch)
     elif a.case == "sliding_prefill":
