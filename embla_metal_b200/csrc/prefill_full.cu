@@ -64,6 +64,8 @@ struct PrefillParams {
     int64_t q_token_stride, q_seq_stride, o_token_stride, o_seq_stride;
     size_t page_bytes;
     int table_stride, layer, n_layers, n_kv_heads, G, scale_bytes, rows_per_page, n_tokens, prenormed, nsplit;
+    int cls;              // cluster size (0: none, else = nsplit): the page ranges of a unit are the CTAs of one thread-block
+                          // cluster, whose partial sums stay in shared memory
 };
 
 // One side (K or V) of a raw int8 page -> fp16 in the UMMA layout. 128 converter threads; lanes of a
@@ -150,7 +152,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     const int jb = split * pps, je = min(n_all, jb + pps);
     const int n = max(0, je - jb);
 
-    if (tid == 0) {
+    // The producer lane sets the barriers up and requests the first pages while the other warps stage the query tiles.
+    if (warp == PF_PRODUCER && lane == 0) {
         for (int i = 0; i < 3; i++) {
             mbar_init(&raw_full[i], 1);
             mbar_init(&raw_empty[i], PF_CONV_WARPS);
@@ -167,15 +170,69 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         s_abort = 0;
         fence_barrier_init();
     }
+    // conversion c = 2 j + side takes ring slot c % 3; page j's scales go to scl[j & 1]
+    auto request = [&](int c) {
+        const int j = jb + (c >> 1), side = c & 1, slot = c % 3;
+        const int block = p.block_table[size_t(b) * p.table_stride + j];
+        const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
+        mbar_expect_tx(&raw_full[slot], CODE_BYTES + (side == 0 ? 2 * BLK * SB : 0));
+        tma_load_2d(raw + slot * CODE_BYTES, &tmap, 0, int(page * p.rows_per_page) + side * BLK, &raw_full[slot]);
+        if (side == 0)
+            bulk_load_1d(scl + ((c >> 1) & 1) * 1024, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB, &raw_full[slot]);
+    };
+    int requested = 0;        // (producer lane) conversions requested so far
+    if (warp == PF_PRODUCER && lane == 0)
+        for (; requested < min(3, 2 * n) && requested != p.ctl.stall_at; requested++) request(requested);
     if (warp == PF_MMA) tmem_alloc(&s_tmem, 512);
+    // the staging warps: every warp but the producer
+    constexpr int SW = PF_THREADS / 32 - 1;
+    const int swarp = warp < PF_PRODUCER ? warp : warp - 1, stid = swarp * 32 + lane;
 
     // ---- Q tiles: [128 tokens][128 dims] of head h as fp16 in the K-major swizzled layout
-    for (int x = 0; x < 2; x++) {
+    if (!QK8 && p.prenormed && warp != PF_PRODUCER) {
+        // rows as they are, times the query scale: 16 bytes a thread and trip, every load of a thread (both tiles) in flight
+        // before the first store
+        constexpr int TRIPS = (BLK * 16 + SW * 32 - 1) / (SW * 32);
+        uint4 v[2][TRIPS];
+#pragma unroll
+        for (int x = 0; x < 2; x++)
+#pragma unroll
+            for (int k = 0; k < TRIPS; k++) {
+                const int i = stid + k * (SW * 32), r = i >> 4, c8 = i & 15;
+                v[x][k] = make_uint4(0, 0, 0, 0);
+                if (i < BLK * 16 && r < rows[x]) {
+                    const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + r) * p.q_token_stride + size_t(h) * HD + c8 * 8;
+                    v[x][k] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
+                }
+            }
+#pragma unroll
+        for (int x = 0; x < 2; x++)
+#pragma unroll
+            for (int k = 0; k < TRIPS; k++) {
+                const int i = stid + k * (SW * 32), r = i >> 4, c8 = i & 15;
+                if (i >= BLK * 16) continue;
+                uint32_t* w = &v[x][k].x;
+                if (DT == EMBLA_BF16) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++)
+                        w[e] = pack_h2(__uint_as_float(w[e] << 16) * PF_QSCALE, __uint_as_float(w[e] & 0xffff0000u) * PF_QSCALE);
+                } else {
+                    const __half2 qs2 = __float2half2_rn(PF_QSCALE);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const __half2 t = __hmul2(*reinterpret_cast<const __half2*>(&w[e]), qs2);
+                        w[e] = *reinterpret_cast<const uint32_t*>(&t);
+                    }
+                }
+                *reinterpret_cast<uint4*>(Qs + x * PF_TILE16 + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v[x][k];
+            }
+    }
+    for (int x = 0; x < 2 && warp != PF_PRODUCER && (QK8 || !p.prenormed); x++) {
         uint8_t* Qx = Qs + x * PF_TILE16;
         if (QK8) {
             // one warp a row, four rows a trip with their loads in flight together: head norm (unless the rows come normed),
             // then the row as int8 codes, K-major [128 rows][128 B] under the 128-byte swizzle, and its scale
-            for (int r4 = warp * 4; r4 < BLK; r4 += 4 * (PF_THREADS / 32)) {
+            for (int r4 = swarp * 4; r4 < BLK; r4 += 4 * SW) {
                 float xq[4][4];
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
@@ -216,33 +273,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                     }
                 }
             }
-        } else if (p.prenormed) {
-            for (int i = tid; i < BLK * 16; i += PF_THREADS) {
-                const int r = i >> 4, c8 = i & 15;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (r < rows[x]) {
-                    const size_t off = size_t(b) * p.q_seq_stride + size_t(t0[x] + r) * p.q_token_stride + size_t(h) * HD + c8 * 8;
-                    v = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.q) + off);
-                    uint32_t* w = &v.x;
-                    if (DT == EMBLA_BF16) {
-#pragma unroll
-                        for (int e = 0; e < 4; e++)
-                            w[e] = pack_h2(__uint_as_float(w[e] << 16) * PF_QSCALE, __uint_as_float(w[e] & 0xffff0000u) * PF_QSCALE);
-                    } else {
-                        const __half2 qs2 = __float2half2_rn(PF_QSCALE);
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const __half2 t = __hmul2(*reinterpret_cast<const __half2*>(&w[e]), qs2);
-                            w[e] = *reinterpret_cast<const uint32_t*>(&t);
-                        }
-                    }
-                }
-                *reinterpret_cast<uint4*>(Qx + (c8 >> 3) * (BLK * 128) + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = v;
-            }
         } else {
             // q_prep_b: head norm with both gains in the oracle's operation order, rounded to the activation dtype; four
             // rows a warp and trip, their loads in flight together before the norms
-            for (int r4 = warp * 4; r4 < BLK; r4 += 4 * (PF_THREADS / 32)) {
+            for (int r4 = swarp * 4; r4 < BLK; r4 += 4 * SW) {
                 float xq[4][4];
 #pragma unroll
                 for (int k = 0; k < 4; k++) {
@@ -287,23 +321,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     // TMEM columns: S/P of tile 0 at 0, of tile 1 at 128 (P overwrites the first 64 columns of its S); O at 256, 384
 
     if (warp == PF_PRODUCER) {
-        // ---- TMA producer: conversion c = 2 j + side takes ring slot c % 3; page j's scales go to scl[j & 1]
+        // ---- TMA producer: the conversions after the first three, each once its ring slot is free
         if (lane == 0) {
-            for (int c = 0; c < 2 * n; c++) {
-                const int j = jb + (c >> 1), side = c & 1, slot = c % 3;
+            for (int c = requested; c < 2 * n; c++) {
+                const int slot = c % 3;
                 if (c == p.ctl.stall_at) break;   // diagnostic stall: the converters' wait for this side runs out
                 if (c >= 3 && !mbar_wait_bounded(p.ctl.wait_cycles, &raw_empty[slot], ((c / 3) - 1) & 1)) {
                     atomicExch(p.ctl.err, ERR_WAIT_EMPTY);
                     break;
                 }
                 if (*reinterpret_cast<volatile int*>(&s_abort)) break;
-                const int block = p.block_table[size_t(b) * p.table_stride + j];
-                const long page = (long(block) * p.n_layers + p.layer) * p.n_kv_heads + kvh;
-                mbar_expect_tx(&raw_full[slot], CODE_BYTES + (side == 0 ? 2 * BLK * SB : 0));
-                tma_load_2d(raw + slot * CODE_BYTES, &tmap, 0, int(page * p.rows_per_page) + side * BLK, &raw_full[slot]);
-                if (side == 0)
-                    bulk_load_1d(scl + ((c >> 1) & 1) * 1024, p.pool + size_t(page) * p.page_bytes + 2 * CODE_BYTES, 2 * BLK * SB,
-                                 &raw_full[slot]);
+                request(c);
             }
         }
     } else if (warp == PF_MMA) {
@@ -491,16 +519,30 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             // unnormalised O and the row sum of this page range into the scratch (zeros if the tile saw no page here)
             tc_fence_after();
             const int unit = (b * gridDim.y + h) * (gridDim.x / p.nsplit) + pair_ix;
-            // column-major [128 + 1][128 rows]: the 32 rows of a warp write 32 consecutive floats of a column
-            float* pcol = p.partials + ((size_t(unit) * p.nsplit + split) * 2 + x) * (BLK * (HD + 1)) + r;
+            if (p.cls) {
+                // cluster: this CTA's partial stays in its own shared memory (everything from the query tiles on is free
+                // once the last product has completed), row-major [2 tiles][128 rows][128 + 1], for the cluster to read
+                float* prow = reinterpret_cast<float*>(smem) + size_t(x * BLK + r) * (HD + 1);
 #pragma unroll 1
-            for (int cc = 0; cc < 4; cc++) {
-                uint32_t acc[32];
-                if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, acc);
+                for (int cc = 0; cc < 4; cc++) {
+                    uint32_t acc[32];
+                    if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, acc);
 #pragma unroll
-                for (int e = 0; e < 32; e++) pcol[size_t(32 * cc + e) * BLK] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
+                    for (int e = 0; e < 32; e++) prow[32 * cc + e] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
+                }
+                prow[HD] = rowsum;
+            } else {
+                // column-major [128 + 1][128 rows]: the 32 rows of a warp write 32 consecutive floats of a column
+                float* pcol = p.partials + ((size_t(unit) * p.nsplit + split) * 2 + x) * (BLK * (HD + 1)) + r;
+#pragma unroll 1
+                for (int cc = 0; cc < 4; cc++) {
+                    uint32_t acc[32];
+                    if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, acc);
+#pragma unroll
+                    for (int e = 0; e < 32; e++) pcol[size_t(32 * cc + e) * BLK] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
+                }
+                pcol[size_t(HD) * BLK] = rowsum;
             }
-            pcol[size_t(HD) * BLK] = rowsum;
         } else if (nx > 0) {
             tc_fence_after();
             const float inv = 1.0f / (sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + r] : 1.0f) + rowsum);
@@ -533,7 +575,65 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             }
         }
     }
-    if (p.nsplit > 1) {
+    if (p.nsplit > 1 && p.cls) {
+        // Cluster combine: after one cluster barrier every range's partial is complete in its CTA's shared memory; the CTA of
+        // rank k then owns a slice of the rows of both tiles and adds the cluster's ranges in order over distributed shared
+        // memory (common.metal:88-99, without a last arriver: every SM of the cluster takes a share). A second barrier
+        // keeps every CTA's shared memory alive until its peers have read it.
+        const int cl = p.cls, rank = split;
+        cluster_arrive();
+        cluster_wait();
+        const int R = (BLK + cl - 1) / cl;                           // rows of a tile this CTA finishes
+        float* den = reinterpret_cast<float*>(smem + (2 + PF_KVBUFS) * PF_TILE16);   // [2][R], behind the partial
+        const uint32_t part0 = smem_u32(smem);
+        {
+            // (the loads of an element from all ranges are issued before the first is used: each crosses the SM-to-SM network)
+            for (int i = tid; i < 2 * R; i += PF_THREADS) {
+                const int x = i / R, r = rank * R + i % R;
+                if (r >= BLK) continue;
+                float v[8];
+#pragma unroll
+                for (int sp = 0; sp < 8; sp++)
+                    v[sp] = sp < cl ? cluster_ld_f32(cluster_map(part0 + uint32_t((x * BLK + r) * (HD + 1) + HD) * 4u, uint32_t(sp))) : 0.0f;
+                float sum = 0.0f;
+#pragma unroll
+                for (int sp = 0; sp < 8; sp++) sum += v[sp];
+                den[i] = sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + r] : 1.0f) + sum;
+            }
+            __syncthreads();
+            for (int it = tid; it < 2 * R * (HD / 2); it += PF_THREADS) {
+                const int i = it / (HD / 2), c = 2 * (it % (HD / 2));
+                const int x = i / R, r = rank * R + i % R;
+                if (r >= rows[x]) continue;
+                const uint32_t at = part0 + uint32_t((x * BLK + r) * (HD + 1) + c) * 4u;
+                float v0[8], v1[8];
+#pragma unroll
+                for (int sp = 0; sp < 8; sp++) {
+                    const uint32_t ra = cluster_map(at, uint32_t(sp < cl ? sp : 0));
+                    v0[sp] = sp < cl ? cluster_ld_f32(ra) : 0.0f;
+                    v1[sp] = sp < cl ? cluster_ld_f32(ra + 4u) : 0.0f;
+                }
+                float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+                for (int sp = 0; sp < 8; sp++) {
+                    a0 += v0[sp];
+                    a1 += v1[sp];
+                }
+                const float inv = 1.0f / den[i];
+                uint32_t w;
+                if (DT == EMBLA_F16) w = pack_h2(a0 * inv, a1 * inv);
+                else {
+                    __nv_bfloat162 t = __floats2bfloat162_rn(a0 * inv, a1 * inv);
+                    w = *reinterpret_cast<uint32_t*>(&t);
+                }
+                const size_t off = size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD + c;
+                *reinterpret_cast<uint32_t*>(static_cast<uint16_t*>(p.o) + off) = w;
+                for (int pr = 0; pr < p.n_peers; pr++) *reinterpret_cast<uint32_t*>(static_cast<uint16_t*>(p.o_peer[pr]) + off) = w;
+            }
+            cluster_arrive();
+            cluster_wait();
+        }
+    } else if (p.nsplit > 1) {
         // the last CTA of the unit to arrive adds the page ranges in order and writes the rows (common.metal:88-99)
         __shared__ int s_last;
         const int unit = (b * gridDim.y + h) * (gridDim.x / p.nsplit) + pair_ix;
@@ -555,16 +655,43 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             float* den = tile + BLK * (HD + 1);                   // [128]
             for (int x = 0; x < 2; x++) {
                 const float* base = p.partials + (size_t(unit) * p.nsplit * 2 + x) * (BLK * (HD + 1));
-                for (int c = warp; c <= HD; c += PF_THREADS / 32) {
-                    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    for (int sp = 0; sp < p.nsplit; sp++) {
+                // A lane takes four consecutive rows of a column (16 bytes a range and load), a warp two columns at a time with
+                // up to eight ranges' loads of each in flight: the partials sit in L2 or are still on their way from the
+                // other SMs, and this one CTA has 1.2 MB of them to read.
+                constexpr int NW = PF_THREADS / 32;
+                for (int c = warp; c <= HD; c += 2 * NW) {
+                    const bool two = c + NW <= HD;
+                    float4 acc[2] = {make_float4(0.0f, 0.0f, 0.0f, 0.0f), make_float4(0.0f, 0.0f, 0.0f, 0.0f)};
+                    for (int sp0 = 0; sp0 < p.nsplit; sp0 += 8) {
+                        float4 t[2][8];
 #pragma unroll
-                        for (int i = 0; i < 4; i++) acc[i] += __ldcg(base + sp * sstride + size_t(c) * BLK + lane + 32 * i);
+                        for (int k = 0; k < 2; k++)
+#pragma unroll
+                            for (int u = 0; u < 8; u++)
+                                t[k][u] = (sp0 + u < p.nsplit && (k == 0 || two))
+                                              ? __ldcg(reinterpret_cast<const float4*>(base + (sp0 + u) * sstride + size_t(c + k * NW) * BLK) + lane)
+                                              : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                        for (int k = 0; k < 2; k++)
+#pragma unroll
+                            for (int u = 0; u < 8; u++) {
+                                acc[k].x += t[k][u].x;
+                                acc[k].y += t[k][u].y;
+                                acc[k].z += t[k][u].z;
+                                acc[k].w += t[k][u].w;
+                            }
                     }
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        if (c < HD) tile[(lane + 32 * i) * (HD + 1) + c] = acc[i];
-                        else den[lane + 32 * i] = sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + lane + 32 * i] : 1.0f) + acc[i];
+                    for (int k = 0; k < 2; k++) {
+                        const int cc = c + k * NW;
+                        if (k == 1 && !two) continue;
+                        const float v[4] = {acc[k].x, acc[k].y, acc[k].z, acc[k].w};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int row = 4 * lane + i;
+                            if (cc < HD) tile[row * (HD + 1) + cc] = v[i];
+                            else den[row] = sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + row] : 1.0f) + v[i];
+                        }
                     }
                 }
                 __syncthreads();
@@ -622,32 +749,82 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     // a unit are split over several CTAs whose partial sums the last one adds (ReLU² partials are additive).
     const int pairs = (p.n_tokens + 2 * BLK - 1) / (2 * BLK);
     const int units = pairs * ctx->cfg.n_q_heads * batch;
-    // Page ranges per unit: the count that minimises (waves of CTAs over the SMs) x (pages of a range + the fixed cost
-    // of a CTA: about 2 pages' worth for the query load, TMEM set-up and pipeline fill, and when the unit is split about 9
-    // (132 KB of partials written, then added by the unit's last CTA)), ranges of at least 8 pages, at most 16. Measured at
-    // 128 units x 252 pages on 148 SMs: 1 range 0.53 ms, 2: 0.57, 4: 0.59, 8: 0.60 - one range is best there.
-    // The partial sums live in scratch that embla_attn_reserve_prefill allocated (this call never allocates or
-    // synchronises): a split is taken only as far as that scratch holds it; without a reserve every unit is one CTA.
+    // Page ranges per unit: the split that minimises (waves of CTAs over the SMs) x (pages of a range + the fixed cost of a
+    // CTA). Two ways to add the ranges' partial sums (ReLU² partials are additive), costs in pages' worth as measured on
+    // the shards of config 3 (a page is 1.8 us of a CTA):
+    //   ns ranges through global scratch, added by the unit's last CTA to arrive: 2 for a lone CTA (query load, TMEM
+    //     set-up, pipeline fill), 9 + ns when split (132 KB of partials written by each, all read back by one SM);
+    //   the ranges as one thread-block cluster of cl <= 8 CTAs, added over distributed shared memory, every CTA finishing a
+    //     slice of the rows: about 9 + cl / 4, and no scratch (32 units x 4 ranges: 141 us against 150).
+    // A cluster split is taken only in as many waves as cudaOccupancyMaxActiveClusters says the GPU holds at once (a
+    // cluster needs its SMs inside one GPC: 15 clusters of 8 CTAs of this kernel, 213 KB of shared memory each, 33 of 4, 74
+    // of 2); EMBLA_NO_CLUSTER=1 turns clusters off. Several clusters a unit, their slices meeting in the scratch, measured
+    // no faster than plain ranges through the scratch (16 units: 86-93 us either way; the CTAs of a unit finish up to 16 us
+    // apart, which either combine waits out) and are not kept. Ranges hold at least 8 pages; at most 16 ranges. The scratch
+    // is what embla_attn_reserve_prefill allocated (this call never allocates or synchronises): a split through it is taken
+    // only as far as it holds; without a reserve only lone CTAs and clusters remain.
     const long slots = long(ctx->prefill_scratch_bytes / PF_SLOT_BYTES);
-    int nsplit = 1;
+    static const bool use_clusters = []() { const char* e = getenv("EMBLA_NO_CLUSTER"); return !(e && e[0] == '1'); }();
+    static int max_clusters[64][9] = {};     // per device and cluster size; 0 = not asked yet, -1 = none
+    auto clusters_at_once = [&](int cl) {
+        int& mc = max_clusters[ctx->device & 63][cl];
+        if (mc == 0) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(cl, 1, 1);
+            cfg.blockDim = dim3(PF_THREADS);
+            cfg.dynamicSmemBytes = PF_SMEM;
+            cudaLaunchAttribute at;
+            at.id = cudaLaunchAttributeClusterDimension;
+            at.val.clusterDim.x = unsigned(cl);
+            at.val.clusterDim.y = 1;
+            at.val.clusterDim.z = 1;
+            cfg.attrs = &at;
+            cfg.numAttrs = 1;
+            int n = 0;
+            mc = (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) ? n : -1;
+            (void)cudaGetLastError();
+        }
+        return mc;
+    };
+    int nsplit = 1, cls = 0;
     long best = -1;
-    for (int ns = 1; ns <= 16 && (ns == 1 || (max_pages / ns >= 8 && long(units) * ns <= slots && units <= ctx->prefill_counters)); ns++) {
-        const long waves = (long(units) * ns + ctx->sm_count - 1) / ctx->sm_count;
-        const long cost = waves * ((max_pages + ns - 1) / ns + (ns > 1 ? 9 : 2));
-        if (best < 0 || cost < best) {
-            best = cost;
-            nsplit = ns;
+    for (int cl = 1; cl <= (use_clusters ? 8 : 1); cl++) {
+        for (int ng = 1; cl * ng <= 16; ng++) {
+            const int ns = cl * ng;
+            if (ns > 1 && max_pages / ns < 8) break;
+            if (cl > 1 && ng > 1) break;                                              // a cluster holds all ranges of its unit
+            if (ng > 1 && (long(units) * ng > slots || units > ctx->prefill_counters)) break;   // the ranges meet in the scratch
+            long waves;
+            if (cl == 1) {
+                waves = (long(units) * ns + ctx->sm_count - 1) / ctx->sm_count;
+            } else {
+                const int mc = clusters_at_once(cl);
+                if (mc <= 0) break;
+                waves = (long(units) * ng + mc - 1) / mc;
+            }
+            const long fixed2 = ns == 1 ? 4 : (cl == 1 ? 18 + 2 * ns : 18 + cl / 2);   // in half pages
+            const long cost = waves * (2 * ((max_pages + ns - 1) / ns) + fixed2);
+            if (best < 0 || cost < best) {
+                best = cost;
+                nsplit = ns;
+                cls = cl > 1 ? cl : 0;
+            }
         }
     }
     p.nsplit = nsplit;
+    p.cls = cls;
     p.partials = nullptr;
     p.counters = nullptr;
-    if (nsplit > 1) {
+    if (nsplit > 1 && !cls) {
         // the counters sit after the partials and are left at zero by every launch
         p.partials = reinterpret_cast<float*>(ctx->prefill_scratch);
         p.counters = reinterpret_cast<int*>(ctx->prefill_scratch + ctx->prefill_scratch_bytes);
     }
     dim3 grid(pairs * nsplit, ctx->cfg.n_q_heads, batch);
+    if (cls) {
+        EMBLA_CUDA_TRY(launch_kernel_cluster(false, cls, kern, grid, dim3(PF_THREADS), PF_SMEM, s, pool->tmap_half, p));
+        return EMBLA_OK;
+    }
     kern<<<grid, PF_THREADS, PF_SMEM, s>>>(pool->tmap_half, p);
     EMBLA_CUDA_TRY(cudaGetLastError());
     return EMBLA_OK;
