@@ -282,6 +282,8 @@ def run_gpu(args, rank, world):
         clocks = sampler.result() if sampler else None
         dom_ms, dom_n = st.read_probe()
         st.set_probe(None)
+        for _ in range(max(3, args.warmup)):     # (its copy streams and events are made on first use)
+            st.step_host()
         e2e_ms = timed(st.step_host, args.steps)
         st.ctx.check()
         ms_per_step = total_ms / args.steps

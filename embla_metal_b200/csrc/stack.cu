@@ -157,8 +157,17 @@ static EmblaStatus probe_mark(EmblaStack* st, int entry, cudaStream_t s) {
     } while (0)
 
 extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackStep* step, void* stream) {
+    if (!st) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_step: null argument");
+    return embla_stack_decode_layers(st, step, 0, int32_t(st->layers.size()), stream);
+}
+
+extern "C" EmblaStatus embla_stack_decode_layers(EmblaStack* st, const EmblaStackStep* step, int32_t first_layer, int32_t n_layers,
+                                                 void* stream) {
     if (!st || !step || !step->qkv_dev || !step->o_dev || !step->seq_lens_dev || !step->pos_dev)
         EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_step: null argument");
+    if (first_layer < 0 || n_layers < 0 || size_t(first_layer) + size_t(n_layers) > st->layers.size())
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_layers: layers %d .. %d of %d", first_layer, first_layer + n_layers,
+                   int(st->layers.size()));
     EmblaAttn* ctx = st->ctx;
     const int Hq = ctx->cfg.n_q_heads, Hkv = ctx->cfg.n_kv_heads, B = step->batch;
     if (B <= 0 || B > ctx->cfg.max_batch) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_decode_step: batch %d", B);
@@ -179,7 +188,7 @@ extern "C" EmblaStatus embla_stack_decode_step(EmblaStack* st, const EmblaStackS
         }
     } pdl_scope(ctx, use_pdl ? 1 : 0);
     int last_write = -2;   // -2: nothing of this step launched yet
-    for (size_t li = 0; li < st->layers.size(); li++) {
+    for (size_t li = size_t(first_layer); li < size_t(first_layer) + size_t(n_layers); li++) {
         const EmblaLayerDesc& L = st->layers[li];
         const uint8_t* row = static_cast<const uint8_t*>(step->qkv_dev) + li * step->qkv_layer_stride * esz;
         const void* qp = row;

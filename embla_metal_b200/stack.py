@@ -160,11 +160,44 @@ class DecodeStack:
                         o.stride(0), pos0.data_ptr(), self.table.data_ptr(), self.table.stride(0), b, t, max_seq_len, kv_only_layers)
         attn._check(attn.lib().embla_stack_prefill_chunk(self.handle, C.byref(ck), attn._stream()))
 
-    def step_host(self):
-        """One decode step from pinned host rows: qkv_host -> device, attention, o -> o_host."""
-        self.qkv.copy_(self.qkv_host, non_blocking=True)
-        self.step()
-        self.o_host.copy_(self.o, non_blocking=True)
+    def step_layers(self, first, count):
+        """The step for layers first .. first + count - 1 only."""
+        st = self._step_struct()
+        attn._check(attn.lib().embla_stack_decode_layers(self.handle, C.byref(st), first, count, attn._stream()))
+
+    def step_host(self, group=4):
+        """One decode step from pinned host rows: qkv_host -> device, attention, o -> o_host. The rows travel in groups of
+        `group` layers on two copy streams of their own, so a group's rows arrive while the groups before it are attended
+        and its outputs leave while the groups after it run; the calling stream ends up behind all of it (a synchronize
+        on it, or an event recorded on it, covers the outputs in o_host). group=0: one copy in, the step, one copy out."""
+        if not group:
+            self.qkv.copy_(self.qkv_host, non_blocking=True)
+            self.step()
+            self.o_host.copy_(self.o, non_blocking=True)
+            return
+        cur = torch.cuda.current_stream()
+        n = len(self.kinds)
+        starts = list(range(0, n, group))
+        if getattr(self, "_copy_streams", None) is None:
+            self._copy_streams = (torch.cuda.Stream(), torch.cuda.Stream())
+            self._copy_events = {}
+        if len(self._copy_events.get("in", ())) != len(starts):
+            self._copy_events = {"in": [torch.cuda.Event() for _ in starts], "done": [torch.cuda.Event() for _ in starts]}
+        s_in, s_out = self._copy_streams
+        s_in.wait_stream(cur)          # the step before has read its rows and handed over its outputs
+        s_out.wait_stream(cur)
+        for i, a in enumerate(starts):
+            with torch.cuda.stream(s_in):
+                self.qkv[a:a + group].copy_(self.qkv_host[a:a + group], non_blocking=True)
+                self._copy_events["in"][i].record(s_in)
+        for i, a in enumerate(starts):
+            cur.wait_event(self._copy_events["in"][i])
+            self.step_layers(a, min(group, n - a))
+            self._copy_events["done"][i].record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(self._copy_events["done"][i])
+                self.o_host[a:a + group].copy_(self.o[a:a + group], non_blocking=True)
+        cur.wait_stream(s_out)
 
     def set_probe(self, name):
         attn._check(attn.lib().embla_stack_set_probe(self.handle, -1 if name is None else ENTRY[name]))

@@ -377,6 +377,12 @@ EmblaStatus embla_stack_create(EmblaAttn* ctx, const EmblaLayerDesc* layers, int
                                EmblaKVPool* sparse_pool, const EmblaRing* rings, int32_t n_rings, EmblaStack** out);
 void        embla_stack_destroy(EmblaStack* stack);
 EmblaStatus embla_stack_decode_step(EmblaStack* stack, const EmblaStackStep* step, void* stream);
+/* The same for layers first_layer .. first_layer + n_layers - 1 only (the step's arrays still hold every layer): a caller
+ * whose query rows arrive layer by layer (the q/k/v projections run between the attention layers; a host that feeds them
+ * copies them in while earlier layers run) calls this once per group of layers. A sparse layer that shares a full
+ * layer's cache and selection must be in a later or the same call as that full layer. */
+EmblaStatus embla_stack_decode_layers(EmblaStack* stack, const EmblaStackStep* step, int32_t first_layer, int32_t n_layers,
+                                      void* stream);
 /* The attention branch of Prefill.encode's per-layer loop (Prefill.swift:282-345) as one call: for a chunk of
  * n_tokens new tokens per sequence at positions pos0_dev[b] + t, every layer of the stack in order:
  *   sliding: kv_sliding_b then attn_sliding(8)_b  -> embla_sliding_write + embla_attn_sliding_prefill

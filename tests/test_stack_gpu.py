@@ -69,6 +69,33 @@ def test_step_host_round_trip_and_probe():
     st.close()
 
 
+def test_step_host_in_groups_of_layers():
+    """The host path feeds the query rows in groups of layers on copy streams of their own (embla_stack_decode_layers a
+    group): whatever the grouping, the outputs are those of one copy in, one step, one copy out; three steps in a row
+    with changing rows check that no group's copy runs ahead of the step before it."""
+    import torch
+    from embla_metal_b200 import stack as stk
+    kinds = stk.cycle_kinds(8) + [stk.FULL, stk.SPARSE_SHARED, stk.SPARSE_SHARED, stk.SLIDING]
+    outs = {}
+    for group in (0, 4, 3, 1):
+        st = stk.DecodeStack(kinds, 3, 2048, window=128, ring=512)
+        st.fill_random(2)
+        g = torch.Generator().manual_seed(7)
+        got = []
+        for step in range(3):
+            st.set_positions([2000 + step, 1200 + step, 300 + step])
+            st.qkv_host.copy_(torch.randn(st.qkv_host.shape, generator=g).to(st.dtype))
+            st.step_host(group=group)
+            torch.cuda.current_stream().synchronize()
+            got.append(st.o_host.clone())
+        st.ctx.check()
+        outs[group] = got
+        st.close()
+    for group in (4, 3, 1):
+        for a, b in zip(outs[0], outs[group]):
+            assert torch.equal(a.view(torch.int16), b.view(torch.int16)), f"groups of {group} layers differ"
+
+
 def test_fused_sliding_step_equals_write_then_attend():
     """embla_attn_sliding_step (ring write + attention in one launch, the reference's attn_sliding) against
     embla_sliding_write followed by embla_attn_sliding_decode: same ring contents, same outputs, bit for bit."""
