@@ -190,6 +190,36 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             cp_async16(Vt + dst, base_v + roff[it], valid);
         }
     };
+    // Gathered rows (sparse and full layers): a row's address is two dependent loads away (index list -> block table), so the
+    // three steps run a tile apart: this iteration loads the index rows of the tile five ahead, looks up the blocks of the
+    // tile four ahead from the rows loaded an iteration ago, and turns the blocks loaded an iteration ago into the
+    // offsets of the tile three ahead; no load is used in the iteration that issued it.
+    int irow[8], bblk[8], brow[8];
+    uint32_t ivalid = 0, bvalid = 0;
+    auto load_rows = [&](int t) {
+        ivalid = 0;
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+            const int j = (tile0 + t) * A16_ROWS + it * 8 + (tid >> 4);
+            const bool ok = t < ntile && j < count;
+            ivalid |= uint32_t(ok) << it;
+            irow[it] = ok ? (selecting ? int(p.idx[(size_t(b) * p.n_kv_heads + kvh) * (EMBLA_TOPK + EMBLA_RECENT) + j]) : j) : 0;
+        }
+    };
+    auto load_blocks = [&]() {
+        bvalid = ivalid;
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+            bblk[it] = p.block_table[size_t(b) * p.table_stride + (irow[it] >> 7)];
+            brow[it] = irow[it] & 127;
+        }
+    };
+    auto make_offsets = [&]() {
+        rvalid = bvalid;
+#pragma unroll
+        for (int it = 0; it < 8; it++)
+            roff[it] = ((size_t(bblk[it]) * p.n_layers + p.layer) * p.n_kv_heads + kvh) * p.page_bytes + brow[it] * (HD * 2) + (tid & 15) * 16;
+    };
     // The queries' loads go out first: their latency then overlaps the address chains below instead of following them.
     constexpr int QPW = 8 / (A16_THREADS / 32);   // heads a warp prepares
     float xq[QPW][4];
@@ -204,12 +234,13 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
         // The first tiles' rows are resolved together: all their index loads in flight at once, then all their block-table
         // loads, then the copies (resolved tile by tile, each chain of two dependent loads would follow the one before).
         if (MODE != A16_SLIDING) {
-            constexpr int PRE = A16_STAGES;   // tiles 0 .. PRE - 2 are issued here, tile PRE - 1 stays resolved for the loop
+            constexpr int PRE = A16_STAGES;   // tiles 0 .. PRE - 2 are issued here, tile PRE - 1 stays resolved for the loop,
+                                              // tile PRE has its blocks on the way and tile PRE + 1 its index rows
             const int ch = tid & 15;
-            int rows[PRE][8];
-            uint32_t valid[PRE];
+            int rows[PRE + 1][8];
+            uint32_t valid[PRE + 1];
 #pragma unroll
-            for (int t = 0; t < PRE; t++) {
+            for (int t = 0; t < PRE + 1; t++) {
                 valid[t] = 0;
 #pragma unroll
                 for (int it = 0; it < 8; it++) {
@@ -219,11 +250,18 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
                     rows[t][it] = ok ? (selecting ? int(p.idx[(size_t(b) * p.n_kv_heads + kvh) * (EMBLA_TOPK + EMBLA_RECENT) + j]) : j) : 0;
                 }
             }
+            load_rows(PRE + 1);
             int blocks[PRE][8];
 #pragma unroll
             for (int t = 0; t < PRE; t++)
 #pragma unroll
                 for (int it = 0; it < 8; it++) blocks[t][it] = p.block_table[size_t(b) * p.table_stride + (rows[t][it] >> 7)];
+            bvalid = valid[PRE];
+#pragma unroll
+            for (int it = 0; it < 8; it++) {
+                bblk[it] = p.block_table[size_t(b) * p.table_stride + (rows[PRE][it] >> 7)];
+                brow[it] = rows[PRE][it] & 127;
+            }
 #pragma unroll
             for (int t = 0; t < PRE; t++) {
                 rvalid = valid[t];
@@ -442,7 +480,13 @@ __global__ void __launch_bounds__(A16_THREADS + (TMA ? 32 : 0))
             cons_sync();   // every warp is done with this stage: the tile STAGES - 1 ahead may overwrite it
             if (t + A16_STAGES - 1 < ntile) issue_tile(t + A16_STAGES - 1);
             asm volatile("cp.async.commit_group;" ::: "memory");
-            resolve_tile(t + A16_STAGES);   // its loads fly during the next tile's wait and compute
+            if (MODE == A16_SLIDING) {
+                resolve_tile(t + A16_STAGES);
+            } else {
+                make_offsets();                      // tile t + STAGES, from the blocks looked up an iteration ago
+                load_blocks();                       // tile t + STAGES + 1, from the index rows loaded an iteration ago
+                load_rows(t + A16_STAGES + 2);       // their loads fly during the next tile's wait and compute
+            }
         }
     }
     trace_last(p.ctl.trace, 2);
