@@ -21,7 +21,9 @@ struct EmblaStack {
     uint32_t* idx;        // [max_batch][n_kv_heads][1152]
     int scores_ld;
     // timing probe: events around every launch of one entry point
-    int probe;
+    int probe;            // entry point whose launches are timed (-1: none)
+    int probe_first;      // 1: only the first such launch of a step call
+    int probe_marks;      // events recorded by the current step call
     std::vector<cudaEvent_t> ev;
     int ev_used;
     int early_ok;         // launches may fetch their cache ahead of the preceding kernel (EMBLA_NO_EARLY=1 turns it off)
@@ -77,6 +79,8 @@ EmblaStatus embla_stack_create(EmblaAttn* ctx, const EmblaLayerDesc* layers, int
     st->scores = nullptr;
     st->idx = nullptr;
     st->probe = -1;
+    st->probe_first = 0;
+    st->probe_marks = 0;
     st->ev_used = 0;
     {
         const char* e = getenv("EMBLA_NO_EARLY");
@@ -112,7 +116,8 @@ void embla_stack_destroy(EmblaStack* st) {
 
 EmblaStatus embla_stack_set_probe(EmblaStack* st, int32_t entry) {
     if (!st) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_stack_set_probe: null stack");
-    st->probe = entry;
+    st->probe = entry < 0 ? -1 : (entry & 255);
+    st->probe_first = entry >= 0 && (entry & EMBLA_PROBE_FIRST_ONLY) != 0;
     st->ev_used = 0;
     return EMBLA_OK;
 }
@@ -134,7 +139,8 @@ EmblaStatus embla_stack_read_probe(EmblaStack* st, float* total_ms, int32_t* lau
 }  // extern "C"
 
 static EmblaStatus probe_mark(EmblaStack* st, int entry, cudaStream_t s) {
-    if (st->probe != entry) return EMBLA_OK;
+    if (st->probe != entry || (st->probe_first && st->probe_marks >= 2)) return EMBLA_OK;
+    st->probe_marks++;
     if (st->ev_used == int(st->ev.size())) {
         cudaEvent_t e;
         EMBLA_CUDA_TRY(cudaEventCreate(&e));
@@ -188,6 +194,7 @@ extern "C" EmblaStatus embla_stack_decode_layers(EmblaStack* st, const EmblaStac
         }
     } pdl_scope(ctx, use_pdl ? 1 : 0);
     int last_write = -2;   // -2: nothing of this step launched yet
+    st->probe_marks = 0;
     for (size_t li = size_t(first_layer); li < size_t(first_layer) + size_t(n_layers); li++) {
         const EmblaLayerDesc& L = st->layers[li];
         const uint8_t* row = static_cast<const uint8_t*>(step->qkv_dev) + li * step->qkv_layer_stride * esz;

@@ -199,8 +199,10 @@ class DecodeStack:
                 self.o_host[a:a + group].copy_(self.o[a:a + group], non_blocking=True)
         cur.wait_stream(s_out)
 
-    def set_probe(self, name):
-        attn._check(attn.lib().embla_stack_set_probe(self.handle, -1 if name is None else ENTRY[name]))
+    def set_probe(self, name, first_only=False):
+        """Times every launch of entry point `name` (None: off) with events on the stream, or only the first one of every
+        step when `first_only` (which leaves the step's other launches overlapping as they do unobserved)."""
+        attn._check(attn.lib().embla_stack_set_probe(self.handle, -1 if name is None else ENTRY[name] | (256 if first_only else 0)))
 
     def read_probe(self):
         ms, n = C.c_float(), C.c_int32()

@@ -411,6 +411,9 @@ EmblaStatus embla_stack_prefill_chunk(EmblaStack* stack, const EmblaStackChunk* 
  * CUDA events are recorded on the stream around every launch of entry point `entry` (-1: off);
  * read_probe returns their summed time and count since the last read, after the caller has
  * synchronised the stream. */
+#define EMBLA_PROBE_FIRST_ONLY 256   /* or-ed into `entry`: only the first launch of that entry point in every step call is
+                                        timed (events between two launches keep the second from overlapping the first's
+                                        tail, so timing all of them slows the step it measures) */
 EmblaStatus embla_stack_set_probe(EmblaStack* stack, int32_t entry);
 EmblaStatus embla_stack_read_probe(EmblaStack* stack, float* total_ms, int32_t* launches);
 

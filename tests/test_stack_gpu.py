@@ -69,6 +69,22 @@ def test_step_host_round_trip_and_probe():
     st.close()
 
 
+def test_probe_every_launch_or_the_first_of_a_step():
+    import torch
+    from embla_metal_b200 import stack as stk
+    st = stk.DecodeStack(stk.cycle_kinds(8), 2, 1536, window=128, ring=512)   # two sparse layers: two scoring launches a step
+    st.fill_random(3)
+    st.set_positions(1535)
+    for first_only, want in ((False, 4), (True, 2)):
+        st.set_probe("score", first_only=first_only)
+        st.step()
+        st.step()
+        torch.cuda.synchronize()
+        ms, n = st.read_probe()
+        assert n == want and ms > 0
+    st.close()
+
+
 def test_step_host_in_groups_of_layers():
     """The host path feeds the query rows in groups of layers on copy streams of their own (embla_stack_decode_layers a
     group): whatever the grouping, the outputs are those of one copy in, one step, one copy out; three steps in a row
