@@ -40,6 +40,20 @@ class Query(C.Structure):
                 ("g1_dev", C.c_void_p), ("g2_dev", C.c_void_p)]
 
 
+class W4Matrix(C.Structure):
+    _fields_ = [("words_dev", C.c_void_p), ("scales_dev", C.c_void_p), ("biases_dev", C.c_void_p), ("rows", C.c_int32)]
+
+
+class W4Weights:
+    """One 4-bit matrix on the device in the reference's layout: words int32 [rows, d_in / 32, 4], scales and biases
+    bfloat16 [rows, d_in / 64]."""
+
+    def __init__(self, words, scales, biases):
+        self.words, self.scales, self.biases = words.contiguous(), scales.contiguous(), biases.contiguous()
+        self.rows, self.d_in = self.words.shape[0], self.words.shape[1] * 32
+        self.desc = W4Matrix(self.words.data_ptr(), self.scales.data_ptr(), self.biases.data_ptr(), self.rows)
+
+
 class KVView(C.Structure):
     _fields_ = [("block_table_dev", C.c_void_p), ("table_stride", C.c_int32), ("seq_lens_dev", C.c_void_p),
                 ("batch", C.c_int32), ("layer", C.c_int32), ("max_seq_len", C.c_int32)]
@@ -178,6 +192,20 @@ class Attention:
         g1, g2 = gains
         ng = 2 if g2 is not None else 1
         return Query(q.data_ptr(), q.stride(0), 0, ng, g1.data_ptr(), None if g2 is None else g2.data_ptr())
+
+    def qkv_project(self, wq, wk, wv, x, qkv):
+        """qkv [batch, >= (Hq + 2 Hkv) * 128] <- the 4-bit GEMVs of x [batch, d_in] (W4Weights), rounded to the dtype."""
+        _check(lib().embla_qkv_project(self.handle, C.byref(wq.desc), C.byref(wk.desc), C.byref(wv.desc), wq.d_in, _ptr(x),
+                                       C.c_int64(x.stride(0)), x.shape[0], _ptr(qkv), C.c_int64(qkv.stride(0)), _stream()))
+
+    def qkv_project_full_step(self, wq, wk, wv, x, qkv, pool, block_table, seq_lens, layer, gains=None, norm_k=True):
+        """The same with the full layer's epilogue: q head-normed with `gains` into qkv (prenormed for full_decode), the
+        token's k and v quantised into the int8 pool at position seq_len - 1."""
+        view = self.view(block_table, seq_lens, layer)
+        qd = self.query(qkv, gains)
+        _check(lib().embla_qkv_project_full_step(self.handle, C.byref(wq.desc), C.byref(wk.desc), C.byref(wv.desc), wq.d_in, _ptr(x),
+                                                 C.c_int64(x.stride(0)), C.byref(qd), pool.handle, C.byref(view), int(norm_k),
+                                                 _ptr(qkv), C.c_int64(qkv.stride(0)), _stream()))
 
     def kv_append(self, pool, block_table, layer, pos0, k, v, norm_k=True):
         """k, v [batch, n_tokens, n_kv_heads * 128 (or wider rows)]; pos0 int32 [batch] first position."""

@@ -160,6 +160,34 @@ EmblaStatus embla_kv_append(EmblaAttn* ctx, EmblaKVPool* pool, const EmblaKVView
                             const void* k_dev, const void* v_dev, int64_t token_stride, int64_t seq_stride,
                             int32_t norm_k, void* stream);
 
+/* ---- the producer of q, k, v: 4-bit stacked GEMV ---------------------------------------------------- */
+/* One 4-bit matrix of the model as the reference stores it (GemvRows, common.metal:105-152; Seg, gemv.metal:21-27):
+ * `rows` rows of d_in four-bit values in d_in / 32 words of 16 bytes (word c, 32-bit part k, nibble n: column
+ * 32 c + 8 k + n), with one bfloat16 scale and one bfloat16 bias per row and 64 columns:
+ * y[row] = sum over words c of scale[c / 2] * (sum nibble * x) + bias[c / 2] * (sum x). */
+typedef struct {
+    const void* words_dev;    /* [rows][d_in / 32] x 16 bytes, 16-byte aligned */
+    const void* scales_dev;   /* bfloat16 [rows][d_in / 64] */
+    const void* biases_dev;   /* bfloat16 [rows][d_in / 64] */
+    int32_t     rows;         /* q: n_q_heads * 128; k, v: n_kv_heads * 128 */
+} EmblaW4Matrix;
+/* Replaces the stacked q/k/v dispatch of gemv (gemv.metal:37-92, EPI 0; Engine.swift:746-752) for `batch` tokens: x_dev
+ * [batch][x_stride] in the activation dtype, outputs rounded to it into qkv_dev [batch][qkv_stride] (q heads, k heads,
+ * v heads, 128 each). Every output is one fp32 chain in a fixed order, equal bit for bit to the CPU restatement. */
+EmblaStatus embla_qkv_project(EmblaAttn* ctx, const EmblaW4Matrix* wq, const EmblaW4Matrix* wk, const EmblaW4Matrix* wv,
+                              int32_t d_in, const void* x_dev, int64_t x_stride, int32_t batch, void* qkv_dev,
+                              int64_t qkv_stride, void* stream);
+/* The same for a full layer with the attention side's work on the rows folded into the GEMV's epilogue (no counterpart in
+ * the reference, which runs kv_append and the in-kernel head norm after it): q is head-normed with `gains` (g1, g2; NULL or
+ * prenormed: stored as computed) and stored as the prenormed queries of embla_attn_full_decode; k (normed first when
+ * norm_k) and v of the token at position seq_lens_dev[b] - 1 are quantised and written into the view's layer of the int8
+ * pool, the same bytes embla_kv_append writes from the rows embla_qkv_project stores; the k and v slots of qkv_dev are
+ * left untouched. batch = view->batch. */
+EmblaStatus embla_qkv_project_full_step(EmblaAttn* ctx, const EmblaW4Matrix* wq, const EmblaW4Matrix* wk,
+                                        const EmblaW4Matrix* wv, int32_t d_in, const void* x_dev, int64_t x_stride,
+                                        const EmblaQuery* gains, EmblaKVPool* pool, const EmblaKVView* view,
+                                        int32_t norm_k, void* qkv_dev, int64_t qkv_stride, void* stream);
+
 /* ---- decode, full layers (ReLU²) ------------------------------------------------------------------ */
 /* Replaces attn_full8 (attention.metal:235-363; dispatch Engine.swift:796-818): ReLU² attention
  * of one query token per sequence over the int8 cache, split over key ranges with a deterministic

@@ -118,9 +118,43 @@ def sliding_prefill(tokens, cached, window, raw=False):
           f"{tokens / med * 1e3:.0f} tok/s")
 
 
+def qkv_project(batch, fused):
+    """The q/k/v producer of a full layer: 4-bit GEMV (d_in 2048 -> 16 + 4 + 4 heads of 128) for `batch` tokens."""
+    d_in = 2048
+    ctx = attn.Attention(HQ, HKV, attn.F16, max_batch=batch, max_context=CTX)
+    ws = []
+    for rows in (HQ * 128, HKV * 128, HKV * 128):
+        words = torch.randint(-2 ** 31, 2 ** 31 - 1, (rows, d_in // 32, 4), dtype=torch.int32, device="cuda")
+        sc = torch.full((rows, d_in // 64), 0.005, device="cuda").to(torch.bfloat16).view(torch.int16)
+        bs = torch.full((rows, d_in // 64), -0.0375, device="cuda").to(torch.bfloat16).view(torch.int16)
+        ws.append(attn.W4Weights(words, sc, bs))
+    x = torch.randn(batch, d_in, device="cuda", dtype=torch.float16)
+    qkv = torch.zeros(batch, (HQ + 2 * HKV) * 128, device="cuda", dtype=torch.float16)
+    npg = CTX // 128
+    pool = attn.KVPool(1, HKV, batch * npg, attn.KV_INT8, attn.SCALE_F16)
+    table = torch.arange(batch * npg, dtype=torch.int32, device="cuda").view(batch, npg).contiguous()
+    lens = torch.full((batch,), CTX, dtype=torch.int32, device="cuda")
+    if fused:
+        fn = lambda: ctx.qkv_project_full_step(ws[0], ws[1], ws[2], x, qkv, pool, table, lens, 0, norm_k=True)
+    else:
+        fn = lambda: ctx.qkv_project(ws[0], ws[1], ws[2], x, qkv)
+    # the kernel is shorter than a launch from Python: twenty launches replayed from a CUDA graph, timed as one
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(20):
+            fn()
+    ts = _events(graph.replay)
+    ctx.check()
+    wbytes = sum(w.words.numel() * 4 + w.scales.numel() * 4 for w in ws)
+    print(f"qkv_project batch {batch} fused {bool(fused)}: {1e3 * ts[len(ts) // 2] / 20:.1f} us/launch ({wbytes / 1e6:.1f} MB of weights)")
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["full_decode", "sparse", "prefill", "sliding_prefill"])
+    ap.add_argument("case", choices=["full_decode", "sparse", "prefill", "sliding_prefill", "qkv_project"])
     ap.add_argument("--window", type=int, default=1024)
     ap.add_argument("--raw", action="store_true", help="sliding_prefill: queries arrive raw (fused head norm + RoPE)")
     ap.add_argument("--batch", type=int, default=8)
@@ -134,6 +168,8 @@ def main():
         full_decode(a.batch, a.scores, a.kv16)
     elif a.case == "sparse":
         sparse(a.batch)
+    elif a.case == "qkv_project":
+        qkv_project(a.batch, a.scores)
     elif a.case == "sliding_prefill":
         sliding_prefill(a.tokens, a.cached if a.cached != 30720 else 2048, a.window, a.raw)
     else:

@@ -457,4 +457,37 @@ void orc_full_decode_batch(int B, int nthreads, const uint16_t* q, int dtype,
     });
 }
 
+// ---- the producer of q, k, v: the 4-bit GEMV (gemv / GemvRows, gemv.metal:37-92, common.metal:105-152) ----------
+// words [rows][d_in / 32][4] 32-bit parts (word c, part k, nibble n: column 32 c + 8 k + n), scales and biases bfloat16
+// [rows][d_in / 64]; x [tokens][ldx] and y [tokens][ldy] in the storage dtype. y = sum over words c of
+// scale[c / 2] * (sum nibble * x) + bias[c / 2] * (sum x). The reference sums across a simdgroup in an unspecified order;
+// here one fp32 chain per output: columns ascending inside a word (fmaf), the word's term a * dq + b * xs (one product, one
+// fmaf), words ascending (plain adds), rounded to the storage dtype at the end (EPI 0).
+void orc_w4_gemv(const uint32_t* words, const uint16_t* scales, const uint16_t* biases, int rows, int d_in,
+                 const uint16_t* x, int ldx, int tokens, int dtype, uint16_t* y, int ldy, int nthreads) {
+    const int nw = d_in / 32;
+    parallel_for(tokens, nthreads, [&](int t) {
+        std::vector<float> xf(d_in), xs(nw);
+        for (int c = 0; c < d_in; c++) xf[c] = load_act(x[size_t(t) * ldx + c], dtype);
+        for (int c = 0; c < nw; c++) {
+            float s = 0.0f;
+            for (int e = 0; e < 32; e++) s = s + xf[32 * c + e];
+            xs[c] = s;
+        }
+        for (int r = 0; r < rows; r++) {
+            float acc = 0.0f;
+            for (int c = 0; c < nw; c++) {
+                const uint32_t* w = words + (size_t(r) * nw + c) * 4;
+                float dq = 0.0f;
+                for (int k = 0; k < 4; k++)
+                    for (int n = 0; n < 8; n++) dq = std::fmaf(float((w[k] >> (4 * n)) & 15u), xf[32 * c + 8 * k + n], dq);
+                const float a = bf16_to_f(scales[size_t(r) * (nw / 2) + c / 2]), b = bf16_to_f(biases[size_t(r) * (nw / 2) + c / 2]);
+                const float prod = a * dq;
+                acc = acc + std::fmaf(b, xs[c], prod);
+            }
+            y[size_t(t) * ldy + r] = store_act(acc, dtype);
+        }
+    });
+}
+
 }  // extern "C"

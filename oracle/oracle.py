@@ -190,3 +190,14 @@ def full_decode_batch(q_bits, dtype, k, ks, v, vs, S, nthreads):
     o = np.empty((B, Hq, HD), np.uint16)
     lib().orc_full_decode_batch(B, nthreads, _p(q), dtype, _p(k), _p(ks), _p(v), _p(vs), Hq, Hkv, S, ldS, _p(o))
     return o
+
+
+def w4_gemv(words, scales, biases, x_bits, dtype, nthreads=1):
+    """words [rows, d_in / 32, 4] uint32, scales / biases [rows, d_in / 64] bfloat16 bits, x [tokens, d_in] storage bits.
+    Returns y [tokens, rows] storage bits."""
+    words = _c(words, np.uint32)
+    scales, biases, x = _c(scales, np.uint16), _c(biases, np.uint16), _c(x_bits, np.uint16)
+    rows, d_in, tokens = words.shape[0], words.shape[1] * 32, x.shape[0]
+    y = np.empty((tokens, rows), np.uint16)
+    lib().orc_w4_gemv(_p(words), _p(scales), _p(biases), rows, d_in, _p(x), x.shape[1], tokens, dtype, _p(y), rows, nthreads)
+    return y
