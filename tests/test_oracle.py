@@ -216,3 +216,27 @@ def test_golden_fixtures_are_reproduced(gold):
     assert np.array_equal(o, g["slide_o"])
     o = orc.full_prefill(g["pre_q"], orc.BF16, g["pre_k"], g["pre_ks"], g["pre_v"], g["pre_vs"], int(g["pre_p0"]))
     assert np.array_equal(o, g["pre_o"])
+
+
+def test_w4_gemv_against_the_dequantised_matrix():
+    """The 4-bit GEMV restatement (GemvRows: word c, part k, nibble n = column 32 c + 8 k + n; y = sum of scale * nibble dot
+    + bias * sum of x per 64 columns) against x @ (scale * nibbles + bias) in float64."""
+    rng = np.random.default_rng(12)
+    rows, d_in, tokens = 24, 256, 5
+    words = rng.integers(0, 2 ** 32, (rows, d_in // 32, 4), dtype=np.uint64).astype(np.uint32)
+    sc = orc.to_bits(rng.uniform(0.002, 0.01, (rows, d_in // 64)), orc.BF16)
+    bs = orc.to_bits(rng.standard_normal((rows, d_in // 64)) * 0.03, orc.BF16)
+    xb = orc.to_bits(rng.standard_normal((tokens, d_in)), orc.BF16)
+    for dtype in (orc.BF16, orc.F16):
+        xd = orc.to_bits(orc.from_bits(xb, orc.BF16), dtype)
+        y = orc.from_bits(orc.w4_gemv(words, sc, bs, xd, dtype), dtype).astype(np.float64)
+        nib = np.zeros((rows, d_in))
+        for c in range(d_in // 32):
+            for k in range(4):
+                for n in range(8):
+                    nib[:, 32 * c + 8 * k + n] = (words[:, c, k] >> np.uint32(4 * n)) & np.uint32(15)
+        w = np.repeat(orc.from_bits(sc, orc.BF16).astype(np.float64), 64, axis=1) * nib + \
+            np.repeat(orc.from_bits(bs, orc.BF16).astype(np.float64), 64, axis=1)
+        ref = orc.from_bits(xd, dtype).astype(np.float64) @ w.T
+        step = 2.0 ** -8 if dtype == orc.BF16 else 2.0 ** -11            # half a step of the storage dtype
+        assert np.all(np.abs(y - ref) <= step * np.abs(ref) + 1e-5)
