@@ -207,6 +207,11 @@ class Attention:
                                                  C.c_int64(x.stride(0)), C.byref(qd), pool.handle, C.byref(view), int(norm_k),
                                                  _ptr(qkv), C.c_int64(qkv.stride(0)), _stream()))
 
+    def oproj(self, wo, o, x, accumulate=True):
+        """x fp32 [batch, >= rows] (+)= the 4-bit GEMV of the attention output rows o [batch, d_in], rounded to the dtype."""
+        _check(lib().embla_oproj(self.handle, C.byref(wo.desc), wo.d_in, _ptr(o), C.c_int64(o.stride(0)), o.shape[0], _ptr(x),
+                                 C.c_int64(x.stride(0)), int(accumulate), _stream()))
+
     def kv_append(self, pool, block_table, layer, pos0, k, v, norm_k=True):
         """k, v [batch, n_tokens, n_kv_heads * 128 (or wider rows)]; pos0 int32 [batch] first position."""
         view = self.view(block_table, None, layer)

@@ -38,6 +38,8 @@ struct QkvProjectParams {
     uint8_t* pool;                // fused: the int8 pool of the layer's cache (else nullptr: k, v go to qkv as computed)
     const int32_t* block_table;
     const int32_t* seq_lens;      // fused: the token's position is seq_len - 1
+    float* resid;                 // o-projection: the fp32 residual rows [batch][qkv_stride] the outputs go (or are added) to
+    int resid_add;
     int64_t x_stride, qkv_stride;
     size_t page_bytes;
     int d_in, batch, n_q_heads, n_kv_heads, ng, table_stride, layer, n_layers, scale_bytes, norm_k;
@@ -203,6 +205,15 @@ __global__ void __launch_bounds__(QP_THREADS) qkv_project_kernel(const QkvProjec
         float v[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) v[i] = y[t * HD + lane + 32 * i];
+        if (p.resid != nullptr) {
+            // the o-projection's epilogues (gemv EPI 3 and 2): x = y or x += y, y rounded to the storage dtype, x in fp32
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                float* at = p.resid + size_t(b) * p.qkv_stride + size_t(head) * HD + lane + 32 * i;
+                *at = p.resid_add ? *at + v[i] : v[i];
+            }
+            continue;
+        }
         if (seg == 0) {
             if (p.ng > 0) norm_rope_round<DT>(v, p.g1, p.g2, p.ng, -1, nullptr, lane);
 #pragma unroll
@@ -329,3 +340,39 @@ extern "C" EmblaStatus embla_qkv_project_full_step(EmblaAttn* ctx, const EmblaW4
     return qkv_project_impl(ctx, wq, wk, wv, d_in, x_dev, x_stride, view->batch, qkv_dev, qkv_stride, gains, pool, view, norm_k, stream,
                             "embla_qkv_project_full_step");
 }
+
+// The consumer of the attention output: the o-projection (gemv with EPI 3 or 2, Engine.swift:830) from the rows
+// embla_attn_*_decode wrote, into the fp32 residual stream.
+extern "C" EmblaStatus embla_oproj(EmblaAttn* ctx, const EmblaW4Matrix* wo, int32_t d_in, const void* o_dev, int64_t o_stride,
+                                   int32_t batch, float* x_dev, int64_t x_stride, int32_t accumulate, void* stream) {
+    if (!ctx || !wo || !o_dev || !x_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_oproj: null argument");
+    EMBLA_CHECK_DEVICE("embla_oproj", ctx, static_cast<const EmblaKVPool*>(nullptr));
+    if (d_in <= 0 || d_in % 64 || d_in > 2048) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_oproj: d_in %d (a multiple of 64, at most 2048)", d_in);
+    if (batch <= 0 || !wo->words_dev || !wo->scales_dev || !wo->biases_dev || wo->rows <= 0 || wo->rows % HD)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_oproj: batch %d, rows %d (a multiple of 128)", batch, wo->rows);
+    if (reinterpret_cast<uintptr_t>(wo->words_dev) % 16 || o_stride % 8 || reinterpret_cast<uintptr_t>(o_dev) % 16 || x_stride < wo->rows)
+        EMBLA_FAIL(EMBLA_BAD_ARG, "embla_oproj: words and input rows must start on 16 bytes, x_stride %lld must hold %d rows",
+                   (long long)x_stride, wo->rows);
+    QkvProjectParams p = {};
+    p.w[0] = static_cast<const uint4*>(wo->words_dev);
+    p.sc[0] = static_cast<const uint16_t*>(wo->scales_dev);
+    p.bs[0] = static_cast<const uint16_t*>(wo->biases_dev);
+    p.x = o_dev;
+    p.x_stride = o_stride;
+    p.qkv_stride = x_stride;
+    p.resid = x_dev;
+    p.resid_add = accumulate;
+    p.d_in = d_in;
+    p.batch = batch;
+    p.n_q_heads = wo->rows / HD;     // every block of 128 rows is a "head" of the first matrix
+    const size_t smem = size_t(QP_TOKENS) * (d_in + 8) * 2 + size_t(d_in / 64) * (QP_TOKENS + 2 * HD) * sizeof(float);
+    const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
+    auto kern = bf ? qkv_project_kernel<EMBLA_BF16> : qkv_project_kernel<EMBLA_F16>;
+    EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        int(size_t(QP_TOKENS) * (2048 + 8) * 2 + 32 * (QP_TOKENS + 2 * HD) * sizeof(float))));
+    dim3 grid(wo->rows / HD, (batch + QP_TOKENS - 1) / QP_TOKENS);
+    kern<<<grid, QP_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p);
+    EMBLA_CUDA_TRY(cudaGetLastError());
+    return EMBLA_OK;
+}
+

@@ -188,6 +188,12 @@ EmblaStatus embla_qkv_project_full_step(EmblaAttn* ctx, const EmblaW4Matrix* wq,
                                         const EmblaQuery* gains, EmblaKVPool* pool, const EmblaKVView* view,
                                         int32_t norm_k, void* qkv_dev, int64_t qkv_stride, void* stream);
 
+/* Replaces the o-projection after attention (gemv with EPI 3 or 2, gemv.metal:85-88; Engine.swift:830): the 4-bit GEMV of
+ * the attention output rows o_dev [batch][o_stride] (activation dtype, d_in = n_q_heads * 128 values), each output rounded
+ * to the activation dtype and stored into (accumulate = 0) or added to (1) the fp32 residual rows x_dev [batch][x_stride]. */
+EmblaStatus embla_oproj(EmblaAttn* ctx, const EmblaW4Matrix* wo, int32_t d_in, const void* o_dev, int64_t o_stride,
+                        int32_t batch, float* x_dev, int64_t x_stride, int32_t accumulate, void* stream);
+
 /* ---- decode, full layers (ReLU²) ------------------------------------------------------------------ */
 /* Replaces attn_full8 (attention.metal:235-363; dispatch Engine.swift:796-818): ReLU² attention
  * of one query token per sequence over the int8 cache, split over key ranges with a deterministic

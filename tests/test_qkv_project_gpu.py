@@ -98,3 +98,25 @@ def test_fused_epilogue_equals_the_separate_calls(dtype, scale_dtype, norm_k):
     for pl in pools:
         pl.close()
     ctx.close()
+
+
+def test_oproj_into_the_residual_stream():
+    """embla_oproj (gemv EPI 3, then EPI 2) on attention-output-like rows against the restatement: x = y, then x += y."""
+    import torch
+    from embla_metal_b200 import attn
+    rng = np.random.default_rng(70)
+    batch, Hq, d = 11, 16, 2048
+    ctx = attn.Attention(Hq, 4, orc.BF16, max_batch=batch, max_context=256)
+    (words, sc, bs), wo = _weights(rng, d, d)
+    ob = orc.to_bits(rng.standard_normal((batch, d)) * 0.3, orc.BF16)
+    ot = util.act_tensor(ob, orc.BF16)
+    x = torch.full((batch, d + 32), 5.0, dtype=torch.float32, device="cuda")
+    ctx.oproj(wo, ot, x, accumulate=False)
+    ctx.oproj(wo, ot, x, accumulate=True)
+    ctx.check()
+    y = orc.from_bits(orc.w4_gemv(words, sc, bs, ob, orc.BF16, nthreads=8), orc.BF16).astype(np.float64)
+    got = x[:, :d].cpu().numpy().astype(np.float64)
+    assert np.all(np.abs(got - 2 * y) <= 2 * (util.BF16_STEP * np.abs(y) + 2e-5))
+    assert bool((x[:, d:] == 5.0).all())
+    ctx.close()
+
