@@ -120,3 +120,57 @@ def test_oproj_into_the_residual_stream():
     assert bool((x[:, d:] == 5.0).all())
     ctx.close()
 
+
+
+def test_attention_sublayer_against_the_restatement():
+    """x -> q/k/v producer with the fused epilogue -> full-layer decode -> o-projection, against the same chain on the CPU
+    restatement (4-bit GEMV, head norm, write_row8 quantisation of the new token, ReLU² attention, 4-bit GEMV), one sequence
+    at a time. The GPU's GEMV outputs may sit one storage step from the restatement's, so a code of the new token's row may
+    differ by one; everything downstream is compared within the attention tolerance carried through the o-projection."""
+    import torch
+    from embla_metal_b200 import attn
+    rng = np.random.default_rng(80)
+    Hq, Hkv, d, dtype = 16, 4, 2048, orc.BF16
+    lens = [300, 129]
+    batch, ctxlen = len(lens), 384
+    ctx = attn.Attention(Hq, Hkv, dtype, max_batch=batch, max_context=ctxlen)
+    host, dev = zip(*[_weights(rng, rows, d) for rows in (Hq * 128, Hkv * 128, Hkv * 128)])
+    (wo_words, wo_sc, wo_bs), wo = _weights(rng, d, Hq * 128)
+    gains = (orc.to_bits(rng.standard_normal(128) * 0.1, dtype), orc.to_bits(rng.standard_normal(128) * 0.1, dtype))
+    xb = orc.to_bits(rng.standard_normal((batch, d)), dtype)
+    npg = ctxlen // 128
+    pool = attn.KVPool(1, Hkv, batch * npg, attn.KV_INT8, attn.SCALE_F32)
+    table = torch.arange(batch * npg, dtype=torch.int32, device="cuda").view(batch, npg).contiguous()
+    caches = []
+    for b, S in enumerate(lens):                      # S - 1 keys already cached; the token at position S - 1 is new
+        k, ks, v, vs = util.int8_cache(rng, Hkv, ctxlen, False)
+        caches.append((k, ks, v, vs))
+        util.fill_pool(pool, 0, table[b].cpu().numpy(), k, ks, v, vs)
+    # ---- GPU
+    xt = util.act_tensor(xb, dtype)
+    qkv = torch.zeros(batch, (Hq + 2 * Hkv) * 128, dtype=xt.dtype, device="cuda")
+    lens_t = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    gt = tuple(util.act_tensor(x, dtype) for x in gains)
+    ctx.qkv_project_full_step(dev[0], dev[1], dev[2], xt, qkv, pool, table, lens_t, 0, gains=gt, norm_k=True)
+    o = torch.zeros(batch, Hq * 128, dtype=xt.dtype, device="cuda")
+    ctx.full_decode(pool, table, lens_t, 0, qkv, o, gains=None, max_seq_len=ctxlen)
+    resid = torch.zeros(batch, d, dtype=torch.float32, device="cuda")
+    ctx.oproj(wo, o, resid, accumulate=False)
+    ctx.check()
+    got = resid.cpu().numpy().astype(np.float64)
+    # ---- the restatement
+    y = [orc.w4_gemv(w, s, bz, xb, dtype, nthreads=8) for (w, s, bz) in host]          # [batch, rows] bits
+    want = np.zeros((batch, d))
+    for b, S in enumerate(lens):
+        k, ks, v, vs = [a.copy() for a in caches[b]]
+        kc, kscale = orc.quantize_rows(y[1][b].reshape(Hkv, 128), dtype, norm=True)
+        vc, vscale = orc.quantize_rows(y[2][b].reshape(Hkv, 128), dtype, norm=False)
+        k[:, S - 1], ks[:, S - 1], v[:, S - 1], vs[:, S - 1] = kc, kscale, vc, vscale
+        ob, _ = orc.full_decode(y[0][b].reshape(Hq, 128), dtype, k, ks, v, vs, S, gains=gains)
+        xo = orc.w4_gemv(wo_words, wo_sc, wo_bs, ob.reshape(1, Hq * 128), dtype)
+        want[b] = orc.from_bits(xo, dtype)[0]
+    err = np.abs(got - want)
+    rms = float(np.sqrt((err ** 2).mean() / (want ** 2).mean()))
+    assert err.max() <= 2e-2 * max(1.0, np.abs(want).max()) and rms <= 1e-2, f"max-abs {err.max():.3e}, rel-rms {rms:.3e}"
+    pool.close()
+    ctx.close()
