@@ -207,6 +207,13 @@ class Attention:
                                                  C.c_int64(x.stride(0)), C.byref(qd), pool.handle, C.byref(view), int(norm_k),
                                                  _ptr(qkv), C.c_int64(qkv.stride(0)), _stream()))
 
+    def qkv_project_sliding_step(self, wq, wk, wv, x, qkv, ring, seq_lens, qgain=None, kgain=None):
+        """The producer for a sliding layer: q normed with qgain and rotated into qkv (prenormed for sliding_decode), the
+        token's k (normed with kgain, rotated) and v written to the ring slot of position seq_len - 1."""
+        _check(lib().embla_qkv_project_sliding_step(self.handle, C.byref(wq.desc), C.byref(wk.desc), C.byref(wv.desc), wq.d_in,
+                                                    _ptr(x), C.c_int64(x.stride(0)), _ptr(qgain), _ptr(kgain), C.byref(ring.desc),
+                                                    _ptr(seq_lens), x.shape[0], _ptr(qkv), C.c_int64(qkv.stride(0)), _stream()))
+
     def oproj(self, wo, o, x, accumulate=True):
         """x fp32 [batch, >= rows] (+)= the 4-bit GEMV of the attention output rows o [batch, d_in], rounded to the dtype."""
         _check(lib().embla_oproj(self.handle, C.byref(wo.desc), wo.d_in, _ptr(o), C.c_int64(o.stride(0)), o.shape[0], _ptr(x),

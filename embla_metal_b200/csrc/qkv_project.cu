@@ -40,6 +40,12 @@ struct QkvProjectParams {
     const int32_t* seq_lens;      // fused: the token's position is seq_len - 1
     float* resid;                 // o-projection: the fp32 residual rows [batch][qkv_stride] the outputs go (or are added) to
     int resid_add;
+    uint8_t* ring_k;              // fused, sliding layer: the rings the token's k (normed with kgain, rotated) and v go to
+    uint8_t* ring_v;
+    const void* kgain;
+    int64_t ring_stride;
+    int ring;
+    float rope_freq[32];
     int64_t x_stride, qkv_stride;
     size_t page_bytes;
     int d_in, batch, n_q_heads, n_kv_heads, ng, table_stride, layer, n_layers, scale_bytes, norm_k;
@@ -215,9 +221,20 @@ __global__ void __launch_bounds__(QP_THREADS) qkv_project_kernel(const QkvProjec
             continue;
         }
         if (seg == 0) {
-            if (p.ng > 0) norm_rope_round<DT>(v, p.g1, p.g2, p.ng, -1, nullptr, lane);
+            // full layers: head norm with both gains; sliding layers: one gain, then RoPE at the token's position
+            if (p.ng > 0) norm_rope_round<DT>(v, p.g1, p.g2, p.ng, p.ring_k ? p.seq_lens[b] - 1 : -1, p.rope_freq, lane);
 #pragma unroll
             for (int i = 0; i < 4; i++) Act<DT>::store(p.qkv, size_t(b) * p.qkv_stride + size_t(head) * HD + lane + 32 * i, v[i]);
+            continue;
+        }
+        if (p.ring_k != nullptr) {
+            // the ring write of attn_sliding (attention.metal:47-62): k normed with its gain and rotated, v as it is
+            const int pos = p.seq_lens[b] - 1;
+            if (seg == 1 && p.kgain != nullptr) norm_rope_round<DT>(v, p.kgain, p.kgain, 1, pos, p.rope_freq, lane);
+            uint8_t* dst = seg == 1 ? p.ring_k : p.ring_v;
+            const size_t slot = size_t(b) * p.ring_stride + (size_t(seg_head) * p.ring + pos % p.ring) * HD;
+#pragma unroll
+            for (int i = 0; i < 4; i++) Act<DT>::store(dst, slot + lane + 32 * i, v[i]);
             continue;
         }
         if (p.pool == nullptr) {
@@ -261,7 +278,8 @@ using namespace embla;
 static EmblaStatus qkv_project_impl(EmblaAttn* ctx, const EmblaW4Matrix* wq, const EmblaW4Matrix* wk, const EmblaW4Matrix* wv,
                                     int32_t d_in, const void* x_dev, int64_t x_stride, int32_t batch, void* qkv_dev,
                                     int64_t qkv_stride, const EmblaQuery* gains, EmblaKVPool* pool, const EmblaKVView* view,
-                                    int32_t norm_k, void* stream, const char* who) {
+                                    int32_t norm_k, void* stream, const char* who, const EmblaRing* ring = nullptr,
+                                    const int32_t* ring_seq_lens = nullptr, const void* kgain = nullptr) {
     if (!ctx || !wq || !wk || !wv || !x_dev || !qkv_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "%s: null argument", who);
     EMBLA_CHECK_DEVICE(who, ctx, pool);
     const int Hq = ctx->cfg.n_q_heads, Hkv = ctx->cfg.n_kv_heads;
@@ -311,6 +329,18 @@ static EmblaStatus qkv_project_impl(EmblaAttn* ctx, const EmblaW4Matrix* wq, con
     }
     if (x_stride % 8 || reinterpret_cast<uintptr_t>(x_dev) % 16)
         EMBLA_FAIL(EMBLA_BAD_ARG, "%s: x rows must start on 16 bytes (x_stride %lld a multiple of 8)", who, (long long)x_stride);
+    if (ring) {
+        if (!ring->k_dev || !ring->v_dev || !ring_seq_lens || ring->ring <= 0)
+            EMBLA_FAIL(EMBLA_BAD_ARG, "%s: null ring or sequence lengths", who);
+        if (p.ng > 1) EMBLA_FAIL(EMBLA_BAD_ARG, "%s: a sliding layer norms q with one gain vector", who);
+        p.ring_k = static_cast<uint8_t*>(ring->k_dev);
+        p.ring_v = static_cast<uint8_t*>(ring->v_dev);
+        p.ring_stride = ring->seq_stride;
+        p.ring = ring->ring;
+        p.seq_lens = ring_seq_lens;
+        p.kgain = kgain;
+        fill_rope_freq(p.rope_freq);
+    }
     const size_t smem = size_t(QP_TOKENS) * (d_in + 8) * 2 + size_t(d_in / 64) * (QP_TOKENS + 2 * HD) * sizeof(float);
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
     auto kern = bf ? qkv_project_kernel<EMBLA_BF16> : qkv_project_kernel<EMBLA_F16>;
@@ -339,6 +369,20 @@ extern "C" EmblaStatus embla_qkv_project_full_step(EmblaAttn* ctx, const EmblaW4
     if (!pool || !view) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_qkv_project_full_step: null pool or view");
     return qkv_project_impl(ctx, wq, wk, wv, d_in, x_dev, x_stride, view->batch, qkv_dev, qkv_stride, gains, pool, view, norm_k, stream,
                             "embla_qkv_project_full_step");
+}
+
+extern "C" EmblaStatus embla_qkv_project_sliding_step(EmblaAttn* ctx, const EmblaW4Matrix* wq, const EmblaW4Matrix* wk,
+                                                      const EmblaW4Matrix* wv, int32_t d_in, const void* x_dev, int64_t x_stride,
+                                                      const void* qgain_dev, const void* kgain_dev, const EmblaRing* ring,
+                                                      const int32_t* seq_lens_dev, int32_t batch, void* qkv_dev,
+                                                      int64_t qkv_stride, void* stream) {
+    if (!ring || !seq_lens_dev) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_qkv_project_sliding_step: null ring or sequence lengths");
+    EmblaQuery gains = {};
+    gains.prenormed = qgain_dev ? 0 : 1;
+    gains.ng = qgain_dev ? 1 : 0;
+    gains.g1_dev = qgain_dev;
+    return qkv_project_impl(ctx, wq, wk, wv, d_in, x_dev, x_stride, batch, qkv_dev, qkv_stride, &gains, nullptr, nullptr, 0, stream,
+                            "embla_qkv_project_sliding_step", ring, seq_lens_dev, kgain_dev);
 }
 
 // The consumer of the attention output: the o-projection (gemv with EPI 3 or 2, Engine.swift:830) from the rows

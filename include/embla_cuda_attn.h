@@ -188,6 +188,7 @@ EmblaStatus embla_qkv_project_full_step(EmblaAttn* ctx, const EmblaW4Matrix* wq,
                                         const EmblaQuery* gains, EmblaKVPool* pool, const EmblaKVView* view,
                                         int32_t norm_k, void* qkv_dev, int64_t qkv_stride, void* stream);
 
+/* The same for a sliding layer (declared after EmblaRing below): embla_qkv_project_sliding_step. */
 /* Replaces the o-projection after attention (gemv with EPI 3 or 2, gemv.metal:85-88; Engine.swift:830): the 4-bit GEMV of
  * the attention output rows o_dev [batch][o_stride] (activation dtype, d_in = n_q_heads * 128 values), each output rounded
  * to the activation dtype and stored into (accumulate = 0) or added to (1) the fp32 residual rows x_dev [batch][x_stride]. */
@@ -296,6 +297,16 @@ typedef struct {
 EmblaStatus embla_sliding_write(EmblaAttn* ctx, const EmblaRing* ring, const int32_t* pos0_dev, int32_t batch,
                                 int32_t n_tokens, const void* k_dev, const void* v_dev, int64_t token_stride,
                                 int64_t seq_stride, int32_t prenormed, const void* kgain_dev, void* stream);
+
+/* embla_qkv_project for a sliding layer with the ring write of attn_sliding (attention.metal:47-62) in its epilogue: q is
+ * normed with qgain_dev, rotated at the token's position seq_lens_dev[b] - 1, rounded and stored as the prenormed query of
+ * embla_attn_sliding_decode; k is normed with kgain_dev, rotated and rounded, v rounded, and both are written to the ring
+ * slot of that position (NULL gains: the rows are stored as computed). The k and v slots of qkv_dev are left untouched. */
+EmblaStatus embla_qkv_project_sliding_step(EmblaAttn* ctx, const EmblaW4Matrix* wq, const EmblaW4Matrix* wk,
+                                           const EmblaW4Matrix* wv, int32_t d_in, const void* x_dev, int64_t x_stride,
+                                           const void* qgain_dev, const void* kgain_dev, const EmblaRing* ring,
+                                           const int32_t* seq_lens_dev, int32_t batch, void* qkv_dev, int64_t qkv_stride,
+                                           void* stream);
 
 /* Replaces the attention of attn_sliding (attention.metal:63-101): softmax over the last
  * min(seq_len, window) positions, which must already be in the ring (embla_sliding_write first).

@@ -174,3 +174,42 @@ def test_attention_sublayer_against_the_restatement():
     assert err.max() <= 2e-2 * max(1.0, np.abs(want).max()) and rms <= 1e-2, f"max-abs {err.max():.3e}, rel-rms {rms:.3e}"
     pool.close()
     ctx.close()
+
+
+@pytest.mark.parametrize("dtype", [orc.F16, orc.BF16])
+def test_fused_sliding_epilogue_equals_the_separate_calls(dtype):
+    """GEMV -> ring write (k normed with its gain and rotated) -> sliding attention with the in-kernel norm and RoPE of q,
+    against the producer with that work in its epilogue followed by sliding attention on prenormed queries: same ring
+    bytes, same attention output."""
+    import torch
+    from embla_metal_b200 import attn
+    batch, Hq, Hkv, d_in = 5, 16, 4, 2048
+    ctx, dev, xt, qkv, rng = _case(batch, Hq, Hkv, dtype, d_in, seed=90)
+    tdt = torch.bfloat16 if dtype == orc.BF16 else torch.float16
+    rings = [attn.Ring(batch, Hkv, 512, 128, tdt) for _ in range(2)]
+    fill_k = torch.randn(rings[0].k.shape, device="cuda").to(tdt)
+    fill_v = torch.randn(rings[0].v.shape, device="cuda").to(tdt)
+    for r in rings:
+        r.k.copy_(fill_k)
+        r.v.copy_(fill_v)
+    lens = torch.tensor([1, 77, 128, 600, 1025], dtype=torch.int32, device="cuda")
+    qg = util.act_tensor(orc.to_bits(rng.standard_normal(128) * 0.1, dtype), dtype)
+    kg = util.act_tensor(orc.to_bits(rng.standard_normal(128) * 0.1, dtype), dtype)
+    width = Hq * 128
+    k = qkv[:, width:width + Hkv * 128].unsqueeze(1)
+    v = qkv[:, width + Hkv * 128:width + 2 * Hkv * 128].unsqueeze(1)
+    ctx.sliding_write(rings[0], lens - 1, k, v, kgain=kg)
+    o_a = torch.zeros(batch, width, dtype=qkv.dtype, device="cuda")
+    ctx.sliding_decode(rings[0], lens, qkv, o_a, qgain=qg)
+    qkv2 = torch.full_like(qkv, 3.0)
+    ctx.qkv_project_sliding_step(dev[0], dev[1], dev[2], xt, qkv2, rings[1], lens, qgain=qg, kgain=kg)
+    o_b = torch.zeros_like(o_a)
+    ctx.sliding_decode(rings[1], lens, qkv2, o_b)
+    ctx.check()
+    torch.cuda.synchronize()
+    assert torch.equal(rings[0].k.view(torch.int16), rings[1].k.view(torch.int16)) and torch.equal(rings[0].v.view(torch.int16), rings[1].v.view(torch.int16)), "ring bytes differ"
+    assert bool((qkv2[:, width:] == 3.0).all())
+    assert torch.equal(o_a.view(torch.int16), o_b.view(torch.int16)), "attention outputs differ"
+    assert torch.isfinite(o_a.float()).all() and o_a.float().abs().sum() > 0
+    ctx.close()
+
