@@ -427,7 +427,7 @@ def prefill_leg(rank, world, barrier, reps=10):
 
 
 def sliding_prefill_case(rank, reps):
-    """BASELINE.json config 1 (b) on one GPU: a 2048-token chunk of a sliding layer (window 1024, ring 4096, fp16) appended
+    """Benchmark configuration 1 (b) on one GPU: a 2048-token chunk of a sliding layer (window 1024, ring 4096, fp16) appended
     after 2048 cached positions; FLOP = 4 x 16 heads x 128 x the keys every token sees."""
     import torch
     from embla_metal_b200 import attn

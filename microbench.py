@@ -100,7 +100,7 @@ def prefill(tokens, cached, qk8=False):
 
 
 def sliding_prefill(tokens, cached, window, raw=False):
-    """BASELINE config 1 (b): a chunk of `tokens` appended after `cached` positions of a sliding layer."""
+    """Benchmark configuration 1 (b): a chunk of `tokens` appended after `cached` positions of a sliding layer."""
     ring_slots = 4096
     ctx = attn.Attention(HQ, HKV, attn.F16, 1, ring_slots)
     ring = attn.Ring(1, HKV, ring_slots, window, torch.float16)

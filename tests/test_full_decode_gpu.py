@@ -59,7 +59,7 @@ def _run_full(S_list, Hq, Hkv, dtype, scale_f16, gains=False, want_scores=False,
 
 
 def test_config0_full_decode():
-    # BASELINE config 0: 16 q / 4 kv heads, context 1024, fp16 q, int8 K/V, fp16 scales, seed 0
+    # benchmark configuration 0: 16 q / 4 kv heads, context 1024, fp16 q, int8 K/V, fp16 scales, seed 0
     _run_full([1024], 16, 4, orc.F16, True, seed=0)
 
 

@@ -50,7 +50,7 @@ def _relu2_64(q, k, ks, v, vs, G):
 
 
 def test_config0_full_decode_vs_float64():
-    # BASELINE config 0: 16 q / 4 kv heads, context 1024, fp16 q ~ N(0,1), int8 K/V, fp16 scales in [0.005, 0.02], seed 0
+    # benchmark configuration 0: 16 q / 4 kv heads, context 1024, fp16 q ~ N(0,1), int8 K/V, fp16 scales in [0.005, 0.02], seed 0
     rng = np.random.default_rng(0)
     q = orc.to_bits(rng.standard_normal((16, 128)), orc.F16)
     k, ks, v, vs = util.int8_cache(rng, 4, 1024, True)

@@ -109,6 +109,6 @@ def test_prefill_golden():
 
 
 def test_config3_prefill_2048_after_30720():
-    # BASELINE config 3: 2048-token chunk after 30720 cached positions, bf16 q, int8 KV + fp16 scales, seed 3.
+    # benchmark configuration 3: 2048-token chunk after 30720 cached positions, bf16 q, int8 KV + fp16 scales, seed 3.
     # The oracle checks every 37th query row (the full 0.5 TFLOP on the CPU would take minutes).
     _case(2048, 30720, 16, 4, orc.BF16, True, seed=3, rows=(5, 37))

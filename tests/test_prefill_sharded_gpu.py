@@ -1,6 +1,6 @@
 """The head-sharded prefill path on one device: the shards that 2, 4 and 8 GPUs would compute are run one after
 another, assembled as the all-gather leaves them (rank-major), placed token-major, and compared with the CPU oracle
-on BASELINE config 3 (2048-token chunk after 30720 cached positions). The collective itself is covered by the 2-rank
+on benchmark configuration 3 (2048-token chunk after 30720 cached positions). The collective itself is covered by the 2-rank
 gloo test of the same placement (tests/test_sharding.py)."""
 import numpy as np
 import pytest

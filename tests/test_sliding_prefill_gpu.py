@@ -51,7 +51,7 @@ def _case(T, p0, W, RING, Hq, Hkv, dtype, seed, gains=False, rows=None, poison=F
 
 
 def test_config1_sliding_prefill():
-    # BASELINE config 1 (b): 2048-token causal chunk appended after 2048 cached positions, window 1024, ring 4096, fp16, seed 1
+    # benchmark configuration 1 (b): 2048-token causal chunk appended after 2048 cached positions, window 1024, ring 4096, fp16, seed 1
     _case(2048, 2048, 1024, 4096, 16, 4, orc.F16, seed=1)
 
 

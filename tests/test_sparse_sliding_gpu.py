@@ -77,7 +77,7 @@ def _sparse_case(S, Hq, Hkv, dtype, seed, gains=False, boost=True):
 
 
 def test_config2_sparse_32k():
-    # BASELINE config 2: 32768 context, fp16, 1 % of keys x4, seed 2
+    # benchmark configuration 2: 32768 context, fp16, 1 % of keys x4, seed 2
     _sparse_case(32768, 16, 4, orc.F16, seed=2)
 
 
@@ -178,7 +178,7 @@ def _sliding_case(pos_list, W, RING, dtype, seed, gains, poison=False):
 
 
 def test_config1_sliding_decode():
-    # BASELINE config 1 (a): window 1024, ring 4096, fp16, decode at 4096 context (pos 4095), seed 1
+    # benchmark configuration 1 (a): window 1024, ring 4096, fp16, decode at 4096 context (pos 4095), seed 1
     _sliding_case([4095], 1024, 4096, orc.F16, seed=1, gains=False)
 
 

@@ -149,7 +149,7 @@ def test_fused_sliding_step_equals_write_then_attend():
 
 
 def test_config4_full_size_step():
-    """BASELINE config 4 at full size: 64 sequences x 32768 context x 24 layers [sparse, sliding 1024, sliding 1024,
+    """Benchmark configuration 4 at full size: 64 sequences x 32768 context x 24 layers [sparse, sliding 1024, sliding 1024,
     full int8], seed 4 (a few sequences shorter, one below the selection threshold). The step run twice from the same
     inputs is bit-identical (appends are idempotent, every combine is ordered); for sampled (sequence, layer) pairs the
     step's rows agree with the CPU restatement fed the very pages and rings the step left behind, and the sparse
