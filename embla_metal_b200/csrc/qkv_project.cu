@@ -38,6 +38,7 @@ struct QkvProjectParams {
     uint8_t* pool;                // fused: the int8 pool of the layer's cache (else nullptr: k, v go to qkv as computed)
     const int32_t* block_table;
     const int32_t* seq_lens;      // fused: the token's position is seq_len - 1
+    KernelCtl ctl;                // error word and wait limit
     float* resid;                 // o-projection: the fp32 residual rows [batch][qkv_stride] the outputs go (or are added) to
     int resid_add;
     uint8_t* ring_k;              // fused, sliding layer: the rings the token's k (normed with kgain, rotated) and v go to
@@ -72,17 +73,31 @@ __device__ __forceinline__ uint32_t nibble_pair(uint32_t part, int c) {
 template <int DT>
 __global__ void __launch_bounds__(QP_THREADS) qkv_project_kernel(const QkvProjectParams p) {
     extern __shared__ __align__(16) uint8_t qp_smem[];
+    __shared__ uint64_t wbar;
     const int words = p.d_in / 32, groups = p.d_in / 64;
     const int xld = p.d_in + 8;                                  // 16-bit elements a token row of x (padded: no bank conflicts)
+    const int wld = words * 16 + 16;                             // bytes a weight row in shared memory (padded likewise)
     uint16_t* xs16 = reinterpret_cast<uint16_t*>(qp_smem);       // [tokens][xld] as stored
     float* xsum = reinterpret_cast<float*>(qp_smem + size_t(QP_TOKENS) * xld * 2);   // [groups][tokens]: sum of x over the group
-    float* wsc = xsum + groups * QP_TOKENS;                      // [128 rows][groups] scales of the head's rows, then the biases
-    float* wbs = wsc + HD * groups;
+    uint16_t* wsc = reinterpret_cast<uint16_t*>(xsum + groups * QP_TOKENS);          // [128 rows][groups] bfloat16 scales, then the biases
+    uint16_t* wbs = wsc + HD * groups;
+    uint8_t* wsm = reinterpret_cast<uint8_t*>(wbs + HD * groups);                    // [128 rows][wld]: the head's weight words
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
     const int head = blockIdx.x, tok0 = blockIdx.y * QP_TOKENS;
     const int ntok = min(QP_TOKENS, p.batch - tok0);
     const int seg = head < p.n_q_heads ? 0 : (head < p.n_q_heads + p.n_kv_heads ? 1 : 2);
     const int seg_head = seg == 0 ? head : (seg == 1 ? head - p.n_q_heads : head - p.n_q_heads - p.n_kv_heads);
+
+    // ---- the head's 128 weight rows into shared memory, one bulk copy a row (a row is contiguous in global memory; read
+    // straight from global by the lanes that use them, 16 bytes from 16 different rows an instruction, they kept the load
+    // path busy for two thirds of the kernel)
+    if (tid == 0) {
+        mbar_init(&wbar, 1);
+        fence_barrier_init();
+        mbar_expect_tx(&wbar, uint32_t(HD) * words * 16);
+    }
+    __syncthreads();
+    if (tid < HD) bulk_load_1d(wsm + tid * wld, p.w[seg] + (size_t(seg_head) * HD + tid) * words, uint32_t(words) * 16, &wbar);
 
     // ---- x of the tile's tokens as stored (16 bytes a thread and trip); rows past the batch are zeros
     {
@@ -104,8 +119,8 @@ __global__ void __launch_bounds__(QP_THREADS) qkv_project_kernel(const QkvProjec
         }
     }
     for (int i = tid; i < HD * groups; i += QP_THREADS) {      // (contiguous in global: the head's rows follow one another)
-        wsc[i] = bf16_bits_to_float(__ldg(p.sc[seg] + size_t(seg_head) * HD * groups + i));
-        wbs[i] = bf16_bits_to_float(__ldg(p.bs[seg] + size_t(seg_head) * HD * groups + i));
+        wsc[i] = __ldg(p.sc[seg] + size_t(seg_head) * HD * groups + i);
+        wbs[i] = __ldg(p.bs[seg] + size_t(seg_head) * HD * groups + i);
     }
     __syncthreads();
     for (int i = tid; i < groups * QP_TOKENS; i += QP_THREADS) {
@@ -134,63 +149,47 @@ __global__ void __launch_bounds__(QP_THREADS) qkv_project_kernel(const QkvProjec
     __syncthreads();
 
     // ---- rows 16 warp + g and + 8 of the head; n-tiles of eight tokens
-    const size_t row0 = size_t(seg_head) * HD + 16 * warp + g;
-    const uint4* wr0 = p.w[seg] + row0 * words;
-    const uint4* wr1 = wr0 + size_t(8) * words;
-    const float* sc0 = wsc + (16 * warp + g) * groups;
-    const float* bs0 = wbs + (16 * warp + g) * groups;
+    const uint4* wr0 = reinterpret_cast<const uint4*>(wsm + (16 * warp + g) * wld);
+    const uint4* wr1 = reinterpret_cast<const uint4*>(wsm + (16 * warp + g + 8) * wld);
+    const uint16_t* sc0 = wsc + (16 * warp + g) * groups;
+    const uint16_t* bs0 = wbs + (16 * warp + g) * groups;
     float acc[QP_NT][4];
 #pragma unroll
     for (int j = 0; j < QP_NT; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
-    // The weight words of the two rows, eight words (four groups) ahead of their use: a word comes from L2 (or HBM the first
-    // time) and a lane has nothing else to do while it waits.
-    constexpr int PF = 8;
-    uint4 q0[PF], q1[PF];
+    const bool have_w = __all_sync(0xffffffffu, mbar_wait_bounded(p.ctl.wait_cycles, &wbar, 0));
+    if (!have_w && lane == 0) atomicCAS(p.ctl.err, 0, ERR_WAIT_FULL);
+    for (int grp = 0; grp < (have_w ? groups : 0); grp++) {
+        float d[QP_NT][4];
 #pragma unroll
-    for (int i = 0; i < PF; i++) {
-        q0[i] = i < words ? __ldg(wr0 + i) : make_uint4(0, 0, 0, 0);
-        q1[i] = i < words ? __ldg(wr1 + i) : make_uint4(0, 0, 0, 0);
-    }
-    for (int grp0 = 0; grp0 < groups; grp0 += PF / 2) {
+        for (int j = 0; j < QP_NT; j++) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.0f;
 #pragma unroll
-        for (int gi = 0; gi < PF / 2; gi++) {
-            const int grp = grp0 + gi;
-            if (grp >= groups) break;
-            float d[QP_NT][4];
+        for (int half = 0; half < 2; half++) {           // a word of 16 bytes: 32 columns, two k-steps
+            const int w = 2 * grp + half;
+            const uint4 u0 = wr0[w], u1 = wr1[w];
+            const uint32_t pa[4] = {u0.x, u0.y, u0.z, u0.w}, pb[4] = {u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
-            for (int j = 0; j < QP_NT; j++) d[j][0] = d[j][1] = d[j][2] = d[j][3] = 0.0f;
+            for (int s2 = 0; s2 < 2; s2++) {             // k-step: columns 32 w + 16 s2 .. + 15 (parts 2 s2 and 2 s2 + 1)
+                const uint32_t a0 = nibble_pair<DT>(pa[2 * s2], c), a1 = nibble_pair<DT>(pb[2 * s2], c);
+                const uint32_t a2 = nibble_pair<DT>(pa[2 * s2 + 1], c), a3 = nibble_pair<DT>(pb[2 * s2 + 1], c);
+                const int k0 = 32 * w + 16 * s2 + 2 * c;
 #pragma unroll
-            for (int half = 0; half < 2; half++) {           // a word of 16 bytes: 32 columns, two k-steps
-                const int w = 2 * grp + half;
-                const uint4 u0 = q0[2 * gi + half], u1 = q1[2 * gi + half];
-                if (w + PF < words) {
-                    q0[2 * gi + half] = __ldg(wr0 + w + PF);
-                    q1[2 * gi + half] = __ldg(wr1 + w + PF);
-                }
-                const uint32_t pa[4] = {u0.x, u0.y, u0.z, u0.w}, pb[4] = {u1.x, u1.y, u1.z, u1.w};
-#pragma unroll
-                for (int s2 = 0; s2 < 2; s2++) {             // k-step: columns 32 w + 16 s2 .. + 15 (parts 2 s2 and 2 s2 + 1)
-                    const uint32_t a0 = nibble_pair<DT>(pa[2 * s2], c), a1 = nibble_pair<DT>(pb[2 * s2], c);
-                    const uint32_t a2 = nibble_pair<DT>(pa[2 * s2 + 1], c), a3 = nibble_pair<DT>(pb[2 * s2 + 1], c);
-                    const int k0 = 32 * w + 16 * s2 + 2 * c;
-#pragma unroll
-                    for (int j = 0; j < QP_NT; j++) {
-                        const uint16_t* xr = xs16 + (8 * j + g) * xld + k0;
-                        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xr), b1 = *reinterpret_cast<const uint32_t*>(xr + 8);
-                        mma16<DT>(d[j], a0, a1, a2, a3, b0, b1);
-                    }
+                for (int j = 0; j < QP_NT; j++) {
+                    const uint16_t* xr = xs16 + (8 * j + g) * xld + k0;
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xr), b1 = *reinterpret_cast<const uint32_t*>(xr + 8);
+                    mma16<DT>(d[j], a0, a1, a2, a3, b0, b1);
                 }
             }
-            // the group's term: scale x (nibbles . x) + bias x (sum of x); rows g (elements 0, 1) and g + 8 (2, 3)
-            const float sa0 = sc0[grp], sa1 = sc0[8 * groups + grp], sb0 = bs0[grp], sb1 = bs0[8 * groups + grp];
+        }
+        // the group's term: scale x (nibbles . x) + bias x (sum of x); rows g (elements 0, 1) and g + 8 (2, 3)
+        const float sa0 = bf16_bits_to_float(sc0[grp]), sa1 = bf16_bits_to_float(sc0[8 * groups + grp]);
+        const float sb0 = bf16_bits_to_float(bs0[grp]), sb1 = bf16_bits_to_float(bs0[8 * groups + grp]);
 #pragma unroll
-            for (int j = 0; j < QP_NT; j++) {
-                const float2 xsv = *reinterpret_cast<const float2*>(xsum + grp * QP_TOKENS + 8 * j + 2 * c);
-                acc[j][0] += fmaf(sb0, xsv.x, sa0 * d[j][0]);
-                acc[j][1] += fmaf(sb0, xsv.y, sa0 * d[j][1]);
-                acc[j][2] += fmaf(sb1, xsv.x, sa1 * d[j][2]);
-                acc[j][3] += fmaf(sb1, xsv.y, sa1 * d[j][3]);
-            }
+        for (int j = 0; j < QP_NT; j++) {
+            const float2 xsv = *reinterpret_cast<const float2*>(xsum + grp * QP_TOKENS + 8 * j + 2 * c);
+            acc[j][0] += fmaf(sb0, xsv.x, sa0 * d[j][0]);
+            acc[j][1] += fmaf(sb0, xsv.y, sa0 * d[j][1]);
+            acc[j][2] += fmaf(sb1, xsv.x, sa1 * d[j][2]);
+            acc[j][3] += fmaf(sb1, xsv.y, sa1 * d[j][3]);
         }
     }
     __syncthreads();      // everyone is done with x: the head's outputs take its place, [tokens][128 rows] fp32
@@ -275,6 +274,12 @@ __global__ void __launch_bounds__(QP_THREADS) qkv_project_kernel(const QkvProjec
 
 using namespace embla;
 
+// x tile, sums of x, the head's scales and biases (bfloat16), the head's weight rows (padded)
+static size_t qp_smem_bytes(int d_in) {
+    return size_t(QP_TOKENS) * (d_in + 8) * 2 + size_t(d_in / 64) * QP_TOKENS * sizeof(float) + size_t(2) * HD * (d_in / 64) * 2 +
+           size_t(HD) * (d_in / 2 + 16);
+}
+
 static EmblaStatus qkv_project_impl(EmblaAttn* ctx, const EmblaW4Matrix* wq, const EmblaW4Matrix* wk, const EmblaW4Matrix* wv,
                                     int32_t d_in, const void* x_dev, int64_t x_stride, int32_t batch, void* qkv_dev,
                                     int64_t qkv_stride, const EmblaQuery* gains, EmblaKVPool* pool, const EmblaKVView* view,
@@ -341,12 +346,13 @@ static EmblaStatus qkv_project_impl(EmblaAttn* ctx, const EmblaW4Matrix* wq, con
         p.kgain = kgain;
         fill_rope_freq(p.rope_freq);
     }
-    const size_t smem = size_t(QP_TOKENS) * (d_in + 8) * 2 + size_t(d_in / 64) * (QP_TOKENS + 2 * HD) * sizeof(float);
+    p.ctl = kernel_ctl(ctx);
+    const size_t smem = qp_smem_bytes(d_in);
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
     auto kern = bf ? qkv_project_kernel<EMBLA_BF16> : qkv_project_kernel<EMBLA_F16>;
     static bool configured[2][64] = {};
     if (!configured[bf][ctx->device & 63]) {
-        EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(size_t(QP_TOKENS) * (2048 + 8) * 2 + 32 * (QP_TOKENS + 2 * HD) * sizeof(float))));
+        EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(qp_smem_bytes(2048))));
         configured[bf][ctx->device & 63] = true;
     }
     dim3 grid(Hq + 2 * Hkv, (batch + QP_TOKENS - 1) / QP_TOKENS);
@@ -409,11 +415,11 @@ extern "C" EmblaStatus embla_oproj(EmblaAttn* ctx, const EmblaW4Matrix* wo, int3
     p.d_in = d_in;
     p.batch = batch;
     p.n_q_heads = wo->rows / HD;     // every block of 128 rows is a "head" of the first matrix
-    const size_t smem = size_t(QP_TOKENS) * (d_in + 8) * 2 + size_t(d_in / 64) * (QP_TOKENS + 2 * HD) * sizeof(float);
+    p.ctl = kernel_ctl(ctx);
+    const size_t smem = qp_smem_bytes(d_in);
     const bool bf = ctx->cfg.act_dtype == EMBLA_BF16;
     auto kern = bf ? qkv_project_kernel<EMBLA_BF16> : qkv_project_kernel<EMBLA_F16>;
-    EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        int(size_t(QP_TOKENS) * (2048 + 8) * 2 + 32 * (QP_TOKENS + 2 * HD) * sizeof(float))));
+    EMBLA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(qp_smem_bytes(2048))));
     dim3 grid(wo->rows / HD, (batch + QP_TOKENS - 1) / QP_TOKENS);
     kern<<<grid, QP_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(p);
     EMBLA_CUDA_TRY(cudaGetLastError());
