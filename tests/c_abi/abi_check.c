@@ -35,6 +35,13 @@ int main(void) {
     CHECK(embla_kv_pool_create(0, 4, EMBLA_KV_INT8, EMBLA_SCALE_F16, 8, &pool) == EMBLA_BAD_ARG);
     CHECK(embla_select_keys(NULL, NULL, 0, NULL, 1, 0, NULL, NULL) == EMBLA_BAD_ARG);
     CHECK(embla_attn_full_decode(NULL, NULL, NULL, NULL, NULL, 0, NULL, 0, NULL) == EMBLA_BAD_ARG);
+    CHECK(embla_attn_full_prefill_scatter(NULL, NULL, NULL, NULL, 0, NULL, 0, NULL, NULL, 9, 0, 0, NULL) == EMBLA_BAD_ARG);
+    CHECK(embla_stack_decode_layers(NULL, NULL, 0, 0, NULL) == EMBLA_BAD_ARG);
+    CHECK(embla_stack_prefill_chunk(NULL, NULL, NULL) == EMBLA_BAD_ARG);
+    CHECK(embla_qkv_project(NULL, NULL, NULL, NULL, 2048, NULL, 0, 1, NULL, 0, NULL) == EMBLA_BAD_ARG);
+    CHECK(embla_qkv_project_full_step(NULL, NULL, NULL, NULL, 2048, NULL, 0, NULL, NULL, NULL, 0, NULL, 0, NULL) == EMBLA_BAD_ARG);
+    CHECK(embla_qkv_project_sliding_step(NULL, NULL, NULL, NULL, 2048, NULL, 0, NULL, NULL, NULL, NULL, 1, NULL, 0, NULL) == EMBLA_BAD_ARG);
+    CHECK(embla_oproj(NULL, NULL, 2048, NULL, 0, 1, NULL, 0, 0, NULL) == EMBLA_BAD_ARG);
 
     /* the prefix store's index runs on the host: a dry run needs no device */
     CHECK(embla_prefix_hash(0, tokens, 0) == 0xcbf29ce484222325ull);
