@@ -33,6 +33,7 @@ constexpr int PF_THREADS = (PF_MMA + 1) * 32;
 constexpr int PF_TILE16 = BLK * HD * 2;            // 32 KiB: 128 rows x 128 dims fp16
 constexpr int PF_KVBUFS = 3;
 constexpr int PF_MAX_PEERS = 8;
+constexpr int PF_SK_UNITS = 256, PF_SK_PIECES = 512;    // most units and pieces (CTAs) of a balanced launch
 // The queries enter the tensor cores scaled by 2^-3 (exact), so the weights p = relu(s)^2, which the kernel keeps as
 // fp16 (P in TMEM, packed row sums), come out scaled by 2^-6: a score of 2047 still squares inside fp16's range (the
 // reference keeps P in fp32, attn_nax.metal:11), and fp16's gradual underflow keeps the small weights to 2^-24 of the
@@ -46,6 +47,7 @@ constexpr float PF_QK8_C0 = 1.0f / 256.0f;
 // alignment slack, 2 Q tiles, 3 converted sides, 3 raw int8 sides, 2 pages' scales, barriers
 constexpr size_t PF_SMEM = 1024 + 2 * PF_TILE16 + PF_KVBUFS * PF_TILE16 + PF_KVBUFS * CODE_BYTES + 2 * 1024 + 256 + 2 * 1024;
 
+struct PfPiece;
 struct PrefillParams {
     const uint8_t* pool;
     const int32_t* block_table;
@@ -60,12 +62,16 @@ struct PrefillParams {
     int n_peers;
     KernelCtl ctl;
     float* partials;      // split-KV: [unit][split][tile][128 + 1 columns][128 rows] fp32 (unnormalised O, then the row sums)
-    int* counters;        // [unit] arrivals
+    int* counters;        // [2][units]: the unit's ranges that have announced themselves, and those whose partials are written
     int64_t q_token_stride, q_seq_stride, o_token_stride, o_seq_stride;
     size_t page_bytes;
     int table_stride, layer, n_layers, n_kv_heads, G, scale_bytes, rows_per_page, n_tokens, prenormed, nsplit;
     int cls;              // cluster size (0: none, else = nsplit): the page ranges of a unit are the CTAs of one thread-block
                           // cluster, whose partial sums stay in shared memory
+    int heads, pairs;     // query heads and 256-token tile pairs of the launch: unit = (sequence x heads + head) x pairs + pair
+    int units;            // sequences x heads x pairs
+    int balanced;         // balanced launch (prefill_pieces_kernel): CTA k takes pieces[k]
+    const struct PfPiece* pieces;
 };
 
 // One side (K or V) of a raw int8 page -> fp16 in the UMMA layout. 128 converter threads; lanes of a
@@ -110,9 +116,25 @@ __device__ __forceinline__ void convert_side(const uint8_t* raw, uint8_t* dst, i
 // the activation dtype, codes rint(x 127 / max|x|), scale max|x| / 127), S = Q8 K8ᵀ runs as tcgen05.mma kind::i8 on the
 // cache's codes as they are (int32 in TMEM, exact), and the ReLU² warps scale it: s = S x qscale(row) x kscale(key) / √D.
 // P V stays fp16 as in the other variant. Twice the tensor rate for Q Kᵀ, and no conversion of the K side at all.
+// the barrier of the eight ReLU² warps among themselves (the other warps are in their own loops or done)
+__device__ __forceinline__ void relu_warps_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// A CTA's work: a page range [jb, je) of one unit (two query tiles of one head), as the kernel at the end of this file
+// works it out from the block index.
+struct PfSegment {
+    int h, b, pair_ix;      // head, sequence, tile pair of the unit
+    int split, nparts;      // which of the unit's page ranges this is, of how many
+    int slot0;              // the unit's first slot in the scratch
+    int jb, je;             // the pages
+};
+
 template <int DT, int SB, bool QK8>
-__global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __grid_constant__ CUtensorMap tmap,
-                                                                     const PrefillParams p) {
+__device__ __forceinline__ void full_prefill_segment(const CUtensorMap& tmap, const PrefillParams& p, const PfSegment sg) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* Qs = smem;                                               // [2 tiles][32 KiB]
@@ -131,11 +153,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
     uint64_t* o_done = bars + 16;
     uint64_t* kf_ready = bars + 17;       // [2 pages] QK8: the page's key factors are set out (converters -> ReLU² warps)
     __shared__ uint32_t s_tmem;
-    __shared__ int s_abort;
+    __shared__ int s_abort, s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.y, b = blockIdx.z;
-    const int pair_ix = blockIdx.x / p.nsplit, split = blockIdx.x % p.nsplit;
+    const int h = sg.h, b = sg.b, pair_ix = sg.pair_ix, split = sg.split, nparts = sg.nparts, slot0 = sg.slot0;
+    const int jb = sg.jb, je = sg.je;
+    const int unit = (b * p.heads + h) * p.pairs + pair_ix;
     const int kvh = h / p.G;
     const int p0 = p.pos0[b];
     // two query tiles of 128 consecutive tokens each share every converted page
@@ -146,12 +169,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         rows[x] = max(0, min(BLK, p.n_tokens - t0[x]));
         npg[x] = rows[x] > 0 ? (p0 + t0[x] + rows[x] - 1) / BLK + 1 : 0;
     }
-    // this CTA's share of the pages (split-KV: ReLU² partial sums of page ranges just add)
-    const int n_all = max(npg[0], npg[1]);
-    const int pps = (n_all + p.nsplit - 1) / p.nsplit;
-    const int jb = split * pps, je = min(n_all, jb + pps);
     const int n = max(0, je - jb);
-
     // The producer lane sets the barriers up and requests the first pages while the other warps stage the query tiles.
     if (warp == PF_PRODUCER && lane == 0) {
         for (int i = 0; i < 3; i++) {
@@ -515,34 +533,116 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         if (!ok) {
             atomicExch(p.ctl.err, ERR_WAIT_FULL);
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
-        } else if (p.nsplit > 1) {
-            // unnormalised O and the row sum of this page range into the scratch (zeros if the tile saw no page here)
+        }
+        if (nparts > 1 && !p.cls) {
+            // The page ranges of the unit meet in the scratch (common.metal:88-99). Each range's CTA announces itself on the
+            // unit's first counter when its products are complete; all but the last to do so leave their unnormalised O and
+            // row sums in their slot and say so on the second counter. The last waits (bounded) for those, adds the ranges in
+            // range order, its own straight from TMEM, and writes the rows: it writes no partial and nothing is staged in
+            // shared memory. All eight warps pass both barriers below, also one whose wait ran out.
             tc_fence_after();
-            const int unit = (b * gridDim.y + h) * (gridDim.x / p.nsplit) + pair_ix;
-            if (p.cls) {
-                // cluster: this CTA's partial stays in its own shared memory (everything from the query tiles on is free
-                // once the last product has completed), row-major [2 tiles][128 rows][128 + 1], for the cluster to read
-                float* prow = reinterpret_cast<float*>(smem) + size_t(x * BLK + r) * (HD + 1);
+            int* arrived = p.counters + unit;
+            int* written = p.counters + p.units + unit;
+            if (tid == 0) s_last = atomicAdd(arrived, 1) == nparts - 1;
+            relu_warps_sync();
+            const bool last = s_last != 0;
+            const size_t tstride = size_t(BLK) * (HD + 1);   // floats of a tile's partial: column-major [128 + 1][128 rows]
+            if (!last) {
+                // the 32 rows of a warp write 32 consecutive floats of a column
+                float* pcol = p.partials + (size_t(slot0 + split) * 2 + x) * tstride + r;
+                if (ok) {
 #pragma unroll 1
-                for (int cc = 0; cc < 4; cc++) {
-                    uint32_t acc[32];
-                    if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, acc);
+                    for (int cc = 0; cc < 4; cc++) {
+                        uint32_t acc[32];
+                        if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, acc);
 #pragma unroll
-                    for (int e = 0; e < 32; e++) prow[32 * cc + e] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
+                        for (int e = 0; e < 32; e++) pcol[size_t(32 * cc + e) * BLK] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
+                    }
+                    pcol[size_t(HD) * BLK] = rowsum;
                 }
-                prow[HD] = rowsum;
+                __threadfence();
+                relu_warps_sync();
+                if (tid == 0) atomicAdd(written, 1);
             } else {
-                // column-major [128 + 1][128 rows]: the 32 rows of a warp write 32 consecutive floats of a column
-                float* pcol = p.partials + ((size_t(unit) * p.nsplit + split) * 2 + x) * (BLK * (HD + 1)) + r;
-#pragma unroll 1
-                for (int cc = 0; cc < 4; cc++) {
-                    uint32_t acc[32];
-                    if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, acc);
-#pragma unroll
-                    for (int e = 0; e < 32; e++) pcol[size_t(32 * cc + e) * BLK] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
+                if (tid == 0) {
+                    bool seen = false;
+                    const long long c0 = clock64();
+                    for (uint32_t i = 0; i < WAIT_LIMIT && !seen; i++) {
+                        seen = ld_acquire_gpu(written) >= nparts - 1;
+                        if (!seen && clock64() - c0 > p.ctl.wait_cycles) break;
+                    }
+                    if (!seen) {
+                        atomicExch(p.ctl.err, ERR_WAIT_FULL);
+                        *reinterpret_cast<volatile int*>(&s_abort) = 1;
+                    }
+                    *arrived = 0;    // (every range of the unit has been at both counters: they are left at zero for the next launch)
+                    *written = 0;
                 }
-                pcol[size_t(HD) * BLK] = rowsum;
+                relu_warps_sync();
+                if (ok && !*reinterpret_cast<volatile int*>(&s_abort)) {
+                    const float* pbase = p.partials + (size_t(slot0) * 2 + x) * tstride + r;   // range 0; range s is 2 tstride x s on
+                    float den = sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + r] : 1.0f);
+                    for (int sp = 0; sp < nparts; sp++) den += sp == split ? rowsum : __ldcg(pbase + size_t(sp) * 2 * tstride + size_t(HD) * BLK);
+                    const float inv = 1.0f / den;
+                    const size_t ooff = size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
+                    uint16_t* orow = static_cast<uint16_t*>(p.o) + ooff;
+#pragma unroll 1
+                    for (int cc = 0; cc < 4; cc++) {
+                        float tot[32];
+#pragma unroll
+                        for (int e = 0; e < 32; e++) tot[e] = 0.0f;
+#pragma unroll 1
+                        for (int sp = 0; sp < nparts; sp++) {
+                            uint32_t v[32];
+                            if (sp == split) {
+                                if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, v);
+                                else {
+#pragma unroll
+                                    for (int e = 0; e < 32; e++) v[e] = 0u;
+                                }
+                            } else {
+                                const float* pc = pbase + size_t(sp) * 2 * tstride + size_t(32 * cc) * BLK;
+#pragma unroll
+                                for (int e = 0; e < 32; e++) v[e] = __float_as_uint(__ldcg(pc + size_t(e) * BLK));
+                            }
+#pragma unroll
+                            for (int e = 0; e < 32; e++) tot[e] += __uint_as_float(v[e]);
+                        }
+                        if (r < rows[x]) {
+                            uint32_t outw[16];
+#pragma unroll
+                            for (int e = 0; e < 32; e += 2) {
+                                if (DT == EMBLA_F16) outw[e >> 1] = pack_h2(tot[e] * inv, tot[e + 1] * inv);
+                                else {
+                                    __nv_bfloat162 t = __floats2bfloat162_rn(tot[e] * inv, tot[e + 1] * inv);
+                                    outw[e >> 1] = *reinterpret_cast<uint32_t*>(&t);
+                                }
+                            }
+#pragma unroll
+                            for (int v4 = 0; v4 < 4; v4++) {
+                                const uint4 val = make_uint4(outw[4 * v4], outw[4 * v4 + 1], outw[4 * v4 + 2], outw[4 * v4 + 3]);
+                                *reinterpret_cast<uint4*>(orow + 32 * cc + 8 * v4) = val;
+                                for (int pr = 0; pr < p.n_peers; pr++)
+                                    *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.o_peer[pr]) + ooff + 32 * cc + 8 * v4) = val;
+                            }
+                        }
+                    }
+                }
             }
+        } else if (!ok) {
+        } else if (nparts > 1) {
+            // cluster: this CTA's partial stays in its own shared memory (everything from the query tiles on is free once the
+            // last product has completed), row-major [2 tiles][128 rows][128 + 1], for the cluster to read
+            tc_fence_after();
+            float* prow = reinterpret_cast<float*>(smem) + size_t(x * BLK + r) * (HD + 1);
+#pragma unroll 1
+            for (int cc = 0; cc < 4; cc++) {
+                uint32_t acc[32];
+                if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, acc);
+#pragma unroll
+                for (int e = 0; e < 32; e++) prow[32 * cc + e] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
+            }
+            prow[HD] = rowsum;
         } else if (nx > 0) {
             tc_fence_after();
             const float inv = 1.0f / (sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + r] : 1.0f) + rowsum);
@@ -575,7 +675,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             }
         }
     }
-    if (p.nsplit > 1 && p.cls) {
+    if (nparts > 1 && p.cls) {
         // Cluster combine: after one cluster barrier every range's partial is complete in its CTA's shared memory; the CTA of
         // rank k then owns a slice of the rows of both tiles and adds the cluster's ranges in order over distributed shared
         // memory (common.metal:88-99, without a last arriver: every SM of the cluster takes a share). A second barrier
@@ -633,81 +733,6 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
             cluster_arrive();
             cluster_wait();
         }
-    } else if (p.nsplit > 1) {
-        // the last CTA of the unit to arrive adds the page ranges in order and writes the rows (common.metal:88-99)
-        __shared__ int s_last;
-        const int unit = (b * gridDim.y + h) * (gridDim.x / p.nsplit) + pair_ix;
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const int prev = atomicAdd(&p.counters[unit], 1);
-            s_last = prev == p.nsplit - 1;
-            if (s_last) p.counters[unit] = 0;
-        }
-        __syncthreads();
-        if (s_last) {
-            __threadfence();
-            // Per tile: the page ranges' columns are added with the lanes across rows (coalesced, the ranges' loads
-            // independent) into a padded tile in shared memory (the K/V buffers are free), then the rows are written with
-            // the lanes across head dims.
-            const size_t sstride = size_t(2) * BLK * (HD + 1);
-            float* tile = reinterpret_cast<float*>(kvb);          // [128 rows][128 + 1]
-            float* den = tile + BLK * (HD + 1);                   // [128]
-            for (int x = 0; x < 2; x++) {
-                const float* base = p.partials + (size_t(unit) * p.nsplit * 2 + x) * (BLK * (HD + 1));
-                // A lane takes four consecutive rows of a column (16 bytes a range and load), a warp two columns at a time with
-                // up to eight ranges' loads of each in flight: the partials sit in L2 or are still on their way from the
-                // other SMs, and this one CTA has 1.2 MB of them to read.
-                constexpr int NW = PF_THREADS / 32;
-                for (int c = warp; c <= HD; c += 2 * NW) {
-                    const bool two = c + NW <= HD;
-                    float4 acc[2] = {make_float4(0.0f, 0.0f, 0.0f, 0.0f), make_float4(0.0f, 0.0f, 0.0f, 0.0f)};
-                    for (int sp0 = 0; sp0 < p.nsplit; sp0 += 8) {
-                        float4 t[2][8];
-#pragma unroll
-                        for (int k = 0; k < 2; k++)
-#pragma unroll
-                            for (int u = 0; u < 8; u++)
-                                t[k][u] = (sp0 + u < p.nsplit && (k == 0 || two))
-                                              ? __ldcg(reinterpret_cast<const float4*>(base + (sp0 + u) * sstride + size_t(c + k * NW) * BLK) + lane)
-                                              : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-                        for (int k = 0; k < 2; k++)
-#pragma unroll
-                            for (int u = 0; u < 8; u++) {
-                                acc[k].x += t[k][u].x;
-                                acc[k].y += t[k][u].y;
-                                acc[k].z += t[k][u].z;
-                                acc[k].w += t[k][u].w;
-                            }
-                    }
-#pragma unroll
-                    for (int k = 0; k < 2; k++) {
-                        const int cc = c + k * NW;
-                        if (k == 1 && !two) continue;
-                        const float v[4] = {acc[k].x, acc[k].y, acc[k].z, acc[k].w};
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            const int row = 4 * lane + i;
-                            if (cc < HD) tile[row * (HD + 1) + cc] = v[i];
-                            else den[row] = sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + row] : 1.0f) + v[i];
-                        }
-                    }
-                }
-                __syncthreads();
-                for (int r = warp; r < rows[x]; r += PF_THREADS / 32) {
-                    const float inv = 1.0f / den[r];
-                    const size_t off = size_t(b) * p.o_seq_stride + size_t(t0[x] + r) * p.o_token_stride + size_t(h) * HD;
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const float val = tile[r * (HD + 1) + lane + 32 * i] * inv;
-                        Act<DT>::store(p.o, off + lane + 32 * i, val);
-                        for (int pr = 0; pr < p.n_peers; pr++) Act<DT>::store(p.o_peer[pr], off + lane + 32 * i, val);
-                    }
-                }
-                __syncthreads();
-            }
-        }
     }
     tc_fence_before();
     __syncthreads();
@@ -715,6 +740,132 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
+}
+
+// Balanced launch (fewer units than SMs, too many for a split into equal ranges to fill the SMs). The pages of all units,
+// laid end to end in unit order, are cut into `runs` equal runs (one an SM) and again wherever a unit ends: every piece (one
+// or two a run) is the work of one CTA, and a unit's pieces meet in the scratch like the ranges of a split. The CTAs take
+// the pieces longest first: as the SMs that drew the shortest of the long pieces come free, they get the longest of the short
+// ones, and every SM ends up with about a run's worth of pages. This kernel (one CTA, ahead of the attention kernel in the
+// stream) lays the pieces out from the chunk positions: pieces[k] is the work of CTA k.
+struct PfPiece {
+    int unit, split, nparts, slot0, jb, je, n_pieces, pad;
+};
+
+__global__ void __launch_bounds__(512) prefill_pieces_kernel(const int32_t* pos0, int n_tokens, int pairs, int heads, int units, int runs,
+                                                             PfPiece* pieces) {
+    __shared__ int pre[PF_SK_UNITS + 1], slot[PF_SK_UNITS + 1], size[PF_SK_PIECES];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int U = units, G = runs;
+    auto scan256 = [&](int* a, int nn) {   // (warp 0) inclusive prefix sums of a[0 .. nn), nn <= 256
+        int v[8], sum = 0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            v[k] = lane * 8 + k < nn ? a[lane * 8 + k] : 0;
+            sum += v[k];
+        }
+        int incl = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        int run = incl - sum;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            run += v[k];
+            if (lane * 8 + k < nn) a[lane * 8 + k] = run;
+        }
+    };
+    // pages the later tile of unit u sees
+    for (int u = tid; u < U; u += blockDim.x) {
+        const int px = u % pairs, bb = u / (pairs * heads);
+        pre[u + 1] = (pos0[bb] + min(n_tokens, (2 * px + 2) * BLK) - 1) / BLK + 1;
+    }
+    if (tid == 0) pre[0] = slot[0] = 0;
+    __syncthreads();
+    if (warp == 0) scan256(pre + 1, U);
+    __syncthreads();
+    const unsigned T = unsigned(pre[U]);
+    // run c holds pages [c T / G, (c + 1) T / G) (the host keeps T x G inside 32 bits); the last run that starts at or
+    // before page x:
+    auto run_of = [&](int x) { return int((unsigned(x + 1) * unsigned(G) + T - 1) / T) - 1; };
+    auto run_start = [&](int c) { return int(unsigned(c) * T / unsigned(G)); };
+    for (int u = tid; u < U; u += blockDim.x) slot[u + 1] = run_of(pre[u + 1] - 1) - run_of(pre[u]) + 1;
+    __syncthreads();
+    if (warp == 0) scan256(slot + 1, U);
+    __syncthreads();
+    const int S = slot[U];   // pieces in all: at most U + G - 1
+    // piece t is part t - slot[u] of the unit u it falls in (the last u with slot[u] <= t)
+    PfPiece mine[(PF_SK_PIECES + 511) / 512];
+    for (int t = tid, k = 0; t < S; t += blockDim.x, k++) {
+        int lo = 0, hi = U - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (slot[mid] <= t) lo = mid;
+            else hi = mid - 1;
+        }
+        const int u = lo, part = t - slot[u], c = run_of(pre[u]) + part;
+        PfPiece& pc = mine[k];
+        pc.unit = u;
+        pc.split = part;
+        pc.nparts = slot[u + 1] - slot[u];
+        pc.slot0 = slot[u];
+        pc.jb = max(run_start(c), pre[u]) - pre[u];
+        pc.je = min(run_start(c + 1), pre[u + 1]) - pre[u];
+        pc.n_pieces = S;
+        pc.pad = 0;
+        size[t] = pc.je - pc.jb;
+    }
+    __syncthreads();
+    for (int t = tid, k = 0; t < S; t += blockDim.x, k++) {
+        const int sz = size[t];
+        int rank = 0;
+        for (int j = 0; j < S; j++) {
+            const int other = size[j];
+            rank += (other > sz) || (other == sz && j < t);
+        }
+        pieces[rank] = mine[k];
+    }
+    // (CTAs past the last piece find this and leave)
+    for (int t = S + tid; t < U + G - 1; t += blockDim.x) {
+        PfPiece none = {};
+        none.n_pieces = S;
+        pieces[t] = none;
+    }
+}
+
+template <int DT, int SB, bool QK8>
+__global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __grid_constant__ CUtensorMap tmap,
+                                                                     const __grid_constant__ PrefillParams p) {
+    PfSegment sg;
+    if (p.balanced) {
+        const int4* e = reinterpret_cast<const int4*>(p.pieces + blockIdx.x);
+        const int4 a = __ldcg(e), c = __ldcg(e + 1);   // unit, split, nparts, slot0 | jb, je, pieces in all
+        if (int(blockIdx.x) >= c.z) return;
+        sg.pair_ix = a.x % p.pairs;
+        sg.h = (a.x / p.pairs) % p.heads;
+        sg.b = a.x / (p.pairs * p.heads);
+        sg.split = a.y;
+        sg.nparts = a.z;
+        sg.slot0 = a.w;
+        sg.jb = c.x;
+        sg.je = c.y;
+    } else {
+        // split-KV: ReLU² partial sums of page ranges just add
+        sg.h = blockIdx.y;
+        sg.b = blockIdx.z;
+        sg.pair_ix = blockIdx.x / p.nsplit;
+        sg.split = blockIdx.x % p.nsplit;
+        sg.nparts = p.nsplit;
+        const int unit = (sg.b * p.heads + sg.h) * p.pairs + sg.pair_ix;
+        const int n_all = (p.pos0[sg.b] + min(p.n_tokens, (2 * sg.pair_ix + 2) * BLK) - 1) / BLK + 1;   // pages the later tile sees
+        const int pps = (n_all + p.nsplit - 1) / p.nsplit;
+        sg.jb = sg.split * pps;
+        sg.je = min(n_all, sg.jb + pps);
+        sg.slot0 = unit * p.nsplit;
+    }
+    full_prefill_segment<DT, SB, QK8>(tmap, p, sg);
 }
 
 }  // namespace embla
@@ -727,10 +878,11 @@ static constexpr size_t PF_SLOT_BYTES = size_t(2) * BLK * (HD + 1) * sizeof(floa
 extern "C" EmblaStatus embla_attn_reserve_prefill(EmblaAttn* ctx, void* stream) {
     if (!ctx) EMBLA_FAIL(EMBLA_BAD_ARG, "embla_attn_reserve_prefill: null context");
     if (ctx->prefill_scratch) return EMBLA_OK;
-    // A split pays only while the CTAs fit one wave or two: two slots an SM, one counter a unit.
-    const size_t slots = 2 * size_t(ctx->sm_count), counters = 2 * size_t(ctx->sm_count);
+    // A split pays only while the CTAs fit one wave or two: two slots an SM, two counters a unit (a multiple of four, so
+    // that the piece table of a balanced launch behind them starts on 16 bytes).
+    const size_t slots = 2 * size_t(ctx->sm_count), counters = (2 * size_t(ctx->sm_count) + 3) & ~size_t(3);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    EMBLA_CUDA_TRY(cudaMalloc(&ctx->prefill_scratch, slots * PF_SLOT_BYTES + counters * sizeof(int)));
+    EMBLA_CUDA_TRY(cudaMalloc(&ctx->prefill_scratch, slots * PF_SLOT_BYTES + counters * sizeof(int) + PF_SK_PIECES * sizeof(PfPiece)));
     EMBLA_CUDA_TRY(cudaMemsetAsync(ctx->prefill_scratch + slots * PF_SLOT_BYTES, 0, counters * sizeof(int), s));
     ctx->prefill_scratch_bytes = slots * PF_SLOT_BYTES;
     ctx->prefill_counters = int(counters);
@@ -793,7 +945,7 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
             const int ns = cl * ng;
             if (ns > 1 && max_pages / ns < 8) break;
             if (cl > 1 && ng > 1) break;                                              // a cluster holds all ranges of its unit
-            if (ng > 1 && (long(units) * ng > slots || units > ctx->prefill_counters)) break;   // the ranges meet in the scratch
+            if (ng > 1 && (long(units) * ng > slots || 2 * units > ctx->prefill_counters)) break;   // the ranges meet in the scratch
             long waves;
             if (cl == 1) {
                 waves = (long(units) * ns + ctx->sm_count - 1) / ctx->sm_count;
@@ -811,16 +963,52 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
             }
         }
     }
+    // The balanced launch (prefill_pieces_kernel): the units' pages in one run an SM, a CTA for every piece of a run that
+    // lies inside one unit (at most units + SMs - 1 of them, each with a slot in the scratch), taken longest first. An SM
+    // then works through a run's worth of pages in two pieces. Costs as measured on config 3 and its shards, in half pages:
+    // 8 a piece (table entry, query tiles, the partial written or the rows finished, the gap between two CTAs of an SM), 2
+    // for every other piece of its unit that the last piece adds, 5 for the kernel that lays the pieces out. 128 units (one
+    // GPU): 0.460 ms against 0.505 with a CTA a unit on the same GPU; 64 units: 0.247 against 0.267; from 32 units down the
+    // cluster split stays ahead. EMBLA_PREFILL_BALANCED=0 turns it off, =1 takes it wherever it fits.
+    const char* bal_env = getenv("EMBLA_PREFILL_BALANCED");
+    const int balanced_mode = bal_env ? atoi(bal_env) : -1;
+    bool balanced = false;
+    const int runs = ctx->sm_count;
+    if (balanced_mode != 0 && units > 1 && units < runs && units <= PF_SK_UNITS && units + runs - 1 <= PF_SK_PIECES &&
+        long(units) + runs - 1 <= slots && 2 * units <= ctx->prefill_counters && (long(units) * max_pages + 1) * runs < (1L << 31) &&
+        (balanced_mode == 1 || long(units) * max_pages >= 16L * runs)) {
+        const long run = (long(units) * max_pages + runs - 1) / runs;
+        const long others2 = 2L * (runs - 1) / units;                 // twice the other pieces of a unit
+        const long cost = 2 * run + 2 * (8 + others2) + 5;
+        balanced = balanced_mode == 1 || cost < best;
+    }
+    if (balanced) {
+        nsplit = 1;
+        cls = 0;
+    }
     p.nsplit = nsplit;
     p.cls = cls;
+    p.heads = ctx->cfg.n_q_heads;
+    p.pairs = pairs;
+    p.units = units;
+    p.balanced = balanced ? 1 : 0;
+    p.pieces = nullptr;
     p.partials = nullptr;
     p.counters = nullptr;
-    if (nsplit > 1 && !cls) {
+    if (balanced || (nsplit > 1 && !cls)) {
         // the counters sit after the partials and are left at zero by every launch
         p.partials = reinterpret_cast<float*>(ctx->prefill_scratch);
         p.counters = reinterpret_cast<int*>(ctx->prefill_scratch + ctx->prefill_scratch_bytes);
     }
     dim3 grid(pairs * nsplit, ctx->cfg.n_q_heads, batch);
+    if (balanced) {
+        // the piece table sits behind the counters
+        PfPiece* pieces = reinterpret_cast<PfPiece*>(ctx->prefill_scratch + ctx->prefill_scratch_bytes + size_t(ctx->prefill_counters) * sizeof(int));
+        prefill_pieces_kernel<<<1, 512, 0, s>>>(p.pos0, p.n_tokens, pairs, p.heads, units, runs, pieces);
+        EMBLA_CUDA_TRY(cudaGetLastError());
+        p.pieces = pieces;
+        grid = dim3(units + runs - 1, 1, 1);
+    }
     if (cls) {
         EMBLA_CUDA_TRY(launch_kernel_cluster(false, cls, kern, grid, dim3(PF_THREADS), PF_SMEM, s, pool->tmap_half, p));
         return EMBLA_OK;

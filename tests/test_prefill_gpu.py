@@ -112,3 +112,65 @@ def test_config3_prefill_2048_after_30720():
     # benchmark configuration 3: 2048-token chunk after 30720 cached positions, bf16 q, int8 KV + fp16 scales, seed 3.
     # The oracle checks every 37th query row (the full 0.5 TFLOP on the CPU would take minutes).
     _case(2048, 30720, 16, 4, orc.BF16, True, seed=3, rows=(5, 37))
+
+
+@pytest.fixture
+def balanced_launch():
+    """The launcher reads EMBLA_PREFILL_BALANCED at every call: 1 takes the balanced launch (one run of pages an SM, cut
+    where units end, pieces longest first) wherever it fits instead of where it is estimated to be faster."""
+    old = os.environ.get("EMBLA_PREFILL_BALANCED")
+    os.environ["EMBLA_PREFILL_BALANCED"] = "1"
+    yield
+    if old is None:
+        del os.environ["EMBLA_PREFILL_BALANCED"]
+    else:
+        os.environ["EMBLA_PREFILL_BALANCED"] = old
+
+
+@pytest.mark.parametrize("T,p0,Hq,Hkv", [(300, 9000, 8, 2), (257, 2047, 16, 4), (600, 20000, 16, 4), (128, 128, 16, 4), (5, 123, 16, 2)])
+def test_prefill_balanced_launch(balanced_launch, T, p0, Hq, Hkv):
+    # units of different lengths cut into pieces: few long units (pieces of many CTAs meet in one unit), many short ones
+    # (runs shorter than a unit's tile pair), and chunks so short that some runs hold a page or none
+    _case(T, p0, Hq, Hkv, orc.BF16, True, seed=T + p0, rows=(1, 3))
+
+
+def test_prefill_balanced_launch_qk8_fp16(balanced_launch):
+    _case(300, 9000, 8, 2, orc.F16, True, seed=31, rows=(0, 7), qk8=True)
+    _case(200, 333, 16, 2, orc.BF16, False, seed=32, gains=True)
+
+
+def test_prefill_balanced_launch_two_sequences(balanced_launch):
+    """Two sequences at different positions in one call: the units of both lie end to end in the piece table. A unit's
+    pieces are added in range order whichever CTA finishes last, so two runs agree bit for bit."""
+    import torch
+    from embla_metal_b200 import attn
+    rng = np.random.default_rng(77)
+    T, Hq, Hkv, p0s = 260, 8, 2, [5000, 1300]
+    caches = [util.int8_cache(rng, Hkv, p0 + T, True) for p0 in p0s]
+    qs = [orc.to_bits(rng.standard_normal((T, Hq, 128)), orc.BF16) for _ in p0s]
+    npgs = [(p0 + T + 127) // 128 for p0 in p0s]
+    ctx = attn.Attention(Hq, Hkv, orc.BF16, 2, max(npgs) * 128)
+    pool = attn.KVPool(1, Hkv, sum(npgs), attn.KV_INT8, attn.SCALE_F16)
+    ids = rng.permutation(sum(npgs)).astype(np.int32)
+    tbl = np.zeros((2, max(npgs)), dtype=np.int32)
+    at = 0
+    for b, (k, ks, v, vs) in enumerate(caches):
+        tbl[b, :npgs[b]] = ids[at:at + npgs[b]]
+        util.fill_pool(pool, 0, tbl[b, :npgs[b]], k, ks, v, vs)
+        at += npgs[b]
+    tblt = torch.from_numpy(tbl).cuda()
+    qt = util.act_tensor(np.stack([q.reshape(T, Hq * 128) for q in qs]), orc.BF16)
+    pos = torch.tensor(p0s, dtype=torch.int32, device="cuda")
+    both, again = torch.zeros_like(qt), torch.zeros_like(qt)
+    attn.full_prefill(ctx, pool, tblt, 0, pos, qt, both)
+    attn.full_prefill(ctx, pool, tblt, 0, pos, qt, again)
+    ctx.check()
+    assert torch.equal(both.view(torch.int16), again.view(torch.int16)), "two runs differ"
+    for b in range(2):
+        got = orc.from_bits(util.act_bits(both[b]), orc.BF16).reshape(T, Hq, 128)
+        k, ks, v, vs = caches[b]
+        _, want = orc.full_prefill(qs[b], orc.BF16, k, ks, v, vs, p0s[b], r0=2, rstep=5, nthreads=8, want_f32=True)
+        ok, msg = util.close_stored(got[2::5], want[2::5], util.BF16_STEP)
+        assert ok, f"sequence {b}: {msg}"
+    pool.close()
+    ctx.close()
