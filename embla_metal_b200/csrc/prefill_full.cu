@@ -746,8 +746,10 @@ __device__ __forceinline__ void full_prefill_segment(const CUtensorMap& tmap, co
 // laid end to end in unit order, are cut into `runs` equal runs (one an SM) and again wherever a unit ends: every piece (one
 // or two a run) is the work of one CTA, and a unit's pieces meet in the scratch like the ranges of a split. The CTAs take
 // the pieces longest first: as the SMs that drew the shortest of the long pieces come free, they get the longest of the short
-// ones, and every SM ends up with about a run's worth of pages. This kernel (one CTA, ahead of the attention kernel in the
-// stream) lays the pieces out from the chunk positions: pieces[k] is the work of CTA k.
+// ones, and every SM ends up with about a run's worth of pages. This kernel (ahead of the attention kernel in the stream,
+// which may become resident meanwhile and waits for it) lays the pieces out from the chunk positions: pieces[k] is the work
+// of CTA k. Each of its CTAs works the whole layout out and places 32 of the pieces, sixteen threads counting the longer
+// pieces of each.
 struct PfPiece {
     int unit, split, nparts, slot0, jb, je, n_pieces, pad;
 };
@@ -757,6 +759,7 @@ __global__ void __launch_bounds__(512) prefill_pieces_kernel(const int32_t* pos0
     __shared__ int pre[PF_SK_UNITS + 1], slot[PF_SK_UNITS + 1], size[PF_SK_PIECES];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int U = units, G = runs;
+    pdl_launch_dependents();
     auto scan256 = [&](int* a, int nn) {   // (warp 0) inclusive prefix sums of a[0 .. nn), nn <= 256
         int v[8], sum = 0;
 #pragma unroll
@@ -797,8 +800,7 @@ __global__ void __launch_bounds__(512) prefill_pieces_kernel(const int32_t* pos0
     __syncthreads();
     const int S = slot[U];   // pieces in all: at most U + G - 1
     // piece t is part t - slot[u] of the unit u it falls in (the last u with slot[u] <= t)
-    PfPiece mine[(PF_SK_PIECES + 511) / 512];
-    for (int t = tid, k = 0; t < S; t += blockDim.x, k++) {
+    auto piece = [&](int t) {
         int lo = 0, hi = U - 1;
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
@@ -806,7 +808,7 @@ __global__ void __launch_bounds__(512) prefill_pieces_kernel(const int32_t* pos0
             else hi = mid - 1;
         }
         const int u = lo, part = t - slot[u], c = run_of(pre[u]) + part;
-        PfPiece& pc = mine[k];
+        PfPiece pc;
         pc.unit = u;
         pc.split = part;
         pc.nparts = slot[u + 1] - slot[u];
@@ -815,20 +817,26 @@ __global__ void __launch_bounds__(512) prefill_pieces_kernel(const int32_t* pos0
         pc.je = min(run_start(c + 1), pre[u + 1]) - pre[u];
         pc.n_pieces = S;
         pc.pad = 0;
+        return pc;
+    };
+    for (int t = tid; t < S; t += blockDim.x) {
+        const PfPiece pc = piece(t);
         size[t] = pc.je - pc.jb;
     }
     __syncthreads();
-    for (int t = tid, k = 0; t < S; t += blockDim.x, k++) {
-        const int sz = size[t];
-        int rank = 0;
-        for (int j = 0; j < S; j++) {
-            const int other = size[j];
-            rank += (other > sz) || (other == sz && j < t);
-        }
-        pieces[rank] = mine[k];
+    // this CTA's 32 pieces: piece t goes to the place that counts the pieces ahead of it (longer, or as long and earlier)
+    const int t = int(blockIdx.x) * 32 + (tid >> 4), sub = tid & 15;
+    const int sz = t < S ? size[t] : 0;
+    int rank = 0;
+    for (int j = sub; j < S; j += 16) {
+        const int other = size[j];
+        rank += (other > sz) || (other == sz && j < t);
     }
-    // (CTAs past the last piece find this and leave)
-    for (int t = S + tid; t < U + G - 1; t += blockDim.x) {
+#pragma unroll
+    for (int d = 8; d >= 1; d >>= 1) rank += __shfl_xor_sync(0xffffffffu, rank, d, 16);
+    if (sub == 0 && t < S) pieces[rank] = piece(t);
+    if (sub == 0 && t >= S && t < U + G - 1) {
+        // (CTAs of the attention kernel past the last piece find this and leave)
         PfPiece none = {};
         none.n_pieces = S;
         pieces[t] = none;
@@ -840,6 +848,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) full_prefill_kernel(const __gri
                                                                      const __grid_constant__ PrefillParams p) {
     PfSegment sg;
     if (p.balanced) {
+        pdl_wait();   // for the kernel that lays the pieces out
         const int4* e = reinterpret_cast<const int4*>(p.pieces + blockIdx.x);
         const int4 a = __ldcg(e), c = __ldcg(e + 1);   // unit, split, nparts, slot0 | jb, je, pieces in all
         if (int(blockIdx.x) >= c.z) return;
@@ -1004,10 +1013,13 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     if (balanced) {
         // the piece table sits behind the counters
         PfPiece* pieces = reinterpret_cast<PfPiece*>(ctx->prefill_scratch + ctx->prefill_scratch_bytes + size_t(ctx->prefill_counters) * sizeof(int));
-        prefill_pieces_kernel<<<1, 512, 0, s>>>(p.pos0, p.n_tokens, pairs, p.heads, units, runs, pieces);
+        prefill_pieces_kernel<<<(units + runs - 1 + 31) / 32, 512, 0, s>>>(p.pos0, p.n_tokens, pairs, p.heads, units, runs, pieces);
         EMBLA_CUDA_TRY(cudaGetLastError());
         p.pieces = pieces;
         grid = dim3(units + runs - 1, 1, 1);
+        static const bool use_pdl = []() { const char* e = getenv("EMBLA_NO_PDL"); return !(e && e[0] == '1'); }();
+        EMBLA_CUDA_TRY(launch_kernel(use_pdl, kern, grid, dim3(PF_THREADS), PF_SMEM, s, pool->tmap_half, p));
+        return EMBLA_OK;
     }
     if (cls) {
         EMBLA_CUDA_TRY(launch_kernel_cluster(false, cls, kern, grid, dim3(PF_THREADS), PF_SMEM, s, pool->tmap_half, p));
