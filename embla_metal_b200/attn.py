@@ -161,6 +161,8 @@ class Attention:
         """Bound of the device-side waits of this context's launches, in SM clocks."""
         _check(lib().embla_attn_set_wait_limit(self.handle, C.c_int64(cycles)))
 
+    STALL_PARTIALS = 1 << 30   # EMBLA_STALL_PARTIALS
+
     def inject_stall(self, item):
         """Diagnostic: producers stop requesting data at `item` of their range (None or -1: off)."""
         _check(lib().embla_attn_inject_stall(self.handle, -1 if item is None else int(item)))

@@ -562,7 +562,7 @@ __device__ __forceinline__ void full_prefill_segment(const CUtensorMap& tmap, co
                 }
                 __threadfence();
                 relu_warps_sync();
-                if (tid == 0) atomicAdd(written, 1);
+                if (tid == 0 && p.ctl.stall_at != EMBLA_STALL_PARTIALS) atomicAdd(written, 1);   // (unless the diagnostic stall withholds it)
             } else {
                 if (tid == 0) {
                     bool seen = false;

@@ -116,7 +116,11 @@ EmblaStatus embla_attn_check(EmblaAttn* ctx, void* stream);
 EmblaStatus embla_attn_set_wait_limit(EmblaAttn* ctx, int64_t cycles);
 /* Diagnostic, for testing the path above without any fault: the producer warps of the launches this
  * context makes from now on stop requesting data at item `item` of their range (page of a key range,
- * tile of a window), so that the consumers' wait for it runs out. -1 turns it off. */
+ * tile of a window), so that the consumers' wait for it runs out. -1 turns it off.
+ * EMBLA_STALL_PARTIALS (an item no producer reaches) instead keeps the page ranges of a prefill unit that
+ * meet in the scratch from reporting their partial sums, so that the wait of the unit's last range, the
+ * only wait of one CTA for others in this library, runs out. */
+#define EMBLA_STALL_PARTIALS (1 << 30)
 EmblaStatus embla_attn_inject_stall(EmblaAttn* ctx, int32_t item);
 
 /* Device-timestamp profiler, the counterpart of the reference's per-part Profiler (StepEncoder.swift:7-65)

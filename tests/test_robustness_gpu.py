@@ -202,3 +202,42 @@ def test_select_keys_long_rows(S):
     assert np.array_equal(idx[0].cpu().numpy().view(np.uint32), want)
     assert orc.verify_selection(scores[0], want, S - 5) == 0
     ctx.close()
+
+
+def test_prefill_partials_wait_runs_out_and_context_survives(monkeypatch):
+    """The one wait of a CTA for other CTAs: the last page range of a prefill unit waits for the partial sums of the ranges
+    that announced themselves before it. The diagnostic stall withholds their reports (nothing faults, nothing hangs: the
+    ranges finish as always), the wait runs out after the short limit, the counters are left at zero, and the next call is
+    right."""
+    import torch
+    from embla_metal_b200 import attn
+    monkeypatch.setenv("EMBLA_PREFILL_BALANCED", "1")   # pieces of a run of pages: every unit's ranges meet in the scratch
+    rng = np.random.default_rng(9)
+    T, p0, Hq, Hkv, dtype = 200, 6000, 8, 2, orc.BF16
+    k, ks, v, vs = util.int8_cache(rng, Hkv, p0 + T, True)
+    npg = (p0 + T + 127) // 128
+    ctx = attn.Attention(Hq, Hkv, dtype, 1, npg * 128)
+    pool = attn.KVPool(1, Hkv, npg, attn.KV_INT8, attn.SCALE_F16)
+    ids = np.arange(npg, dtype=np.int32)
+    util.fill_pool(pool, 0, ids, k, ks, v, vs)
+    tbl = torch.from_numpy(ids[None]).cuda()
+    qb = orc.to_bits(rng.standard_normal((T, Hq, 128)), dtype)
+    qt = util.act_tensor(qb.reshape(1, T, Hq * 128), dtype)
+    ot = torch.zeros_like(qt)
+    pos0 = torch.tensor([p0], dtype=torch.int32, device="cuda")
+    ctx.set_wait_limit(SHORT_WAIT)
+    ctx.inject_stall(attn.Attention.STALL_PARTIALS)
+    attn.full_prefill(ctx, pool, tbl, 0, pos0, qt, ot)
+    with pytest.raises(attn.EmblaError) as e:
+        ctx.check()
+    assert e.value.status == attn.TIMEOUT
+    ctx.inject_stall(None)
+    ctx.set_wait_limit(1 << 30)
+    attn.full_prefill(ctx, pool, tbl, 0, pos0, qt, ot)
+    ctx.check()
+    got = orc.from_bits(util.act_bits(ot), dtype).reshape(T, Hq, 128)
+    _, want = orc.full_prefill(qb, dtype, k, ks, v, vs, p0, r0=1, rstep=4, nthreads=8, want_f32=True)
+    ok, msg = util.close_stored(got[1::4], want[1::4], util.BF16_STEP)
+    assert ok, msg
+    pool.close()
+    ctx.close()
