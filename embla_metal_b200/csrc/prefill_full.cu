@@ -72,6 +72,9 @@ struct PrefillParams {
     int units;            // sequences x heads x pairs
     int balanced;         // balanced launch (prefill_pieces_kernel): CTA k takes pieces[k]
     const struct PfPiece* pieces;
+    int reduce_later;     // every range leaves its partial in the scratch and prefill_reduce_kernel adds them (units cut into
+                          // more ranges than one CTA should add up alone)
+    int2* unit_slots;     // [unit] (first slot, ranges) for that kernel
 };
 
 // One side (K or V) of a raw int8 page -> fp16 in the UMMA layout. 128 converter threads; lanes of a
@@ -540,14 +543,28 @@ __device__ __forceinline__ void full_prefill_segment(const CUtensorMap& tmap, co
             // row sums in their slot and say so on the second counter. The last waits (bounded) for those, adds the ranges in
             // range order, its own straight from TMEM, and writes the rows: it writes no partial and nothing is staged in
             // shared memory. All eight warps pass both barriers below, also one whose wait ran out.
+            // With many ranges a unit (p.reduce_later) none of this happens: every range leaves its partial, the first one with
+            // the sink of the denominator in its row sums, and prefill_reduce_kernel, next in the stream, adds them.
             tc_fence_after();
             int* arrived = p.counters + unit;
             int* written = p.counters + p.units + unit;
-            if (tid == 0) s_last = atomicAdd(arrived, 1) == nparts - 1;
-            relu_warps_sync();
-            const bool last = s_last != 0;
+            if (tid == 0 && !p.reduce_later) s_last = atomicAdd(arrived, 1) == nparts - 1;
+            if (!p.reduce_later) relu_warps_sync();
+            const bool last = !p.reduce_later && s_last != 0;
             const size_t tstride = size_t(BLK) * (HD + 1);   // floats of a tile's partial: column-major [128 + 1][128 rows]
-            if (!last) {
+            if (p.reduce_later) {
+                float* pcol = p.partials + (size_t(slot0 + split) * 2 + x) * tstride + r;
+                if (ok) {
+#pragma unroll 1
+                    for (int cc = 0; cc < 4; cc++) {
+                        uint32_t acc[32];
+                        if (nx > 0) tmem_ld32(tO + 32 * cc + lane_sel, acc);
+#pragma unroll
+                        for (int e = 0; e < 32; e++) pcol[size_t(32 * cc + e) * BLK] = nx > 0 ? __uint_as_float(acc[e]) : 0.0f;
+                    }
+                    pcol[size_t(HD) * BLK] = split == 0 ? sqrtf(float(HD)) * PF_PSCALE * (QK8 ? qsc[x * BLK + r] : 1.0f) + rowsum : rowsum;
+                }
+            } else if (!last) {
                 // the 32 rows of a warp write 32 consecutive floats of a column
                 float* pcol = p.partials + (size_t(slot0 + split) * 2 + x) * tstride + r;
                 if (ok) {
@@ -755,7 +772,7 @@ struct PfPiece {
 };
 
 __global__ void __launch_bounds__(512) prefill_pieces_kernel(const int32_t* pos0, int n_tokens, int pairs, int heads, int units, int runs,
-                                                             PfPiece* pieces) {
+                                                             PfPiece* pieces, int2* unit_slots) {
     __shared__ int pre[PF_SK_UNITS + 1], slot[PF_SK_UNITS + 1], size[PF_SK_PIECES];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int U = units, G = runs;
@@ -799,6 +816,8 @@ __global__ void __launch_bounds__(512) prefill_pieces_kernel(const int32_t* pos0
     if (warp == 0) scan256(slot + 1, U);
     __syncthreads();
     const int S = slot[U];   // pieces in all: at most U + G - 1
+    if (blockIdx.x == 0 && unit_slots)
+        for (int u = tid; u < U; u += blockDim.x) unit_slots[u] = make_int2(slot[u], slot[u + 1] - slot[u]);
     // piece t is part t - slot[u] of the unit u it falls in (the last u with slot[u] <= t)
     auto piece = [&](int t) {
         int lo = 0, hi = U - 1;
@@ -840,6 +859,70 @@ __global__ void __launch_bounds__(512) prefill_pieces_kernel(const int32_t* pos0
         PfPiece none = {};
         none.n_pieces = S;
         pieces[t] = none;
+    }
+}
+
+// Adds the partial sums that the ranges of every unit left in the scratch (p.reduce_later) and writes the rows: a CTA takes 32
+// rows of one tile of one unit. Its warps read the ranges' columns with the lanes across the rows (coalesced: a partial is
+// column-major), add them in range order into a padded tile in shared memory, and write each row with the lanes across the
+// head dims (common.metal:88-99, shared out over many SMs instead of a unit's last CTA).
+template <int DT>
+__global__ void __launch_bounds__(256) prefill_reduce_kernel(const __grid_constant__ PrefillParams p) {
+    __shared__ __align__(16) float tile[32][HD + 4];   // column HD: the denominator (rows 16-byte aligned)
+    pdl_wait();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rb = blockIdx.x, x = blockIdx.y, unit = blockIdx.z;
+    const int pair_ix = unit % p.pairs, h = (unit / p.pairs) % p.heads, b = unit / (p.pairs * p.heads);
+    const int t0 = (2 * pair_ix + x) * BLK, rows = max(0, min(BLK, p.n_tokens - t0));
+    if (32 * rb >= rows) return;
+    int slot0 = unit * p.nsplit, nparts = p.nsplit;
+    if (p.balanced) {
+        const int2 us = p.unit_slots[unit];
+        slot0 = us.x;
+        nparts = us.y;
+    }
+    if (nparts <= 1) return;   // (a unit inside one run of a balanced launch: its CTA has written the rows itself)
+    const size_t tstride = size_t(BLK) * (HD + 1);
+    const float* base = p.partials + (size_t(slot0) * 2 + x) * tstride + 32 * rb + lane;
+    // a warp takes columns warp, warp + 8, ...: four columns at a time, the ranges' loads of each in flight together
+    for (int c0 = warp; c0 <= HD; c0 += 32) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int sp0 = 0; sp0 < nparts; sp0 += 4) {
+            float v[4][4];
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int c = c0 + 8 * k;
+                    v[k][u] = (c <= HD && sp0 + u < nparts) ? __ldcg(base + size_t(sp0 + u) * 2 * tstride + size_t(c) * BLK) : 0.0f;
+                }
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+#pragma unroll
+                for (int u = 0; u < 4; u++) acc[k] += v[k][u];
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            if (c0 + 8 * k <= HD) tile[lane][c0 + 8 * k] = acc[k];
+    }
+    __syncthreads();
+    for (int rr = warp; rr < 32; rr += 8) {
+        const int r = 32 * rb + rr;
+        if (r >= rows) break;
+        const float inv = 1.0f / tile[rr][HD];
+        const size_t off = size_t(b) * p.o_seq_stride + size_t(t0 + r) * p.o_token_stride + size_t(h) * HD + 4 * lane;
+        const float4 v = *reinterpret_cast<const float4*>(&tile[rr][4 * lane]);
+        uint2 w;
+        if (DT == EMBLA_F16) {
+            w.x = pack_h2(v.x * inv, v.y * inv);
+            w.y = pack_h2(v.z * inv, v.w * inv);
+        } else {
+            __nv_bfloat162 t0b = __floats2bfloat162_rn(v.x * inv, v.y * inv), t1b = __floats2bfloat162_rn(v.z * inv, v.w * inv);
+            w.x = *reinterpret_cast<uint32_t*>(&t0b);
+            w.y = *reinterpret_cast<uint32_t*>(&t1b);
+        }
+        *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.o) + off) = w;
+        for (int pr = 0; pr < p.n_peers; pr++) *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.o_peer[pr]) + off) = w;
     }
 }
 
@@ -891,7 +974,7 @@ extern "C" EmblaStatus embla_attn_reserve_prefill(EmblaAttn* ctx, void* stream) 
     // that the piece table of a balanced launch behind them starts on 16 bytes).
     const size_t slots = 2 * size_t(ctx->sm_count), counters = (2 * size_t(ctx->sm_count) + 3) & ~size_t(3);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    EMBLA_CUDA_TRY(cudaMalloc(&ctx->prefill_scratch, slots * PF_SLOT_BYTES + counters * sizeof(int) + PF_SK_PIECES * sizeof(PfPiece)));
+    EMBLA_CUDA_TRY(cudaMalloc(&ctx->prefill_scratch, slots * PF_SLOT_BYTES + counters * sizeof(int) + PF_SK_PIECES * sizeof(PfPiece) + PF_SK_UNITS * sizeof(int2)));
     EMBLA_CUDA_TRY(cudaMemsetAsync(ctx->prefill_scratch + slots * PF_SLOT_BYTES, 0, counters * sizeof(int), s));
     ctx->prefill_scratch_bytes = slots * PF_SLOT_BYTES;
     ctx->prefill_counters = int(counters);
@@ -925,7 +1008,8 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     // is what embla_attn_reserve_prefill allocated (this call never allocates or synchronises): a split through it is taken
     // only as far as it holds; without a reserve only lone CTAs and clusters remain.
     const long slots = long(ctx->prefill_scratch_bytes / PF_SLOT_BYTES);
-    static const bool use_clusters = []() { const char* e = getenv("EMBLA_NO_CLUSTER"); return !(e && e[0] == '1'); }();
+    const char* ncl_env = getenv("EMBLA_NO_CLUSTER");
+    const bool use_clusters = !(ncl_env && ncl_env[0] == '1');
     static int max_clusters[64][9] = {};     // per device and cluster size; 0 = not asked yet, -1 = none
     auto clusters_at_once = [&](int cl) {
         int& mc = max_clusters[ctx->device & 63][cl];
@@ -947,7 +1031,15 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
         }
         return mc;
     };
+    // Ranges that meet in the scratch are added by the unit's last range in its epilogue while they are few; from four ranges
+    // a unit on every range only leaves its partial and prefill_reduce_kernel, launched behind, adds them on many SMs (8 half
+    // pages a range for the query tiles and the partial, 6 for that kernel; one CTA adding eight others' partials alone took
+    // 25 us). EMBLA_PREFILL_REDUCE=0 / 1 takes the first / second way regardless.
+    const char* red_env = getenv("EMBLA_PREFILL_REDUCE");
+    const int reduce_mode = red_env ? atoi(red_env) : -1;
+    auto reduce_for = [&](long ranges) { return reduce_mode < 0 ? ranges >= 4 : reduce_mode == 1; };
     int nsplit = 1, cls = 0;
+    bool reduce_later = false;
     long best = -1;
     for (int cl = 1; cl <= (use_clusters ? 8 : 1); cl++) {
         for (int ng = 1; cl * ng <= 16; ng++) {
@@ -963,12 +1055,14 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
                 if (mc <= 0) break;
                 waves = (long(units) * ng + mc - 1) / mc;
             }
-            const long fixed2 = ns == 1 ? 4 : (cl == 1 ? 18 + 2 * ns : 18 + cl / 2);   // in half pages
-            const long cost = waves * (2 * ((max_pages + ns - 1) / ns) + fixed2);
+            const bool red = cl == 1 && ns > 1 && reduce_for(ns);
+            const long fixed2 = ns == 1 ? 4 : (cl == 1 ? (red ? 16 : 10 + 4 * (ns - 1)) : 18 + cl / 2);   // in half pages
+            const long cost = waves * (2 * ((max_pages + ns - 1) / ns) + fixed2) + (red ? 6 : 0);
             if (best < 0 || cost < best) {
                 best = cost;
                 nsplit = ns;
                 cls = cl > 1 ? cl : 0;
+                reduce_later = red;
             }
         }
     }
@@ -988,8 +1082,10 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
         (balanced_mode == 1 || long(units) * max_pages >= 16L * runs)) {
         const long run = (long(units) * max_pages + runs - 1) / runs;
         const long others2 = 2L * (runs - 1) / units;                 // twice the other pieces of a unit
-        const long cost = 2 * run + 2 * (8 + others2) + 5;
+        const bool red = reduce_for((runs - 1) / units + 2);          // (the most pieces a unit is cut into)
+        const long cost = 2 * run + 2 * (8 + (red ? 0 : others2)) + 5 + (red ? 6 : 0);
         balanced = balanced_mode == 1 || cost < best;
+        if (balanced) reduce_later = red;
     }
     if (balanced) {
         nsplit = 1;
@@ -1001,6 +1097,8 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     p.pairs = pairs;
     p.units = units;
     p.balanced = balanced ? 1 : 0;
+    p.reduce_later = reduce_later ? 1 : 0;
+    p.unit_slots = nullptr;
     p.pieces = nullptr;
     p.partials = nullptr;
     p.counters = nullptr;
@@ -1010,23 +1108,24 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
         p.counters = reinterpret_cast<int*>(ctx->prefill_scratch + ctx->prefill_scratch_bytes);
     }
     dim3 grid(pairs * nsplit, ctx->cfg.n_q_heads, batch);
+    static const bool use_pdl = []() { const char* e = getenv("EMBLA_NO_PDL"); return !(e && e[0] == '1'); }();
     if (balanced) {
         // the piece table sits behind the counters
         PfPiece* pieces = reinterpret_cast<PfPiece*>(ctx->prefill_scratch + ctx->prefill_scratch_bytes + size_t(ctx->prefill_counters) * sizeof(int));
-        prefill_pieces_kernel<<<(units + runs - 1 + 31) / 32, 512, 0, s>>>(p.pos0, p.n_tokens, pairs, p.heads, units, runs, pieces);
+        p.unit_slots = reinterpret_cast<int2*>(pieces + PF_SK_PIECES);   // (and the units' slots behind that)
+        prefill_pieces_kernel<<<(units + runs - 1 + 31) / 32, 512, 0, s>>>(p.pos0, p.n_tokens, pairs, p.heads, units, runs, pieces, p.unit_slots);
         EMBLA_CUDA_TRY(cudaGetLastError());
         p.pieces = pieces;
         grid = dim3(units + runs - 1, 1, 1);
-        static const bool use_pdl = []() { const char* e = getenv("EMBLA_NO_PDL"); return !(e && e[0] == '1'); }();
         EMBLA_CUDA_TRY(launch_kernel(use_pdl, kern, grid, dim3(PF_THREADS), PF_SMEM, s, pool->tmap_half, p));
-        return EMBLA_OK;
-    }
-    if (cls) {
+    } else if (cls) {
         EMBLA_CUDA_TRY(launch_kernel_cluster(false, cls, kern, grid, dim3(PF_THREADS), PF_SMEM, s, pool->tmap_half, p));
-        return EMBLA_OK;
+    } else {
+        kern<<<grid, PF_THREADS, PF_SMEM, s>>>(pool->tmap_half, p);
+        EMBLA_CUDA_TRY(cudaGetLastError());
     }
-    kern<<<grid, PF_THREADS, PF_SMEM, s>>>(pool->tmap_half, p);
-    EMBLA_CUDA_TRY(cudaGetLastError());
+    if (reduce_later)
+        EMBLA_CUDA_TRY(launch_kernel(use_pdl, prefill_reduce_kernel<DT>, dim3(BLK / 32, 2, units), dim3(256), 0, s, p));
     return EMBLA_OK;
 }
 

@@ -174,3 +174,16 @@ def test_prefill_balanced_launch_two_sequences(balanced_launch):
         assert ok, f"sequence {b}: {msg}"
     pool.close()
     ctx.close()
+
+
+@pytest.mark.parametrize("balanced,reduce", [("0", "1"), ("0", "0"), ("1", "1"), ("1", "0")])
+def test_prefill_ranges_through_scratch_both_ways(monkeypatch, balanced, reduce):
+    """Page ranges that meet in the scratch, as an even split of every unit (balanced 0: clusters off, so the split goes
+    through the scratch) or as pieces of the balanced launch, added by the unit's last range (reduce 0) or by the kernel
+    launched behind (reduce 1)."""
+    monkeypatch.setenv("EMBLA_PREFILL_BALANCED", balanced)
+    monkeypatch.setenv("EMBLA_PREFILL_REDUCE", reduce)
+    monkeypatch.setenv("EMBLA_NO_CLUSTER", "1")
+    _case(200, 12000, 16, 4, orc.BF16, True, seed=41, rows=(3, 5))
+    _case(300, 9000, 8, 2, orc.F16, True, seed=42, rows=(0, 7))
+    _case(257, 4000, 16, 2, orc.BF16, False, seed=43, gains=True, rows=(2, 9), qk8=True)

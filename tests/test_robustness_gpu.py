@@ -212,6 +212,7 @@ def test_prefill_partials_wait_runs_out_and_context_survives(monkeypatch):
     import torch
     from embla_metal_b200 import attn
     monkeypatch.setenv("EMBLA_PREFILL_BALANCED", "1")   # pieces of a run of pages: every unit's ranges meet in the scratch
+    monkeypatch.setenv("EMBLA_PREFILL_REDUCE", "0")     # ... and are added by the unit's last range, not by the kernel behind
     rng = np.random.default_rng(9)
     T, p0, Hq, Hkv, dtype = 200, 6000, 8, 2, orc.BF16
     k, ks, v, vs = util.int8_cache(rng, Hkv, p0 + T, True)
