@@ -7,7 +7,8 @@
 //   S = Q Kᵀ   tcgen05.mma kind::f16, M = 128 queries, N = 128 keys (one page), K = 128 dims, fp32 in TMEM
 //   O += P V   tcgen05.mma kind::f16, A = P read straight from TMEM, B = V from shared memory (MN-major)
 // One CTA owns 256 consecutive tokens of one query head as two tiles of 128 and walks the sequence's pages;
-// both tiles use every converted page, which halves the conversion work per MMA:
+// both tiles use every converted page, which halves the conversion work per MMA (with fewer such units than SMs a unit's
+// pages are shared among CTAs: launch_prefill chooses how, and how their partial sums meet):
 //   warp 12     TMA producer: one side (K or V: 128 int8 code rows, swizzled box) at a time into a 3-slot ring,
 //               the page's scales with its K side
 //   warps 8-11  converters: int8 codes -> fp16 (exact), times the row's factor (kscale/√D or vscale), into the
@@ -990,16 +991,16 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
         configured[ctx->device & 63] = true;
     }
     // A unit = 256 tokens of one head. With fewer units than SMs (short chunks, few heads on this GPU) the pages of
-    // a unit are split over several CTAs whose partial sums the last one adds (ReLU² partials are additive).
+    // a unit are shared among several CTAs whose partial sums are added up (ReLU² partials are additive).
     const int pairs = (p.n_tokens + 2 * BLK - 1) / (2 * BLK);
     const int units = pairs * ctx->cfg.n_q_heads * batch;
-    // Page ranges per unit: the split that minimises (waves of CTAs over the SMs) x (pages of a range + the fixed cost of a
-    // CTA). Two ways to add the ranges' partial sums (ReLU² partials are additive), costs in pages' worth as measured on
-    // the shards of config 3 (a page is 1.8 us of a CTA):
-    //   ns ranges through global scratch, added by the unit's last CTA to arrive: 2 for a lone CTA (query load, TMEM
-    //     set-up, pipeline fill), 9 + ns when split (132 KB of partials written by each, all read back by one SM);
+    // Page ranges per unit: the even split that minimises (waves of CTAs over the SMs) x (pages of a range + the fixed cost
+    // of a CTA), against the balanced launch further down. Two ways for the ranges of an even split to meet (ReLU² partials
+    // are additive), costs in half pages' worth as measured on the shards of config 3 (a page is 1.8 us of a CTA):
+    //   ns ranges through global scratch: 4 for a lone CTA (query load, TMEM set-up, pipeline fill); split, 10 and 4 for every
+    //     other range when the unit's last range adds them, 16 and 6 for the reduce kernel when that does (below);
     //   the ranges as one thread-block cluster of cl <= 8 CTAs, added over distributed shared memory, every CTA finishing a
-    //     slice of the rows: about 9 + cl / 4, and no scratch (32 units x 4 ranges: 141 us against 150).
+    //     slice of the rows: about 18 + cl / 2, and no scratch.
     // A cluster split is taken only in as many waves as cudaOccupancyMaxActiveClusters says the GPU holds at once (a
     // cluster needs its SMs inside one GPC: 15 clusters of 8 CTAs of this kernel, 213 KB of shared memory each, 33 of 4, 74
     // of 2); EMBLA_NO_CLUSTER=1 turns clusters off. Several clusters a unit, their slices meeting in the scratch, measured
