@@ -34,7 +34,7 @@ constexpr int PF_THREADS = (PF_MMA + 1) * 32;
 constexpr int PF_TILE16 = BLK * HD * 2;            // 32 KiB: 128 rows x 128 dims fp16
 constexpr int PF_KVBUFS = 3;
 constexpr int PF_MAX_PEERS = 8;
-constexpr int PF_SK_UNITS = 256, PF_SK_PIECES = 512;    // most units and pieces (CTAs) of a balanced launch
+constexpr int PF_BAL_UNITS = 256, PF_BAL_PIECES = 512;    // most units and pieces (CTAs) of a balanced launch
 // The queries enter the tensor cores scaled by 2^-3 (exact), so the weights p = relu(s)^2, which the kernel keeps as
 // fp16 (P in TMEM, packed row sums), come out scaled by 2^-6: a score of 2047 still squares inside fp16's range (the
 // reference keeps P in fp32, attn_nax.metal:11), and fp16's gradual underflow keeps the small weights to 2^-24 of the
@@ -774,7 +774,7 @@ struct PfPiece {
 
 __global__ void __launch_bounds__(512) prefill_pieces_kernel(const int32_t* pos0, int n_tokens, int pairs, int heads, int units, int runs,
                                                              PfPiece* pieces, int2* unit_slots) {
-    __shared__ int pre[PF_SK_UNITS + 1], slot[PF_SK_UNITS + 1], size[PF_SK_PIECES];
+    __shared__ int pre[PF_BAL_UNITS + 1], slot[PF_BAL_UNITS + 1], size[PF_BAL_PIECES];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int U = units, G = runs;
     pdl_launch_dependents();
@@ -975,7 +975,7 @@ extern "C" EmblaStatus embla_attn_reserve_prefill(EmblaAttn* ctx, void* stream) 
     // that the piece table of a balanced launch behind them starts on 16 bytes).
     const size_t slots = 2 * size_t(ctx->sm_count), counters = (2 * size_t(ctx->sm_count) + 3) & ~size_t(3);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    EMBLA_CUDA_TRY(cudaMalloc(&ctx->prefill_scratch, slots * PF_SLOT_BYTES + counters * sizeof(int) + PF_SK_PIECES * sizeof(PfPiece) + PF_SK_UNITS * sizeof(int2)));
+    EMBLA_CUDA_TRY(cudaMalloc(&ctx->prefill_scratch, slots * PF_SLOT_BYTES + counters * sizeof(int) + PF_BAL_PIECES * sizeof(PfPiece) + PF_BAL_UNITS * sizeof(int2)));
     EMBLA_CUDA_TRY(cudaMemsetAsync(ctx->prefill_scratch + slots * PF_SLOT_BYTES, 0, counters * sizeof(int), s));
     ctx->prefill_scratch_bytes = slots * PF_SLOT_BYTES;
     ctx->prefill_counters = int(counters);
@@ -1078,7 +1078,7 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     const int balanced_mode = bal_env ? atoi(bal_env) : -1;
     bool balanced = false;
     const int runs = ctx->sm_count;
-    if (balanced_mode != 0 && units > 1 && units < runs && units <= PF_SK_UNITS && units + runs - 1 <= PF_SK_PIECES &&
+    if (balanced_mode != 0 && units > 1 && units < runs && units <= PF_BAL_UNITS && units + runs - 1 <= PF_BAL_PIECES &&
         long(units) + runs - 1 <= slots && 2 * units <= ctx->prefill_counters && (long(units) * max_pages + 1) * runs < (1L << 31) &&
         (balanced_mode == 1 || long(units) * max_pages >= 16L * runs)) {
         const long run = (long(units) * max_pages + runs - 1) / runs;
@@ -1113,7 +1113,7 @@ static EmblaStatus launch_prefill(EmblaAttn* ctx, const EmblaKVPool* pool, Prefi
     if (balanced) {
         // the piece table sits behind the counters
         PfPiece* pieces = reinterpret_cast<PfPiece*>(ctx->prefill_scratch + ctx->prefill_scratch_bytes + size_t(ctx->prefill_counters) * sizeof(int));
-        p.unit_slots = reinterpret_cast<int2*>(pieces + PF_SK_PIECES);   // (and the units' slots behind that)
+        p.unit_slots = reinterpret_cast<int2*>(pieces + PF_BAL_PIECES);   // (and the units' slots behind that)
         prefill_pieces_kernel<<<(units + runs - 1 + 31) / 32, 512, 0, s>>>(p.pos0, p.n_tokens, pairs, p.heads, units, runs, pieces, p.unit_slots);
         EMBLA_CUDA_TRY(cudaGetLastError());
         p.pieces = pieces;
